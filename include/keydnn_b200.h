@@ -1,0 +1,270 @@
+/*
+ * keydnn_b200.h - C ABI of libkeydnn_b200.so, the sm_100a (B200) operator library
+ * that stands in for KeyDNN's KeyDNNV2CudaNative DLL on the pool / reduce /
+ * elementwise / optimizer path.
+ *
+ * Conventions (those of the reference library):
+ *   - plain C symbols, default visibility, opened once per process with ctypes.CDLL;
+ *   - device pointers cross as T* or as uint64_t integers;
+ *   - every function returns int: 0 = ok, > 0 = cudaError_t (mul family: 1/2/3,
+ *     memcpy_d2d: 1/2, broadcast_to: 1..4, transpose2d: 1/2/3), < 0 = argument guard;
+ *   - tensors are dense, contiguous, row-major (NCHW for pooling);
+ *   - all work is enqueued on one stream (the legacy default stream unless
+ *     keydnn_cuda_set_stream is called); nothing synchronises unless stated.
+ *
+ * "ref:" names the reference declaration each entry replaces, as a path inside
+ * the reference project.  NC/ = src/keydnn/infrastructure/native_cuda/
+ * keydnn_v2_cuda_native/KeyDNNV2CudaNative/.  Entries marked "additive" have no
+ * counterpart in the reference library.
+ */
+#ifndef KEYDNN_B200_H
+#define KEYDNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------- */
+/* Runtime: device, memory, copies, stream, events                            */
+/* ref: NC/keydnn_cuda_utils.hpp:30-42, NC/keydnn_cuda_ops.hpp:18             */
+/* ------------------------------------------------------------------------- */
+int keydnn_cuda_set_device(int device);
+/* malloc/free go through a per-device caching pool (no cudaFree sync per op). */
+int keydnn_cuda_malloc(uint64_t* out_dev_ptr, size_t nbytes);
+int keydnn_cuda_free(uint64_t dev_ptr);
+/* h2d / d2h return when the copy is complete. */
+int keydnn_cuda_memcpy_h2d(uint64_t dst_dev_ptr, const void* src_host_ptr, size_t nbytes);
+int keydnn_cuda_memcpy_d2h(void* dst_host_ptr, uint64_t src_dev_ptr, size_t nbytes);
+int keydnn_cuda_memcpy_d2d(void* dst, const void* src, size_t nbytes);
+int keydnn_cuda_memset(uint64_t dev_ptr, int value, size_t nbytes);
+int keydnn_cuda_synchronize(void);
+/* additive */
+int keydnn_cuda_memcpy_h2d_async(uint64_t dst_dev_ptr, const void* src_host_ptr, size_t nbytes);
+int keydnn_cuda_empty_cache(void);
+int keydnn_cuda_pool_stats(uint64_t* out4); /* reserved, in use, driver mallocs, requests */
+int keydnn_cuda_host_alloc(void** out, size_t nbytes); /* pinned host memory */
+int keydnn_cuda_host_free(void* p);
+int keydnn_cuda_get_stream(uint64_t* out);
+int keydnn_cuda_set_stream(uint64_t stream);
+int keydnn_cuda_stream_create(uint64_t* out);
+int keydnn_cuda_stream_destroy(uint64_t stream);
+int keydnn_cuda_stream_synchronize(void);
+/* additive; the names the reference's backward profiler looks up
+ * (src/keydnn/infrastructure/tensor/_tensor.py:1619-1629) */
+int keydnn_cuda_event_create(uint64_t* out);
+int keydnn_cuda_event_record(uint64_t ev);
+int keydnn_cuda_event_synchronize(uint64_t ev);
+int keydnn_cuda_event_elapsed_ms(uint64_t start, uint64_t stop, float* out_ms);
+int keydnn_cuda_event_destroy(uint64_t ev);
+int keydnn_cuda_device_count(int* out);
+int keydnn_cuda_sm_count(int* out);
+const char* keydnn_cuda_error_string(int code);
+int keydnn_b200_abi_version(void);
+
+/* ------------------------------------------------------------------------- */
+/* Pooling, reference signatures (planes already padded by the caller)         */
+/* ref: NC/keydnn_maxpool2d_cuda.hpp:28-72                                     */
+/* ------------------------------------------------------------------------- */
+int keydnn_cuda_maxpool2d_forward_f32(const float* x_pad, float* y, int64_t* argmax_idx, int N, int C, int H_pad,
+                                      int W_pad, int H_out, int W_out, int k_h, int k_w, int s_h, int s_w);
+int keydnn_cuda_maxpool2d_forward_f64(const double* x_pad, double* y, int64_t* argmax_idx, int N, int C, int H_pad,
+                                      int W_pad, int H_out, int W_out, int k_h, int k_w, int s_h, int s_w);
+/* grad_x_pad[argmax] += grad_out; the caller zero-fills grad_x_pad first. */
+int keydnn_cuda_maxpool2d_backward_f32(const float* grad_out, const int64_t* argmax_idx, float* grad_x_pad, int N,
+                                       int C, int H_out, int W_out, int H_pad, int W_pad);
+int keydnn_cuda_maxpool2d_backward_f64(const double* grad_out, const int64_t* argmax_idx, double* grad_x_pad, int N,
+                                       int C, int H_out, int W_out, int H_pad, int W_pad);
+/* ref: NC/keydnn_avgpool2d_cuda.hpp:38-76 */
+int keydnn_cuda_avgpool2d_forward_f32(const float* x_pad, float* y, int N, int C, int H_pad, int W_pad, int H_out,
+                                      int W_out, int k_h, int k_w, int s_h, int s_w);
+int keydnn_cuda_avgpool2d_forward_f64(const double* x_pad, double* y, int N, int C, int H_pad, int W_pad, int H_out,
+                                      int W_out, int k_h, int k_w, int s_h, int s_w);
+/* grad_x_pad += gathered gradient; the caller zero-fills grad_x_pad first. */
+int keydnn_cuda_avgpool2d_backward_f32(const float* grad_out, float* grad_x_pad, int N, int C, int H_out, int W_out,
+                                       int H_pad, int W_pad, int k_h, int k_w, int s_h, int s_w);
+int keydnn_cuda_avgpool2d_backward_f64(const double* grad_out, double* grad_x_pad, int N, int C, int H_out, int W_out,
+                                       int H_pad, int W_pad, int k_h, int k_w, int s_h, int s_w);
+/* ref: NC/keydnn_global_avgpool2d_cuda.hpp:34-60 */
+int keydnn_cuda_global_avgpool2d_forward_f32(const float* x, float* y, int N, int C, int H, int W);
+int keydnn_cuda_global_avgpool2d_forward_f64(const double* x, double* y, int N, int C, int H, int W);
+int keydnn_cuda_global_avgpool2d_backward_f32(const float* grad_out, float* grad_x, int N, int C, int H, int W);
+int keydnn_cuda_global_avgpool2d_backward_f64(const double* grad_out, double* grad_x, int N, int C, int H, int W);
+/* ref: NC/keydnn_pad2d_cuda.hpp (pad2d / crop2d declarations) */
+int keydnn_cuda_pad2d_f32(const float* x, float* y_pad, int N, int C, int H, int W, int p_h, int p_w, float pad_value);
+int keydnn_cuda_pad2d_f64(const double* x, double* y_pad, int N, int C, int H, int W, int p_h, int p_w,
+                          double pad_value);
+int keydnn_cuda_crop2d_f32(const float* x_pad, float* y, int N, int C, int H_pad, int W_pad, int p_h, int p_w, int H,
+                           int W);
+int keydnn_cuda_crop2d_f64(const double* x_pad, double* y, int N, int C, int H_pad, int W_pad, int p_h, int p_w, int H,
+                           int W);
+
+/* ------------------------------------------------------------------------- */
+/* Pooling, fused entries (additive): un-padded tensors, explicit padding.      */
+/* Replace the pad->pool and memset->pool-backward->crop call sequences of      */
+/* src/keydnn/infrastructure/ops/pool2d_cuda_ext.py:56-522.  argmax keeps the   */
+/* reference encoding h*W_pad + w in the padded plane.  Backward overwrites     */
+/* every element of grad_x.                                                     */
+/* ------------------------------------------------------------------------- */
+int keydnn_cuda_maxpool2d_forward_ex_f32(const float* x, float* y, int64_t* argmax_idx, int N, int C, int H, int W,
+                                         int H_out, int W_out, int k_h, int k_w, int s_h, int s_w, int p_h, int p_w);
+int keydnn_cuda_maxpool2d_forward_ex_f64(const double* x, double* y, int64_t* argmax_idx, int N, int C, int H, int W,
+                                         int H_out, int W_out, int k_h, int k_w, int s_h, int s_w, int p_h, int p_w);
+int keydnn_cuda_maxpool2d_backward_ex_f32(const float* grad_out, const int64_t* argmax_idx, float* grad_x, int N,
+                                          int C, int H, int W, int H_out, int W_out, int k_h, int k_w, int s_h,
+                                          int s_w, int p_h, int p_w);
+int keydnn_cuda_maxpool2d_backward_ex_f64(const double* grad_out, const int64_t* argmax_idx, double* grad_x, int N,
+                                          int C, int H, int W, int H_out, int W_out, int k_h, int k_w, int s_h,
+                                          int s_w, int p_h, int p_w);
+int keydnn_cuda_avgpool2d_forward_ex_f32(const float* x, float* y, int N, int C, int H, int W, int H_out, int W_out,
+                                         int k_h, int k_w, int s_h, int s_w, int p_h, int p_w);
+int keydnn_cuda_avgpool2d_forward_ex_f64(const double* x, double* y, int N, int C, int H, int W, int H_out, int W_out,
+                                         int k_h, int k_w, int s_h, int s_w, int p_h, int p_w);
+int keydnn_cuda_avgpool2d_backward_ex_f32(const float* grad_out, float* grad_x, int N, int C, int H, int W, int H_out,
+                                          int W_out, int k_h, int k_w, int s_h, int s_w, int p_h, int p_w);
+int keydnn_cuda_avgpool2d_backward_ex_f64(const double* grad_out, double* grad_x, int N, int C, int H, int W,
+                                          int H_out, int W_out, int k_h, int k_w, int s_h, int s_w, int p_h, int p_w);
+
+/* ------------------------------------------------------------------------- */
+/* Reductions.  ref: NC/keydnn_reduce_cuda.hpp:56-140                          */
+/* ------------------------------------------------------------------------- */
+int keydnn_cuda_sum_all_f32(const float* x, float* y, int64_t numel);
+int keydnn_cuda_sum_all_f64(const double* x, double* y, int64_t numel);
+int keydnn_cuda_mean_all_f32(const float* x, float* y, int64_t numel);
+int keydnn_cuda_mean_all_f64(const double* x, double* y, int64_t numel);
+int keydnn_cuda_sum_backward_fill_f32(const float* grad_out, float* grad_x, int64_t numel);
+int keydnn_cuda_sum_backward_fill_f64(const double* grad_out, double* grad_x, int64_t numel);
+int keydnn_cuda_mean_backward_fill_f32(const float* grad_out, float* grad_x, int64_t numel);
+int keydnn_cuda_mean_backward_fill_f64(const double* grad_out, double* grad_x, int64_t numel);
+int keydnn_cuda_max_axis2d_forward_f32(const float* x, float* y, int64_t* idx, int rows, int cols, int axis);
+int keydnn_cuda_max_axis2d_forward_f64(const double* x, double* y, int64_t* idx, int rows, int cols, int axis);
+/* grad_x[argmax] += grad_out; the caller zero-fills grad_x first. */
+int keydnn_cuda_max_axis2d_backward_f32(const float* grad_out, const int64_t* idx, float* grad_x, int rows, int cols,
+                                        int axis);
+int keydnn_cuda_max_axis2d_backward_f64(const double* grad_out, const int64_t* idx, double* grad_x, int rows,
+                                        int cols, int axis);
+int keydnn_cuda_sum_axis2d_forward_f32(const float* x, float* y, int rows, int cols, int axis);
+int keydnn_cuda_sum_axis2d_forward_f64(const double* x, double* y, int rows, int cols, int axis);
+int keydnn_cuda_sum_axis2d_backward_f32(const float* grad_out, float* grad_x, int rows, int cols, int axis);
+int keydnn_cuda_sum_axis2d_backward_f64(const double* grad_out, double* grad_x, int rows, int cols, int axis);
+/* in_shape / out_shape are HOST arrays of ndim extents (out extent is 1 or the in extent). */
+int keydnn_cuda_sum_to_shape_f32(const float* x, float* y, const int64_t* in_shape, const int64_t* out_shape,
+                                 int ndim);
+int keydnn_cuda_sum_to_shape_f64(const double* x, double* y, const int64_t* in_shape, const int64_t* out_shape,
+                                 int ndim);
+/* additive: the reference has no axis-wise mean (tensor/mixins/reduction/_tensor_mean.py:91-192
+ * is all-elements only), no all-elements max (_tensor_max.py:70-85 is 2-D, axis 0/1), and its max
+ * backward needs a zero-fill pass before it (ops/reduce_cuda.py:409-414). */
+int keydnn_cuda_max_axis2d_backward_ex_f32(const float* grad_out, const int64_t* idx, float* grad_x, int rows,
+                                           int cols, int axis);
+int keydnn_cuda_max_axis2d_backward_ex_f64(const double* grad_out, const int64_t* idx, double* grad_x, int rows,
+                                           int cols, int axis);
+int keydnn_cuda_mean_axis2d_forward_f32(const float* x, float* y, int rows, int cols, int axis);
+int keydnn_cuda_mean_axis2d_forward_f64(const double* x, double* y, int rows, int cols, int axis);
+int keydnn_cuda_mean_axis2d_backward_f32(const float* grad_out, float* grad_x, int rows, int cols, int axis);
+int keydnn_cuda_mean_axis2d_backward_f64(const double* grad_out, double* grad_x, int rows, int cols, int axis);
+int keydnn_cuda_max_all_forward_f32(const float* x, float* y, int64_t* idx, int64_t numel);
+int keydnn_cuda_max_all_forward_f64(const double* x, double* y, int64_t* idx, int64_t numel);
+int keydnn_cuda_max_all_backward_f32(const float* grad_out, const int64_t* idx, float* grad_x, int64_t numel);
+int keydnn_cuda_max_all_backward_f64(const double* grad_out, const int64_t* idx, double* grad_x, int64_t numel);
+
+/* ------------------------------------------------------------------------- */
+/* Elementwise.  ref: NC/keydnn_tensor_arithmetic.hpp:19-108,164-183           */
+/* Compares write float32 1.0/0.0 masks for both input types.                  */
+/* ------------------------------------------------------------------------- */
+int keydnn_cuda_neg_f32(const float* x, float* y, int64_t n);
+int keydnn_cuda_neg_f64(const double* x, double* y, int64_t n);
+int keydnn_cuda_add_f32(const float* a, const float* b, float* y, int64_t n);
+int keydnn_cuda_add_f64(const double* a, const double* b, double* y, int64_t n);
+int keydnn_cuda_sub_f32(const float* a, const float* b, float* y, int64_t n);
+int keydnn_cuda_sub_f64(const double* a, const double* b, double* y, int64_t n);
+int keydnn_cuda_div_f32(const float* a, const float* b, float* y, int64_t n);
+int keydnn_cuda_div_f64(const double* a, const double* b, double* y, int64_t n);
+int keydnn_cuda_gt_f32(const float* a, const float* b, float* y, int64_t n);
+int keydnn_cuda_gt_f64(const double* a, const double* b, float* y, int64_t n);
+int keydnn_cuda_ge_f32(const float* a, const float* b, float* y, int64_t n);
+int keydnn_cuda_ge_f64(const double* a, const double* b, float* y, int64_t n);
+int keydnn_cuda_lt_f32(const float* a, const float* b, float* y, int64_t n);
+int keydnn_cuda_lt_f64(const double* a, const double* b, float* y, int64_t n);
+int keydnn_cuda_le_f32(const float* a, const float* b, float* y, int64_t n);
+int keydnn_cuda_le_f64(const double* a, const double* b, float* y, int64_t n);
+int keydnn_cuda_eq_f32(const float* a, const float* b, float* y, int64_t n);
+int keydnn_cuda_eq_f64(const double* a, const double* b, float* y, int64_t n);
+int keydnn_cuda_ne_f32(const float* a, const float* b, float* y, int64_t n);
+int keydnn_cuda_ne_f64(const double* a, const double* b, float* y, int64_t n);
+int keydnn_cuda_add_scalar_f32(const float* a, float alpha, float* y, int64_t n);
+int keydnn_cuda_add_scalar_f64(const double* a, double alpha, double* y, int64_t n);
+int keydnn_cuda_sub_scalar_f32(const float* a, float alpha, float* y, int64_t n);
+int keydnn_cuda_sub_scalar_f64(const double* a, double alpha, double* y, int64_t n);
+int keydnn_cuda_div_scalar_f32(const float* a, float alpha, float* y, int64_t n);
+int keydnn_cuda_div_scalar_f64(const double* a, double alpha, double* y, int64_t n);
+int keydnn_cuda_gt_scalar_f32(const float* a, float alpha, float* y, int64_t n);
+int keydnn_cuda_gt_scalar_f64(const double* a, double alpha, float* y, int64_t n);
+int keydnn_cuda_ge_scalar_f32(const float* a, float alpha, float* y, int64_t n);
+int keydnn_cuda_ge_scalar_f64(const double* a, double alpha, float* y, int64_t n);
+int keydnn_cuda_lt_scalar_f32(const float* a, float alpha, float* y, int64_t n);
+int keydnn_cuda_lt_scalar_f64(const double* a, double alpha, float* y, int64_t n);
+int keydnn_cuda_le_scalar_f32(const float* a, float alpha, float* y, int64_t n);
+int keydnn_cuda_le_scalar_f64(const double* a, double alpha, float* y, int64_t n);
+int keydnn_cuda_eq_scalar_f32(const float* a, float alpha, float* y, int64_t n);
+int keydnn_cuda_eq_scalar_f64(const double* a, double alpha, float* y, int64_t n);
+int keydnn_cuda_ne_scalar_f32(const float* a, float alpha, float* y, int64_t n);
+int keydnn_cuda_ne_scalar_f64(const double* a, double alpha, float* y, int64_t n);
+int keydnn_cuda_add_inplace_f32(float* a, const float* b, int64_t n);
+int keydnn_cuda_add_inplace_f64(double* a, const double* b, int64_t n);
+int keydnn_cuda_sub_inplace_f32(float* a, const float* b, int64_t n);
+int keydnn_cuda_sub_inplace_f64(double* a, const double* b, int64_t n);
+int keydnn_cuda_div_inplace_f32(float* a, const float* b, int64_t n);
+int keydnn_cuda_div_inplace_f64(double* a, const double* b, int64_t n);
+int keydnn_cuda_add_scalar_inplace_f32(float* a, float alpha, int64_t n);
+int keydnn_cuda_add_scalar_inplace_f64(double* a, double alpha, int64_t n);
+int keydnn_cuda_sub_scalar_inplace_f32(float* a, float alpha, int64_t n);
+int keydnn_cuda_sub_scalar_inplace_f64(double* a, double alpha, int64_t n);
+int keydnn_cuda_div_scalar_inplace_f32(float* a, float alpha, int64_t n);
+int keydnn_cuda_div_scalar_inplace_f64(double* a, double alpha, int64_t n);
+/* mul family: `int numel`, status 0/1/2/3.  ref: NC/keydnn_cuda_ops.hpp:33-46 */
+int keydnn_cuda_mul_f32(const float* a, const float* b, float* y, int numel);
+int keydnn_cuda_mul_f64(const double* a, const double* b, double* y, int numel);
+int keydnn_cuda_mul_scalar_f32(const float* a, float alpha, float* y, int numel);
+int keydnn_cuda_mul_scalar_f64(const double* a, double alpha, double* y, int numel);
+int keydnn_cuda_mul_inplace_f32(float* a, const float* b, int numel);
+int keydnn_cuda_mul_inplace_f64(double* a, const double* b, int numel);
+int keydnn_cuda_mul_scalar_inplace_f32(float* a, float alpha, int numel);
+int keydnn_cuda_mul_scalar_inplace_f64(double* a, double alpha, int numel);
+/* additive: 64-bit element counts for mul */
+int keydnn_cuda_mul64_f32(const float* a, const float* b, float* y, int64_t n);
+int keydnn_cuda_mul64_f64(const double* a, const double* b, double* y, int64_t n);
+/* ref: NC/keydnn_fill_cuda.hpp:36-46 */
+int keydnn_cuda_fill_f32(float* y, int64_t numel, float value);
+int keydnn_cuda_fill_f64(double* y, int64_t numel, double value);
+/* additive: fused optimizer step.  Replaces the five tensor passes of
+ * src/keydnn/infrastructure/optimizers/_sgd.py:119-140 with one; v may be NULL
+ * (no momentum).  Separately rounded ops in the reference order:
+ * g' = g*grad_scale (skipped when 1); g' += p*wd (skipped when 0);
+ * v = v*mu + g'; p -= (v or g')*lr. */
+int keydnn_cuda_sgd_momentum_step_f32(float* p, const float* g, float* v, int64_t n, float lr, float momentum,
+                                      float weight_decay, float grad_scale);
+int keydnn_cuda_sgd_momentum_step_f64(double* p, const double* g, double* v, int64_t n, double lr, double momentum,
+                                      double weight_decay, double grad_scale);
+
+/* ------------------------------------------------------------------------- */
+/* Layer glue.  ref: NC/keydnn_cuda_ops.hpp:20-21,57-67;                       */
+/*              NC/keydnn_tensor_arithmetic.hpp:130-159                        */
+/* ------------------------------------------------------------------------- */
+int keydnn_cuda_broadcast_to_f32(const float* x, float* y, const int64_t* in_shape, int in_ndim,
+                                 const int64_t* out_shape, int out_ndim);
+int keydnn_cuda_broadcast_to_f64(const double* x, double* y, const int64_t* in_shape, int in_ndim,
+                                 const int64_t* out_shape, int out_ndim);
+int keydnn_cuda_bias_add_f32(const float* x, const float* b, float* y, int64_t batch, int64_t out);
+int keydnn_cuda_bias_add_f64(const double* x, const double* b, double* y, int64_t batch, int64_t out);
+int keydnn_cuda_bias_add_inplace_f32(float* y, const float* b, int64_t batch, int64_t out);
+int keydnn_cuda_bias_add_inplace_f64(double* y, const double* b, int64_t batch, int64_t out);
+int keydnn_cuda_transpose2d_f32(const float* x, float* y, int rows, int cols);
+int keydnn_cuda_transpose2d_f64(const double* x, double* y, int rows, int cols);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KEYDNN_B200_H */

@@ -1,0 +1,844 @@
+// 2-D pooling on NCHW planes: MaxPool2d, AvgPool2d, GlobalAvgPool2d (forward and
+// backward), plus the pad2d / crop2d passes the reference runs around them.
+//
+// Reference kernels replaced (all one element per thread, 4-byte accesses,
+// N*C planes in gridDim.z, which stops at 65,535 planes):
+//   KeyDNNV2CudaNative/kernel.cu:97-185               max forward / backward
+//   keydnn_avgpool2d_cuda.cu:55-92, 143-198           avg forward / gather backward
+//   keydnn_global_avgpool2d_cuda.cu:32-97             global average
+//   keydnn_pad2d_cuda.cu:30-97                        pad / crop
+//
+// Two entry styles are exported:
+//   * the reference signatures (pre-padded planes; backward accumulates into a
+//     caller-zeroed padded buffer), and
+//   * `_ex` entries that take the un-padded tensor with explicit padding, so the
+//     pad pass before and the memset + crop passes after disappear: forward
+//     treats out-of-range taps as the pad value, backward writes every element of
+//     the un-padded gradient exactly once.
+// Planes are flattened into the x dimension of a grid-stride loop, so any
+// N*C works.
+#include "common.cuh"
+
+namespace {
+
+using kd::Pack4;
+
+constexpr int kThreads = 256;
+
+struct PoolGeom {
+    int H, W;        // un-padded input plane
+    int Ho, Wo;      // output plane
+    int kh, kw, sh, sw;
+    int ph, pw;      // symmetric zero / -inf padding
+};
+
+// ===========================================================================
+// MaxPool
+// ===========================================================================
+// Selection rule (kernel.cu:122-145): best starts at -inf and the recorded
+// position at the window origin; taps are scanned row-major and replace the best
+// only when strictly greater.  NaN therefore never wins, ties keep the first
+// tap, and a window without any tap above -inf reports (-inf, origin).  Taps
+// that fall into the padding hold -inf in the reference and can never win, so
+// they are skipped here.  The index is h*W_pad + w in the padded plane.
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+maxpool_fwd_generic(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, PoolGeom g,
+                    int64_t total) {
+    const int Wp = g.W + 2 * g.pw;
+    for (int64_t o = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; o < total;
+         o += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const int j = static_cast<int>(o % g.Wo);
+        const int64_t t = o / g.Wo;
+        const int i = static_cast<int>(t % g.Ho);
+        const int64_t nc = t / g.Ho;
+        const T* plane = x + nc * g.H * g.W;
+        const int hp0 = i * g.sh, wp0 = j * g.sw;
+        T best = kd::neg_inf<T>();
+        int bh = hp0, bw = wp0;
+        for (int a = 0; a < g.kh; ++a) {
+            const int h = hp0 + a - g.ph;
+            if (h < 0 || h >= g.H) continue;
+            for (int b = 0; b < g.kw; ++b) {
+                const int w = wp0 + b - g.pw;
+                if (w < 0 || w >= g.W) continue;
+                const T v = __ldg(plane + static_cast<int64_t>(h) * g.W + w);
+                if (v > best) { best = v; bh = hp0 + a; bw = wp0 + b; }
+            }
+        }
+        y[o] = best;
+        idx[o] = static_cast<long long>(bh) * Wp + bw;
+    }
+}
+
+// kernel 2x2, stride 2, no padding, W % 8 == 0.  A thread owns four adjacent
+// windows: two rows of eight inputs come in as four 16-byte loads, the four
+// maxima leave as one 16-byte store and the four int64 positions as two.
+template <typename T, int U>
+__global__ void __launch_bounds__(kThreads)
+maxpool2x2_fwd(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, int H, int W, int Ho, int Wo,
+               int64_t groups) {
+    const int gpr = Wo >> 2;   // groups per output row
+    const int64_t tile = static_cast<int64_t>(kThreads) * U;
+    for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < groups;
+         base += static_cast<int64_t>(gridDim.x) * tile) {
+        Pack4<T> t0[U], t1[U], b0[U], b1[U];
+        int64_t row[U];
+        int jg[U], i2[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t gi = base + u * kThreads + threadIdx.x;
+            if (gi < groups) {
+                row[u] = gi / gpr;
+                jg[u] = static_cast<int>(gi - row[u] * gpr);
+                const int64_t nc = row[u] / Ho;
+                i2[u] = 2 * static_cast<int>(row[u] - nc * Ho);
+                const T* r0 = x + (nc * H + i2[u]) * W + 8 * jg[u];
+                t0[u] = kd::load4_stream(r0);
+                t1[u] = kd::load4_stream(r0 + 4);
+                b0[u] = kd::load4_stream(r0 + W);
+                b1[u] = kd::load4_stream(r0 + W + 4);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t gi = base + u * kThreads + threadIdx.x;
+            if (gi < groups) {
+                T top[8], bot[8];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    top[k] = t0[u].v[k]; top[4 + k] = t1[u].v[k];
+                    bot[k] = b0[u].v[k]; bot[4 + k] = b1[u].v[k];
+                }
+                Pack4<T> out;
+                Pack4<long long> pos;
+                const long long origin = static_cast<long long>(i2[u]) * W + 8 * jg[u];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    T best = kd::neg_inf<T>();
+                    long long off = 0;
+                    if (top[2 * q] > best) { best = top[2 * q]; off = 0; }
+                    if (top[2 * q + 1] > best) { best = top[2 * q + 1]; off = 1; }
+                    if (bot[2 * q] > best) { best = bot[2 * q]; off = W; }
+                    if (bot[2 * q + 1] > best) { best = bot[2 * q + 1]; off = W + 1; }
+                    out.v[q] = best;
+                    pos.v[q] = origin + 2 * q + off;
+                }
+                const int64_t o = row[u] * Wo + 4 * jg[u];
+                kd::store4(y + o, out);
+                kd::store4(idx + o, pos);
+            }
+        }
+    }
+}
+
+// Backward for kernel 2x2, stride 2, no padding, H even, W % 8 == 0: windows
+// tile the plane, so the thread that owns four windows writes their 2x8 block of
+// the gradient (the routed value at the recorded tap, zero elsewhere).  No
+// memset, no atomics.  `0 + go` reproduces the reference's accumulation onto a
+// zeroed buffer (it turns -0 into +0).
+template <typename T, int U>
+__global__ void __launch_bounds__(kThreads)
+maxpool2x2_bwd(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, int H, int W, int Ho,
+               int Wo, int64_t groups) {
+    const int gpr = Wo >> 2;
+    const int64_t tile = static_cast<int64_t>(kThreads) * U;
+    for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < groups;
+         base += static_cast<int64_t>(gridDim.x) * tile) {
+        Pack4<T> gv[U];
+        Pack4<long long> pv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t gi = base + u * kThreads + threadIdx.x;
+            if (gi < groups) {
+                gv[u] = kd::load4_stream(go + 4 * gi);
+                pv[u] = kd::load4_stream(idx + 4 * gi);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t gi = base + u * kThreads + threadIdx.x;
+            if (gi < groups) {
+                const int64_t row = gi / gpr;
+                const int jg = static_cast<int>(gi - row * gpr);
+                const int64_t nc = row / Ho;
+                const int i2 = 2 * static_cast<int>(row - nc * Ho);
+                const long long origin = static_cast<long long>(i2) * W + 8 * jg;
+                Pack4<T> t0, t1, b0, b1;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const long long off = pv[u].v[q] - (origin + 2 * q);
+                    const T g = T(0) + gv[u].v[q];
+                    const T a = off == 0 ? g : T(0);
+                    const T b = off == 1 ? g : T(0);
+                    const T c = off == W ? g : T(0);
+                    const T d = off == W + 1 ? g : T(0);
+                    if (q < 2) { t0.v[2 * q] = a; t0.v[2 * q + 1] = b; b0.v[2 * q] = c; b0.v[2 * q + 1] = d; }
+                    else { t1.v[2 * q - 4] = a; t1.v[2 * q - 3] = b; b1.v[2 * q - 4] = c; b1.v[2 * q - 3] = d; }
+                }
+                T* r0 = gx + (nc * H + i2) * W + 8 * jg;
+                kd::store4(r0, t0);
+                kd::store4(r0 + 4, t1);
+                kd::store4(r0 + W, b0);
+                kd::store4(r0 + W + 4, b1);
+            }
+        }
+    }
+}
+
+// Any geometry: one thread per un-padded input element gathers, in ascending
+// (i, j) order, the gradients of the windows that recorded it.  Writes every
+// element once.  (The reference sums overlapping windows with float atomics in
+// arbitrary order, kernel.cu:173-184, so only non-overlapping results are
+// bit-comparable.)
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+maxpool_bwd_gather(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, PoolGeom g,
+                   int64_t total) {
+    const int Wp = g.W + 2 * g.pw;
+    for (int64_t e = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; e < total;
+         e += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const int w = static_cast<int>(e % g.W);
+        const int64_t t = e / g.W;
+        const int h = static_cast<int>(t % g.H);
+        const int64_t nc = t / g.H;
+        const int hp = h + g.ph, wp = w + g.pw;
+        const long long target = static_cast<long long>(hp) * Wp + wp;
+        const int a0 = hp - g.kh + 1, c0 = wp - g.kw + 1;
+        const int i_lo = a0 <= 0 ? 0 : (a0 + g.sh - 1) / g.sh;
+        const int j_lo = c0 <= 0 ? 0 : (c0 + g.sw - 1) / g.sw;
+        const int i_hi = min(g.Ho - 1, hp / g.sh);
+        const int j_hi = min(g.Wo - 1, wp / g.sw);
+        const int64_t obase = nc * g.Ho * g.Wo;
+        T acc = T(0);
+        for (int i = i_lo; i <= i_hi; ++i)
+            for (int j = j_lo; j <= j_hi; ++j) {
+                const int64_t o = obase + static_cast<int64_t>(i) * g.Wo + j;
+                if (__ldg(idx + o) == target) acc += __ldg(go + o);
+            }
+        gx[e] = acc;
+    }
+}
+
+// Reference-signature backward (kernel.cu:153-185): grad_x_pad[idx] += go with
+// atomics on whatever the caller put in grad_x_pad (it zero-fills it).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+maxpool_bwd_scatter(const T* __restrict__ go, const long long* __restrict__ idx, T* gx_pad, int Ho, int Wo, int Hp,
+                    int Wp, int64_t total) {
+    const int64_t plane_o = static_cast<int64_t>(Ho) * Wo;
+    const int64_t plane_i = static_cast<int64_t>(Hp) * Wp;
+    for (int64_t o = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; o < total;
+         o += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const long long p = idx[o];
+        if (p < 0 || p >= plane_i) continue;
+        const int64_t nc = o / plane_o;
+        atomicAdd(gx_pad + nc * plane_i + p, go[o]);
+    }
+}
+
+// ===========================================================================
+// AvgPool (count_include_pad: divisor is always kh*kw)
+// ===========================================================================
+// Reference arithmetic (keydnn_avgpool2d_cuda.cu:79-91): sum = 0; sum += tap in
+// row-major order over the zero-padded window; y = sum / T(kh*kw).  A padded tap
+// adds +0, which never changes the running sum (it starts at +0 and so is never
+// -0), so skipping those taps is bit-identical.
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+avgpool_fwd_generic(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int64_t total) {
+    const T denom = static_cast<T>(g.kh * g.kw);
+    for (int64_t o = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; o < total;
+         o += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const int j = static_cast<int>(o % g.Wo);
+        const int64_t t = o / g.Wo;
+        const int i = static_cast<int>(t % g.Ho);
+        const int64_t nc = t / g.Ho;
+        const T* plane = x + nc * g.H * g.W;
+        const int h0 = i * g.sh - g.ph, w0 = j * g.sw - g.pw;
+        T sum = T(0);
+        for (int a = 0; a < g.kh; ++a) {
+            const int h = h0 + a;
+            if (h < 0 || h >= g.H) continue;
+            for (int b = 0; b < g.kw; ++b) {
+                const int w = w0 + b;
+                if (w < 0 || w >= g.W) continue;
+                sum += __ldg(plane + static_cast<int64_t>(h) * g.W + w);
+            }
+        }
+        y[o] = sum / denom;
+    }
+}
+
+// kernel 3x3, stride 2, padding 1, W % 8 == 0 (so Wo = W/2, Wo % 4 == 0).
+// A thread owns four adjacent outputs of one output row: from each of the three
+// input rows it takes eight aligned inputs (two 16-byte loads) plus the one
+// input left of them, which the neighbouring thread also loads (an L1 hit).
+// Odd input rows serve two output rows; the second read comes from L1/L2.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+avgpool3x3s2p1_fwd(const T* __restrict__ x, T* __restrict__ y, int H, int W, int Ho, int Wo, int64_t groups) {
+    const int gpr = Wo >> 2;
+    const T denom = T(9);
+    for (int64_t gi = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; gi < groups;
+         gi += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const int64_t row = gi / gpr;
+        const int jg = static_cast<int>(gi - row * gpr);
+        const int64_t nc = row / Ho;
+        const int i = static_cast<int>(row - nc * Ho);
+        const T* plane = x + nc * H * W;
+        T c[3][9];
+        bool live[3];
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            const int h = 2 * i - 1 + r;
+            live[r] = (h >= 0 && h < H);
+            if (live[r]) {
+                const T* p = plane + static_cast<int64_t>(h) * W + 8 * jg;
+                const Pack4<T> a = kd::load4(p);
+                const Pack4<T> b = kd::load4(p + 4);
+                c[r][0] = jg > 0 ? __ldg(p - 1) : T(0);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { c[r][1 + k] = a.v[k]; c[r][5 + k] = b.v[k]; }
+            }
+        }
+        Pack4<T> out;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            T sum = T(0);
+#pragma unroll
+            for (int r = 0; r < 3; ++r) {
+                if (live[r]) {
+                    sum += c[r][2 * q];
+                    sum += c[r][2 * q + 1];
+                    sum += c[r][2 * q + 2];
+                }
+            }
+            out.v[q] = sum / denom;
+        }
+        kd::store4(y + row * Wo + 4 * jg, out);
+    }
+}
+
+// Reference backward arithmetic (keydnn_avgpool2d_cuda.cu:164-197): for each
+// input, acc = 0; acc += go[i,j] / T(kh*kw) over the covering windows in
+// ascending (i, j); result = 0 + acc.  Each term is divided on its own.
+// `ACCUM` keeps the reference-signature behaviour of adding onto the buffer.
+template <typename T, bool ACCUM>
+__global__ void __launch_bounds__(kThreads)
+avgpool_bwd_gather(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int64_t total) {
+    const T denom = static_cast<T>(g.kh * g.kw);
+    for (int64_t e = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; e < total;
+         e += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const int w = static_cast<int>(e % g.W);
+        const int64_t t = e / g.W;
+        const int h = static_cast<int>(t % g.H);
+        const int64_t nc = t / g.H;
+        const int hp = h + g.ph, wp = w + g.pw;
+        const int a0 = hp - g.kh + 1, c0 = wp - g.kw + 1;
+        const int i_lo = a0 <= 0 ? 0 : (a0 + g.sh - 1) / g.sh;
+        const int j_lo = c0 <= 0 ? 0 : (c0 + g.sw - 1) / g.sw;
+        const int i_hi = min(g.Ho - 1, hp / g.sh);
+        const int j_hi = min(g.Wo - 1, wp / g.sw);
+        const int64_t obase = nc * g.Ho * g.Wo;
+        T acc = T(0);
+        for (int i = i_lo; i <= i_hi; ++i)
+            for (int j = j_lo; j <= j_hi; ++j)
+                acc += __ldg(go + obase + static_cast<int64_t>(i) * g.Wo + j) / denom;
+        if (ACCUM) gx[e] += acc;
+        else gx[e] = acc;
+    }
+}
+
+// kernel 3x3, stride 2, padding 1, W % 8 == 0.  A thread owns the 2x8 block of
+// gradient rows (2m, 2m+1), columns [8jg, 8jg+8).  Row 2m is covered by output
+// row m only, row 2m+1 by rows m and m+1; even columns by one output column, odd
+// columns by two.  Five quotients go/9 per output row feed all sixteen sums.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+avgpool3x3s2p1_bwd(const T* __restrict__ go, T* __restrict__ gx, int H, int W, int Ho, int Wo, int64_t blocks) {
+    const int bpr = W >> 3;            // 8-column blocks per row
+    const int Hh = (H + 1) >> 1;       // row pairs per plane
+    const T denom = T(9);
+    for (int64_t bi = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; bi < blocks;
+         bi += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const int64_t rowp = bi / bpr;
+        const int jg = static_cast<int>(bi - rowp * bpr);
+        const int64_t nc = rowp / Hh;
+        const int m = static_cast<int>(rowp - nc * Hh);
+        const T* gplane = go + nc * Ho * Wo;
+        T q[2][5];
+        bool live[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int i = m + r;
+            live[r] = i < Ho;
+            if (live[r]) {
+                const T* p = gplane + static_cast<int64_t>(i) * Wo + 4 * jg;
+                const Pack4<T> a = kd::load4(p);
+                const T e = (4 * jg + 4 < Wo) ? __ldg(p + 4) : T(0);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) q[r][k] = a.v[k] / denom;
+                q[r][4] = e / denom;
+            }
+        }
+        const bool last_col = !(4 * jg + 4 < Wo);   // the fifth quotient has no window
+        T* r0 = gx + (nc * H + 2 * m) * W + 8 * jg;
+        // row 2m: covered by output row m (always live: m < Ho for every row pair)
+        {
+            Pack4<T> lo, hi;
+#pragma unroll
+            for (int cidx = 0; cidx < 8; ++cidx) {
+                T acc = T(0);
+                acc += q[0][cidx >> 1];
+                if ((cidx & 1) && !(last_col && cidx == 7)) acc += q[0][(cidx >> 1) + 1];
+                if (cidx < 4) lo.v[cidx] = acc; else hi.v[cidx - 4] = acc;
+            }
+            kd::store4(r0, lo);
+            kd::store4(r0 + 4, hi);
+        }
+        if (2 * m + 1 < H) {
+            Pack4<T> lo, hi;
+#pragma unroll
+            for (int cidx = 0; cidx < 8; ++cidx) {
+                const bool two = (cidx & 1) && !(last_col && cidx == 7);
+                T acc = T(0);
+                acc += q[0][cidx >> 1];
+                if (two) acc += q[0][(cidx >> 1) + 1];
+                if (live[1]) {
+                    acc += q[1][cidx >> 1];
+                    if (two) acc += q[1][(cidx >> 1) + 1];
+                }
+                if (cidx < 4) lo.v[cidx] = acc; else hi.v[cidx - 4] = acc;
+            }
+            kd::store4(r0 + W, lo);
+            kd::store4(r0 + W + 4, hi);
+        }
+    }
+}
+
+// ===========================================================================
+// Global average pool
+// ===========================================================================
+// Short rows (L = H*W <= 64): a warp stages 32 consecutive rows (one contiguous,
+// 16-byte aligned span) in shared memory with coalesced 16-byte loads, then lane
+// r adds row r serially in (h, w) order and divides by T(L): the arithmetic of the
+// reference's one-thread-per-row loop (keydnn_global_avgpool2d_cuda.cu:47-60),
+// bit for bit, but with coalesced traffic.  Odd L makes the per-lane stride
+// conflict-free; even L is padded by one word per row.
+template <typename T, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
+gap_fwd_short(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int L, int Ls) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T* sm = reinterpret_cast<T*>(smem_raw) + static_cast<size_t>(threadIdx.x >> 5) * 32 * Ls;
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * WARPS;
+    const int64_t chunks = (rows + 31) >> 5;
+    for (int64_t ch = static_cast<int64_t>(blockIdx.x) * WARPS + (threadIdx.x >> 5); ch < chunks; ch += nwarps) {
+        const int64_t r0 = ch << 5;
+        const int nrow = (rows - r0 < 32) ? static_cast<int>(rows - r0) : 32;
+        const int count = nrow * L;
+        const T* src = x + r0 * L;
+        const int c4 = count >> 2;
+        if (Ls == L) {
+            // shared layout == global layout: plain 16-byte copies
+            for (int p = lane; p < c4; p += 32) {
+                const Pack4<T> v = kd::load4_stream(src + 4 * p);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) sm[4 * p + k] = v.v[k];
+            }
+            for (int e = (c4 << 2) + lane; e < count; e += 32) sm[e] = src[e];
+        } else {
+            for (int p = lane; p < c4; p += 32) {
+                const Pack4<T> v = kd::load4_stream(src + 4 * p);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int e = 4 * p + k;
+                    const int rr = e / L;
+                    sm[rr * Ls + (e - rr * L)] = v.v[k];
+                }
+            }
+            for (int e = (c4 << 2) + lane; e < count; e += 32) {
+                const int rr = e / L;
+                sm[rr * Ls + (e - rr * L)] = src[e];
+            }
+        }
+        __syncwarp();
+        if (lane < nrow) {
+            const T* rp = sm + lane * Ls;
+            T sum = T(0);
+            for (int k = 0; k < L; ++k) sum += rp[k];
+            y[r0 + lane] = sum / static_cast<T>(L);
+        }
+        __syncwarp();
+    }
+}
+
+// Long rows: one warp per row, 16-byte loads when rows are aligned, partial sums
+// in T per lane, combined in double.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+gap_fwd_long(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int L) {
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5); r < rows; r += nwarps) {
+        const T* src = x + r * L;
+        T s0 = T(0), s1 = T(0), s2 = T(0), s3 = T(0);
+        if (VEC) {
+            const int c4 = L >> 2;
+            for (int p = lane; p < c4; p += 32) {
+                const Pack4<T> v = kd::load4_stream(src + 4 * p);
+                s0 += v.v[0]; s1 += v.v[1]; s2 += v.v[2]; s3 += v.v[3];
+            }
+        } else {
+            for (int e = lane; e < L; e += 32) s0 += src[e];
+        }
+        double s = (static_cast<double>(s0) + static_cast<double>(s1)) +
+                   (static_cast<double>(s2) + static_cast<double>(s3));
+        s = kd::warp_sum(s);
+        if (lane == 0) y[r] = static_cast<T>(s) / static_cast<T>(L);
+    }
+}
+
+// Backward (keydnn_global_avgpool2d_cuda.cu:69-97): gx = go[row] * (T(1)/T(L)),
+// a multiply by the rounded reciprocal.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+gap_bwd(const T* __restrict__ go, T* __restrict__ gx, int64_t total, int L, bool vec) {
+    const T scale = T(1) / static_cast<T>(L);
+    if (vec) {
+        const int64_t n4 = total >> 2;
+        for (int64_t p = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; p < n4;
+             p += static_cast<int64_t>(gridDim.x) * kThreads) {
+            const int64_t e0 = p << 2;
+            int64_t row = e0 / L;
+            int rem = static_cast<int>(e0 - row * L);
+            Pack4<T> out;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                while (rem >= L) { rem -= L; ++row; }
+                out.v[k] = __ldg(go + row) * scale;
+                ++rem;
+            }
+            kd::store4(gx + e0, out);
+        }
+        if (blockIdx.x == 0 && threadIdx.x < 4) {
+            const int64_t e = (n4 << 2) + threadIdx.x;
+            if (e < total) gx[e] = go[e / L] * scale;
+        }
+    } else {
+        for (int64_t e = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; e < total;
+             e += static_cast<int64_t>(gridDim.x) * kThreads)
+            gx[e] = __ldg(go + e / L) * scale;
+    }
+}
+
+// ===========================================================================
+// pad / crop
+// ===========================================================================
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+pad2d_kernel(const T* __restrict__ x, T* __restrict__ y, int H, int W, int ph, int pw, T value, int64_t total) {
+    const int Hp = H + 2 * ph, Wp = W + 2 * pw;
+    for (int64_t o = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; o < total;
+         o += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const int wp = static_cast<int>(o % Wp);
+        const int64_t t = o / Wp;
+        const int hp = static_cast<int>(t % Hp);
+        const int64_t nc = t / Hp;
+        const int h = hp - ph, w = wp - pw;
+        y[o] = (h >= 0 && h < H && w >= 0 && w < W) ? x[(nc * H + h) * W + w] : value;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+crop2d_kernel(const T* __restrict__ xp, T* __restrict__ y, int Hp, int Wp, int ph, int pw, int H, int W,
+              int64_t total) {
+    for (int64_t o = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; o < total;
+         o += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const int w = static_cast<int>(o % W);
+        const int64_t t = o / W;
+        const int h = static_cast<int>(t % H);
+        const int64_t nc = t / H;
+        const int hp = h + ph, wp = w + pw;
+        if (hp < Hp && wp < Wp) y[o] = xp[(nc * Hp + hp) * Wp + wp];
+    }
+}
+
+// ===========================================================================
+// Host-side dispatch
+// ===========================================================================
+inline unsigned flat_grid(int64_t items, int per_sm = 8) {
+    return kd::grid_for((items + kThreads - 1) / kThreads, per_sm);
+}
+
+inline bool out_dims_ok(const PoolGeom& g) {
+    // every window must start inside the padded plane
+    return (static_cast<int64_t>(g.Ho - 1) * g.sh < g.H + 2 * g.ph) &&
+           (static_cast<int64_t>(g.Wo - 1) * g.sw < g.W + 2 * g.pw);
+}
+
+template <typename T>
+int maxpool_forward(const T* x, T* y, long long* idx, int N, int C, PoolGeom g) {
+    if (!x || !y || !idx) return -1;
+    if (N <= 0 || C <= 0 || g.H <= 0 || g.W <= 0) return -2;
+    if (g.Ho <= 0 || g.Wo <= 0 || g.kh <= 0 || g.kw <= 0) return -3;
+    if (g.sh <= 0 || g.sw <= 0) return -4;
+    if (g.ph < 0 || g.pw < 0 || !out_dims_ok(g)) return -5;
+    (void)cudaGetLastError();
+    const int64_t nc = static_cast<int64_t>(N) * C;
+    const int64_t total = nc * g.Ho * g.Wo;
+    const bool fast = g.kh == 2 && g.kw == 2 && g.sh == 2 && g.sw == 2 && g.ph == 0 && g.pw == 0 &&
+                      (g.W % 8 == 0) && g.Wo == g.W / 2 && g.Ho <= g.H / 2 && kd::aligned16(x) &&
+                      kd::aligned16(y) && kd::aligned16(idx);
+    if (fast) {
+        constexpr int U = 2;
+        const int64_t groups = total >> 2;
+        const unsigned grid = kd::grid_for((groups + kThreads * U - 1) / (kThreads * U), 8);
+        maxpool2x2_fwd<T, U><<<grid, kThreads, 0, kd::stream()>>>(x, y, idx, g.H, g.W, g.Ho, g.Wo, groups);
+    } else {
+        maxpool_fwd_generic<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(x, y, idx, g, total);
+    }
+    return kd::launch_status();
+}
+
+template <typename T>
+int maxpool_backward_ex(const T* go, const long long* idx, T* gx, int N, int C, PoolGeom g) {
+    if (!go || !idx || !gx) return -1;
+    if (N <= 0 || C <= 0 || g.H <= 0 || g.W <= 0) return -2;
+    if (g.Ho <= 0 || g.Wo <= 0 || g.kh <= 0 || g.kw <= 0) return -3;
+    if (g.sh <= 0 || g.sw <= 0) return -4;
+    if (g.ph < 0 || g.pw < 0 || !out_dims_ok(g)) return -5;
+    (void)cudaGetLastError();
+    const int64_t nc = static_cast<int64_t>(N) * C;
+    const bool fast = g.kh == 2 && g.kw == 2 && g.sh == 2 && g.sw == 2 && g.ph == 0 && g.pw == 0 &&
+                      (g.W % 8 == 0) && (g.H % 2 == 0) && g.Wo == g.W / 2 && g.Ho == g.H / 2 &&
+                      kd::aligned16(go) && kd::aligned16(gx) && kd::aligned16(idx);
+    if (fast) {
+        constexpr int U = 2;
+        const int64_t groups = (nc * g.Ho * g.Wo) >> 2;
+        const unsigned grid = kd::grid_for((groups + kThreads * U - 1) / (kThreads * U), 8);
+        maxpool2x2_bwd<T, U><<<grid, kThreads, 0, kd::stream()>>>(go, idx, gx, g.H, g.W, g.Ho, g.Wo, groups);
+    } else {
+        const int64_t total = nc * g.H * g.W;
+        maxpool_bwd_gather<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(go, idx, gx, g, total);
+    }
+    return kd::launch_status();
+}
+
+template <typename T>
+int maxpool_backward_legacy(const T* go, const long long* idx, T* gx_pad, int N, int C, int Ho, int Wo, int Hp,
+                            int Wp) {
+    if (!go || !idx || !gx_pad) return -1;
+    if (N <= 0 || C <= 0) return -2;
+    if (Ho <= 0 || Wo <= 0 || Hp <= 0 || Wp <= 0) return -3;
+    (void)cudaGetLastError();
+    const int64_t total = static_cast<int64_t>(N) * C * Ho * Wo;
+    maxpool_bwd_scatter<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(go, idx, gx_pad, Ho, Wo, Hp, Wp, total);
+    return kd::launch_status();
+}
+
+template <typename T>
+int avgpool_forward(const T* x, T* y, int N, int C, PoolGeom g) {
+    if (!x || !y) return -1;
+    if (N <= 0 || C <= 0) return -2;
+    if (g.H <= 0 || g.W <= 0 || g.Ho <= 0 || g.Wo <= 0) return -3;
+    if (g.kh <= 0 || g.kw <= 0 || g.sh <= 0 || g.sw <= 0) return -4;
+    if (g.ph < 0 || g.pw < 0 || !out_dims_ok(g)) return -5;
+    (void)cudaGetLastError();
+    const int64_t nc = static_cast<int64_t>(N) * C;
+    const int64_t total = nc * g.Ho * g.Wo;
+    const bool fast = g.kh == 3 && g.kw == 3 && g.sh == 2 && g.sw == 2 && g.ph == 1 && g.pw == 1 &&
+                      (g.W % 8 == 0) && g.Wo == g.W / 2 && g.Ho == (g.H - 1) / 2 + 1 && kd::aligned16(x) &&
+                      kd::aligned16(y);
+    if (fast) {
+        const int64_t groups = total >> 2;
+        avgpool3x3s2p1_fwd<T><<<flat_grid(groups), kThreads, 0, kd::stream()>>>(x, y, g.H, g.W, g.Ho, g.Wo, groups);
+    } else {
+        avgpool_fwd_generic<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(x, y, g, total);
+    }
+    return kd::launch_status();
+}
+
+template <typename T>
+int avgpool_backward(const T* go, T* gx, int N, int C, PoolGeom g, bool accumulate) {
+    if (!go || !gx) return -1;
+    if (N <= 0 || C <= 0) return -2;
+    if (g.Ho <= 0 || g.Wo <= 0 || g.H <= 0 || g.W <= 0) return -3;
+    if (g.kh <= 0 || g.kw <= 0 || g.sh <= 0 || g.sw <= 0) return -4;
+    if (g.ph < 0 || g.pw < 0) return -5;
+    (void)cudaGetLastError();
+    const int64_t nc = static_cast<int64_t>(N) * C;
+    const int64_t total = nc * g.H * g.W;
+    const bool fast = !accumulate && g.kh == 3 && g.kw == 3 && g.sh == 2 && g.sw == 2 && g.ph == 1 && g.pw == 1 &&
+                      (g.W % 8 == 0) && g.Wo == g.W / 2 && g.Ho == (g.H - 1) / 2 + 1 && kd::aligned16(go) &&
+                      kd::aligned16(gx);
+    if (fast) {
+        const int64_t blocks = nc * ((g.H + 1) / 2) * (g.W / 8);
+        avgpool3x3s2p1_bwd<T><<<flat_grid(blocks), kThreads, 0, kd::stream()>>>(go, gx, g.H, g.W, g.Ho, g.Wo, blocks);
+    } else if (accumulate) {
+        avgpool_bwd_gather<T, true><<<flat_grid(total), kThreads, 0, kd::stream()>>>(go, gx, g, total);
+    } else {
+        avgpool_bwd_gather<T, false><<<flat_grid(total), kThreads, 0, kd::stream()>>>(go, gx, g, total);
+    }
+    return kd::launch_status();
+}
+
+template <typename T>
+int gap_forward(const T* x, T* y, int N, int C, int H, int W) {
+    if (!x || !y) return -1;
+    if (N <= 0 || C <= 0 || H <= 0 || W <= 0) return -2;
+    (void)cudaGetLastError();
+    const int64_t rows = static_cast<int64_t>(N) * C;
+    const int64_t L64 = static_cast<int64_t>(H) * W;
+    if (L64 > std::numeric_limits<int>::max()) return -2;
+    const int L = static_cast<int>(L64);
+    if (L <= 64 && kd::aligned16(x)) {
+        constexpr int WARPS = 4;
+        const int Ls = (L & 1) ? L : L + 1;
+        const size_t smem = static_cast<size_t>(WARPS) * 32 * Ls * sizeof(T);   // <= 66,560 bytes
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(gap_fwd_short<T, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        const int64_t chunks = (rows + 31) / 32;
+        const unsigned grid = kd::grid_for((chunks + WARPS - 1) / WARPS, 8);
+        gap_fwd_short<T, WARPS><<<grid, WARPS * 32, smem, kd::stream()>>>(x, y, rows, L, Ls);
+    } else {
+        const unsigned grid = kd::grid_for((rows + 7) / 8, 8);
+        const bool vec = kd::aligned16(x) && (L % 4 == 0);
+        if (vec) gap_fwd_long<T, true><<<grid, kThreads, 0, kd::stream()>>>(x, y, rows, L);
+        else gap_fwd_long<T, false><<<grid, kThreads, 0, kd::stream()>>>(x, y, rows, L);
+    }
+    return kd::launch_status();
+}
+
+template <typename T>
+int gap_backward(const T* go, T* gx, int N, int C, int H, int W) {
+    if (!go || !gx) return -1;
+    if (N <= 0 || C <= 0 || H <= 0 || W <= 0) return -2;
+    (void)cudaGetLastError();
+    const int64_t L64 = static_cast<int64_t>(H) * W;
+    if (L64 > std::numeric_limits<int>::max()) return -2;
+    const int64_t total = static_cast<int64_t>(N) * C * L64;
+    const bool vec = kd::aligned16(gx);
+    const int64_t items = vec ? (total >> 2) + 1 : total;
+    gap_bwd<T><<<flat_grid(items), kThreads, 0, kd::stream()>>>(go, gx, total, static_cast<int>(L64), vec);
+    return kd::launch_status();
+}
+
+template <typename T>
+int pad2d(const T* x, T* y, int N, int C, int H, int W, int ph, int pw, T value) {
+    if (!x || !y) return -1;
+    if (N <= 0 || C <= 0 || H <= 0 || W <= 0) return -2;
+    if (ph < 0 || pw < 0) return -3;
+    (void)cudaGetLastError();
+    const int64_t total = static_cast<int64_t>(N) * C * (H + 2 * ph) * (W + 2 * pw);
+    pad2d_kernel<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(x, y, H, W, ph, pw, value, total);
+    return kd::launch_status();
+}
+
+template <typename T>
+int crop2d(const T* xp, T* y, int N, int C, int Hp, int Wp, int ph, int pw, int H, int W) {
+    if (!xp || !y) return -1;
+    if (N <= 0 || C <= 0 || H <= 0 || W <= 0) return -2;
+    if (Hp <= 0 || Wp <= 0) return -3;
+    if (ph < 0 || pw < 0) return -4;
+    (void)cudaGetLastError();
+    const int64_t total = static_cast<int64_t>(N) * C * H * W;
+    crop2d_kernel<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(xp, y, Hp, Wp, ph, pw, H, W, total);
+    return kd::launch_status();
+}
+
+inline PoolGeom geom(int H, int W, int Ho, int Wo, int kh, int kw, int sh, int sw, int ph, int pw) {
+    PoolGeom g;
+    g.H = H; g.W = W; g.Ho = Ho; g.Wo = Wo; g.kh = kh; g.kw = kw; g.sh = sh; g.sw = sw; g.ph = ph; g.pw = pw;
+    return g;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// C ABI: reference signatures (keydnn_maxpool2d_cuda.hpp:28-72,
+// keydnn_avgpool2d_cuda.hpp:38-76, keydnn_global_avgpool2d_cuda.hpp:34-60,
+// keydnn_pad2d_cuda.hpp).  The plane handed in is already padded, so these run
+// the same kernels with padding 0 on (H_pad, W_pad).
+// ---------------------------------------------------------------------------
+#define KD_POOL_LEGACY(T, SUF)                                                                                     \
+    KD_API int keydnn_cuda_maxpool2d_forward_##SUF(const T* x_pad, T* y, std::int64_t* argmax_idx, int N, int C,   \
+                                                   int H_pad, int W_pad, int H_out, int W_out, int k_h, int k_w,   \
+                                                   int s_h, int s_w) {                                             \
+        return maxpool_forward<T>(x_pad, y, reinterpret_cast<long long*>(argmax_idx), N, C,                        \
+                                  geom(H_pad, W_pad, H_out, W_out, k_h, k_w, s_h, s_w, 0, 0));                     \
+    }                                                                                                              \
+    KD_API int keydnn_cuda_maxpool2d_backward_##SUF(const T* grad_out, const std::int64_t* argmax_idx,             \
+                                                    T* grad_x_pad, int N, int C, int H_out, int W_out, int H_pad,  \
+                                                    int W_pad) {                                                   \
+        return maxpool_backward_legacy<T>(grad_out, reinterpret_cast<const long long*>(argmax_idx), grad_x_pad, N, \
+                                          C, H_out, W_out, H_pad, W_pad);                                          \
+    }                                                                                                              \
+    KD_API int keydnn_cuda_avgpool2d_forward_##SUF(const T* x_pad, T* y, int N, int C, int H_pad, int W_pad,       \
+                                                   int H_out, int W_out, int k_h, int k_w, int s_h, int s_w) {     \
+        return avgpool_forward<T>(x_pad, y, N, C, geom(H_pad, W_pad, H_out, W_out, k_h, k_w, s_h, s_w, 0, 0));     \
+    }                                                                                                              \
+    KD_API int keydnn_cuda_avgpool2d_backward_##SUF(const T* grad_out, T* grad_x_pad, int N, int C, int H_out,     \
+                                                    int W_out, int H_pad, int W_pad, int k_h, int k_w, int s_h,    \
+                                                    int s_w) {                                                     \
+        return avgpool_backward<T>(grad_out, grad_x_pad, N, C,                                                     \
+                                   geom(H_pad, W_pad, H_out, W_out, k_h, k_w, s_h, s_w, 0, 0), true);              \
+    }                                                                                                              \
+    KD_API int keydnn_cuda_global_avgpool2d_forward_##SUF(const T* x, T* y, int N, int C, int H, int W) {          \
+        return gap_forward<T>(x, y, N, C, H, W);                                                                   \
+    }                                                                                                              \
+    KD_API int keydnn_cuda_global_avgpool2d_backward_##SUF(const T* grad_out, T* grad_x, int N, int C, int H,      \
+                                                           int W) {                                                \
+        return gap_backward<T>(grad_out, grad_x, N, C, H, W);                                                      \
+    }                                                                                                              \
+    KD_API int keydnn_cuda_pad2d_##SUF(const T* x, T* y_pad, int N, int C, int H, int W, int p_h, int p_w,         \
+                                       T pad_value) {                                                              \
+        return pad2d<T>(x, y_pad, N, C, H, W, p_h, p_w, pad_value);                                                \
+    }                                                                                                              \
+    KD_API int keydnn_cuda_crop2d_##SUF(const T* x_pad, T* y, int N, int C, int H_pad, int W_pad, int p_h,         \
+                                        int p_w, int H, int W) {                                                   \
+        return crop2d<T>(x_pad, y, N, C, H_pad, W_pad, p_h, p_w, H, W);                                            \
+    }
+
+KD_POOL_LEGACY(float, f32)
+KD_POOL_LEGACY(double, f64)
+
+// ---------------------------------------------------------------------------
+// C ABI: fused entries (additive).  x / grad_x are the un-padded (N,C,H,W)
+// tensors; argmax positions keep the reference encoding h*W_pad + w in the padded
+// plane, W_pad = W + 2*p_w.  Backward overwrites grad_x (no zero-fill needed).
+// They replace the pad -> pool and memset -> pool-backward -> crop sequences of
+// ops/pool2d_cuda_ext.py:56-522.
+// ---------------------------------------------------------------------------
+#define KD_POOL_EX(T, SUF)                                                                                         \
+    KD_API int keydnn_cuda_maxpool2d_forward_ex_##SUF(const T* x, T* y, std::int64_t* argmax_idx, int N, int C,    \
+                                                      int H, int W, int H_out, int W_out, int k_h, int k_w,        \
+                                                      int s_h, int s_w, int p_h, int p_w) {                        \
+        return maxpool_forward<T>(x, y, reinterpret_cast<long long*>(argmax_idx), N, C,                            \
+                                  geom(H, W, H_out, W_out, k_h, k_w, s_h, s_w, p_h, p_w));                         \
+    }                                                                                                              \
+    KD_API int keydnn_cuda_maxpool2d_backward_ex_##SUF(const T* grad_out, const std::int64_t* argmax_idx,          \
+                                                       T* grad_x, int N, int C, int H, int W, int H_out,           \
+                                                       int W_out, int k_h, int k_w, int s_h, int s_w, int p_h,     \
+                                                       int p_w) {                                                  \
+        return maxpool_backward_ex<T>(grad_out, reinterpret_cast<const long long*>(argmax_idx), grad_x, N, C,      \
+                                      geom(H, W, H_out, W_out, k_h, k_w, s_h, s_w, p_h, p_w));                     \
+    }                                                                                                              \
+    KD_API int keydnn_cuda_avgpool2d_forward_ex_##SUF(const T* x, T* y, int N, int C, int H, int W, int H_out,     \
+                                                      int W_out, int k_h, int k_w, int s_h, int s_w, int p_h,      \
+                                                      int p_w) {                                                   \
+        return avgpool_forward<T>(x, y, N, C, geom(H, W, H_out, W_out, k_h, k_w, s_h, s_w, p_h, p_w));             \
+    }                                                                                                              \
+    KD_API int keydnn_cuda_avgpool2d_backward_ex_##SUF(const T* grad_out, T* grad_x, int N, int C, int H, int W,   \
+                                                       int H_out, int W_out, int k_h, int k_w, int s_h, int s_w,   \
+                                                       int p_h, int p_w) {                                         \
+        return avgpool_backward<T>(grad_out, grad_x, N, C,                                                         \
+                                   geom(H, W, H_out, W_out, k_h, k_w, s_h, s_w, p_h, p_w), false);                 \
+    }
+
+KD_POOL_EX(float, f32)
+KD_POOL_EX(double, f64)

@@ -1,0 +1,980 @@
+// Reductions over flat vectors and 2-D matrices, their gradient broadcast / mask
+// kernels, and the N-D un-broadcast sum.
+//
+// Reference kernels replaced (KeyDNNV2CudaNative/keydnn_reduce_cuda.cu):
+//   sum_all_kernel :58-70          one atomicAdd per element onto one address
+//   scale_scalar_kernel :98-101    <<<1,1>>> mean scale
+//   fill_with_scalar_kernel :122-132
+//   max_axis2d_forward_axis{1,0} :156-205   one thread per row / per column, serial
+//   max_axis2d_backward_axis{1,0} :235-263  scatter onto a caller-zeroed matrix
+//   sum_axis2d_forward_axis{1,0} :292-323   one thread per row / per column, serial
+//   sum_axis2d_backward_axis{1,0} :355-381  int64 div/mod per element
+//   sum_to_shape_kernel :418-458   one atomicAdd per input element, 4 cudaMalloc per call
+//
+// Design: every forward reduction is a streaming pass with 16-byte loads and
+// per-thread partials, then warp shuffles, then a block tree in shared memory.
+// Cross-CTA combination is deterministic: each CTA publishes its partial to a
+// scratch array and the last CTA to arrive (an atomic ticket) folds the partials
+// in a fixed order; the counter is returned to zero for the next call.  Sums are
+// accumulated in the element type per thread (a few dozen terms) and combined in
+// double.  Maxima carry the position of the first occurrence through every merge.
+#include "common.cuh"
+
+namespace {
+
+using kd::ArgMax;
+using kd::Pack4;
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+template <typename T> __device__ __forceinline__ T ld_cg(const T* p) { return __ldcg(p); }
+
+// ---------------------------------------------------------------------------
+// Full reductions: sum / mean / max over all elements
+// ---------------------------------------------------------------------------
+// Folds the partials published by all CTAs; runs in the last CTA only.
+__device__ __forceinline__ bool take_ticket(unsigned int* counter, unsigned int expected) {
+    __shared__ bool last;
+    __threadfence();            // publish this thread's partials device-wide
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int t = atomicAdd(counter, 1u);
+        last = (t == expected - 1);
+    }
+    __syncthreads();
+    if (last) __threadfence();
+    return last;
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+sum_all_kernel(const T* __restrict__ x, int64_t n, double* partials, unsigned int* counter, T* out, T scale,
+               bool apply_scale) {
+    __shared__ double sm[kWarps];
+    constexpr int U = 4;
+    T acc[4 * U];
+#pragma unroll
+    for (int k = 0; k < 4 * U; ++k) acc[k] = T(0);
+    if (VEC) {
+        const int64_t n4 = n >> 2;
+        const int64_t tile = static_cast<int64_t>(kThreads) * U;
+        for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < n4;
+             base += static_cast<int64_t>(gridDim.x) * tile) {
+            Pack4<T> v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t p = base + u * kThreads + threadIdx.x;
+                if (p < n4) v[u] = kd::load4_stream(x + 4 * p);
+                else v[u].v[0] = v[u].v[1] = v[u].v[2] = v[u].v[3] = T(0);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[4 * u + k] += v[u].v[k];
+        }
+        if (blockIdx.x == 0 && threadIdx.x < 4) {
+            const int64_t i = (n4 << 2) + threadIdx.x;
+            if (i < n) acc[0] += x[i];
+        }
+    } else {
+        for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
+             i += static_cast<int64_t>(gridDim.x) * kThreads)
+            acc[0] += x[i];
+    }
+    double s = 0.0;
+#pragma unroll
+    for (int k = 0; k < 4 * U; ++k) s += static_cast<double>(acc[k]);
+    s = kd::block_sum(s, sm);
+    if (threadIdx.x == 0) partials[blockIdx.x] = s;
+    if (take_ticket(counter, gridDim.x)) {
+        double v = 0.0;
+        for (unsigned i = threadIdx.x; i < gridDim.x; i += kThreads) v += ld_cg(partials + i);
+        v = kd::block_sum(v, sm);
+        if (threadIdx.x == 0) {
+            T r = static_cast<T>(v);
+            if (apply_scale) r = r * scale;
+            out[0] = r;
+            *counter = 0u;
+        }
+    }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+max_all_kernel(const T* __restrict__ x, int64_t n, T* pval, long long* pidx, unsigned int* counter, T* out,
+               long long* out_idx) {
+    __shared__ T smv[kWarps];
+    __shared__ long long smi[kWarps];
+    ArgMax<T> a = kd::argmax_init<T>();
+    if (VEC) {
+        const int64_t n4 = n >> 2;
+        for (int64_t p = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; p < n4;
+             p += static_cast<int64_t>(gridDim.x) * kThreads) {
+            const Pack4<T> v = kd::load4_stream(x + 4 * p);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) kd::argmax_step(a, v.v[k], 4 * p + k);
+        }
+        if (blockIdx.x == 0 && threadIdx.x < 4) {
+            const int64_t i = (n4 << 2) + threadIdx.x;
+            if (i < n) kd::argmax_merge(a, x[i], static_cast<long long>(i));
+        }
+    } else {
+        for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
+             i += static_cast<int64_t>(gridDim.x) * kThreads)
+            kd::argmax_step(a, x[i], static_cast<long long>(i));
+    }
+    auto block_reduce = [&](ArgMax<T> v) {
+        v = kd::warp_argmax(v);
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        if (lane == 0) { smv[warp] = v.val; smi[warp] = v.idx; }
+        __syncthreads();
+        if (warp == 0) {
+            ArgMax<T> w = kd::argmax_init<T>();
+            if (lane < kWarps) { w.val = smv[lane]; w.idx = smi[lane]; }
+            v = kd::warp_argmax(w);
+        }
+        __syncthreads();
+        return v;
+    };
+    a = block_reduce(a);
+    if (threadIdx.x == 0) { pval[blockIdx.x] = a.val; pidx[blockIdx.x] = a.idx; }
+    if (take_ticket(counter, gridDim.x)) {
+        ArgMax<T> v = kd::argmax_init<T>();
+        for (unsigned i = threadIdx.x; i < gridDim.x; i += kThreads)
+            kd::argmax_merge(v, ld_cg(pval + i), ld_cg(pidx + i));
+        v = block_reduce(v);
+        if (threadIdx.x == 0) {
+            out[0] = v.val;
+            out_idx[0] = (v.idx == kd::kNoIndex) ? 0 : v.idx;
+            *counter = 0u;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Row reductions (axis = 1): y[r] = reduce over c of x[r, c]
+// ---------------------------------------------------------------------------
+// TPR threads cooperate on a row (32 = one warp, 256 = the CTA).
+template <typename T, int TPR, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+sum_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int cols, T scale, bool apply_scale) {
+    __shared__ double sm[kWarps];
+    constexpr int RPB = kThreads / TPR;              // rows per CTA trip
+    const int t = threadIdx.x % TPR;
+    const int sub = threadIdx.x / TPR;
+    for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * RPB; r0 < rows; r0 += static_cast<int64_t>(gridDim.x) * RPB) {
+        const int64_t r = r0 + sub;
+        T a0 = T(0), a1 = T(0), a2 = T(0), a3 = T(0);
+        if (r < rows) {
+            const T* src = x + r * cols;
+            if (VEC) {
+                const int c4 = cols >> 2;
+                int p = t;
+                for (; p + 3 * TPR < c4; p += 4 * TPR) {
+                    const Pack4<T> v0 = kd::load4_stream(src + 4 * p);
+                    const Pack4<T> v1 = kd::load4_stream(src + 4 * (p + TPR));
+                    const Pack4<T> v2 = kd::load4_stream(src + 4 * (p + 2 * TPR));
+                    const Pack4<T> v3 = kd::load4_stream(src + 4 * (p + 3 * TPR));
+                    a0 += v0.v[0]; a1 += v0.v[1]; a2 += v0.v[2]; a3 += v0.v[3];
+                    a0 += v1.v[0]; a1 += v1.v[1]; a2 += v1.v[2]; a3 += v1.v[3];
+                    a0 += v2.v[0]; a1 += v2.v[1]; a2 += v2.v[2]; a3 += v2.v[3];
+                    a0 += v3.v[0]; a1 += v3.v[1]; a2 += v3.v[2]; a3 += v3.v[3];
+                }
+                for (; p < c4; p += TPR) {
+                    const Pack4<T> v0 = kd::load4_stream(src + 4 * p);
+                    a0 += v0.v[0]; a1 += v0.v[1]; a2 += v0.v[2]; a3 += v0.v[3];
+                }
+            } else {
+                for (int c = t; c < cols; c += TPR) a0 += src[c];
+            }
+        }
+        double s = (static_cast<double>(a0) + static_cast<double>(a1)) +
+                   (static_cast<double>(a2) + static_cast<double>(a3));
+        if (TPR == 32) {
+            s = kd::warp_sum(s);
+        } else {
+            s = kd::block_sum(s, sm);
+        }
+        if (t == 0 && r < rows) {
+            T out = static_cast<T>(s);
+            if (apply_scale) out = out * scale;
+            y[r] = out;
+        }
+    }
+}
+
+template <typename T, int TPR, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+max_rows_kernel(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, int64_t rows, int cols) {
+    __shared__ T smv[kWarps];
+    __shared__ long long smi[kWarps];
+    constexpr int RPB = kThreads / TPR;
+    const int t = threadIdx.x % TPR;
+    const int sub = threadIdx.x / TPR;
+    for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * RPB; r0 < rows; r0 += static_cast<int64_t>(gridDim.x) * RPB) {
+        const int64_t r = r0 + sub;
+        ArgMax<T> a = kd::argmax_init<T>();
+        if (r < rows) {
+            const T* src = x + r * cols;
+            if (VEC) {
+                const int c4 = cols >> 2;
+                int p = t;
+                for (; p + 3 * TPR < c4; p += 4 * TPR) {
+                    Pack4<T> v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) v[u] = kd::load4_stream(src + 4 * (p + u * TPR));
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) kd::argmax_step(a, v[u].v[k], 4 * (p + u * TPR) + k);
+                }
+                for (; p < c4; p += TPR) {
+                    const Pack4<T> v0 = kd::load4_stream(src + 4 * p);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) kd::argmax_step(a, v0.v[k], 4 * p + k);
+                }
+            } else {
+                for (int c = t; c < cols; c += TPR) kd::argmax_step(a, src[c], static_cast<long long>(c));
+            }
+        }
+        a = kd::warp_argmax(a);
+        if (TPR != 32) {
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+            if (lane == 0) { smv[warp] = a.val; smi[warp] = a.idx; }
+            __syncthreads();
+            if (warp == 0) {
+                ArgMax<T> w = kd::argmax_init<T>();
+                if (lane < kWarps) { w.val = smv[lane]; w.idx = smi[lane]; }
+                a = kd::warp_argmax(w);
+            }
+            __syncthreads();
+        }
+        if (t == 0 && r < rows) {
+            y[r] = a.val;
+            idx[r] = (a.idx == kd::kNoIndex) ? 0 : a.idx;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Column reductions (axis = 0): y[c] = reduce over r of x[r, c]
+// ---------------------------------------------------------------------------
+// A CTA is 32 lanes x 8 row phases and owns a tile of 32*V columns by `rch`
+// rows.  Lanes read V adjacent columns (16 bytes when V = 4), so a warp reads a
+// contiguous 512-byte (f32) or 1-KiB (f64) piece of a row.  Each tile leaves one
+// partial per column in scratch; the last tile of a column stripe to finish folds
+// the stripe's partials in row order.
+template <typename T, int V> struct ColLoad {
+    static __device__ __forceinline__ void get(const T* p, T* out) {
+        if (V == 4) {
+            const Pack4<T> v = kd::load4_stream(p);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) out[k] = v.v[k];
+        } else {
+            out[0] = *p;
+        }
+    }
+};
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kThreads)
+sum_cols_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int cols, int rch, T* partials,
+                unsigned int* counters, T scale, bool apply_scale) {
+    __shared__ T sm[kWarps][32 * V + 1];
+    const int lane = threadIdx.x & 31, phase = threadIdx.x >> 5;
+    const int stripe = blockIdx.x;                    // column stripe
+    const int chunk = blockIdx.y;                     // row chunk
+    const int nchunks = gridDim.y;
+    const int c0 = (stripe * 32 + lane) * V;
+    const int r_begin = chunk * rch;
+    const int r_end = min(rows, r_begin + rch);
+    T acc[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) acc[k] = T(0);
+    if (c0 < cols) {
+        const T* src = x + c0;
+        int r = r_begin + phase;
+        for (; r + 3 * kWarps < r_end; r += 4 * kWarps) {
+            T v[4][V];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) ColLoad<T, V>::get(src + static_cast<int64_t>(r + u * kWarps) * cols, v[u]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc[k] += v[u][k];
+        }
+        for (; r < r_end; r += kWarps) {
+            T v[V];
+            ColLoad<T, V>::get(src + static_cast<int64_t>(r) * cols, v);
+#pragma unroll
+            for (int k = 0; k < V; ++k) acc[k] += v[k];
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < V; ++k) sm[phase][lane * V + k] = acc[k];
+    __syncthreads();
+    // fold the 8 row phases; thread j (< 32*V) owns column stripe*32*V + j
+    const int ncol_tile = 32 * V;
+    for (int j = threadIdx.x; j < ncol_tile; j += kThreads) {
+        const int c = stripe * ncol_tile + j;
+        if (c < cols) {
+            double s = 0.0;
+#pragma unroll
+            for (int p = 0; p < kWarps; ++p) s += static_cast<double>(sm[p][j]);
+            if (nchunks == 1) {
+                T out = static_cast<T>(s);
+                if (apply_scale) out = out * scale;
+                y[c] = out;
+            } else {
+                partials[static_cast<int64_t>(chunk) * cols + c] = static_cast<T>(s);
+            }
+        }
+    }
+    if (nchunks == 1) return;
+    if (take_ticket(counters + stripe, nchunks)) {
+        for (int j = threadIdx.x; j < ncol_tile; j += kThreads) {
+            const int c = stripe * ncol_tile + j;
+            if (c < cols) {
+                double s = 0.0;
+                for (int q = 0; q < nchunks; ++q) s += static_cast<double>(ld_cg(partials + static_cast<int64_t>(q) * cols + c));
+                T out = static_cast<T>(s);
+                if (apply_scale) out = out * scale;
+                y[c] = out;
+            }
+        }
+        if (threadIdx.x == 0) counters[stripe] = 0u;
+    }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kThreads)
+max_cols_kernel(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, int rows, int cols, int rch,
+                T* pval, int* pidx, unsigned int* counters) {
+    __shared__ T smv[kWarps][32 * V + 1];
+    __shared__ int smi[kWarps][32 * V + 1];
+    constexpr int kNone = std::numeric_limits<int>::max();
+    const int lane = threadIdx.x & 31, phase = threadIdx.x >> 5;
+    const int stripe = blockIdx.x, chunk = blockIdx.y, nchunks = gridDim.y;
+    const int c0 = (stripe * 32 + lane) * V;
+    const int r_begin = chunk * rch;
+    const int r_end = min(rows, r_begin + rch);
+    T best[V];
+    int brow[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) { best[k] = kd::neg_inf<T>(); brow[k] = kNone; }
+    if (c0 < cols) {
+        const T* src = x + c0;
+        int r = r_begin + phase;
+        for (; r + 3 * kWarps < r_end; r += 4 * kWarps) {
+            T v[4][V];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) ColLoad<T, V>::get(src + static_cast<int64_t>(r + u * kWarps) * cols, v[u]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int k = 0; k < V; ++k)
+                    if (v[u][k] > best[k]) { best[k] = v[u][k]; brow[k] = r + u * kWarps; }
+        }
+        for (; r < r_end; r += kWarps) {
+            T v[V];
+            ColLoad<T, V>::get(src + static_cast<int64_t>(r) * cols, v);
+#pragma unroll
+            for (int k = 0; k < V; ++k)
+                if (v[k] > best[k]) { best[k] = v[k]; brow[k] = r; }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < V; ++k) { smv[phase][lane * V + k] = best[k]; smi[phase][lane * V + k] = brow[k]; }
+    __syncthreads();
+    const int ncol_tile = 32 * V;
+    for (int j = threadIdx.x; j < ncol_tile; j += kThreads) {
+        const int c = stripe * ncol_tile + j;
+        if (c < cols) {
+            T bv = kd::neg_inf<T>();
+            int bi = kNone;
+#pragma unroll
+            for (int p = 0; p < kWarps; ++p) {
+                const T v = smv[p][j];
+                const int i = smi[p][j];
+                if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+            }
+            if (nchunks == 1) {
+                y[c] = bv;
+                idx[c] = (bi == kNone) ? 0 : bi;
+            } else {
+                pval[static_cast<int64_t>(chunk) * cols + c] = bv;
+                pidx[static_cast<int64_t>(chunk) * cols + c] = bi;
+            }
+        }
+    }
+    if (nchunks == 1) return;
+    if (take_ticket(counters + stripe, nchunks)) {
+        for (int j = threadIdx.x; j < ncol_tile; j += kThreads) {
+            const int c = stripe * ncol_tile + j;
+            if (c < cols) {
+                T bv = kd::neg_inf<T>();
+                int bi = kNone;
+                for (int q = 0; q < nchunks; ++q) {
+                    const T v = ld_cg(pval + static_cast<int64_t>(q) * cols + c);
+                    const int i = ld_cg(pidx + static_cast<int64_t>(q) * cols + c);
+                    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+                }
+                y[c] = bv;
+                idx[c] = (bi == kNone) ? 0 : bi;
+            }
+        }
+        if (threadIdx.x == 0) counters[stripe] = 0u;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Gradient kernels (pure writes)
+// ---------------------------------------------------------------------------
+// gx[i] = go[0] * scale   (keydnn_reduce_cuda.cu:122-149; scale is 1 for sum)
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+bcast_scalar_kernel(const T* __restrict__ go, T* __restrict__ gx, int64_t n, T scale, int head) {
+    const T v = __ldg(go) * scale;
+    const int64_t body = n - head;
+    const int64_t n4 = body >> 2;
+    T* gb = gx + head;
+    Pack4<T> r;
+    r.v[0] = r.v[1] = r.v[2] = r.v[3] = v;
+    for (int64_t p = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; p < n4;
+         p += static_cast<int64_t>(gridDim.x) * kThreads)
+        kd::store4(gb + 4 * p, r);
+    if (blockIdx.x == 0) {
+        if (threadIdx.x < head) gx[threadIdx.x] = v;
+        const int64_t i = head + (n4 << 2) + (threadIdx.x - 32);
+        if (threadIdx.x >= 32 && threadIdx.x < 36 && i < n) gx[i] = v;
+    }
+}
+
+// gx[i] = (i == idx[0]) ? 0 + go[0] : 0   (gradient of max over all elements)
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+onehot_kernel(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, int64_t n, int head) {
+    const T g = T(0) + __ldg(go);
+    const long long target = __ldg(idx);
+    const int64_t body = n - head;
+    const int64_t n4 = body >> 2;
+    T* gb = gx + head;
+    for (int64_t p = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; p < n4;
+         p += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const long long i0 = head + 4 * p;
+        Pack4<T> r;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) r.v[k] = (i0 + k == target) ? g : T(0);
+        kd::store4(gb + 4 * p, r);
+    }
+    if (blockIdx.x == 0) {
+        if (threadIdx.x < head) gx[threadIdx.x] = (threadIdx.x == target) ? g : T(0);
+        const int64_t i = head + (n4 << 2) + (threadIdx.x - 32);
+        if (threadIdx.x >= 32 && threadIdx.x < 36 && i < n) gx[i] = (i == target) ? g : T(0);
+    }
+}
+
+// Matrix-shaped gradients.  MODE selects the value written at (r, c):
+//   0: go[r]                      sum over axis 1
+//   1: go[c]                      sum over axis 0
+//   2: idx[r] == c ? 0+go[r] : 0  max over axis 1
+//   3: idx[c] == r ? 0+go[c] : 0  max over axis 0
+// `scale` multiplies modes 0/1 when apply_scale (mean over an axis).
+// blockIdx.x / threadIdx.x walk 4-column packets of a row, blockIdx.y walks
+// rows, so column-indexed operands are loaded once per thread and no division
+// is needed.
+template <typename T, int MODE, int V>
+__global__ void __launch_bounds__(kThreads)
+grad_matrix_kernel(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, int rows, int cols,
+                   T scale, bool apply_scale) {
+    const int ppr = (cols + V - 1) / V;
+    for (int p = blockIdx.x * kThreads + threadIdx.x; p < ppr; p += gridDim.x * kThreads) {
+        const int c0 = p * V;
+        T gcol[V];
+        long long icol[V];
+        if (MODE == 1 || MODE == 3) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                gcol[k] = __ldg(go + c0 + k);
+                if (MODE == 1 && apply_scale) gcol[k] = gcol[k] * scale;
+                if (MODE == 3) { icol[k] = __ldg(idx + c0 + k); gcol[k] = T(0) + gcol[k]; }
+            }
+        }
+        for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+            T out[V];
+            if (MODE == 0) {
+                T g = __ldg(go + r);
+                if (apply_scale) g = g * scale;
+#pragma unroll
+                for (int k = 0; k < V; ++k) out[k] = g;
+            } else if (MODE == 1) {
+#pragma unroll
+                for (int k = 0; k < V; ++k) out[k] = gcol[k];
+            } else if (MODE == 2) {
+                const long long target = __ldg(idx + r);
+                const T g = T(0) + __ldg(go + r);
+#pragma unroll
+                for (int k = 0; k < V; ++k) out[k] = (target == c0 + k) ? g : T(0);
+            } else {
+#pragma unroll
+                for (int k = 0; k < V; ++k) out[k] = (icol[k] == r) ? gcol[k] : T(0);
+            }
+            T* dst = gx + static_cast<int64_t>(r) * cols + c0;
+            if (V == 4) {
+                Pack4<T> pk;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) pk.v[k] = out[k];
+                kd::store4(dst, pk);
+            } else {
+                dst[0] = out[0];
+            }
+        }
+    }
+}
+
+// Reference-signature max backward: grad_x[argmax] += grad_out onto the caller's
+// (zero-filled) matrix (keydnn_reduce_cuda.cu:235-263).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+max_scatter_kernel(const T* __restrict__ go, const long long* __restrict__ idx, T* gx, int rows, int cols, int axis) {
+    const int n = axis == 1 ? rows : cols;
+    for (int i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
+        const long long k = idx[i];
+        if (axis == 1) {
+            if (k >= 0 && k < cols) gx[static_cast<int64_t>(i) * cols + k] += go[i];
+        } else {
+            if (k >= 0 && k < rows) gx[k * cols + i] += go[i];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// sum_to_shape: out[k] = sum over (a, b) of x[a, k, b]   (outer A, kept K, inner B)
+// ---------------------------------------------------------------------------
+// One CTA per (k, slice of a): reads `ach` contiguous runs of B elements, leaves
+// one partial; the last slice of k folds them in order.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+sum_akb_kernel(const T* __restrict__ x, T* __restrict__ y, int A, int K, int64_t B, int ach, double* partials,
+               unsigned int* counters) {
+    __shared__ double sm[kWarps];
+    const int k = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
+    const int a_begin = slice * ach;
+    const int a_end = min(A, a_begin + ach);
+    T a0 = T(0), a1 = T(0), a2 = T(0), a3 = T(0);
+    for (int a = a_begin; a < a_end; ++a) {
+        const T* src = x + (static_cast<int64_t>(a) * K + k) * B;
+        if (VEC) {
+            const int64_t b4 = B >> 2;
+            for (int64_t p = threadIdx.x; p < b4; p += kThreads) {
+                const Pack4<T> v = kd::load4_stream(src + 4 * p);
+                a0 += v.v[0]; a1 += v.v[1]; a2 += v.v[2]; a3 += v.v[3];
+            }
+        } else {
+            for (int64_t b = threadIdx.x; b < B; b += kThreads) a0 += src[b];
+        }
+    }
+    double s = (static_cast<double>(a0) + static_cast<double>(a1)) +
+               (static_cast<double>(a2) + static_cast<double>(a3));
+    s = kd::block_sum(s, sm);
+    if (nslices == 1) {
+        if (threadIdx.x == 0) y[k] = static_cast<T>(s);
+        return;
+    }
+    if (threadIdx.x == 0) partials[static_cast<int64_t>(slice) * K + k] = s;
+    if (take_ticket(counters + k, nslices)) {
+        double v = 0.0;
+        for (int q = threadIdx.x; q < nslices; q += kThreads) v += ld_cg(partials + static_cast<int64_t>(q) * K + k);
+        v = kd::block_sum(v, sm);
+        if (threadIdx.x == 0) { y[k] = static_cast<T>(v); counters[k] = 0u; }
+    }
+}
+
+constexpr int kMaxDims = 8;
+struct ShapeMeta {
+    int ndim;
+    int64_t in_stride[kMaxDims];
+    int64_t out_stride[kMaxDims];   // 0 where the dimension is reduced
+};
+
+// Fallback for arbitrary kept/reduced interleavings: atomics onto a zeroed y.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+sum_to_shape_atomic_kernel(const T* __restrict__ x, T* y, int64_t n, ShapeMeta m) {
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * kThreads) {
+        int64_t rem = i, off = 0;
+#pragma unroll
+        for (int d = 0; d < kMaxDims; ++d) {
+            if (d >= m.ndim) break;
+            const int64_t q = rem / m.in_stride[d];
+            rem -= q * m.in_stride[d];
+            off += q * m.out_stride[d];
+        }
+        atomicAdd(y + off, x[i]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host-side launchers
+// ---------------------------------------------------------------------------
+template <typename T>
+int sum_all(const T* x, T* y, int64_t n, bool mean) {
+    if (!x || !y) return -1;
+    if (n <= 0) return -2;
+    (void)cudaGetLastError();
+    const bool vec = kd::aligned16(x);
+    const int64_t tiles = vec ? ((n >> 2) + kThreads * 4 - 1) / (kThreads * 4) : (n + kThreads - 1) / kThreads;
+    const unsigned grid = kd::grid_for(tiles < 1 ? 1 : tiles, 8);
+    double* partials = static_cast<double*>(kd::scratch(grid * sizeof(double)));
+    unsigned int* counter = kd::counters(1);
+    if (!partials || !counter) return static_cast<int>(cudaErrorMemoryAllocation);
+    const T scale = T(1) / static_cast<T>(n);
+    if (vec) sum_all_kernel<T, true><<<grid, kThreads, 0, kd::stream()>>>(x, n, partials, counter, y, scale, mean);
+    else sum_all_kernel<T, false><<<grid, kThreads, 0, kd::stream()>>>(x, n, partials, counter, y, scale, mean);
+    return kd::launch_status();
+}
+
+template <typename T>
+int max_all(const T* x, T* y, long long* idx, int64_t n) {
+    if (!x || !y || !idx) return -1;
+    if (n <= 0) return -2;
+    (void)cudaGetLastError();
+    const bool vec = kd::aligned16(x);
+    const int64_t tiles = vec ? ((n >> 2) + kThreads - 1) / kThreads : (n + kThreads - 1) / kThreads;
+    const unsigned grid = kd::grid_for(tiles < 1 ? 1 : tiles, 8);
+    char* buf = static_cast<char*>(kd::scratch(grid * 16));
+    unsigned int* counter = kd::counters(1);
+    if (!buf || !counter) return static_cast<int>(cudaErrorMemoryAllocation);
+    long long* pidx = reinterpret_cast<long long*>(buf);
+    T* pval = reinterpret_cast<T*>(buf + static_cast<size_t>(grid) * 8);
+    if (vec) max_all_kernel<T, true><<<grid, kThreads, 0, kd::stream()>>>(x, n, pval, pidx, counter, y, idx);
+    else max_all_kernel<T, false><<<grid, kThreads, 0, kd::stream()>>>(x, n, pval, pidx, counter, y, idx);
+    return kd::launch_status();
+}
+
+template <typename T>
+int sum_rows(const T* x, T* y, int64_t rows, int cols, T scale, bool apply_scale) {
+    const bool vec = kd::aligned16(x) && (cols % 4 == 0);
+    cudaStream_t s = kd::stream();
+    if (cols >= 2048) {
+        const unsigned grid = kd::grid_for(rows, 8);
+        if (vec) sum_rows_kernel<T, kThreads, true><<<grid, kThreads, 0, s>>>(x, y, rows, cols, scale, apply_scale);
+        else sum_rows_kernel<T, kThreads, false><<<grid, kThreads, 0, s>>>(x, y, rows, cols, scale, apply_scale);
+    } else {
+        const unsigned grid = kd::grid_for((rows + kWarps - 1) / kWarps, 8);
+        if (vec) sum_rows_kernel<T, 32, true><<<grid, kThreads, 0, s>>>(x, y, rows, cols, scale, apply_scale);
+        else sum_rows_kernel<T, 32, false><<<grid, kThreads, 0, s>>>(x, y, rows, cols, scale, apply_scale);
+    }
+    return kd::launch_status();
+}
+
+template <typename T>
+int max_rows(const T* x, T* y, long long* idx, int64_t rows, int cols) {
+    const bool vec = kd::aligned16(x) && (cols % 4 == 0);
+    cudaStream_t s = kd::stream();
+    if (cols >= 2048) {
+        const unsigned grid = kd::grid_for(rows, 8);
+        if (vec) max_rows_kernel<T, kThreads, true><<<grid, kThreads, 0, s>>>(x, y, idx, rows, cols);
+        else max_rows_kernel<T, kThreads, false><<<grid, kThreads, 0, s>>>(x, y, idx, rows, cols);
+    } else {
+        const unsigned grid = kd::grid_for((rows + kWarps - 1) / kWarps, 8);
+        if (vec) max_rows_kernel<T, 32, true><<<grid, kThreads, 0, s>>>(x, y, idx, rows, cols);
+        else max_rows_kernel<T, 32, false><<<grid, kThreads, 0, s>>>(x, y, idx, rows, cols);
+    }
+    return kd::launch_status();
+}
+
+// Row-chunk height for column reductions: tiles of about 128 rows keep several
+// waves of CTAs in flight while the partial traffic stays near 1% of the input.
+inline int pick_row_chunk(int rows, int stripes) {
+    int rch = 128;
+    // small matrices: do not split below what fills the machine once
+    const int64_t want_ctas = static_cast<int64_t>(kd::sm_count()) * 4;
+    while (rch > 32 && static_cast<int64_t>(stripes) * ((rows + rch - 1) / rch) < want_ctas) rch >>= 1;
+    if (rch > rows) rch = ((rows + kWarps - 1) / kWarps) * kWarps;
+    return rch;
+}
+
+template <typename T>
+int sum_cols(const T* x, T* y, int rows, int cols, T scale, bool apply_scale) {
+    const bool vec = kd::aligned16(x) && (cols % 4 == 0);
+    const int V = vec ? 4 : 1;
+    const int stripes = (cols + 32 * V - 1) / (32 * V);
+    const int rch = pick_row_chunk(rows, stripes);
+    const int nchunks = (rows + rch - 1) / rch;
+    if (nchunks > 65535) return -2;
+    T* partials = nullptr;
+    unsigned int* counters = nullptr;
+    if (nchunks > 1) {
+        partials = static_cast<T*>(kd::scratch(static_cast<size_t>(nchunks) * cols * sizeof(T)));
+        counters = kd::counters(stripes);
+        if (!partials || !counters) return static_cast<int>(cudaErrorMemoryAllocation);
+    }
+    dim3 grid(stripes, nchunks);
+    cudaStream_t s = kd::stream();
+    if (vec) sum_cols_kernel<T, 4><<<grid, kThreads, 0, s>>>(x, y, rows, cols, rch, partials, counters, scale, apply_scale);
+    else sum_cols_kernel<T, 1><<<grid, kThreads, 0, s>>>(x, y, rows, cols, rch, partials, counters, scale, apply_scale);
+    return kd::launch_status();
+}
+
+template <typename T>
+int max_cols(const T* x, T* y, long long* idx, int rows, int cols) {
+    const bool vec = kd::aligned16(x) && (cols % 4 == 0);
+    const int V = vec ? 4 : 1;
+    const int stripes = (cols + 32 * V - 1) / (32 * V);
+    const int rch = pick_row_chunk(rows, stripes);
+    const int nchunks = (rows + rch - 1) / rch;
+    if (nchunks > 65535) return -2;
+    T* pval = nullptr;
+    int* pidx = nullptr;
+    unsigned int* counters = nullptr;
+    if (nchunks > 1) {
+        const size_t cells = static_cast<size_t>(nchunks) * cols;
+        char* buf = static_cast<char*>(kd::scratch(cells * (sizeof(T) + sizeof(int))));
+        counters = kd::counters(stripes);
+        if (!buf || !counters) return static_cast<int>(cudaErrorMemoryAllocation);
+        pval = reinterpret_cast<T*>(buf);
+        pidx = reinterpret_cast<int*>(buf + cells * sizeof(T));
+    }
+    dim3 grid(stripes, nchunks);
+    cudaStream_t s = kd::stream();
+    if (vec) max_cols_kernel<T, 4><<<grid, kThreads, 0, s>>>(x, y, idx, rows, cols, rch, pval, pidx, counters);
+    else max_cols_kernel<T, 1><<<grid, kThreads, 0, s>>>(x, y, idx, rows, cols, rch, pval, pidx, counters);
+    return kd::launch_status();
+}
+
+template <typename T>
+int reduce_axis2d_sum(const T* x, T* y, int rows, int cols, int axis, bool mean) {
+    if (!x || !y) return -1;
+    if (rows <= 0 || cols <= 0) return -2;
+    if (!(axis == 0 || axis == 1)) return -3;
+    (void)cudaGetLastError();
+    const T scale = T(1) / static_cast<T>(axis == 1 ? cols : rows);
+    return axis == 1 ? sum_rows<T>(x, y, rows, cols, scale, mean) : sum_cols<T>(x, y, rows, cols, scale, mean);
+}
+
+template <typename T>
+int reduce_axis2d_max(const T* x, T* y, long long* idx, int rows, int cols, int axis) {
+    if (!x || !y || !idx) return -1;
+    if (rows <= 0 || cols <= 0) return -2;
+    if (!(axis == 0 || axis == 1)) return -3;
+    (void)cudaGetLastError();
+    return axis == 1 ? max_rows<T>(x, y, idx, rows, cols) : max_cols<T>(x, y, idx, rows, cols);
+}
+
+template <typename T>
+int bcast_scalar(const T* go, T* gx, int64_t n, T scale) {
+    if (!go || !gx) return -1;
+    if (n <= 0) return -2;
+    (void)cudaGetLastError();
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(gx);
+    if (addr % sizeof(T)) return static_cast<int>(cudaErrorMisalignedAddress);
+    int head = static_cast<int>(((16 - (addr & 15)) & 15) / sizeof(T));
+    if (head > n) head = static_cast<int>(n);
+    const unsigned grid = kd::grid_for(((n >> 2) + kThreads - 1) / kThreads + 1, 8);
+    bcast_scalar_kernel<T><<<grid, kThreads, 0, kd::stream()>>>(go, gx, n, scale, head);
+    return kd::launch_status();
+}
+
+template <typename T, int MODE>
+int grad_matrix(const T* go, const long long* idx, T* gx, int rows, int cols, T scale, bool apply_scale) {
+    const bool vec = kd::aligned16(gx) && (cols % 4 == 0);
+    const int V = vec ? 4 : 1;
+    const int ppr = (cols + V - 1) / V;
+    int gx_dim = (ppr + kThreads - 1) / kThreads;
+    if (gx_dim > 64) gx_dim = 64;
+    int64_t want = static_cast<int64_t>(kd::sm_count()) * 8;
+    int gy = static_cast<int>((want + gx_dim - 1) / gx_dim);
+    if (gy > rows) gy = rows;
+    if (gy > 65535) gy = 65535;
+    if (gy < 1) gy = 1;
+    dim3 grid(gx_dim, gy);
+    cudaStream_t s = kd::stream();
+    if (vec) grad_matrix_kernel<T, MODE, 4><<<grid, kThreads, 0, s>>>(go, idx, gx, rows, cols, scale, apply_scale);
+    else grad_matrix_kernel<T, MODE, 1><<<grid, kThreads, 0, s>>>(go, idx, gx, rows, cols, scale, apply_scale);
+    return kd::launch_status();
+}
+
+template <typename T>
+int sum_axis2d_backward(const T* go, T* gx, int rows, int cols, int axis, bool mean) {
+    if (!go || !gx) return -1;
+    if (rows <= 0 || cols <= 0) return -2;
+    if (!(axis == 0 || axis == 1)) return -3;
+    (void)cudaGetLastError();
+    const T scale = T(1) / static_cast<T>(axis == 1 ? cols : rows);
+    return axis == 1 ? grad_matrix<T, 0>(go, nullptr, gx, rows, cols, scale, mean)
+                     : grad_matrix<T, 1>(go, nullptr, gx, rows, cols, scale, mean);
+}
+
+template <typename T>
+int max_axis2d_backward_full(const T* go, const long long* idx, T* gx, int rows, int cols, int axis) {
+    if (!go || !idx || !gx) return -1;
+    if (rows <= 0 || cols <= 0) return -2;
+    if (!(axis == 0 || axis == 1)) return -3;
+    (void)cudaGetLastError();
+    return axis == 1 ? grad_matrix<T, 2>(go, idx, gx, rows, cols, T(1), false)
+                     : grad_matrix<T, 3>(go, idx, gx, rows, cols, T(1), false);
+}
+
+template <typename T>
+int max_axis2d_backward_legacy(const T* go, const long long* idx, T* gx, int rows, int cols, int axis) {
+    if (!go || !idx || !gx) return -1;
+    if (rows <= 0 || cols <= 0) return -2;
+    if (!(axis == 0 || axis == 1)) return -3;
+    (void)cudaGetLastError();
+    const int n = axis == 1 ? rows : cols;
+    const unsigned grid = kd::grid_for((n + kThreads - 1) / kThreads, 8);
+    max_scatter_kernel<T><<<grid, kThreads, 0, kd::stream()>>>(go, idx, gx, rows, cols, axis);
+    return kd::launch_status();
+}
+
+template <typename T>
+int max_all_backward(const T* go, const long long* idx, T* gx, int64_t n) {
+    if (!go || !idx || !gx) return -1;
+    if (n <= 0) return -2;
+    (void)cudaGetLastError();
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(gx);
+    if (addr % sizeof(T)) return static_cast<int>(cudaErrorMisalignedAddress);
+    int head = static_cast<int>(((16 - (addr & 15)) & 15) / sizeof(T));
+    if (head > n) head = static_cast<int>(n);
+    const unsigned grid = kd::grid_for(((n >> 2) + kThreads - 1) / kThreads + 1, 8);
+    onehot_kernel<T><<<grid, kThreads, 0, kd::stream()>>>(go, idx, gx, n, head);
+    return kd::launch_status();
+}
+
+template <typename T>
+int sum_to_shape(const T* x, T* y, const int64_t* in_shape, const int64_t* out_shape, int ndim) {
+    if (!x || !y || !in_shape || !out_shape) return -1;
+    if (ndim <= 0) return -2;
+    if (ndim > kMaxDims) return -3;
+    int64_t numel_in = 1, numel_out = 1;
+    for (int d = 0; d < ndim; ++d) {
+        const int64_t id = in_shape[d], od = out_shape[d];
+        if (id < 0 || od < 0) return -4;
+        if (!(od == 1 || od == id)) return -5;
+        numel_in *= id;
+        numel_out *= od;
+    }
+    if (numel_out == 0) return 0;
+    (void)cudaGetLastError();
+    cudaStream_t s = kd::stream();
+    if (numel_in == 0) return kd::status(cudaMemsetAsync(y, 0, numel_out * sizeof(T), s));
+
+    // Collapse to alternating groups of reduced (R) / kept (K) extents.
+    int64_t ext[kMaxDims];
+    bool red[kMaxDims];
+    int ng = 0;
+    for (int d = 0; d < ndim; ++d) {
+        if (in_shape[d] == 1) continue;
+        const bool r = (out_shape[d] == 1);
+        if (ng > 0 && red[ng - 1] == r) ext[ng - 1] *= in_shape[d];
+        else { ext[ng] = in_shape[d]; red[ng] = r; ++ng; }
+    }
+    const int64_t imax = std::numeric_limits<int>::max();
+    if (ng == 0 || (ng == 1 && !red[0]))
+        return kd::status(cudaMemcpyAsync(y, x, numel_in * sizeof(T), cudaMemcpyDeviceToDevice, s));
+    if (ng == 1) return sum_all<T>(x, y, numel_in, false);
+    if (ng == 2 && red[0] && ext[0] <= imax && ext[1] <= imax)
+        return sum_cols<T>(x, y, static_cast<int>(ext[0]), static_cast<int>(ext[1]), T(1), false);
+    if (ng == 2 && !red[0] && ext[1] <= imax)
+        return sum_rows<T>(x, y, ext[0], static_cast<int>(ext[1]), T(1), false);
+    if (ng == 3 && red[0] && ext[0] <= imax && ext[1] <= imax) {
+        const int A = static_cast<int>(ext[0]), K = static_cast<int>(ext[1]);
+        const int64_t B = ext[2];
+        // enough (k, slice) CTAs to cover the machine a few times
+        int nslices = static_cast<int>((static_cast<int64_t>(kd::sm_count()) * 8 + K - 1) / K);
+        if (nslices > A) nslices = A;
+        if (nslices < 1) nslices = 1;
+        const int ach = (A + nslices - 1) / nslices;
+        nslices = (A + ach - 1) / ach;
+        double* partials = nullptr;
+        unsigned int* counters = nullptr;
+        if (nslices > 1) {
+            partials = static_cast<double*>(kd::scratch(static_cast<size_t>(nslices) * K * sizeof(double)));
+            counters = kd::counters(K);
+            if (!partials || !counters) return static_cast<int>(cudaErrorMemoryAllocation);
+        }
+        dim3 grid(K, nslices);
+        const bool vec = kd::aligned16(x) && (B % 4 == 0);
+        if (vec) sum_akb_kernel<T, true><<<grid, kThreads, 0, s>>>(x, y, A, K, B, ach, partials, counters);
+        else sum_akb_kernel<T, false><<<grid, kThreads, 0, s>>>(x, y, A, K, B, ach, partials, counters);
+        return kd::launch_status();
+    }
+    // general interleaving
+    ShapeMeta m;
+    m.ndim = ndim;
+    int64_t si = 1, so = 1;
+    for (int d = ndim - 1; d >= 0; --d) {
+        m.in_stride[d] = si;
+        m.out_stride[d] = (out_shape[d] == 1) ? 0 : so;
+        si *= in_shape[d];
+        so *= out_shape[d];
+    }
+    cudaError_t st = cudaMemsetAsync(y, 0, numel_out * sizeof(T), s);
+    if (st != cudaSuccess) return kd::status(st);
+    const unsigned grid = kd::grid_for((numel_in + kThreads - 1) / kThreads, 8);
+    sum_to_shape_atomic_kernel<T><<<grid, kThreads, 0, s>>>(x, y, numel_in, m);
+    return kd::launch_status();
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// C ABI: reference signatures (keydnn_reduce_cuda.hpp:56-140).  Guards: -1 null
+// pointer, -2 non-positive extent, -3 bad axis (keydnn_reduce_cuda.cu:74-75,
+// 209-211); sum_to_shape -1..-5 (:467-489).
+// ---------------------------------------------------------------------------
+#define KD_REDUCE(T, SUF)                                                                                           \
+    KD_API int keydnn_cuda_sum_all_##SUF(const T* x, T* y, int64_t numel) { return sum_all<T>(x, y, numel, false); } \
+    KD_API int keydnn_cuda_mean_all_##SUF(const T* x, T* y, int64_t numel) { return sum_all<T>(x, y, numel, true); } \
+    KD_API int keydnn_cuda_sum_backward_fill_##SUF(const T* grad_out, T* grad_x, int64_t numel) {                   \
+        return bcast_scalar<T>(grad_out, grad_x, numel, T(1));                                                      \
+    }                                                                                                               \
+    KD_API int keydnn_cuda_mean_backward_fill_##SUF(const T* grad_out, T* grad_x, int64_t numel) {                  \
+        if (numel <= 0) return (!grad_out || !grad_x) ? -1 : -2;                                                    \
+        return bcast_scalar<T>(grad_out, grad_x, numel, T(1) / static_cast<T>(numel));                              \
+    }                                                                                                               \
+    KD_API int keydnn_cuda_max_axis2d_forward_##SUF(const T* x, T* y, int64_t* idx, int rows, int cols, int axis) { \
+        return reduce_axis2d_max<T>(x, y, reinterpret_cast<long long*>(idx), rows, cols, axis);                     \
+    }                                                                                                               \
+    KD_API int keydnn_cuda_max_axis2d_backward_##SUF(const T* grad_out, const int64_t* idx, T* grad_x, int rows,    \
+                                                     int cols, int axis) {                                          \
+        return max_axis2d_backward_legacy<T>(grad_out, reinterpret_cast<const long long*>(idx), grad_x, rows, cols, \
+                                             axis);                                                                 \
+    }                                                                                                               \
+    KD_API int keydnn_cuda_sum_axis2d_forward_##SUF(const T* x, T* y, int rows, int cols, int axis) {               \
+        return reduce_axis2d_sum<T>(x, y, rows, cols, axis, false);                                                 \
+    }                                                                                                               \
+    KD_API int keydnn_cuda_sum_axis2d_backward_##SUF(const T* grad_out, T* grad_x, int rows, int cols, int axis) {  \
+        return sum_axis2d_backward<T>(grad_out, grad_x, rows, cols, axis, false);                                   \
+    }                                                                                                               \
+    KD_API int keydnn_cuda_sum_to_shape_##SUF(const T* x, T* y, const int64_t* in_shape, const int64_t* out_shape,  \
+                                              int ndim) {                                                           \
+        return sum_to_shape<T>(x, y, in_shape, out_shape, ndim);                                                    \
+    }                                                                                                               \
+    /* ---- additive entries (no counterpart in the reference library) ---- */                                      \
+    /* max backward that writes the whole matrix: no zero-fill pass before it */                                    \
+    KD_API int keydnn_cuda_max_axis2d_backward_ex_##SUF(const T* grad_out, const int64_t* idx, T* grad_x, int rows, \
+                                                        int cols, int axis) {                                       \
+        return max_axis2d_backward_full<T>(grad_out, reinterpret_cast<const long long*>(idx), grad_x, rows, cols,   \
+                                           axis);                                                                   \
+    }                                                                                                               \
+    /* mean over one axis of a matrix: sum * (1/extent), and its gradient */                                        \
+    KD_API int keydnn_cuda_mean_axis2d_forward_##SUF(const T* x, T* y, int rows, int cols, int axis) {              \
+        return reduce_axis2d_sum<T>(x, y, rows, cols, axis, true);                                                  \
+    }                                                                                                               \
+    KD_API int keydnn_cuda_mean_axis2d_backward_##SUF(const T* grad_out, T* grad_x, int rows, int cols, int axis) { \
+        return sum_axis2d_backward<T>(grad_out, grad_x, rows, cols, axis, true);                                    \
+    }                                                                                                               \
+    /* max over all elements with the flat position of its first occurrence */                                      \
+    KD_API int keydnn_cuda_max_all_forward_##SUF(const T* x, T* y, int64_t* idx, int64_t numel) {                   \
+        return max_all<T>(x, y, reinterpret_cast<long long*>(idx), numel);                                          \
+    }                                                                                                               \
+    KD_API int keydnn_cuda_max_all_backward_##SUF(const T* grad_out, const int64_t* idx, T* grad_x, int64_t numel) { \
+        return max_all_backward<T>(grad_out, reinterpret_cast<const long long*>(idx), grad_x, numel);               \
+    }
+
+KD_REDUCE(float, f32)
+KD_REDUCE(double, f64)

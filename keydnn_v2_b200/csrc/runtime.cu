@@ -1,0 +1,364 @@
+// Device runtime behind the C ABI: device selection, the caching allocator,
+// host<->device copies, the library stream, events and reduction scratch.
+//
+// Replaces the reference exports defined in
+// native_cuda/.../KeyDNNV2CudaNative/keydnn_cuda_utils.cu:13-54 and
+// keydnn_memcpy_d2d.cu:4-9 (raw cudaMalloc / cudaFree / cudaMemcpy wrappers).
+//
+// Differences that callers can observe only as speed:
+//  * keydnn_cuda_malloc / keydnn_cuda_free go through a per-device caching pool.
+//    Every kernel and copy of this library is ordered on one stream, so a block
+//    handed back by `free` can be handed out again at once: work that still
+//    reads it was enqueued earlier on the same stream.  cudaFree's implicit
+//    device synchronisation disappears from the per-op path.
+//  * copies are enqueued on the library stream and the host waits on that
+//    stream only.
+#include "common.cuh"
+
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+namespace {
+
+constexpr int kMaxDevices = 16;
+constexpr size_t kGranule = 512;             // allocation granularity (bytes)
+constexpr size_t kSmallLimit = 1u << 20;     // below this, round up to a power of two
+
+struct DevicePool {
+    std::multimap<size_t, void*> free_blocks;          // size -> block
+    std::unordered_map<void*, size_t> live;            // block -> rounded size
+    size_t bytes_reserved = 0;                         // total held from the driver
+    size_t bytes_in_use = 0;
+    size_t n_driver_mallocs = 0;
+    size_t n_requests = 0;
+};
+
+struct DeviceState {
+    bool inited = false;
+    int sm_count = 0;
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    unsigned int* counters = nullptr;
+    size_t counters_len = 0;
+    DevicePool pool;
+};
+
+std::mutex g_mu;
+DeviceState g_dev[kMaxDevices];
+cudaStream_t g_stream = nullptr;   // legacy default stream unless the caller sets one
+bool g_pool_enabled = true;
+
+int current_device() {
+    int d = 0;
+    cudaGetDevice(&d);
+    return (d >= 0 && d < kMaxDevices) ? d : 0;
+}
+
+DeviceState& state() {
+    DeviceState& s = g_dev[current_device()];
+    if (!s.inited) {
+        int d = current_device();
+        cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, d);
+        if (s.sm_count <= 0) s.sm_count = 148;
+        const char* e = std::getenv("KEYDNN_B200_NO_POOL");
+        if (e && e[0] == '1') g_pool_enabled = false;
+        s.inited = true;
+    }
+    return s;
+}
+
+size_t round_size(size_t n) {
+    if (n == 0) n = 1;
+    if (n < kSmallLimit) {
+        size_t p = kGranule;
+        while (p < n) p <<= 1;
+        return p;
+    }
+    // large blocks: 2 MiB granularity keeps reuse likely without doubling.
+    const size_t big = size_t(2) << 20;
+    return (n + big - 1) / big * big;
+}
+
+void release_cached(DevicePool& p) {
+    for (auto& kv : p.free_blocks) {
+        cudaFree(kv.second);
+        p.bytes_reserved -= kv.first;
+    }
+    p.free_blocks.clear();
+}
+
+}  // namespace
+
+namespace kd {
+
+cudaStream_t stream() { return g_stream; }
+
+int sm_count() {
+    std::lock_guard<std::mutex> lk(g_mu);
+    return state().sm_count;
+}
+
+void* scratch(size_t nbytes) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& s = state();
+    if (nbytes > s.scratch_bytes) {
+        // Earlier kernels that use the old buffer are ordered before the free
+        // by cudaFree's own synchronisation.
+        if (s.scratch) cudaFree(s.scratch);
+        size_t want = nbytes < (size_t(8) << 20) ? (size_t(8) << 20) : nbytes;
+        if (cudaMalloc(&s.scratch, want) != cudaSuccess) {
+            s.scratch = nullptr;
+            s.scratch_bytes = 0;
+            return nullptr;
+        }
+        s.scratch_bytes = want;
+    }
+    return s.scratch;
+}
+
+unsigned int* counters(size_t count) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& s = state();
+    if (count > s.counters_len) {
+        if (s.counters) cudaFree(s.counters);
+        size_t want = count < 4096 ? 4096 : count;
+        if (cudaMalloc(reinterpret_cast<void**>(&s.counters), want * sizeof(unsigned int)) != cudaSuccess) {
+            s.counters = nullptr;
+            s.counters_len = 0;
+            return nullptr;
+        }
+        cudaMemset(s.counters, 0, want * sizeof(unsigned int));
+        s.counters_len = want;
+    }
+    return s.counters;
+}
+
+}  // namespace kd
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+
+KD_API int keydnn_cuda_set_device(int device) {
+    return kd::status(cudaSetDevice(device));
+}
+
+KD_API int keydnn_cuda_malloc(std::uint64_t* out_ptr, std::size_t nbytes) {
+    if (!out_ptr) return -1;
+    *out_ptr = 0;
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& s = state();
+    DevicePool& p = s.pool;
+    p.n_requests++;
+    if (!g_pool_enabled) {
+        void* q = nullptr;
+        cudaError_t st = cudaMalloc(&q, nbytes);
+        if (st != cudaSuccess) return static_cast<int>(st);
+        *out_ptr = reinterpret_cast<std::uint64_t>(q);
+        return 0;
+    }
+    const size_t want = round_size(nbytes);
+    auto it = p.free_blocks.lower_bound(want);
+    // Accept a cached block only if it wastes less than half of itself.
+    if (it != p.free_blocks.end() && it->first <= want + want / 2 + kGranule) {
+        void* q = it->second;
+        size_t sz = it->first;
+        p.free_blocks.erase(it);
+        p.live.emplace(q, sz);
+        p.bytes_in_use += sz;
+        *out_ptr = reinterpret_cast<std::uint64_t>(q);
+        return 0;
+    }
+    void* q = nullptr;
+    cudaError_t st = cudaMalloc(&q, want);
+    if (st != cudaSuccess) {
+        // Give cached memory back to the driver and try once more.
+        (void)cudaGetLastError();
+        release_cached(p);
+        st = cudaMalloc(&q, want);
+        if (st != cudaSuccess) {
+            (void)cudaGetLastError();
+            return static_cast<int>(st);
+        }
+    }
+    p.n_driver_mallocs++;
+    p.bytes_reserved += want;
+    p.bytes_in_use += want;
+    p.live.emplace(q, want);
+    *out_ptr = reinterpret_cast<std::uint64_t>(q);
+    return 0;
+}
+
+KD_API int keydnn_cuda_free(std::uint64_t ptr) {
+    if (ptr == 0) return 0;
+    void* q = reinterpret_cast<void*>(ptr);
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& s = state();
+    DevicePool& p = s.pool;
+    auto it = p.live.find(q);
+    if (it == p.live.end()) {
+        // Not one of ours (pool disabled, or allocated on another device).
+        for (int d = 0; d < kMaxDevices; ++d) {
+            auto jt = g_dev[d].pool.live.find(q);
+            if (jt != g_dev[d].pool.live.end()) {
+                size_t sz = jt->second;
+                g_dev[d].pool.live.erase(jt);
+                g_dev[d].pool.bytes_in_use -= sz;
+                g_dev[d].pool.free_blocks.emplace(sz, q);
+                return 0;
+            }
+        }
+        return kd::status(cudaFree(q));
+    }
+    size_t sz = it->second;
+    p.live.erase(it);
+    p.bytes_in_use -= sz;
+    p.free_blocks.emplace(sz, q);
+    return 0;
+}
+
+// Additive: hand every cached block back to the driver.
+KD_API int keydnn_cuda_empty_cache() {
+    cudaError_t st = cudaStreamSynchronize(g_stream);
+    std::lock_guard<std::mutex> lk(g_mu);
+    release_cached(state().pool);
+    return kd::status(st);
+}
+
+// Additive: out[0]=bytes reserved from the driver, out[1]=bytes handed out,
+// out[2]=driver allocations made, out[3]=allocation requests served.
+KD_API int keydnn_cuda_pool_stats(std::uint64_t* out4) {
+    if (!out4) return -1;
+    std::lock_guard<std::mutex> lk(g_mu);
+    DevicePool& p = state().pool;
+    out4[0] = p.bytes_reserved;
+    out4[1] = p.bytes_in_use;
+    out4[2] = p.n_driver_mallocs;
+    out4[3] = p.n_requests;
+    return 0;
+}
+
+KD_API int keydnn_cuda_memcpy_h2d(std::uint64_t dst_dev, const void* src_host, std::size_t nbytes) {
+    if (nbytes == 0) return 0;
+    cudaError_t st = cudaMemcpyAsync(reinterpret_cast<void*>(dst_dev), src_host, nbytes,
+                                     cudaMemcpyHostToDevice, g_stream);
+    if (st != cudaSuccess) return static_cast<int>(st);
+    // Pageable sources are staged before the call returns; pinned sources are
+    // read by the DMA engine, so wait for it: the caller may reuse the buffer.
+    return kd::status(cudaStreamSynchronize(g_stream));
+}
+
+KD_API int keydnn_cuda_memcpy_d2h(void* dst_host, std::uint64_t src_dev, std::size_t nbytes) {
+    if (nbytes == 0) return 0;
+    cudaError_t st = cudaMemcpyAsync(dst_host, reinterpret_cast<const void*>(src_dev), nbytes,
+                                     cudaMemcpyDeviceToHost, g_stream);
+    if (st != cudaSuccess) return static_cast<int>(st);
+    return kd::status(cudaStreamSynchronize(g_stream));
+}
+
+// Additive: host->device copy that returns as soon as it is enqueued (the
+// source must stay valid and, to overlap, be pinned).
+KD_API int keydnn_cuda_memcpy_h2d_async(std::uint64_t dst_dev, const void* src_host, std::size_t nbytes) {
+    if (nbytes == 0) return 0;
+    return kd::status(cudaMemcpyAsync(reinterpret_cast<void*>(dst_dev), src_host, nbytes,
+                                      cudaMemcpyHostToDevice, g_stream));
+}
+
+KD_API int keydnn_cuda_memcpy_d2d(void* dst, const void* src, std::size_t nbytes) {
+    if (nbytes == 0) return 0;
+    if (!dst || !src) return 1;
+    cudaError_t st = cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToDevice, g_stream);
+    return st == cudaSuccess ? 0 : 2;
+}
+
+KD_API int keydnn_cuda_memset(std::uint64_t dev_ptr, int value, std::size_t nbytes) {
+    if (nbytes == 0) return 0;
+    return kd::status(cudaMemsetAsync(reinterpret_cast<void*>(dev_ptr), value, nbytes, g_stream));
+}
+
+KD_API int keydnn_cuda_synchronize() {
+    return kd::status(cudaDeviceSynchronize());
+}
+
+// Additive: pinned host buffers for the end-to-end path.
+KD_API int keydnn_cuda_host_alloc(void** out, std::size_t nbytes) {
+    if (!out) return -1;
+    *out = nullptr;
+    return kd::status(cudaMallocHost(out, nbytes ? nbytes : 1));
+}
+KD_API int keydnn_cuda_host_free(void* p) {
+    if (!p) return 0;
+    return kd::status(cudaFreeHost(p));
+}
+
+// Additive: the stream all work of this library is enqueued on.
+KD_API int keydnn_cuda_get_stream(std::uint64_t* out) {
+    if (!out) return -1;
+    *out = reinterpret_cast<std::uint64_t>(g_stream);
+    return 0;
+}
+KD_API int keydnn_cuda_set_stream(std::uint64_t s) {
+    g_stream = reinterpret_cast<cudaStream_t>(s);
+    return 0;
+}
+KD_API int keydnn_cuda_stream_create(std::uint64_t* out) {
+    if (!out) return -1;
+    cudaStream_t s = nullptr;
+    cudaError_t st = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
+    *out = reinterpret_cast<std::uint64_t>(s);
+    return kd::status(st);
+}
+KD_API int keydnn_cuda_stream_destroy(std::uint64_t s) {
+    if (!s) return 0;
+    if (reinterpret_cast<cudaStream_t>(s) == g_stream) g_stream = nullptr;
+    return kd::status(cudaStreamDestroy(reinterpret_cast<cudaStream_t>(s)));
+}
+KD_API int keydnn_cuda_stream_synchronize() {
+    return kd::status(cudaStreamSynchronize(g_stream));
+}
+
+// Additive: CUDA events on the library stream.  These are the names the
+// reference's backward profiler probes for (tensor/_tensor.py:1619-1629) and
+// never finds in its own DLL.
+KD_API int keydnn_cuda_event_create(std::uint64_t* out) {
+    if (!out) return -1;
+    cudaEvent_t e = nullptr;
+    cudaError_t st = cudaEventCreate(&e);
+    *out = reinterpret_cast<std::uint64_t>(e);
+    return kd::status(st);
+}
+KD_API int keydnn_cuda_event_record(std::uint64_t ev) {
+    return kd::status(cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev), g_stream));
+}
+KD_API int keydnn_cuda_event_synchronize(std::uint64_t ev) {
+    return kd::status(cudaEventSynchronize(reinterpret_cast<cudaEvent_t>(ev)));
+}
+KD_API int keydnn_cuda_event_elapsed_ms(std::uint64_t start, std::uint64_t stop, float* out_ms) {
+    if (!out_ms) return -1;
+    return kd::status(cudaEventElapsedTime(out_ms, reinterpret_cast<cudaEvent_t>(start),
+                                           reinterpret_cast<cudaEvent_t>(stop)));
+}
+KD_API int keydnn_cuda_event_destroy(std::uint64_t ev) {
+    if (!ev) return 0;
+    return kd::status(cudaEventDestroy(reinterpret_cast<cudaEvent_t>(ev)));
+}
+
+// Additive: device facts for the harness.
+KD_API int keydnn_cuda_device_count(int* out) {
+    if (!out) return -1;
+    return kd::status(cudaGetDeviceCount(out));
+}
+KD_API int keydnn_cuda_sm_count(int* out) {
+    if (!out) return -1;
+    *out = kd::sm_count();
+    return 0;
+}
+KD_API const char* keydnn_cuda_error_string(int code) {
+    if (code <= 0) return code == 0 ? "ok" : "argument guard";
+    return cudaGetErrorString(static_cast<cudaError_t>(code));
+}
+KD_API int keydnn_b200_abi_version() { return 1; }

@@ -1,0 +1,246 @@
+"""Generate ``tests/golden/ref_cpu_golden.npz`` by RUNNING THE REFERENCE ITSELF.
+
+Run from the repository root, on a machine that has a checkout of the reference
+project (default ``/root/reference``):
+
+    python tests/golden/make_golden.py [REFERENCE_ROOT]
+
+Two sources, both the reference's own code, neither modified:
+  * its Python/NumPy CPU path, imported from ``REFERENCE_ROOT/src`` (Tensor ops with
+    autograd, pooling Functions, the SGD optimizer);
+  * its C++ CPU pooling kernels, compiled by ``oracle/build.py`` from the sources
+    where they lie into ``oracle/_ref/libkeydnn_ref_native.so`` and called through
+    the C ABI of ``native/src/keydnn_maxpool2d.hpp`` / ``keydnn_avgpool2d.hpp``.
+
+The fixtures are small seeded cases; the test-suite compares both the CPU oracle
+(``oracle/``) and the CUDA library against them.  The generated file is committed;
+the reference is not needed to run the tests.
+"""
+from __future__ import annotations
+
+import ctypes
+import sys
+import warnings
+from pathlib import Path
+
+import numpy as np
+
+REPO = Path(__file__).resolve().parents[2]
+REF_ROOT = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+sys.dont_write_bytecode = True
+sys.path.insert(0, str(REF_ROOT / "src"))
+sys.path.insert(0, str(REPO))
+warnings.simplefilter("ignore")
+
+from keydnn.domain.device._device import Device  # noqa: E402
+from keydnn.infrastructure.optimizers._sgd import SGD  # noqa: E402
+from keydnn.infrastructure._parameter import Parameter  # noqa: E402
+from keydnn.infrastructure.pooling._pooling_function import (  # noqa: E402
+    AvgPool2dFn,
+    GlobalAvgPool2dFn,
+    MaxPool2dFn,
+)
+from keydnn.infrastructure.tensor._tensor import Tensor  # noqa: E402
+from keydnn.infrastructure.tensor._tensor_context import Context  # noqa: E402
+
+from oracle import build as oracle_build  # noqa: E402
+
+CPU = Device("cpu")
+OUT: dict[str, np.ndarray] = {}
+
+
+def tensor(a: np.ndarray, requires_grad: bool = False) -> Tensor:
+    t = Tensor(shape=a.shape, device=CPU, requires_grad=requires_grad)
+    t.copy_from_numpy(a)
+    return t
+
+
+def put(name: str, a) -> None:
+    OUT[name] = np.ascontiguousarray(np.asarray(a))
+
+
+# ---------------------------------------------------------------------------
+# pooling through the reference Functions (NumPy loops on this path)
+# ---------------------------------------------------------------------------
+POOL_CASES = [
+    # name, shape, kernel, stride, padding
+    ("k2s2p0", (2, 3, 8, 8), 2, 2, 0),
+    ("k3s2p1", (2, 2, 8, 8), 3, 2, 1),
+    ("k3s1p1", (1, 2, 7, 5), 3, 1, 1),
+    ("k2s2p0_odd", (1, 2, 7, 9), 2, 2, 0),
+    ("k23s21p10", (1, 1, 9, 10), (2, 3), (2, 1), (1, 0)),
+]
+
+
+def pool_cases() -> None:
+    rng = np.random.default_rng(1)
+    for name, shape, k, s, p in POOL_CASES:
+        x = rng.uniform(-1, 1, shape).astype(np.float32)
+        put(f"pool/{name}/x", x)
+        for kind, Fn in (("max", MaxPool2dFn), ("avg", AvgPool2dFn)):
+            xt = tensor(x, True)
+            ctx = Context(parents=(xt,), backward_fn=lambda g: None)
+            y = Fn.forward(ctx, xt, kernel_size=k, stride=s, padding=p)
+            yn = y.to_numpy()
+            go = rng.standard_normal(yn.shape).astype(np.float32)
+            (gx,) = Fn.backward(ctx, tensor(go))
+            put(f"pool/{name}/{kind}_y", yn)
+            put(f"pool/{name}/{kind}_go", go)
+            put(f"pool/{name}/{kind}_gx", gx.to_numpy())
+            if kind == "max":
+                put(f"pool/{name}/max_idx", np.asarray(ctx.saved_meta["argmax_idx"], dtype=np.int64))
+    # tie-heavy input: first index must win (tests/infrastructure/pool2d/test_pool2d_tie_breaking.py)
+    x = (np.round(rng.uniform(-1, 1, (1, 2, 6, 6)) * 2) / 2).astype(np.float32)
+    put("pool/ties/x", x)
+    xt = tensor(x, True)
+    ctx = Context(parents=(xt,), backward_fn=lambda g: None)
+    y = MaxPool2dFn.forward(ctx, xt, kernel_size=2, stride=2, padding=0)
+    go = np.ones(y.shape, np.float32)
+    (gx,) = MaxPool2dFn.backward(ctx, tensor(go))
+    put("pool/ties/max_y", y.to_numpy())
+    put("pool/ties/max_idx", np.asarray(ctx.saved_meta["argmax_idx"], dtype=np.int64))
+    put("pool/ties/max_gx", gx.to_numpy())
+    # global average pool
+    x = rng.standard_normal((3, 5, 7, 7)).astype(np.float32)
+    xt = tensor(x, True)
+    ctx = Context(parents=(xt,), backward_fn=lambda g: None)
+    y = GlobalAvgPool2dFn.forward(ctx, xt)
+    go = rng.standard_normal(y.shape).astype(np.float32)
+    (gx,) = GlobalAvgPool2dFn.backward(ctx, tensor(go))
+    put("gap/x", x)
+    put("gap/y", y.to_numpy())
+    put("gap/go", go)
+    put("gap/gx", gx.to_numpy())
+
+
+# ---------------------------------------------------------------------------
+# pooling through the reference's C++ kernels (padded-plane C ABI)
+# ---------------------------------------------------------------------------
+def native_pool_cases() -> None:
+    libs = oracle_build.build_reference(REF_ROOT)
+    lib = ctypes.CDLL(str(libs["native"]))
+    rng = np.random.default_rng(2)
+    P = lambda a: ctypes.c_void_p(a.ctypes.data)  # noqa: E731
+    for tag, dt in (("f32", np.float32), ("f64", np.float64)):
+        N, C, H, W, k, s, p = 2, 3, 9, 10, 3, 2, 1
+        x = rng.uniform(-1, 1, (N, C, H, W)).astype(dt)
+        Hp, Wp = H + 2 * p, W + 2 * p
+        Ho, Wo = (Hp - k) // s + 1, (Wp - k) // s + 1
+        for kind, padv in (("max", -np.inf), ("avg", 0.0)):
+            xp = np.pad(x, ((0, 0), (0, 0), (p, p), (p, p)), constant_values=dt(padv))
+            xp = np.ascontiguousarray(xp)
+            y = np.zeros((N, C, Ho, Wo), dt)
+            go = rng.standard_normal((N, C, Ho, Wo)).astype(dt)
+            gxp = np.zeros((N, C, Hp, Wp), dt)
+            if kind == "max":
+                idx = np.zeros((N, C, Ho, Wo), np.int64)
+                getattr(lib, f"keydnn_maxpool2d_forward_{tag}")(P(xp), P(y), P(idx), N, C, Hp, Wp, Ho, Wo, k, k, s, s)
+                getattr(lib, f"keydnn_maxpool2d_backward_{tag}")(P(go), P(idx), P(gxp), N, C, Ho, Wo, Hp, Wp)
+                put(f"native/{tag}/max_idx", idx)
+            else:
+                getattr(lib, f"keydnn_avgpool2d_forward_{tag}")(P(xp), P(y), N, C, Hp, Wp, Ho, Wo, k, k, s, s)
+                getattr(lib, f"keydnn_avgpool2d_backward_{tag}")(P(go), P(gxp), N, C, Ho, Wo, Hp, Wp, k, k, s, s)
+            put(f"native/{tag}/{kind}_y", y)
+            put(f"native/{tag}/{kind}_go", go)
+            put(f"native/{tag}/{kind}_gx", gxp[:, :, p:p + H, p:p + W])
+        put(f"native/{tag}/x", x)
+    put("native/geom", np.array([2, 3, 9, 10, 3, 2, 1], np.int64))
+
+
+# ---------------------------------------------------------------------------
+# Tensor ops with autograd on the reference CPU path
+# ---------------------------------------------------------------------------
+def tensor_cases() -> None:
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((6, 10)).astype(np.float32)
+    b = rng.uniform(0.5, 2.0, (6, 10)).astype(np.float32)
+    g = rng.standard_normal((6, 10)).astype(np.float32)
+    put("ew/a", a)
+    put("ew/b", b)
+    put("ew/g", g)
+    ops = {"add": lambda x, y: x + y, "sub": lambda x, y: x - y, "mul": lambda x, y: x * y, "div": lambda x, y: x / y}
+    for name, fn in ops.items():
+        ta, tb = tensor(a, True), tensor(b, True)
+        y = fn(ta, tb)
+        y.backward(tensor(g))
+        put(f"ew/{name}_y", y.to_numpy())
+        put(f"ew/{name}_ga", ta.grad.to_numpy())
+        put(f"ew/{name}_gb", tb.grad.to_numpy())
+    ta = tensor(a, True)
+    y = -ta
+    y.backward(tensor(g))
+    put("ew/neg_y", y.to_numpy())
+    put("ew/neg_ga", ta.grad.to_numpy())
+    cmps = {"gt": lambda x, y: x > y, "ge": lambda x, y: x >= y, "lt": lambda x, y: x < y, "le": lambda x, y: x <= y}
+    a2 = np.round(a * 2) / 2
+    b2 = np.round(b * 2) / 2
+    put("ew/a2", a2.astype(np.float32))
+    put("ew/b2", b2.astype(np.float32))
+    for name, fn in cmps.items():
+        put(f"ew/{name}_y", fn(tensor(a2.astype(np.float32)), tensor(b2.astype(np.float32))).to_numpy())
+    put("ew/gt_scalar_y", (tensor(a) > 0.0).to_numpy())
+    put("ew/add_scalar_y", (tensor(a) + 1.5).to_numpy())
+    put("ew/mul_scalar_y", (tensor(a) * 0.3).to_numpy())
+    put("ew/div_scalar_y", (tensor(a) / 0.7).to_numpy())
+    put("ew/sub_scalar_y", (tensor(a) - 0.25).to_numpy())
+
+    # reductions
+    x = rng.standard_normal((7, 12)).astype(np.float32)
+    put("red/x", x)
+    tx = tensor(x, True)
+    y = tx.sum()
+    y.backward()
+    put("red/sum_all_y", y.to_numpy())
+    put("red/sum_all_gx", tx.grad.to_numpy())
+    tx = tensor(x, True)
+    y = tx.mean()
+    y.backward()
+    put("red/mean_all_y", y.to_numpy())
+    put("red/mean_all_gx", tx.grad.to_numpy())
+    for axis in (0, 1):
+        tx = tensor(x, True)
+        y = tx.sum(axis=axis)
+        go = rng.standard_normal(y.shape).astype(np.float32)
+        y.backward(tensor(go))
+        put(f"red/sum_axis{axis}_y", y.to_numpy())
+        put(f"red/sum_axis{axis}_go", go)
+        put(f"red/sum_axis{axis}_gx", tx.grad.to_numpy())
+        tx = tensor(x, True)
+        y = tx.max(axis=axis)
+        go = rng.standard_normal(y.shape).astype(np.float32)
+        y.backward(tensor(go))
+        put(f"red/max_axis{axis}_y", y.to_numpy())
+        put(f"red/max_axis{axis}_go", go)
+        put(f"red/max_axis{axis}_gx", tx.grad.to_numpy())
+
+    # SGD with coupled weight decay, two steps (optimizers/_sgd.py:119-140)
+    p0 = rng.standard_normal(37).astype(np.float32)
+    g1 = (rng.standard_normal(37) * 1e-2).astype(np.float32)
+    g2 = (rng.standard_normal(37) * 1e-2).astype(np.float32)
+    par = Parameter(shape=p0.shape, device=CPU, requires_grad=True)
+    par.copy_from_numpy(p0)
+    opt = SGD([par], lr=0.01, weight_decay=1e-4)
+    steps = []
+    for gi in (g1, g2):
+        par.zero_grad()
+        par._set_grad(tensor(gi)) if hasattr(par, "_set_grad") else setattr(par, "_grad", tensor(gi))
+        opt.step()
+        steps.append(par.to_numpy().copy())
+    put("sgd/p0", p0)
+    put("sgd/g1", g1)
+    put("sgd/g2", g2)
+    put("sgd/p1", steps[0])
+    put("sgd/p2", steps[1])
+
+
+def main() -> None:
+    pool_cases()
+    native_pool_cases()
+    tensor_cases()
+    out = REPO / "tests" / "golden" / "ref_cpu_golden.npz"
+    np.savez_compressed(out, **OUT)
+    print(f"wrote {out} ({out.stat().st_size} bytes, {len(OUT)} arrays)")
+
+
+if __name__ == "__main__":
+    main()
