@@ -69,7 +69,7 @@ def parse_header(path: Path = HEADER_PATH) -> Dict[str, Tuple[object, List[objec
 class Native:
     """Handle to the loaded library; ``native.call("keydnn_cuda_add_f32", a, b, y, n)``."""
 
-    def __init__(self, path: Path):
+    def __init__(self, path: Path, strict: bool = True):
         self.path = Path(path)
         if not self.path.exists():
             raise NativeLibraryError(
@@ -89,7 +89,8 @@ class Native:
             f.restype = restype
             f.argtypes = argtypes
             self._fn[name] = f
-        if missing:
+        self.missing = missing
+        if missing and strict:
             raise NativeLibraryError(f"{self.path} lacks {len(missing)} declared symbols: {missing[:8]}")
 
     def raw(self, name: str) -> Callable:
@@ -97,6 +98,8 @@ class Native:
         return self._fn[name]
 
     def error_string(self, code: int) -> str:
+        if "keydnn_cuda_error_string" not in self._fn:
+            return "status code"
         s = self._fn["keydnn_cuda_error_string"](int(code))
         return s.decode() if s else "?"
 
