@@ -1,0 +1,446 @@
+"""Benchmark of the reduction hot path (BASELINE.json configs[1]) on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--kernels all|none]
+
+A step is one pass of sum / mean / max over axis 0, axis 1 and all axes, each followed by its
+backward with an upstream gradient of ones, on an fp32 (8192, 8192) and an fp64 (4096, 4096)
+matrix per GPU (rows sharded across ranks; partials of axis-0 and all-axes reductions cross
+NVLink through NCCL).  `value` is algorithmic bytes moved per second by all ranks, inputs
+resident in HBM; `e2e` is the same through the Tensor API with pinned host inputs copied in and
+results copied out every step.  Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+REPO = Path(__file__).resolve().parent
+if str(REPO) not in sys.path:
+    sys.path.insert(0, str(REPO))
+
+ROWS32, COLS32 = 8192, 8192
+ROWS64, COLS64 = 4096, 4096
+OPS = [(op, ax) for op in ("sum", "mean", "max") for ax in (0, 1, None)]
+METRIC = "fwd+bwd HBM GB/s (sum/mean/max reductions over axis 0, axis 1, all axes; fp32 8192^2 + fp64 4096^2)"
+
+
+def _env_int(name: str, default: int) -> int:
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# clocks sampled during the timed region
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self) -> None:
+        assert self.proc and self.proc.stdout
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# device-side timing with the library's own events (its launches are on its own stream)
+# ---------------------------------------------------------------------------
+class Timer:
+    def __init__(self, lib) -> None:
+        self.lib = lib
+        a, b = ctypes.c_uint64(0), ctypes.c_uint64(0)
+        lib.call("keydnn_cuda_event_create", ctypes.byref(a))
+        lib.call("keydnn_cuda_event_create", ctypes.byref(b))
+        self.a, self.b = a.value, b.value
+
+    def start(self) -> None:
+        self.lib.call("keydnn_cuda_event_record", self.a)
+
+    def stop_ms(self) -> float:
+        self.lib.call("keydnn_cuda_event_record", self.b)
+        self.lib.call("keydnn_cuda_event_synchronize", self.b)
+        ms = ctypes.c_float(0)
+        self.lib.call("keydnn_cuda_event_elapsed_ms", self.a, self.b, ctypes.byref(ms))
+        return float(ms.value)
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def algorithmic_bytes_per_step() -> float:
+    """Forward reads the matrix, backward writes the gradient (outputs <= 96 KB are ignored)."""
+    per_matrix = ROWS32 * COLS32 * 4 + ROWS64 * COLS64 * 8
+    return float(len(OPS) * 2 * per_matrix)
+
+
+def kernel_table(lib, reducers, timer, reps: int, peak: float) -> list[dict]:
+    """Average device time of each forward and backward kernel, `reps` launches back to back."""
+    rows = []
+    for red, tag in reducers:
+        nbytes = red.x.nbytes
+        for op, ax in OPS:
+            for phase in ("fwd", "bwd"):
+                red.forward(op, ax)
+                fn = (lambda: red.forward(op, ax)) if phase == "fwd" else (lambda: red.backward(op, ax))
+                for _ in range(3):
+                    fn()
+                timer.start()
+                for _ in range(reps):
+                    fn()
+                ms = timer.stop_ms() / reps
+                gbs = nbytes / ms / 1e6
+                rows.append({"kernel": f"{op}_{'all' if ax is None else 'axis%d' % ax}_{phase}_{tag}", "us": round(ms * 1e3, 2),
+                             "gbs": round(gbs, 1), "frac": round(gbs / peak, 4), "bytes": nbytes})
+    return rows
+
+
+def suite_table(lib, timer, peak: float, reps: int = 10, warm: int = 3) -> list[dict]:
+    """Per-kernel device time for the other BASELINE.json configurations (pool, elementwise,
+    optimizer step), each launched `reps` times back to back on inputs larger than L2."""
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import pooling
+
+    T = kd.Tensor
+    rng = np.random.default_rng(7)
+    rows: list[dict] = []
+
+    def timed(name: str, nbytes: float, fn) -> None:
+        for _ in range(warm):
+            fn()
+        timer.start()
+        for _ in range(reps):
+            fn()
+        ms = timer.stop_ms() / reps
+        gbs = nbytes / ms / 1e6
+        rows.append({"kernel": name, "us": round(ms * 1e3, 2), "gbs": round(gbs, 1), "frac": round(gbs / peak, 4),
+                     "bytes": int(nbytes)})
+
+    def rand(shape, lo=None):
+        a = rng.standard_normal(shape, dtype=np.float32) if lo is None else rng.uniform(lo[0], lo[1], shape).astype(np.float32)
+        return T.from_numpy(a)
+
+    # configs[0]: MaxPool2d k2 s2 p0 on (32,64,112,112)
+    x = rand((32, 64, 112, 112), (-1, 1))
+    go = rand((32, 64, 56, 56))
+    y, idx = pooling.maxpool2d_forward(x, kernel_size=2, stride=2, padding=0)
+    gx = T.empty(x.shape)
+    nb = x.nbytes + y.nbytes + y.numel * 8
+    timed("maxpool2d_fwd_c1_f32", nb, lambda: lib.call("keydnn_cuda_maxpool2d_forward_ex_f32", x.data, y.data, idx.dev_ptr,
+                                                      32, 64, 112, 112, 56, 56, 2, 2, 2, 2, 0, 0))
+    timed("maxpool2d_bwd_c1_f32", nb, lambda: lib.call("keydnn_cuda_maxpool2d_backward_ex_f32", go.data, idx.dev_ptr, gx.data,
+                                                      32, 64, 112, 112, 56, 56, 2, 2, 2, 2, 0, 0))
+    del x, go, y, idx, gx
+    # configs[3]: AvgPool2d k3 s2 p1 on (256,256,56,56); GlobalAvgPool on (256,2048,7,7)
+    x = rand((256, 256, 56, 56), (-1, 1))
+    y = T.empty((256, 256, 28, 28))
+    gx = T.empty(x.shape)
+    nb = x.nbytes + y.nbytes
+    timed("avgpool2d_fwd_c4_f32", nb, lambda: lib.call("keydnn_cuda_avgpool2d_forward_ex_f32", x.data, y.data, 256, 256, 56, 56,
+                                                      28, 28, 3, 3, 2, 2, 1, 1))
+    timed("avgpool2d_bwd_c4_f32", nb, lambda: lib.call("keydnn_cuda_avgpool2d_backward_ex_f32", y.data, gx.data, 256, 256, 56,
+                                                      56, 28, 28, 3, 3, 2, 2, 1, 1))
+    del x, y, gx
+    x = rand((256, 2048, 7, 7))
+    y = T.empty((256, 2048, 1, 1))
+    gx = T.empty(x.shape)
+    nb = x.nbytes + y.nbytes
+    timed("global_avgpool_fwd_c4_f32", nb, lambda: lib.call("keydnn_cuda_global_avgpool2d_forward_f32", x.data, y.data, 256, 2048, 7, 7))
+    timed("global_avgpool_bwd_c4_f32", nb, lambda: lib.call("keydnn_cuda_global_avgpool2d_backward_f32", y.data, gx.data, 256, 2048, 7, 7))
+    del x, y, gx
+    # configs[2]: elementwise on 2^28 fp32 elements, SGD-momentum on 25,165,824
+    n = 1 << 28
+    a = T.from_numpy(rng.standard_normal(n, dtype=np.float32))
+    b = T.from_numpy(rng.uniform(0.5, 2.0, n).astype(np.float32))
+    y = T.empty((n,))
+    for op in ("add", "sub", "mul", "div", "gt"):
+        timed(f"{op}_c3_f32", 3.0 * a.nbytes, lambda op=op: lib.call(f"keydnn_cuda_{op}_f32", a.data, b.data, y.data, n))
+    timed("neg_c3_f32", 2.0 * a.nbytes, lambda: lib.call("keydnn_cuda_neg_f32", a.data, y.data, n))
+    y2 = T.empty((n,))
+    # mul backward = two products (g*b, g*a): 6 tensor passes; the minimum is 5
+    timed("mul_backward_c3_f32", 5.0 * a.nbytes, lambda: (lib.call("keydnn_cuda_mul_f32", y.data, b.data, y2.data, n),
+                                                         lib.call("keydnn_cuda_mul_f32", y.data, a.data, y2.data, n)))
+    del a, b, y, y2
+    n = 25_165_824
+    p = T.from_numpy(rng.standard_normal(n, dtype=np.float32))
+    g = T.from_numpy((rng.standard_normal(n, dtype=np.float32) * np.float32(1e-2)))
+    v = T.zeros((n,))
+    timed("sgd_momentum_step_c3_f32", 5.0 * p.nbytes, lambda: lib.call(
+        "keydnn_cuda_sgd_momentum_step_f32", p.data, g.data, v.data, n, ctypes.c_float(0.01), ctypes.c_float(0.9),
+        ctypes.c_float(1e-4), ctypes.c_float(1.0)))
+    return rows
+
+
+def run_ours(args) -> None:
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import distributed
+    from keydnn_v2_b200.sharded import ShardedReductions
+
+    rank, world, local = _env_int("RANK", 0), _env_int("WORLD_SIZE", 1), _env_int("LOCAL_RANK", 0)
+    lib = kd.load()
+    lib.call("keydnn_cuda_set_device", local)
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
+        group = distributed.init_from_torch(device=local)
+    else:
+        group = distributed.single(lib)
+
+    rng = np.random.default_rng(1 + rank)
+    T = kd.Tensor
+    h32 = rng.standard_normal((ROWS32, COLS32), dtype=np.float32)
+    h64 = rng.standard_normal((ROWS64, COLS64))
+    r32 = ShardedReductions(T.from_numpy(h32), group)
+    r64 = ShardedReductions(T.from_numpy(h64), group)
+    reducers = [(r32, "f32"), (r64, "f64")]
+    timer = Timer(lib)
+    launches = [0]
+
+    def step() -> None:
+        for red, _ in reducers:
+            for op, ax in OPS:
+                red.forward(op, ax)
+                red.backward(op, ax)
+        launches[0] += 2 * len(OPS) * len(reducers)
+
+    def barrier() -> None:
+        lib.call("keydnn_cuda_synchronize")
+        if dist is not None:
+            dist.barrier()
+
+    if args.once:
+        # one launch of every kernel, for a profiler capture (`ncu -k ... python bench.py --once`)
+        step()
+        lib.call("keydnn_cuda_synchronize")
+        del r32, r64, reducers
+        lib.call("keydnn_cuda_empty_cache")
+        suite_table(lib, timer, 1.0, reps=1, warm=0)
+        lib.call("keydnn_cuda_synchronize")
+        print("once: every kernel launched one time", flush=True)
+        return
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches[0] = 0
+    timer.start()
+    for _ in range(args.steps):
+        step()
+    ms = timer.stop_ms()
+    barrier()
+    n_launch = launches[0]
+
+    # ---- end to end: pinned host inputs in, results out, through the public Tensor API ----
+    def pinned_like(a: np.ndarray) -> np.ndarray:
+        p = ctypes.c_void_p(0)
+        lib.call("keydnn_cuda_host_alloc", ctypes.byref(p), a.nbytes)
+        buf = (ctypes.c_char * a.nbytes).from_address(p.value)
+        out = np.frombuffer(buf, dtype=a.dtype).reshape(a.shape)
+        out[...] = a
+        return out
+
+    p32, p64 = pinned_like(h32), pinned_like(h64)
+    del h32, h64
+    host_out = {id(r32): np.empty(max(ROWS32, COLS32), np.float32), id(r64): np.empty(max(ROWS64, COLS64), np.float64)}
+    d2h = [0]
+
+    def e2e_step() -> None:
+        d2h[0] = 0
+        for (red, _), src in zip(reducers, (p32, p64)):
+            red.x.copy_from_numpy(src)
+            for op, ax in OPS:
+                ptr, n = red.forward(op, ax)
+                red.backward(op, ax)
+                nb = n * red.dt.itemsize
+                lib.call("keydnn_cuda_memcpy_d2h", host_out[id(red)].ctypes.data, ptr, nb)
+                d2h[0] += nb
+            # the step's gradient result: first row of the last gradient
+            lib.call("keydnn_cuda_memcpy_d2h", host_out[id(red)].ctypes.data, red.gx.data, red.cols * red.dt.itemsize)
+            d2h[0] += red.cols * red.dt.itemsize
+
+    e2e_step()
+    barrier()
+    e2e_steps = max(2, min(args.steps, 5))
+    t0 = time.perf_counter()
+    timer.start()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2e_ms = timer.stop_ms()
+    e2e_wall = (time.perf_counter() - t0) * 1e3
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+
+    if dist is not None:
+        import torch
+
+        t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peak, peak_src = measured_peak_gbs()
+        bytes_step = algorithmic_bytes_per_step()
+        value = bytes_step * world * args.steps / ms / 1e6
+        e2e_val = bytes_step * world * e2e_steps / max(e2e_ms, e2e_wall) / 1e6
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32+f64", "data": "synthetic",
+            "config": {"workload": "configs[1]: sum/mean/max over axis 0, axis 1, all axes, fwd + bwd (grad of ones), "
+                                   "fp32 (8192,8192) N(0,1) + fp64 (4096,4096) N(0,1) per GPU, rows sharded across GPUs",
+                       "l2": "inputs larger than L2 (268 MB and 134 MB vs 126 MB); no flush",
+                       "collectives": "none" if world == 1 else "NCCL all-reduce / all-gather of axis-0 and all-axes partials"},
+            "e2e": {"value": round(e2e_val, 1), "unit": "GB/s", "h2d_bytes_per_step": int(p32.nbytes + p64.nbytes),
+                    "d2h_bytes_per_step": int(d2h[0]), "steps": e2e_steps},
+            "gpu_launches": n_launch, "clocks": clocks,
+        }
+        if args.kernels != "none":
+            table = kernel_table(lib, reducers, timer, 20, peak)
+            top = max(table, key=lambda r: r["us"])
+            line["roofline"] = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["gbs"], "peak": peak,
+                                "unit": "GB/s", "frac": top["frac"], "traffic": None, "peak_source": peak_src,
+                                "frac_of_nominal_8000": round(top["gbs"] / 8000.0, 4)}
+            line["kernels"] = table
+            if args.kernels == "suite":
+                del r32, r64
+                line["suite"] = suite_table(lib, timer, peak)
+            line["whole_step_frac"] = round(value / world / peak, 4)
+        line["cpu_baseline"] = cpu_baseline_sample() if world == 1 or rank == 0 else None
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        group.destroy()
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------
+# CPU baseline and the reference arm
+# ---------------------------------------------------------------------------
+def cpu_baseline_sample(rows32: int = 1024, rows64: int = 512) -> dict:
+    """The reference's CPU path (single-threaded NumPy expressions) on a row slice of the workload."""
+    from oracle import cpu_baseline
+
+    rng = np.random.default_rng(1)
+    x32 = rng.standard_normal((rows32, COLS32), dtype=np.float32)
+    x64 = rng.standard_normal((rows64, COLS64))
+    cpu_baseline.time_reduce_workload(x32[:64], x64[:64])
+    r = cpu_baseline.time_reduce_workload(x32, x64)
+    return {"value": round(r["bytes"] / r["seconds"] / 1e9, 3), "unit": "GB/s", "cores": 1, "kind": "port",
+            "sample": f"rows [0,{rows32}) of the fp32 matrix and [0,{rows64}) of the fp64 matrix, all 9 reductions fwd+bwd, "
+                      f"{r['seconds']:.2f} s; NumPy expressions of the reference's CPU Tensor methods",
+            "host_cores": os.cpu_count()}
+
+
+def run_reference(args) -> None:
+    rank, world = _env_int("RANK", 0), _env_int("WORLD_SIZE", 1)
+    if rank != 0:
+        return
+    from oracle import cpu_baseline
+
+    rng = np.random.default_rng(1)
+    rows32, rows64 = 1024, 512
+    x32 = rng.standard_normal((rows32, COLS32), dtype=np.float32)
+    x64 = rng.standard_normal((rows64, COLS64))
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_baseline.time_reduce_workload(x32, x64)
+    t0 = time.perf_counter()
+    nbytes = 0.0
+    for _ in range(args.steps):
+        nbytes += cpu_baseline.time_reduce_workload(x32, x64)["bytes"]
+    dt = time.perf_counter() - t0
+    value = nbytes / dt / 1e9
+    sample = (f"each step = rows [0,{rows32}) of the fp32 matrix and [0,{rows64}) of the fp64 matrix, all 9 reductions "
+              "fwd+bwd, on the host cores (NumPy is single-threaded for these expressions)")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32+f64", "data": "synthetic",
+        "config": {"workload": "configs[1] reductions fwd+bwd, CPU path of the reference (NumPy), bounded row sample"},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample,
+                         "host_cores": os.cpu_count()},
+        "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kernels", default="all", choices=["all", "none", "suite"])
+    ap.add_argument("--once", action="store_true", help="launch every kernel once and exit (profiler captures)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -264,6 +264,28 @@ int keydnn_cuda_bias_add_inplace_f64(double* y, const double* b, int64_t batch, 
 int keydnn_cuda_transpose2d_f32(const float* x, float* y, int rows, int cols);
 int keydnn_cuda_transpose2d_f64(const double* x, double* y, int rows, int cols);
 
+/* ------------------------------------------------------------------------- */
+/* Multi-GPU (additive; the reference has no distributed code).  One process   */
+/* per GPU; NCCL is opened with dlopen at first use; collectives run on the    */
+/* library stream.  Status: -10 not initialised, -11 NCCL not loadable,        */
+/* 200000 + ncclResult_t on NCCL errors.                                       */
+/* ------------------------------------------------------------------------- */
+int keydnn_nccl_unique_id(void* out128);                       /* 128-byte id, made on rank 0 */
+int keydnn_nccl_init(const void* id128, int world, int rank);
+int keydnn_nccl_destroy(void);
+int keydnn_nccl_world(int* world, int* rank);
+int keydnn_nccl_allreduce_sum_f32(float* buf, int64_t count);  /* in place */
+int keydnn_nccl_allreduce_sum_f64(double* buf, int64_t count);
+int keydnn_nccl_allgather(const void* send, void* recv, int64_t nbytes);
+int keydnn_nccl_broadcast(void* buf, int64_t nbytes, int root);
+/* Winner per column among `world` per-rank (value, local position) maxima gathered rank-major:
+ * greater value, else lower rank; global position = rank*span + local; out_local is the position
+ * inside this rank's shard or -1 when another rank owns the maximum. */
+int keydnn_cuda_argmax_select_f32(const float* vals, const int64_t* idx, int world, int rank, int64_t span, int64_t n,
+                                  float* out_val, int64_t* out_global, int64_t* out_local);
+int keydnn_cuda_argmax_select_f64(const double* vals, const int64_t* idx, int world, int rank, int64_t span, int64_t n,
+                                  double* out_val, int64_t* out_global, int64_t* out_local);
+
 #ifdef __cplusplus
 }
 #endif

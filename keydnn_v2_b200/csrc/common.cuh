@@ -9,6 +9,7 @@
 #include <cstddef>
 #include <cstdint>
 #include <limits>
+#include <unordered_map>
 
 #define KD_API extern "C" __attribute__((visibility("default")))
 
@@ -30,6 +31,10 @@ inline int status(cudaError_t e) { return e == cudaSuccess ? 0 : static_cast<int
 inline int launch_status() { return status(cudaGetLastError()); }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+// A 4-element packet is one access: 16 bytes for float, 32 bytes for double / int64.
+template <typename T> inline bool aligned_pack(const void* p) {
+    return (reinterpret_cast<uintptr_t>(p) & (sizeof(T) * 4 - 1)) == 0;
+}
 
 // Grid for a grid-stride kernel: enough CTAs to fill every SM `per_sm` times,
 // never more than the work available.
@@ -39,8 +44,37 @@ inline unsigned grid_for(int64_t work_items, int per_sm) {
     return static_cast<unsigned>(g < 1 ? 1 : g);
 }
 
+// CTAs of `kernel` that one SM holds at once (cached per kernel).
+template <typename K> inline int occupancy(K kernel, int threads, size_t smem = 0) {
+    static std::unordered_map<const void*, int> cache;
+    const void* key = reinterpret_cast<const void*>(kernel);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem) != cudaSuccess || n < 1) n = 1;
+    cache.emplace(key, n);
+    return n;
+}
+
+// Grid for a grid-stride kernel: one resident wave (every SM holds as many CTAs of
+// this kernel as fit), or fewer when there is less work.  All CTAs then run
+// concurrently from start to end and take the same number of trips.
+template <typename K> inline unsigned grid_fit(K kernel, int threads, int64_t work_ctas, size_t smem = 0) {
+    const int64_t cap = static_cast<int64_t>(sm_count()) * occupancy(kernel, threads, smem);
+    const int64_t g = work_ctas < cap ? work_ctas : cap;
+    return static_cast<unsigned>(g < 1 ? 1 : g);
+}
+
+#define KD_LAUNCH(KERNEL, WORK, THREADS, SMEM, ...)                                                           \
+    do {                                                                                                      \
+        auto kd_fn_ = (KERNEL);                                                                               \
+        kd_fn_<<<kd::grid_fit(kd_fn_, (THREADS), (WORK), (SMEM)), (THREADS), (SMEM), kd::stream()>>>(__VA_ARGS__); \
+    } while (0)
+
 // ---------------------------------------------------------------------------
-// 4-element packets: one 16-byte access for float, two for double.
+// 4-element packets: one 16-byte access for float, one 32-byte access (256-bit
+// ld/st, sm_100) for double and int64, so that a warp always touches whole,
+// contiguous sectors with a single instruction.
 // ---------------------------------------------------------------------------
 template <typename T> struct Pack4 { T v[4]; };
 
@@ -50,14 +84,16 @@ template <> __device__ __forceinline__ Pack4<float> load4<float>(const float* p)
     Pack4<float> r; r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w; return r;
 }
 template <> __device__ __forceinline__ Pack4<double> load4<double>(const double* p) {
-    double2 a = __ldg(reinterpret_cast<const double2*>(p));
-    double2 b = __ldg(reinterpret_cast<const double2*>(p) + 1);
-    Pack4<double> r; r.v[0] = a.x; r.v[1] = a.y; r.v[2] = b.x; r.v[3] = b.y; return r;
+    Pack4<double> r;
+    asm volatile("ld.global.nc.v4.f64 {%0,%1,%2,%3}, [%4];"
+                 : "=d"(r.v[0]), "=d"(r.v[1]), "=d"(r.v[2]), "=d"(r.v[3]) : "l"(p));
+    return r;
 }
 template <> __device__ __forceinline__ Pack4<long long> load4<long long>(const long long* p) {
-    longlong2 a = __ldg(reinterpret_cast<const longlong2*>(p));
-    longlong2 b = __ldg(reinterpret_cast<const longlong2*>(p) + 1);
-    Pack4<long long> r; r.v[0] = a.x; r.v[1] = a.y; r.v[2] = b.x; r.v[3] = b.y; return r;
+    Pack4<long long> r;
+    asm volatile("ld.global.nc.v4.s64 {%0,%1,%2,%3}, [%4];"
+                 : "=l"(r.v[0]), "=l"(r.v[1]), "=l"(r.v[2]), "=l"(r.v[3]) : "l"(p));
+    return r;
 }
 
 // Streaming loads: data that is touched once (evict-first in L1/L2).
@@ -67,14 +103,16 @@ template <> __device__ __forceinline__ Pack4<float> load4_stream<float>(const fl
     Pack4<float> r; r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w; return r;
 }
 template <> __device__ __forceinline__ Pack4<double> load4_stream<double>(const double* p) {
-    double2 a = __ldcs(reinterpret_cast<const double2*>(p));
-    double2 b = __ldcs(reinterpret_cast<const double2*>(p) + 1);
-    Pack4<double> r; r.v[0] = a.x; r.v[1] = a.y; r.v[2] = b.x; r.v[3] = b.y; return r;
+    Pack4<double> r;
+    asm volatile("ld.global.cs.v4.f64 {%0,%1,%2,%3}, [%4];"
+                 : "=d"(r.v[0]), "=d"(r.v[1]), "=d"(r.v[2]), "=d"(r.v[3]) : "l"(p));
+    return r;
 }
 template <> __device__ __forceinline__ Pack4<long long> load4_stream<long long>(const long long* p) {
-    longlong2 a = __ldcs(reinterpret_cast<const longlong2*>(p));
-    longlong2 b = __ldcs(reinterpret_cast<const longlong2*>(p) + 1);
-    Pack4<long long> r; r.v[0] = a.x; r.v[1] = a.y; r.v[2] = b.x; r.v[3] = b.y; return r;
+    Pack4<long long> r;
+    asm volatile("ld.global.cs.v4.s64 {%0,%1,%2,%3}, [%4];"
+                 : "=l"(r.v[0]), "=l"(r.v[1]), "=l"(r.v[2]), "=l"(r.v[3]) : "l"(p));
+    return r;
 }
 
 template <typename T> __device__ __forceinline__ void store4(T* p, const Pack4<T>& r);
@@ -82,12 +120,65 @@ template <> __device__ __forceinline__ void store4<float>(float* p, const Pack4<
     __stcs(reinterpret_cast<float4*>(p), make_float4(r.v[0], r.v[1], r.v[2], r.v[3]));
 }
 template <> __device__ __forceinline__ void store4<double>(double* p, const Pack4<double>& r) {
-    __stcs(reinterpret_cast<double2*>(p), make_double2(r.v[0], r.v[1]));
-    __stcs(reinterpret_cast<double2*>(p) + 1, make_double2(r.v[2], r.v[3]));
+    asm volatile("st.global.cs.v4.f64 [%0], {%1,%2,%3,%4};"
+                 :: "l"(p), "d"(r.v[0]), "d"(r.v[1]), "d"(r.v[2]), "d"(r.v[3]) : "memory");
 }
 template <> __device__ __forceinline__ void store4<long long>(long long* p, const Pack4<long long>& r) {
-    __stcs(reinterpret_cast<longlong2*>(p), make_longlong2(r.v[0], r.v[1]));
-    __stcs(reinterpret_cast<longlong2*>(p) + 1, make_longlong2(r.v[2], r.v[3]));
+    asm volatile("st.global.cs.v4.s64 [%0], {%1,%2,%3,%4};"
+                 :: "l"(p), "l"(r.v[0]), "l"(r.v[1]), "l"(r.v[2]), "l"(r.v[3]) : "memory");
+}
+
+// 8 contiguous elements of one row owned by one thread.  For float this is a single
+// 256-bit access, so a warp instruction covers 1 KiB of whole sectors instead of
+// every other half sector; for double it is two 256-bit accesses.
+template <typename T> struct Row8 { T v[8]; };
+template <typename T> inline bool aligned_row8(const void* p) {
+    return (reinterpret_cast<uintptr_t>(p) & 31u) == 0;
+}
+
+template <typename T> __device__ __forceinline__ Row8<T> load8(const T* p);          // read-only, cached
+template <typename T> __device__ __forceinline__ Row8<T> load8_stream(const T* p);   // touched once
+template <typename T> __device__ __forceinline__ void store8(T* p, const Row8<T>& r);
+
+template <> __device__ __forceinline__ Row8<float> load8<float>(const float* p) {
+    Row8<float> r;
+    asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]), "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]),
+                   "=f"(r.v[7]) : "l"(p));
+    return r;
+}
+template <> __device__ __forceinline__ Row8<float> load8_stream<float>(const float* p) {
+    Row8<float> r;
+    asm volatile("ld.global.cs.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]), "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]),
+                   "=f"(r.v[7]) : "l"(p));
+    return r;
+}
+template <> __device__ __forceinline__ void store8<float>(float* p, const Row8<float>& r) {
+    asm volatile("st.global.cs.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 :: "l"(p), "f"(r.v[0]), "f"(r.v[1]), "f"(r.v[2]), "f"(r.v[3]), "f"(r.v[4]), "f"(r.v[5]), "f"(r.v[6]),
+                    "f"(r.v[7]) : "memory");
+}
+template <> __device__ __forceinline__ Row8<double> load8<double>(const double* p) {
+    const Pack4<double> a = load4(p), b = load4(p + 4);
+    Row8<double> r;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { r.v[k] = a.v[k]; r.v[4 + k] = b.v[k]; }
+    return r;
+}
+template <> __device__ __forceinline__ Row8<double> load8_stream<double>(const double* p) {
+    const Pack4<double> a = load4_stream(p), b = load4_stream(p + 4);
+    Row8<double> r;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { r.v[k] = a.v[k]; r.v[4 + k] = b.v[k]; }
+    return r;
+}
+template <> __device__ __forceinline__ void store8<double>(double* p, const Row8<double>& r) {
+    Pack4<double> a, b;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { a.v[k] = r.v[k]; b.v[k] = r.v[4 + k]; }
+    store4(p, a);
+    store4(p + 4, b);
 }
 
 template <typename T> __device__ __forceinline__ T neg_inf();

@@ -82,12 +82,11 @@ ew_scalar_kernel(const TI* a, const TI* b, TI alpha, TO* y, int64_t n, Op op) {
 template <typename TI, typename TO, int MODE, typename Op>
 int launch_ew(const TI* a, const TI* b, TI alpha, TO* y, int64_t n, Op op) {
     (void)cudaGetLastError();   // report this launch, not a stale error
-    const bool vec = kd::aligned16(a) && kd::aligned16(y) && (MODE != kBinary || kd::aligned16(b));
+    const bool vec = kd::aligned_pack<TI>(a) && kd::aligned_pack<TO>(y) && (MODE != kBinary || kd::aligned_pack<TI>(b));
     if (vec) {
         constexpr int UNROLL = (MODE == kBinary) ? 4 : 8;
         const int64_t tiles = ((n >> 2) + kThreads * UNROLL - 1) / (kThreads * UNROLL);
-        const unsigned grid = kd::grid_for(tiles, 8);
-        ew_packet_kernel<TI, TO, MODE, UNROLL, Op><<<grid, kThreads, 0, kd::stream()>>>(a, b, alpha, y, n, op);
+        KD_LAUNCH((ew_packet_kernel<TI, TO, MODE, UNROLL, Op>), tiles, kThreads, 0, a, b, alpha, y, n, op);
     } else {
         const unsigned grid = kd::grid_for((n + kThreads - 1) / kThreads, 16);
         ew_scalar_kernel<TI, TO, MODE, Op><<<grid, kThreads, 0, kd::stream()>>>(a, b, alpha, y, n, op);
@@ -122,10 +121,10 @@ int launch_fill(T* y, int64_t n, T value) {
     (void)cudaGetLastError();
     const uintptr_t addr = reinterpret_cast<uintptr_t>(y);
     if (addr % sizeof(T)) return static_cast<int>(cudaErrorMisalignedAddress);
-    int head = static_cast<int>(((16 - (addr & 15)) & 15) / sizeof(T));
+    constexpr uintptr_t kA = sizeof(T) * 4;   // packet alignment
+    int head = static_cast<int>(((kA - (addr & (kA - 1))) & (kA - 1)) / sizeof(T));
     if (head > n) head = static_cast<int>(n);
-    const unsigned grid = kd::grid_for(((n >> 2) + kThreads - 1) / kThreads + 1, 8);
-    fill_kernel<T><<<grid, kThreads, 0, kd::stream()>>>(y, n, value, head);
+    KD_LAUNCH(fill_kernel<T>, ((n >> 2) + kThreads - 1) / kThreads + 1, kThreads, 0, y, n, value, head);
     return kd::launch_status();
 }
 
@@ -217,18 +216,16 @@ int launch_sgd(T* p, const T* g, T* v, int64_t n, T lr, T mu, T wd, T gscale) {
     if (n < 0) return -2;
     if (n == 0) return 0;
     (void)cudaGetLastError();
-    const bool vec = kd::aligned16(p) && kd::aligned16(g) && (!v || kd::aligned16(v));
+    const bool vec = kd::aligned_pack<T>(p) && kd::aligned_pack<T>(g) && (!v || kd::aligned_pack<T>(v));
     const bool use_scale = !(gscale == T(1));
     const bool use_wd = !(wd == T(0));
     const int64_t tiles = vec ? ((n >> 2) + kThreads * 2 - 1) / (kThreads * 2) : (n + kThreads - 1) / kThreads;
-    const unsigned grid = kd::grid_for(tiles < 1 ? 1 : tiles, 8);
-    cudaStream_t s = kd::stream();
     if (v) {
-        if (vec) sgd_kernel<T, true, true><<<grid, kThreads, 0, s>>>(p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
-        else sgd_kernel<T, true, false><<<grid, kThreads, 0, s>>>(p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
+        if (vec) KD_LAUNCH((sgd_kernel<T, true, true>), tiles, kThreads, 0, p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
+        else KD_LAUNCH((sgd_kernel<T, true, false>), tiles, kThreads, 0, p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
     } else {
-        if (vec) sgd_kernel<T, false, true><<<grid, kThreads, 0, s>>>(p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
-        else sgd_kernel<T, false, false><<<grid, kThreads, 0, s>>>(p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
+        if (vec) KD_LAUNCH((sgd_kernel<T, false, true>), tiles, kThreads, 0, p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
+        else KD_LAUNCH((sgd_kernel<T, false, false>), tiles, kThreads, 0, p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
     }
     return kd::launch_status();
 }

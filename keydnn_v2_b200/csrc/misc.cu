@@ -134,7 +134,7 @@ int broadcast_to(const T* x, T* y, const int64_t* in_shape, int in_ndim, const i
             if (gy < 1) gy = 1;
             if (gy > 65535) gy = 65535;
             const dim3 grid(gx, static_cast<unsigned>(gy));
-            const bool vec = kd::aligned16(y) && (B % 4 == 0);
+            const bool vec = kd::aligned_pack<T>(y) && (B % 4 == 0);
             if (vec) broadcast_rows_kernel<T, true><<<grid, kThreads, 0, s>>>(x, y, rows, static_cast<int>(K), B);
             else broadcast_rows_kernel<T, false><<<grid, kThreads, 0, s>>>(x, y, rows, static_cast<int>(K), B);
         }

@@ -83,7 +83,7 @@ maxpool2x2_fwd(const T* __restrict__ x, T* __restrict__ y, long long* __restrict
     const int64_t tile = static_cast<int64_t>(kThreads) * U;
     for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < groups;
          base += static_cast<int64_t>(gridDim.x) * tile) {
-        Pack4<T> t0[U], t1[U], b0[U], b1[U];
+        kd::Row8<T> top8[U], bot8[U];
         int64_t row[U];
         int jg[U], i2[U];
 #pragma unroll
@@ -95,22 +95,16 @@ maxpool2x2_fwd(const T* __restrict__ x, T* __restrict__ y, long long* __restrict
                 const int64_t nc = row[u] / Ho;
                 i2[u] = 2 * static_cast<int>(row[u] - nc * Ho);
                 const T* r0 = x + (nc * H + i2[u]) * W + 8 * jg[u];
-                t0[u] = kd::load4_stream(r0);
-                t1[u] = kd::load4_stream(r0 + 4);
-                b0[u] = kd::load4_stream(r0 + W);
-                b1[u] = kd::load4_stream(r0 + W + 4);
+                top8[u] = kd::load8_stream(r0);
+                bot8[u] = kd::load8_stream(r0 + W);
             }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int64_t gi = base + u * kThreads + threadIdx.x;
             if (gi < groups) {
-                T top[8], bot[8];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    top[k] = t0[u].v[k]; top[4 + k] = t1[u].v[k];
-                    bot[k] = b0[u].v[k]; bot[4 + k] = b1[u].v[k];
-                }
+                const T* top = top8[u].v;
+                const T* bot = bot8[u].v;
                 Pack4<T> out;
                 Pack4<long long> pos;
                 const long long origin = static_cast<long long>(i2[u]) * W + 8 * jg[u];
@@ -165,7 +159,7 @@ maxpool2x2_bwd(const T* __restrict__ go, const long long* __restrict__ idx, T* _
                 const int64_t nc = row / Ho;
                 const int i2 = 2 * static_cast<int>(row - nc * Ho);
                 const long long origin = static_cast<long long>(i2) * W + 8 * jg;
-                Pack4<T> t0, t1, b0, b1;
+                kd::Row8<T> top, bot;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const long long off = pv[u].v[q] - (origin + 2 * q);
@@ -174,14 +168,12 @@ maxpool2x2_bwd(const T* __restrict__ go, const long long* __restrict__ idx, T* _
                     const T b = off == 1 ? g : T(0);
                     const T c = off == W ? g : T(0);
                     const T d = off == W + 1 ? g : T(0);
-                    if (q < 2) { t0.v[2 * q] = a; t0.v[2 * q + 1] = b; b0.v[2 * q] = c; b0.v[2 * q + 1] = d; }
-                    else { t1.v[2 * q - 4] = a; t1.v[2 * q - 3] = b; b1.v[2 * q - 4] = c; b1.v[2 * q - 3] = d; }
+                    top.v[2 * q] = a; top.v[2 * q + 1] = b;
+                    bot.v[2 * q] = c; bot.v[2 * q + 1] = d;
                 }
                 T* r0 = gx + (nc * H + i2) * W + 8 * jg;
-                kd::store4(r0, t0);
-                kd::store4(r0 + 4, t1);
-                kd::store4(r0 + W, b0);
-                kd::store4(r0 + W + 4, b1);
+                kd::store8(r0, top);
+                kd::store8(r0 + W, bot);
             }
         }
     }
@@ -297,11 +289,10 @@ avgpool3x3s2p1_fwd(const T* __restrict__ x, T* __restrict__ y, int H, int W, int
             live[r] = (h >= 0 && h < H);
             if (live[r]) {
                 const T* p = plane + static_cast<int64_t>(h) * W + 8 * jg;
-                const Pack4<T> a = kd::load4(p);
-                const Pack4<T> b = kd::load4(p + 4);
+                const kd::Row8<T> a = kd::load8(p);
                 c[r][0] = jg > 0 ? __ldg(p - 1) : T(0);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) { c[r][1 + k] = a.v[k]; c[r][5 + k] = b.v[k]; }
+                for (int k = 0; k < 8; ++k) c[r][1 + k] = a.v[k];
             }
         }
         Pack4<T> out;
@@ -388,19 +379,18 @@ avgpool3x3s2p1_bwd(const T* __restrict__ go, T* __restrict__ gx, int H, int W, i
         T* r0 = gx + (nc * H + 2 * m) * W + 8 * jg;
         // row 2m: covered by output row m (always live: m < Ho for every row pair)
         {
-            Pack4<T> lo, hi;
+            kd::Row8<T> out;
 #pragma unroll
             for (int cidx = 0; cidx < 8; ++cidx) {
                 T acc = T(0);
                 acc += q[0][cidx >> 1];
                 if ((cidx & 1) && !(last_col && cidx == 7)) acc += q[0][(cidx >> 1) + 1];
-                if (cidx < 4) lo.v[cidx] = acc; else hi.v[cidx - 4] = acc;
+                out.v[cidx] = acc;
             }
-            kd::store4(r0, lo);
-            kd::store4(r0 + 4, hi);
+            kd::store8(r0, out);
         }
         if (2 * m + 1 < H) {
-            Pack4<T> lo, hi;
+            kd::Row8<T> out;
 #pragma unroll
             for (int cidx = 0; cidx < 8; ++cidx) {
                 const bool two = (cidx & 1) && !(last_col && cidx == 7);
@@ -411,10 +401,9 @@ avgpool3x3s2p1_bwd(const T* __restrict__ go, T* __restrict__ gx, int H, int W, i
                     acc += q[1][cidx >> 1];
                     if (two) acc += q[1][(cidx >> 1) + 1];
                 }
-                if (cidx < 4) lo.v[cidx] = acc; else hi.v[cidx - 4] = acc;
+                out.v[cidx] = acc;
             }
-            kd::store4(r0 + W, lo);
-            kd::store4(r0 + W + 4, hi);
+            kd::store8(r0 + W, out);
         }
     }
 }
@@ -442,28 +431,33 @@ gap_fwd_short(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int L, i
         const int count = nrow * L;
         const T* src = x + r0 * L;
         const int c4 = count >> 2;
-        if (Ls == L) {
-            // shared layout == global layout: plain 16-byte copies
-            for (int p = lane; p < c4; p += 32) {
-                const Pack4<T> v = kd::load4_stream(src + 4 * p);
+        // four packets per lane in flight per trip
+        for (int p0 = lane; p0 < c4; p0 += 128) {
+            Pack4<T> v[4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) sm[4 * p + k] = v.v[k];
-            }
-            for (int e = (c4 << 2) + lane; e < count; e += 32) sm[e] = src[e];
-        } else {
-            for (int p = lane; p < c4; p += 32) {
-                const Pack4<T> v = kd::load4_stream(src + 4 * p);
+            for (int u = 0; u < 4; ++u)
+                if (p0 + 32 * u < c4) v[u] = kd::load4_stream(src + 4 * (p0 + 32 * u));
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int e = 4 * p + k;
-                    const int rr = e / L;
-                    sm[rr * Ls + (e - rr * L)] = v.v[k];
+            for (int u = 0; u < 4; ++u) {
+                const int p = p0 + 32 * u;
+                if (p < c4) {
+                    if (Ls == L) {          // shared layout == global layout
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) sm[4 * p + k] = v[u].v[k];
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int e = 4 * p + k;
+                            const int rr = e / L;
+                            sm[rr * Ls + (e - rr * L)] = v[u].v[k];
+                        }
+                    }
                 }
             }
-            for (int e = (c4 << 2) + lane; e < count; e += 32) {
-                const int rr = e / L;
-                sm[rr * Ls + (e - rr * L)] = src[e];
-            }
+        }
+        for (int e = (c4 << 2) + lane; e < count; e += 32) {
+            const int rr = e / L;
+            sm[rr * Ls + (e - rr * L)] = src[e];
         }
         __syncwarp();
         if (lane < nrow) {
@@ -510,11 +504,21 @@ gap_bwd(const T* __restrict__ go, T* __restrict__ gx, int64_t total, int L, bool
     const T scale = T(1) / static_cast<T>(L);
     if (vec) {
         const int64_t n4 = total >> 2;
+        const bool small = total < (int64_t(1) << 31);      // 32-bit index arithmetic is enough
         for (int64_t p = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; p < n4;
              p += static_cast<int64_t>(gridDim.x) * kThreads) {
             const int64_t e0 = p << 2;
-            int64_t row = e0 / L;
-            int rem = static_cast<int>(e0 - row * L);
+            int64_t row;
+            int rem;
+            if (small) {
+                const unsigned e32 = static_cast<unsigned>(e0);
+                const unsigned r32 = e32 / static_cast<unsigned>(L);
+                row = r32;
+                rem = static_cast<int>(e32 - r32 * static_cast<unsigned>(L));
+            } else {
+                row = e0 / L;
+                rem = static_cast<int>(e0 - row * L);
+            }
             Pack4<T> out;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -592,13 +596,13 @@ int maxpool_forward(const T* x, T* y, long long* idx, int N, int C, PoolGeom g) 
     const int64_t nc = static_cast<int64_t>(N) * C;
     const int64_t total = nc * g.Ho * g.Wo;
     const bool fast = g.kh == 2 && g.kw == 2 && g.sh == 2 && g.sw == 2 && g.ph == 0 && g.pw == 0 &&
-                      (g.W % 8 == 0) && g.Wo == g.W / 2 && g.Ho <= g.H / 2 && kd::aligned16(x) &&
-                      kd::aligned16(y) && kd::aligned16(idx);
+                      (g.W % 8 == 0) && g.Wo == g.W / 2 && g.Ho <= g.H / 2 && kd::aligned_row8<T>(x) &&
+                      kd::aligned_pack<T>(y) && kd::aligned_pack<long long>(idx);
     if (fast) {
         constexpr int U = 2;
         const int64_t groups = total >> 2;
-        const unsigned grid = kd::grid_for((groups + kThreads * U - 1) / (kThreads * U), 8);
-        maxpool2x2_fwd<T, U><<<grid, kThreads, 0, kd::stream()>>>(x, y, idx, g.H, g.W, g.Ho, g.Wo, groups);
+        KD_LAUNCH((maxpool2x2_fwd<T, U>), (groups + kThreads * U - 1) / (kThreads * U), kThreads, 0, x, y, idx, g.H, g.W,
+                  g.Ho, g.Wo, groups);
     } else {
         maxpool_fwd_generic<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(x, y, idx, g, total);
     }
@@ -616,12 +620,12 @@ int maxpool_backward_ex(const T* go, const long long* idx, T* gx, int N, int C, 
     const int64_t nc = static_cast<int64_t>(N) * C;
     const bool fast = g.kh == 2 && g.kw == 2 && g.sh == 2 && g.sw == 2 && g.ph == 0 && g.pw == 0 &&
                       (g.W % 8 == 0) && (g.H % 2 == 0) && g.Wo == g.W / 2 && g.Ho == g.H / 2 &&
-                      kd::aligned16(go) && kd::aligned16(gx) && kd::aligned16(idx);
+                      kd::aligned_pack<T>(go) && kd::aligned_row8<T>(gx) && kd::aligned_pack<long long>(idx);
     if (fast) {
         constexpr int U = 2;
         const int64_t groups = (nc * g.Ho * g.Wo) >> 2;
-        const unsigned grid = kd::grid_for((groups + kThreads * U - 1) / (kThreads * U), 8);
-        maxpool2x2_bwd<T, U><<<grid, kThreads, 0, kd::stream()>>>(go, idx, gx, g.H, g.W, g.Ho, g.Wo, groups);
+        KD_LAUNCH((maxpool2x2_bwd<T, U>), (groups + kThreads * U - 1) / (kThreads * U), kThreads, 0, go, idx, gx, g.H,
+                  g.W, g.Ho, g.Wo, groups);
     } else {
         const int64_t total = nc * g.H * g.W;
         maxpool_bwd_gather<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(go, idx, gx, g, total);
@@ -652,11 +656,11 @@ int avgpool_forward(const T* x, T* y, int N, int C, PoolGeom g) {
     const int64_t nc = static_cast<int64_t>(N) * C;
     const int64_t total = nc * g.Ho * g.Wo;
     const bool fast = g.kh == 3 && g.kw == 3 && g.sh == 2 && g.sw == 2 && g.ph == 1 && g.pw == 1 &&
-                      (g.W % 8 == 0) && g.Wo == g.W / 2 && g.Ho == (g.H - 1) / 2 + 1 && kd::aligned16(x) &&
-                      kd::aligned16(y);
+                      (g.W % 8 == 0) && g.Wo == g.W / 2 && g.Ho == (g.H - 1) / 2 + 1 && kd::aligned_row8<T>(x) &&
+                      kd::aligned_pack<T>(y);
     if (fast) {
         const int64_t groups = total >> 2;
-        avgpool3x3s2p1_fwd<T><<<flat_grid(groups), kThreads, 0, kd::stream()>>>(x, y, g.H, g.W, g.Ho, g.Wo, groups);
+        KD_LAUNCH(avgpool3x3s2p1_fwd<T>, (groups + kThreads - 1) / kThreads, kThreads, 0, x, y, g.H, g.W, g.Ho, g.Wo, groups);
     } else {
         avgpool_fwd_generic<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(x, y, g, total);
     }
@@ -674,11 +678,11 @@ int avgpool_backward(const T* go, T* gx, int N, int C, PoolGeom g, bool accumula
     const int64_t nc = static_cast<int64_t>(N) * C;
     const int64_t total = nc * g.H * g.W;
     const bool fast = !accumulate && g.kh == 3 && g.kw == 3 && g.sh == 2 && g.sw == 2 && g.ph == 1 && g.pw == 1 &&
-                      (g.W % 8 == 0) && g.Wo == g.W / 2 && g.Ho == (g.H - 1) / 2 + 1 && kd::aligned16(go) &&
-                      kd::aligned16(gx);
+                      (g.W % 8 == 0) && g.Wo == g.W / 2 && g.Ho == (g.H - 1) / 2 + 1 && kd::aligned_pack<T>(go) &&
+                      kd::aligned_row8<T>(gx);
     if (fast) {
         const int64_t blocks = nc * ((g.H + 1) / 2) * (g.W / 8);
-        avgpool3x3s2p1_bwd<T><<<flat_grid(blocks), kThreads, 0, kd::stream()>>>(go, gx, g.H, g.W, g.Ho, g.Wo, blocks);
+        KD_LAUNCH(avgpool3x3s2p1_bwd<T>, (blocks + kThreads - 1) / kThreads, kThreads, 0, go, gx, g.H, g.W, g.Ho, g.Wo, blocks);
     } else if (accumulate) {
         avgpool_bwd_gather<T, true><<<flat_grid(total), kThreads, 0, kd::stream()>>>(go, gx, g, total);
     } else {
@@ -696,18 +700,17 @@ int gap_forward(const T* x, T* y, int N, int C, int H, int W) {
     const int64_t L64 = static_cast<int64_t>(H) * W;
     if (L64 > std::numeric_limits<int>::max()) return -2;
     const int L = static_cast<int>(L64);
-    if (L <= 64 && kd::aligned16(x)) {
+    if (L <= 64 && kd::aligned_pack<T>(x)) {
         constexpr int WARPS = 4;
         const int Ls = (L & 1) ? L : L + 1;
         const size_t smem = static_cast<size_t>(WARPS) * 32 * Ls * sizeof(T);   // <= 66,560 bytes
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(gap_fwd_short<T, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
         const int64_t chunks = (rows + 31) / 32;
-        const unsigned grid = kd::grid_for((chunks + WARPS - 1) / WARPS, 8);
-        gap_fwd_short<T, WARPS><<<grid, WARPS * 32, smem, kd::stream()>>>(x, y, rows, L, Ls);
+        KD_LAUNCH((gap_fwd_short<T, WARPS>), (chunks + WARPS - 1) / WARPS, WARPS * 32, smem, x, y, rows, L, Ls);
     } else {
         const unsigned grid = kd::grid_for((rows + 7) / 8, 8);
-        const bool vec = kd::aligned16(x) && (L % 4 == 0);
+        const bool vec = kd::aligned_pack<T>(x) && (L % 4 == 0);
         if (vec) gap_fwd_long<T, true><<<grid, kThreads, 0, kd::stream()>>>(x, y, rows, L);
         else gap_fwd_long<T, false><<<grid, kThreads, 0, kd::stream()>>>(x, y, rows, L);
     }
@@ -722,9 +725,9 @@ int gap_backward(const T* go, T* gx, int N, int C, int H, int W) {
     const int64_t L64 = static_cast<int64_t>(H) * W;
     if (L64 > std::numeric_limits<int>::max()) return -2;
     const int64_t total = static_cast<int64_t>(N) * C * L64;
-    const bool vec = kd::aligned16(gx);
+    const bool vec = kd::aligned_pack<T>(gx);
     const int64_t items = vec ? (total >> 2) + 1 : total;
-    gap_bwd<T><<<flat_grid(items), kThreads, 0, kd::stream()>>>(go, gx, total, static_cast<int>(L64), vec);
+    KD_LAUNCH(gap_bwd<T>, (items + kThreads - 1) / kThreads, kThreads, 0, go, gx, total, static_cast<int>(L64), vec);
     return kd::launch_status();
 }
 

@@ -624,9 +624,10 @@ int sum_all(const T* x, T* y, int64_t n, bool mean) {
     if (!x || !y) return -1;
     if (n <= 0) return -2;
     (void)cudaGetLastError();
-    const bool vec = kd::aligned16(x);
+    const bool vec = kd::aligned_pack<T>(x);
     const int64_t tiles = vec ? ((n >> 2) + kThreads * 4 - 1) / (kThreads * 4) : (n + kThreads - 1) / kThreads;
-    const unsigned grid = kd::grid_for(tiles < 1 ? 1 : tiles, 8);
+    const unsigned grid = vec ? kd::grid_fit(sum_all_kernel<T, true>, kThreads, tiles)
+                              : kd::grid_fit(sum_all_kernel<T, false>, kThreads, tiles);
     double* partials = static_cast<double*>(kd::scratch(grid * sizeof(double)));
     unsigned int* counter = kd::counters(1);
     if (!partials || !counter) return static_cast<int>(cudaErrorMemoryAllocation);
@@ -641,9 +642,10 @@ int max_all(const T* x, T* y, long long* idx, int64_t n) {
     if (!x || !y || !idx) return -1;
     if (n <= 0) return -2;
     (void)cudaGetLastError();
-    const bool vec = kd::aligned16(x);
+    const bool vec = kd::aligned_pack<T>(x);
     const int64_t tiles = vec ? ((n >> 2) + kThreads - 1) / kThreads : (n + kThreads - 1) / kThreads;
-    const unsigned grid = kd::grid_for(tiles < 1 ? 1 : tiles, 8);
+    const unsigned grid = vec ? kd::grid_fit(max_all_kernel<T, true>, kThreads, tiles)
+                              : kd::grid_fit(max_all_kernel<T, false>, kThreads, tiles);
     char* buf = static_cast<char*>(kd::scratch(grid * 16));
     unsigned int* counter = kd::counters(1);
     if (!buf || !counter) return static_cast<int>(cudaErrorMemoryAllocation);
@@ -656,53 +658,54 @@ int max_all(const T* x, T* y, long long* idx, int64_t n) {
 
 template <typename T>
 int sum_rows(const T* x, T* y, int64_t rows, int cols, T scale, bool apply_scale) {
-    const bool vec = kd::aligned16(x) && (cols % 4 == 0);
+    const bool vec = kd::aligned_pack<T>(x) && (cols % 4 == 0);
     cudaStream_t s = kd::stream();
     if (cols >= 2048) {
-        const unsigned grid = kd::grid_for(rows, 8);
-        if (vec) sum_rows_kernel<T, kThreads, true><<<grid, kThreads, 0, s>>>(x, y, rows, cols, scale, apply_scale);
-        else sum_rows_kernel<T, kThreads, false><<<grid, kThreads, 0, s>>>(x, y, rows, cols, scale, apply_scale);
+        if (vec) KD_LAUNCH((sum_rows_kernel<T, kThreads, true>), rows, kThreads, 0, x, y, rows, cols, scale, apply_scale);
+        else KD_LAUNCH((sum_rows_kernel<T, kThreads, false>), rows, kThreads, 0, x, y, rows, cols, scale, apply_scale);
     } else {
-        const unsigned grid = kd::grid_for((rows + kWarps - 1) / kWarps, 8);
-        if (vec) sum_rows_kernel<T, 32, true><<<grid, kThreads, 0, s>>>(x, y, rows, cols, scale, apply_scale);
-        else sum_rows_kernel<T, 32, false><<<grid, kThreads, 0, s>>>(x, y, rows, cols, scale, apply_scale);
+        if (vec) KD_LAUNCH((sum_rows_kernel<T, 32, true>), (rows + kWarps - 1) / kWarps, kThreads, 0, x, y, rows, cols, scale, apply_scale);
+        else KD_LAUNCH((sum_rows_kernel<T, 32, false>), (rows + kWarps - 1) / kWarps, kThreads, 0, x, y, rows, cols, scale, apply_scale);
     }
     return kd::launch_status();
 }
 
 template <typename T>
 int max_rows(const T* x, T* y, long long* idx, int64_t rows, int cols) {
-    const bool vec = kd::aligned16(x) && (cols % 4 == 0);
+    const bool vec = kd::aligned_pack<T>(x) && (cols % 4 == 0);
     cudaStream_t s = kd::stream();
     if (cols >= 2048) {
-        const unsigned grid = kd::grid_for(rows, 8);
-        if (vec) max_rows_kernel<T, kThreads, true><<<grid, kThreads, 0, s>>>(x, y, idx, rows, cols);
-        else max_rows_kernel<T, kThreads, false><<<grid, kThreads, 0, s>>>(x, y, idx, rows, cols);
+        if (vec) KD_LAUNCH((max_rows_kernel<T, kThreads, true>), rows, kThreads, 0, x, y, idx, rows, cols);
+        else KD_LAUNCH((max_rows_kernel<T, kThreads, false>), rows, kThreads, 0, x, y, idx, rows, cols);
     } else {
-        const unsigned grid = kd::grid_for((rows + kWarps - 1) / kWarps, 8);
-        if (vec) max_rows_kernel<T, 32, true><<<grid, kThreads, 0, s>>>(x, y, idx, rows, cols);
-        else max_rows_kernel<T, 32, false><<<grid, kThreads, 0, s>>>(x, y, idx, rows, cols);
+        if (vec) KD_LAUNCH((max_rows_kernel<T, 32, true>), (rows + kWarps - 1) / kWarps, kThreads, 0, x, y, idx, rows, cols);
+        else KD_LAUNCH((max_rows_kernel<T, 32, false>), (rows + kWarps - 1) / kWarps, kThreads, 0, x, y, idx, rows, cols);
     }
     return kd::launch_status();
 }
 
-// Row-chunk height for column reductions: tiles of about 128 rows keep several
-// waves of CTAs in flight while the partial traffic stays near 1% of the input.
-inline int pick_row_chunk(int rows, int stripes) {
-    int rch = 128;
-    // small matrices: do not split below what fills the machine once
-    const int64_t want_ctas = static_cast<int64_t>(kd::sm_count()) * 4;
-    while (rch > 32 && static_cast<int64_t>(stripes) * ((rows + rch - 1) / rch) < want_ctas) rch >>= 1;
-    if (rch > rows) rch = ((rows + kWarps - 1) / kWarps) * kWarps;
+// Row-chunk height for column reductions.  The (stripe, chunk) grid is sized to
+// what the machine holds at once, so every CTA is resident from the start, all do
+// the same amount of work and there is no partial last wave; partial traffic is
+// nchunks * cols elements (under 1% of the input at the benchmark sizes).
+inline int pick_row_chunk(int rows, int stripes, int ctas_per_sm) {
+    const int64_t slots = static_cast<int64_t>(kd::sm_count()) * ctas_per_sm;
+    int64_t nchunks = slots / stripes;
+    const int64_t max_chunks = (rows + 4 * kWarps - 1) / (4 * kWarps);   // at least 32 rows per chunk
+    if (nchunks > max_chunks) nchunks = max_chunks;
+    if (nchunks < 1) nchunks = 1;
+    int rch = static_cast<int>((rows + nchunks - 1) / nchunks);
+    rch = ((rch + kWarps - 1) / kWarps) * kWarps;
     return rch;
 }
 
 template <typename T>
 int sum_cols(const T* x, T* y, int rows, int cols, T scale, bool apply_scale) {
-    const bool vec = kd::aligned16(x) && (cols % 4 == 0);
+    const bool vec = kd::aligned_pack<T>(x) && (cols % 4 == 0);
     const int V = vec ? 4 : 1;
     const int stripes = (cols + 32 * V - 1) / (32 * V);
-    const int rch = pick_row_chunk(rows, stripes);
+    const int occ = vec ? kd::occupancy(sum_cols_kernel<T, 4>, kThreads) : kd::occupancy(sum_cols_kernel<T, 1>, kThreads);
+    const int rch = pick_row_chunk(rows, stripes, occ);
     const int nchunks = (rows + rch - 1) / rch;
     if (nchunks > 65535) return -2;
     T* partials = nullptr;
@@ -721,10 +724,11 @@ int sum_cols(const T* x, T* y, int rows, int cols, T scale, bool apply_scale) {
 
 template <typename T>
 int max_cols(const T* x, T* y, long long* idx, int rows, int cols) {
-    const bool vec = kd::aligned16(x) && (cols % 4 == 0);
+    const bool vec = kd::aligned_pack<T>(x) && (cols % 4 == 0);
     const int V = vec ? 4 : 1;
     const int stripes = (cols + 32 * V - 1) / (32 * V);
-    const int rch = pick_row_chunk(rows, stripes);
+    const int occ = vec ? kd::occupancy(max_cols_kernel<T, 4>, kThreads) : kd::occupancy(max_cols_kernel<T, 1>, kThreads);
+    const int rch = pick_row_chunk(rows, stripes, occ);
     const int nchunks = (rows + rch - 1) / rch;
     if (nchunks > 65535) return -2;
     T* pval = nullptr;
@@ -771,16 +775,16 @@ int bcast_scalar(const T* go, T* gx, int64_t n, T scale) {
     (void)cudaGetLastError();
     const uintptr_t addr = reinterpret_cast<uintptr_t>(gx);
     if (addr % sizeof(T)) return static_cast<int>(cudaErrorMisalignedAddress);
-    int head = static_cast<int>(((16 - (addr & 15)) & 15) / sizeof(T));
+    constexpr uintptr_t kA = sizeof(T) * 4;   // packet alignment
+    int head = static_cast<int>(((kA - (addr & (kA - 1))) & (kA - 1)) / sizeof(T));
     if (head > n) head = static_cast<int>(n);
-    const unsigned grid = kd::grid_for(((n >> 2) + kThreads - 1) / kThreads + 1, 8);
-    bcast_scalar_kernel<T><<<grid, kThreads, 0, kd::stream()>>>(go, gx, n, scale, head);
+    KD_LAUNCH(bcast_scalar_kernel<T>, ((n >> 2) + kThreads - 1) / kThreads + 1, kThreads, 0, go, gx, n, scale, head);
     return kd::launch_status();
 }
 
 template <typename T, int MODE>
 int grad_matrix(const T* go, const long long* idx, T* gx, int rows, int cols, T scale, bool apply_scale) {
-    const bool vec = kd::aligned16(gx) && (cols % 4 == 0);
+    const bool vec = kd::aligned_pack<T>(gx) && (cols % 4 == 0);
     const int V = vec ? 4 : 1;
     const int ppr = (cols + V - 1) / V;
     int gx_dim = (ppr + kThreads - 1) / kThreads;
@@ -837,10 +841,10 @@ int max_all_backward(const T* go, const long long* idx, T* gx, int64_t n) {
     (void)cudaGetLastError();
     const uintptr_t addr = reinterpret_cast<uintptr_t>(gx);
     if (addr % sizeof(T)) return static_cast<int>(cudaErrorMisalignedAddress);
-    int head = static_cast<int>(((16 - (addr & 15)) & 15) / sizeof(T));
+    constexpr uintptr_t kA = sizeof(T) * 4;   // packet alignment
+    int head = static_cast<int>(((kA - (addr & (kA - 1))) & (kA - 1)) / sizeof(T));
     if (head > n) head = static_cast<int>(n);
-    const unsigned grid = kd::grid_for(((n >> 2) + kThreads - 1) / kThreads + 1, 8);
-    onehot_kernel<T><<<grid, kThreads, 0, kd::stream()>>>(go, idx, gx, n, head);
+    KD_LAUNCH(onehot_kernel<T>, ((n >> 2) + kThreads - 1) / kThreads + 1, kThreads, 0, go, idx, gx, n, head);
     return kd::launch_status();
 }
 
@@ -897,7 +901,7 @@ int sum_to_shape(const T* x, T* y, const int64_t* in_shape, const int64_t* out_s
             if (!partials || !counters) return static_cast<int>(cudaErrorMemoryAllocation);
         }
         dim3 grid(K, nslices);
-        const bool vec = kd::aligned16(x) && (B % 4 == 0);
+        const bool vec = kd::aligned_pack<T>(x) && (B % 4 == 0);
         if (vec) sum_akb_kernel<T, true><<<grid, kThreads, 0, s>>>(x, y, A, K, B, ach, partials, counters);
         else sum_akb_kernel<T, false><<<grid, kThreads, 0, s>>>(x, y, A, K, B, ach, partials, counters);
         return kd::launch_status();
