@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <cstddef>
 #include <cstdint>
+#include <cstdlib>
 #include <limits>
 #include <unordered_map>
 
@@ -56,11 +57,19 @@ template <typename K> inline int occupancy(K kernel, int threads, size_t smem = 
     return n;
 }
 
-// Grid for a grid-stride kernel: one resident wave (every SM holds as many CTAs of
-// this kernel as fit), or fewer when there is less work.  All CTAs then run
-// concurrently from start to end and take the same number of trips.
-template <typename K> inline unsigned grid_fit(K kernel, int threads, int64_t work_ctas, size_t smem = 0) {
-    const int64_t cap = static_cast<int64_t>(sm_count()) * occupancy(kernel, threads, smem);
+// Grid for a grid-stride kernel: `waves` times what the machine holds at once (every SM
+// holds as many CTAs of this kernel as fit), or fewer when there is less work.
+//   waves = 1: all CTAs resident from start to end; for kernels whose CTAs split the work
+//              evenly themselves and publish one partial each.
+//   waves >> 1: pure streaming kernels; the hardware scheduler hands out the many small CTAs
+//              as SMs free up, which evens out the last trips (measured on B200: element-wise
+//              kernels gain 5% from 1 to 8 waves and 5% more up to 64; write-only fills peak
+//              at 8-16 and collapse when a CTA has less than a few packets per thread).
+constexpr int kStreamWaves = 8;
+inline int stream_waves() { return kStreamWaves; }
+template <typename K>
+inline unsigned grid_fit(K kernel, int threads, int64_t work_ctas, size_t smem = 0, int waves = 1) {
+    const int64_t cap = static_cast<int64_t>(sm_count()) * occupancy(kernel, threads, smem) * waves;
     const int64_t g = work_ctas < cap ? work_ctas : cap;
     return static_cast<unsigned>(g < 1 ? 1 : g);
 }
@@ -68,7 +77,22 @@ template <typename K> inline unsigned grid_fit(K kernel, int threads, int64_t wo
 #define KD_LAUNCH(KERNEL, WORK, THREADS, SMEM, ...)                                                           \
     do {                                                                                                      \
         auto kd_fn_ = (KERNEL);                                                                               \
-        kd_fn_<<<kd::grid_fit(kd_fn_, (THREADS), (WORK), (SMEM)), (THREADS), (SMEM), kd::stream()>>>(__VA_ARGS__); \
+        kd_fn_<<<kd::grid_fit(kd_fn_, (THREADS), (WORK), (SMEM), kd::stream_waves()), (THREADS), (SMEM),        \
+                 kd::stream()>>>(__VA_ARGS__);                                                                \
+    } while (0)
+
+// Same with an explicit number of waves.
+#define KD_LAUNCH_W(KERNEL, WAVES, WORK, THREADS, SMEM, ...)                                                  \
+    do {                                                                                                      \
+        auto kd_fn_ = (KERNEL);                                                                               \
+        kd_fn_<<<kd::grid_fit(kd_fn_, (THREADS), (WORK), (SMEM), (WAVES)), (THREADS), (SMEM), kd::stream()>>>(__VA_ARGS__); \
+    } while (0)
+
+// Same with exactly one resident wave.
+#define KD_LAUNCH1(KERNEL, WORK, THREADS, SMEM, ...)                                                          \
+    do {                                                                                                      \
+        auto kd_fn_ = (KERNEL);                                                                               \
+        kd_fn_<<<kd::grid_fit(kd_fn_, (THREADS), (WORK), (SMEM), 1), (THREADS), (SMEM), kd::stream()>>>(__VA_ARGS__); \
     } while (0)
 
 // ---------------------------------------------------------------------------
@@ -186,6 +210,36 @@ template <> __device__ __forceinline__ float neg_inf<float>() { return __int_as_
 template <> __device__ __forceinline__ double neg_inf<double>() {
     return __longlong_as_double(static_cast<long long>(0xfff0000000000000ULL));
 }
+
+// ---------------------------------------------------------------------------
+// Division of a 31-bit index by a launch-invariant divisor: one multiply-high and
+// one shift instead of the ~20 (32-bit) or ~100 (64-bit) instruction division
+// sequence.  q = floor(n / d) for every 0 <= n < 2^31, 1 <= d < 2^31.
+// ---------------------------------------------------------------------------
+struct FastDiv {
+    unsigned d, mul, shr;
+    FastDiv() : d(1), mul(0), shr(0) {}
+    explicit FastDiv(unsigned divisor) : d(divisor), mul(0), shr(0) {
+        if (d > 1) {
+            unsigned lg = 0;
+            while ((1ull << lg) < d) ++lg;                 // ceil(log2(d))
+            const unsigned p = 31 + lg;
+            mul = static_cast<unsigned>(((1ull << p) + d - 1) / d);
+            shr = p - 32;
+        }
+    }
+    __host__ __device__ __forceinline__ unsigned div(unsigned n) const {
+#ifdef __CUDA_ARCH__
+        return d == 1 ? n : (__umulhi(n, mul) >> shr);
+#else
+        return d == 1 ? n : static_cast<unsigned>((static_cast<unsigned long long>(n) * mul) >> 32) >> shr;
+#endif
+    }
+    __host__ __device__ __forceinline__ void divmod(unsigned n, unsigned& q, unsigned& r) const {
+        q = div(n);
+        r = n - q * d;
+    }
+};
 
 // ---------------------------------------------------------------------------
 // Warp / block reductions (sum in double; arg-max pairs)

@@ -86,7 +86,7 @@ int launch_ew(const TI* a, const TI* b, TI alpha, TO* y, int64_t n, Op op) {
     if (vec) {
         constexpr int UNROLL = (MODE == kBinary) ? 4 : 8;
         const int64_t tiles = ((n >> 2) + kThreads * UNROLL - 1) / (kThreads * UNROLL);
-        KD_LAUNCH((ew_packet_kernel<TI, TO, MODE, UNROLL, Op>), tiles, kThreads, 0, a, b, alpha, y, n, op);
+        KD_LAUNCH_W((ew_packet_kernel<TI, TO, MODE, UNROLL, Op>), 64, tiles, kThreads, 0, a, b, alpha, y, n, op);
     } else {
         const unsigned grid = kd::grid_for((n + kThreads - 1) / kThreads, 16);
         ew_scalar_kernel<TI, TO, MODE, Op><<<grid, kThreads, 0, kd::stream()>>>(a, b, alpha, y, n, op);
@@ -124,7 +124,7 @@ int launch_fill(T* y, int64_t n, T value) {
     constexpr uintptr_t kA = sizeof(T) * 4;   // packet alignment
     int head = static_cast<int>(((kA - (addr & (kA - 1))) & (kA - 1)) / sizeof(T));
     if (head > n) head = static_cast<int>(n);
-    KD_LAUNCH(fill_kernel<T>, ((n >> 2) + kThreads - 1) / kThreads + 1, kThreads, 0, y, n, value, head);
+    KD_LAUNCH_W(fill_kernel<T>, 16, ((n >> 2) + kThreads - 1) / kThreads + 1, kThreads, 0, y, n, value, head);
     return kd::launch_status();
 }
 
@@ -221,11 +221,11 @@ int launch_sgd(T* p, const T* g, T* v, int64_t n, T lr, T mu, T wd, T gscale) {
     const bool use_wd = !(wd == T(0));
     const int64_t tiles = vec ? ((n >> 2) + kThreads * 2 - 1) / (kThreads * 2) : (n + kThreads - 1) / kThreads;
     if (v) {
-        if (vec) KD_LAUNCH((sgd_kernel<T, true, true>), tiles, kThreads, 0, p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
-        else KD_LAUNCH((sgd_kernel<T, true, false>), tiles, kThreads, 0, p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
+        if (vec) KD_LAUNCH_W((sgd_kernel<T, true, true>), 16, tiles, kThreads, 0, p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
+        else KD_LAUNCH_W((sgd_kernel<T, true, false>), 16, tiles, kThreads, 0, p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
     } else {
-        if (vec) KD_LAUNCH((sgd_kernel<T, false, true>), tiles, kThreads, 0, p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
-        else KD_LAUNCH((sgd_kernel<T, false, false>), tiles, kThreads, 0, p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
+        if (vec) KD_LAUNCH_W((sgd_kernel<T, false, true>), 16, tiles, kThreads, 0, p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
+        else KD_LAUNCH_W((sgd_kernel<T, false, false>), 16, tiles, kThreads, 0, p, g, v, n, lr, mu, wd, gscale, use_scale, use_wd);
     }
     return kd::launch_status();
 }

@@ -52,26 +52,30 @@ __global__ void __launch_bounds__(kThreads)
 sum_all_kernel(const T* __restrict__ x, int64_t n, double* partials, unsigned int* counter, T* out, T scale,
                bool apply_scale) {
     __shared__ double sm[kWarps];
-    constexpr int U = 4;
-    T acc[4 * U];
+    constexpr int U = 8;     // packets in flight per thread and trip
+    constexpr int A = 8;     // independent accumulators
+    T acc[A];
 #pragma unroll
-    for (int k = 0; k < 4 * U; ++k) acc[k] = T(0);
+    for (int k = 0; k < A; ++k) acc[k] = T(0);
     if (VEC) {
+        // every CTA owns an equal, contiguous share of the packets (a multiple of the CTA width)
         const int64_t n4 = n >> 2;
+        const int64_t share = ((n4 + gridDim.x - 1) / gridDim.x + kThreads - 1) / kThreads * kThreads;
+        const int64_t begin = static_cast<int64_t>(blockIdx.x) * share;
+        const int64_t end = begin + share < n4 ? begin + share : n4;
         const int64_t tile = static_cast<int64_t>(kThreads) * U;
-        for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < n4;
-             base += static_cast<int64_t>(gridDim.x) * tile) {
+        for (int64_t base = begin; base < end; base += tile) {
             Pack4<T> v[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int64_t p = base + u * kThreads + threadIdx.x;
-                if (p < n4) v[u] = kd::load4_stream(x + 4 * p);
+                if (p < end) v[u] = kd::load4_stream(x + 4 * p);
                 else v[u].v[0] = v[u].v[1] = v[u].v[2] = v[u].v[3] = T(0);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u)
 #pragma unroll
-                for (int k = 0; k < 4; ++k) acc[4 * u + k] += v[u].v[k];
+                for (int k = 0; k < 4; ++k) acc[(4 * u + k) % A] += v[u].v[k];
         }
         if (blockIdx.x == 0 && threadIdx.x < 4) {
             const int64_t i = (n4 << 2) + threadIdx.x;
@@ -84,7 +88,7 @@ sum_all_kernel(const T* __restrict__ x, int64_t n, double* partials, unsigned in
     }
     double s = 0.0;
 #pragma unroll
-    for (int k = 0; k < 4 * U; ++k) s += static_cast<double>(acc[k]);
+    for (int k = 0; k < A; ++k) s += static_cast<double>(acc[k]);
     s = kd::block_sum(s, sm);
     if (threadIdx.x == 0) partials[blockIdx.x] = s;
     if (take_ticket(counter, gridDim.x)) {
@@ -108,12 +112,26 @@ max_all_kernel(const T* __restrict__ x, int64_t n, T* pval, long long* pidx, uns
     __shared__ long long smi[kWarps];
     ArgMax<T> a = kd::argmax_init<T>();
     if (VEC) {
+        constexpr int U = 4;
         const int64_t n4 = n >> 2;
-        for (int64_t p = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; p < n4;
-             p += static_cast<int64_t>(gridDim.x) * kThreads) {
-            const Pack4<T> v = kd::load4_stream(x + 4 * p);
+        const int64_t share = ((n4 + gridDim.x - 1) / gridDim.x + kThreads - 1) / kThreads * kThreads;
+        const int64_t begin = static_cast<int64_t>(blockIdx.x) * share;
+        const int64_t end = begin + share < n4 ? begin + share : n4;
+        for (int64_t base = begin; base < end; base += static_cast<int64_t>(kThreads) * U) {
+            Pack4<T> v[U];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) kd::argmax_step(a, v.v[k], 4 * p + k);
+            for (int u = 0; u < U; ++u) {
+                const int64_t p = base + u * kThreads + threadIdx.x;
+                if (p < end) v[u] = kd::load4_stream(x + 4 * p);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t p = base + u * kThreads + threadIdx.x;
+                if (p < end) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) kd::argmax_step(a, v[u].v[k], 4 * p + k);
+                }
+            }
         }
         if (blockIdx.x == 0 && threadIdx.x < 4) {
             const int64_t i = (n4 << 2) + threadIdx.x;
@@ -267,7 +285,11 @@ max_rows_kernel(const T* __restrict__ x, T* __restrict__ y, long long* __restric
 // the stripe's partials in row order.
 template <typename T, int V> struct ColLoad {
     static __device__ __forceinline__ void get(const T* p, T* out) {
-        if (V == 4) {
+        if (V == 8) {
+            const kd::Row8<T> v = kd::load8_stream(p);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) out[k] = v.v[k];
+        } else if (V == 4) {
             const Pack4<T> v = kd::load4_stream(p);
 #pragma unroll
             for (int k = 0; k < 4; ++k) out[k] = v.v[k];
@@ -276,6 +298,15 @@ template <typename T, int V> struct ColLoad {
         }
     }
 };
+
+// Columns per lane: 32 bytes when the matrix allows it (8 floats / 4 doubles, one
+// 256-bit load, 1 KiB contiguous per warp and row), else one packet, else one element.
+template <typename T> inline int col_vector_width(const void* x, int cols) {
+    constexpr int kWide = 32 / static_cast<int>(sizeof(T));
+    if ((reinterpret_cast<uintptr_t>(x) & 31u) == 0 && cols % kWide == 0) return kWide;
+    if (kd::aligned_pack<T>(x) && cols % 4 == 0) return 4;
+    return 1;
+}
 
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
@@ -482,8 +513,8 @@ onehot_kernel(const T* __restrict__ go, const long long* __restrict__ idx, T* __
 //   3: idx[c] == r ? 0+go[c] : 0  max over axis 0
 // `scale` multiplies modes 0/1 when apply_scale (mean over an axis).
 // blockIdx.x / threadIdx.x walk 4-column packets of a row, blockIdx.y walks
-// rows, so column-indexed operands are loaded once per thread and no division
-// is needed.
+// blocks of consecutive rows, so column-indexed operands are loaded once per
+// thread and no division is needed.
 template <typename T, int MODE, int V>
 __global__ void __launch_bounds__(kThreads)
 grad_matrix_kernel(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, int rows, int cols,
@@ -501,7 +532,11 @@ grad_matrix_kernel(const T* __restrict__ go, const long long* __restrict__ idx, 
                 if (MODE == 3) { icol[k] = __ldg(idx + c0 + k); gcol[k] = T(0) + gcol[k]; }
             }
         }
-        for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+        // blockIdx.y owns a block of consecutive rows: the grid writes the matrix front to back
+        const int rpb = (rows + gridDim.y - 1) / gridDim.y;
+        const int r_begin = blockIdx.y * rpb;
+        const int r_end = min(rows, r_begin + rpb);
+        for (int r = r_begin; r < r_end; ++r) {
             T out[V];
             if (MODE == 0) {
                 T g = __ldg(go + r);
@@ -625,7 +660,7 @@ int sum_all(const T* x, T* y, int64_t n, bool mean) {
     if (n <= 0) return -2;
     (void)cudaGetLastError();
     const bool vec = kd::aligned_pack<T>(x);
-    const int64_t tiles = vec ? ((n >> 2) + kThreads * 4 - 1) / (kThreads * 4) : (n + kThreads - 1) / kThreads;
+    const int64_t tiles = vec ? ((n >> 2) + kThreads * 8 - 1) / (kThreads * 8) : (n + kThreads - 1) / kThreads;   // one wave
     const unsigned grid = vec ? kd::grid_fit(sum_all_kernel<T, true>, kThreads, tiles)
                               : kd::grid_fit(sum_all_kernel<T, false>, kThreads, tiles);
     double* partials = static_cast<double*>(kd::scratch(grid * sizeof(double)));
@@ -699,13 +734,10 @@ inline int pick_row_chunk(int rows, int stripes, int ctas_per_sm) {
     return rch;
 }
 
-template <typename T>
-int sum_cols(const T* x, T* y, int rows, int cols, T scale, bool apply_scale) {
-    const bool vec = kd::aligned_pack<T>(x) && (cols % 4 == 0);
-    const int V = vec ? 4 : 1;
+template <typename T, int V>
+int sum_cols_v(const T* x, T* y, int rows, int cols, T scale, bool apply_scale) {
     const int stripes = (cols + 32 * V - 1) / (32 * V);
-    const int occ = vec ? kd::occupancy(sum_cols_kernel<T, 4>, kThreads) : kd::occupancy(sum_cols_kernel<T, 1>, kThreads);
-    const int rch = pick_row_chunk(rows, stripes, occ);
+    const int rch = pick_row_chunk(rows, stripes, kd::occupancy(sum_cols_kernel<T, V>, kThreads));
     const int nchunks = (rows + rch - 1) / rch;
     if (nchunks > 65535) return -2;
     T* partials = nullptr;
@@ -715,20 +747,23 @@ int sum_cols(const T* x, T* y, int rows, int cols, T scale, bool apply_scale) {
         counters = kd::counters(stripes);
         if (!partials || !counters) return static_cast<int>(cudaErrorMemoryAllocation);
     }
-    dim3 grid(stripes, nchunks);
-    cudaStream_t s = kd::stream();
-    if (vec) sum_cols_kernel<T, 4><<<grid, kThreads, 0, s>>>(x, y, rows, cols, rch, partials, counters, scale, apply_scale);
-    else sum_cols_kernel<T, 1><<<grid, kThreads, 0, s>>>(x, y, rows, cols, rch, partials, counters, scale, apply_scale);
+    sum_cols_kernel<T, V><<<dim3(stripes, nchunks), kThreads, 0, kd::stream()>>>(x, y, rows, cols, rch, partials, counters,
+                                                                               scale, apply_scale);
     return kd::launch_status();
 }
 
 template <typename T>
-int max_cols(const T* x, T* y, long long* idx, int rows, int cols) {
-    const bool vec = kd::aligned_pack<T>(x) && (cols % 4 == 0);
-    const int V = vec ? 4 : 1;
+int sum_cols(const T* x, T* y, int rows, int cols, T scale, bool apply_scale) {
+    const int V = col_vector_width<T>(x, cols);
+    if (sizeof(T) == 4 && V == 8) return sum_cols_v<T, (sizeof(T) == 4 ? 8 : 4)>(x, y, rows, cols, scale, apply_scale);
+    if (V >= 4) return sum_cols_v<T, 4>(x, y, rows, cols, scale, apply_scale);
+    return sum_cols_v<T, 1>(x, y, rows, cols, scale, apply_scale);
+}
+
+template <typename T, int V>
+int max_cols_v(const T* x, T* y, long long* idx, int rows, int cols) {
     const int stripes = (cols + 32 * V - 1) / (32 * V);
-    const int occ = vec ? kd::occupancy(max_cols_kernel<T, 4>, kThreads) : kd::occupancy(max_cols_kernel<T, 1>, kThreads);
-    const int rch = pick_row_chunk(rows, stripes, occ);
+    const int rch = pick_row_chunk(rows, stripes, kd::occupancy(max_cols_kernel<T, V>, kThreads));
     const int nchunks = (rows + rch - 1) / rch;
     if (nchunks > 65535) return -2;
     T* pval = nullptr;
@@ -742,11 +777,17 @@ int max_cols(const T* x, T* y, long long* idx, int rows, int cols) {
         pval = reinterpret_cast<T*>(buf);
         pidx = reinterpret_cast<int*>(buf + cells * sizeof(T));
     }
-    dim3 grid(stripes, nchunks);
-    cudaStream_t s = kd::stream();
-    if (vec) max_cols_kernel<T, 4><<<grid, kThreads, 0, s>>>(x, y, idx, rows, cols, rch, pval, pidx, counters);
-    else max_cols_kernel<T, 1><<<grid, kThreads, 0, s>>>(x, y, idx, rows, cols, rch, pval, pidx, counters);
+    max_cols_kernel<T, V><<<dim3(stripes, nchunks), kThreads, 0, kd::stream()>>>(x, y, idx, rows, cols, rch, pval, pidx,
+                                                                               counters);
     return kd::launch_status();
+}
+
+template <typename T>
+int max_cols(const T* x, T* y, long long* idx, int rows, int cols) {
+    const int V = col_vector_width<T>(x, cols);
+    if (sizeof(T) == 4 && V == 8) return max_cols_v<T, (sizeof(T) == 4 ? 8 : 4)>(x, y, idx, rows, cols);
+    if (V >= 4) return max_cols_v<T, 4>(x, y, idx, rows, cols);
+    return max_cols_v<T, 1>(x, y, idx, rows, cols);
 }
 
 template <typename T>
@@ -778,7 +819,7 @@ int bcast_scalar(const T* go, T* gx, int64_t n, T scale) {
     constexpr uintptr_t kA = sizeof(T) * 4;   // packet alignment
     int head = static_cast<int>(((kA - (addr & (kA - 1))) & (kA - 1)) / sizeof(T));
     if (head > n) head = static_cast<int>(n);
-    KD_LAUNCH(bcast_scalar_kernel<T>, ((n >> 2) + kThreads - 1) / kThreads + 1, kThreads, 0, go, gx, n, scale, head);
+    KD_LAUNCH_W(bcast_scalar_kernel<T>, 16, ((n >> 2) + kThreads - 1) / kThreads + 1, kThreads, 0, go, gx, n, scale, head);
     return kd::launch_status();
 }
 
@@ -789,9 +830,9 @@ int grad_matrix(const T* go, const long long* idx, T* gx, int rows, int cols, T 
     const int ppr = (cols + V - 1) / V;
     int gx_dim = (ppr + kThreads - 1) / kThreads;
     if (gx_dim > 64) gx_dim = 64;
-    int64_t want = static_cast<int64_t>(kd::sm_count()) * 8;
+    int64_t want = static_cast<int64_t>(kd::sm_count()) * 8 * 16;     // many small CTAs: see grid_fit
     int gy = static_cast<int>((want + gx_dim - 1) / gx_dim);
-    if (gy > rows) gy = rows;
+    if (gy > (rows + 3) / 4) gy = (rows + 3) / 4;      // at least four rows per CTA: column operands amortise
     if (gy > 65535) gy = 65535;
     if (gy < 1) gy = 1;
     dim3 grid(gx_dim, gy);
@@ -844,7 +885,7 @@ int max_all_backward(const T* go, const long long* idx, T* gx, int64_t n) {
     constexpr uintptr_t kA = sizeof(T) * 4;   // packet alignment
     int head = static_cast<int>(((kA - (addr & (kA - 1))) & (kA - 1)) / sizeof(T));
     if (head > n) head = static_cast<int>(n);
-    KD_LAUNCH(onehot_kernel<T>, ((n >> 2) + kThreads - 1) / kThreads + 1, kThreads, 0, go, idx, gx, n, head);
+    KD_LAUNCH_W(onehot_kernel<T>, 16, ((n >> 2) + kThreads - 1) / kThreads + 1, kThreads, 0, go, idx, gx, n, head);
     return kd::launch_status();
 }
 
@@ -982,3 +1023,4 @@ int sum_to_shape(const T* x, T* y, const int64_t* in_shape, const int64_t* out_s
 
 KD_REDUCE(float, f32)
 KD_REDUCE(double, f64)
+
