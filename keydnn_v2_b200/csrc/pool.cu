@@ -268,13 +268,12 @@ avgpool_fwd_generic(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int6
 // else (zeros, subnormal-range, huge, inf, NaN, and double) takes the true division.
 template <typename T> __device__ __forceinline__ T div9(T x) { return x / T(9); }
 template <> __device__ __forceinline__ float div9<float>(float x) {
+    constexpr float r = 1.0f / 9.0f;
+    const float q0 = __fmul_rn(x, r);
+    const float e = __fmaf_rn(-q0, 9.0f, x);
+    const float q = __fmaf_rn(e, r, q0);
     const float ax = fabsf(x);
-    if (ax >= 0x1p-100f && ax <= 0x1p100f) {
-        constexpr float r = 1.0f / 9.0f;
-        const float q0 = __fmul_rn(x, r);
-        const float e = __fmaf_rn(-q0, 9.0f, x);
-        return __fmaf_rn(e, r, q0);
-    }
+    if (__builtin_expect(ax >= 0x1p-100f && ax <= 0x1p100f, 1)) return q;
     return x / 9.0f;
 }
 
@@ -356,53 +355,68 @@ avgpool_bwd_gather(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int
     }
 }
 
-// kernel 3x3, stride 2, padding 1, W % 8 == 0.  A thread owns eight adjacent gradient
-// elements of ONE input row (one 32-byte store; the grid writes the tensor front to back).
-// An even row 2m is covered by output row m only, an odd row 2m+1 by rows m and m+1; even
-// columns by one output column, odd columns by two.  Five quotients go/9 per output row feed
-// the eight sums, added in ascending (i, j) as the reference does.
+// kernel 3x3, stride 2, padding 1, W % 8 == 0.  A thread owns the 2x8 block of gradient rows
+// (2m, 2m+1), columns [8jg, 8jg+8): two 32-byte stores.  Row 2m is covered by output row m
+// only, row 2m+1 by rows m and m+1; even columns by one output column, odd columns by two.
+// Ten quotients go/9 (five per output row) feed all sixteen sums, which are added in
+// ascending (i, j) as the reference does.  The kernel is bound by instruction issue as much
+// as by memory, hence the two rows per thread (index arithmetic and quotients are shared).
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 avgpool3x3s2p1_bwd(const T* __restrict__ go, T* __restrict__ gx, int H, int W, int Ho, int Wo, int64_t blocks,
-                   kd::FastDiv by_bpr, kd::FastDiv by_h) {
+                   kd::FastDiv by_bpr, kd::FastDiv by_hh) {
     for (int64_t bi = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; bi < blocks;
          bi += static_cast<int64_t>(gridDim.x) * kThreads) {
-        unsigned rowflat, ujg, nc, uh;                 // rowflat = nc * H + h
-        by_bpr.divmod(static_cast<unsigned>(bi), rowflat, ujg);
-        by_h.divmod(rowflat, nc, uh);
-        const int jg = static_cast<int>(ujg), h = static_cast<int>(uh);
-        const int m = h >> 1;
-        const bool odd = h & 1;
+        unsigned rowp, ujg, nc, um;                    // rowp = nc * ceil(H/2) + m
+        by_bpr.divmod(static_cast<unsigned>(bi), rowp, ujg);
+        by_hh.divmod(rowp, nc, um);
+        const int jg = static_cast<int>(ujg), m = static_cast<int>(um);
         const T* gplane = go + static_cast<int64_t>(nc) * Ho * Wo;
         const bool has_fifth = 4 * jg + 4 < Wo;        // the fifth quotient has a window
+        const bool second = m + 1 < Ho;                // output row m+1 exists
+        const T* p0 = gplane + static_cast<int64_t>(m) * Wo + 4 * jg;
+        const Pack4<T> a0 = kd::load4(p0);
+        const T e0 = has_fifth ? __ldg(p0 + 4) : T(0);
+        Pack4<T> a1;
+        a1.v[0] = a1.v[1] = a1.v[2] = a1.v[3] = T(0);
+        T e1 = T(0);
+        if (second) {
+            a1 = kd::load4(p0 + Wo);
+            e1 = has_fifth ? __ldg(p0 + Wo + 4) : T(0);
+        }
         T q[2][5];
-        bool live[2];
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            live[r] = (r == 0) || (odd && m + 1 < Ho);
-            if (live[r]) {
-                const T* p = gplane + static_cast<int64_t>(m + r) * Wo + 4 * jg;
-                const Pack4<T> a = kd::load4(p);
-                const T e = has_fifth ? __ldg(p + 4) : T(0);
+        for (int k = 0; k < 4; ++k) { q[0][k] = div9<T>(a0.v[k]); q[1][k] = div9<T>(a1.v[k]); }
+        q[0][4] = div9<T>(e0);
+        q[1][4] = div9<T>(e1);
+        T* r0 = gx + (static_cast<int64_t>(nc) * H + 2 * m) * W + 8 * jg;
+        {   // row 2m: output row m
+            kd::Row8<T> out;
 #pragma unroll
-                for (int k = 0; k < 4; ++k) q[r][k] = div9<T>(a.v[k]);
-                q[r][4] = div9<T>(e);
+            for (int cidx = 0; cidx < 8; ++cidx) {
+                T acc = T(0);
+                acc += q[0][cidx >> 1];
+                if ((cidx & 1) && (has_fifth || cidx != 7)) acc += q[0][(cidx >> 1) + 1];
+                out.v[cidx] = acc;
             }
+            kd::store8(r0, out);
         }
-        kd::Row8<T> out;
+        if (2 * m + 1 < H) {   // row 2m+1: output rows m and m+1
+            kd::Row8<T> out;
 #pragma unroll
-        for (int cidx = 0; cidx < 8; ++cidx) {
-            const bool two = (cidx & 1) && !(!has_fifth && cidx == 7);
-            T acc = T(0);
-            acc += q[0][cidx >> 1];
-            if (two) acc += q[0][(cidx >> 1) + 1];
-            if (live[1]) {
-                acc += q[1][cidx >> 1];
-                if (two) acc += q[1][(cidx >> 1) + 1];
+            for (int cidx = 0; cidx < 8; ++cidx) {
+                const bool two = (cidx & 1) && (has_fifth || cidx != 7);
+                T acc = T(0);
+                acc += q[0][cidx >> 1];
+                if (two) acc += q[0][(cidx >> 1) + 1];
+                if (second) {
+                    acc += q[1][cidx >> 1];
+                    if (two) acc += q[1][(cidx >> 1) + 1];
+                }
+                out.v[cidx] = acc;
             }
-            out.v[cidx] = acc;
+            kd::store8(r0 + W, out);
         }
-        kd::store8(gx + 8 * bi, out);
     }
 }
 
@@ -699,9 +713,9 @@ int avgpool_backward(const T* go, T* gx, int N, int C, PoolGeom g, bool accumula
                       (g.W % 8 == 0) && g.Wo == g.W / 2 && g.Ho == (g.H - 1) / 2 + 1 && kd::aligned_pack<T>(go) &&
                       kd::aligned_row8<T>(gx) && total < (int64_t(1) << 33);
     if (fast) {
-        const int64_t blocks = (nc * g.H * g.W) >> 3;
+        const int64_t blocks = nc * ((g.H + 1) / 2) * (g.W / 8);
         KD_LAUNCH(avgpool3x3s2p1_bwd<T>, (blocks + kThreads - 1) / kThreads, kThreads, 0, go, gx, g.H, g.W, g.Ho, g.Wo, blocks,
-                  kd::FastDiv(g.W / 8), kd::FastDiv(g.H));
+                  kd::FastDiv(g.W / 8), kd::FastDiv((g.H + 1) / 2));
     } else if (accumulate) {
         avgpool_bwd_gather<T, true><<<flat_grid(total), kThreads, 0, kd::stream()>>>(go, gx, g, total);
     } else {
