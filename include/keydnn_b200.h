@@ -154,6 +154,14 @@ int keydnn_cuda_sum_to_shape_f32(const float* x, float* y, const int64_t* in_sha
                                  int ndim);
 int keydnn_cuda_sum_to_shape_f64(const double* x, double* y, const int64_t* in_shape, const int64_t* out_shape,
                                  int ndim);
+/* No counterpart in the reference.  Column sums (axis 0) of a float32 (rows, cols) matrix for
+ * callers that may not allocate device memory at call time (hosts whose own allocator owns the
+ * device heap, latency-critical loops, fixed-budget processes): no cudaMalloc / cudaFree; partials
+ * live in a static 2,113,536-byte device array that each GPU holds while the library is loaded.
+ * cols <= KEYDNN_NOALLOC_MAX_COLS, else -20.  First call per device resolves the array's address
+ * (do it outside stream capture).  Calls that overlap on the GPU race on the shared array. */
+#define KEYDNN_NOALLOC_MAX_COLS 65536
+int keydnn_cuda_sum_axis0_noalloc_f32(const float* x, float* y, int rows, int cols);
 /* additive: the reference has no axis-wise mean (tensor/mixins/reduction/_tensor_mean.py:91-192
  * is all-elements only), no all-elements max (_tensor_max.py:70-85 is 2-D, axis 0/1), and its max
  * backward needs a zero-fill pass before it (ops/reduce_cuda.py:409-414). */

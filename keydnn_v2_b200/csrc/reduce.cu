@@ -1024,3 +1024,95 @@ int sum_to_shape(const T* x, T* y, const int64_t* in_shape, const int64_t* out_s
 KD_REDUCE(float, f32)
 KD_REDUCE(double, f64)
 
+// ---------------------------------------------------------------------------
+// Column sums without any device allocation
+// ---------------------------------------------------------------------------
+// For callers that must not allocate device memory when they call in: code running inside a
+// framework that owns the whole device heap (its caching allocator has reserved the memory and a
+// stray cudaMalloc can fail or fragment it), latency-critical serving loops where an allocation
+// would stall every stream of the process, and processes that run under a fixed memory budget
+// checked at start-up.  The regular column-sum entry may grow the library's scratch buffer with
+// cudaMalloc the first time a shape needs it; this one never does: its partial sums and completion
+// tickets live in the file-scope array below, which every GPU that loads the library holds from
+// load to exit (kNoAllocCounterBytes + kNoAllocPartialBytes = 2,113,536 bytes).
+namespace {
+
+constexpr size_t kNoAllocCounterBytes = 16 * 1024;        // 4096 completion tickets
+constexpr size_t kNoAllocPartialBytes = size_t(2) << 20;  // per-chunk column partials
+constexpr int kNoAllocMaxCols = 65536;
+constexpr int kNoAllocTooLarge = -20;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocCounterBytes + kNoAllocPartialBytes];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not a device address; the
+// address the kernel needs comes from cudaGetSymbolAddress, once per device, with that device current.
+struct NoAllocDevice {
+    bool ready = false;
+    unsigned char* base = nullptr;
+};
+NoAllocDevice g_noalloc_device[16];
+
+int noalloc_base(unsigned char** out) {
+    int dev = -1;
+    cudaError_t st = cudaGetDevice(&dev);
+    if (st != cudaSuccess) return static_cast<int>(st);
+    if (dev < 0 || dev >= 16) return static_cast<int>(cudaErrorInvalidDevice);
+    NoAllocDevice& d = g_noalloc_device[dev];
+    if (!d.ready) {
+        void* p = nullptr;
+        st = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (st != cudaSuccess) return static_cast<int>(st);
+        if (!p) return static_cast<int>(cudaErrorInvalidSymbol);
+        d.base = static_cast<unsigned char*>(p);
+        d.ready = true;
+    }
+    *out = d.base;
+    return 0;
+}
+
+template <int V>
+int noalloc_sum_cols(const float* x, float* y, int rows, int cols, unsigned char* base) {
+    const int stripes = (cols + 32 * V - 1) / (32 * V);
+    if (static_cast<size_t>(stripes) * sizeof(unsigned int) > kNoAllocCounterBytes) return kNoAllocTooLarge;
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, sum_cols_kernel<float, V>, kThreads, 0) != cudaSuccess || occ < 1)
+        occ = 1;
+    int rch = pick_row_chunk(rows, stripes, occ);
+    // fewer, taller chunks until the partials fit the static array
+    while (static_cast<size_t>((rows + rch - 1) / rch) * cols * sizeof(float) > kNoAllocPartialBytes) rch *= 2;
+    const int nchunks = (rows + rch - 1) / rch;
+    if (nchunks > 65535) return kNoAllocTooLarge;
+    unsigned int* counters = reinterpret_cast<unsigned int*>(base);
+    float* partials = reinterpret_cast<float*>(base + kNoAllocCounterBytes);
+    cudaStream_t s = kd::stream();
+    // the array keeps whatever the previous call left: tickets must start at zero
+    cudaError_t st = cudaMemsetAsync(counters, 0, static_cast<size_t>(stripes) * sizeof(unsigned int), s);
+    if (st != cudaSuccess) return static_cast<int>(st);
+    sum_cols_kernel<float, V><<<dim3(stripes, nchunks), kThreads, 0, s>>>(x, y, rows, cols, rch, partials, counters, 1.0f,
+                                                                       false);
+    return kd::launch_status();
+}
+
+}  // namespace
+
+// y[c] = sum over r of x[r, c] for a dense row-major float32 (rows, cols) matrix, same result
+// contract as keydnn_cuda_sum_axis2d_forward_f32(x, y, rows, cols, 0), but this call allocates
+// nothing: no cudaMalloc / cudaFree, no allocating library routine.
+//   * limits: cols <= 65,536 (KEYDNN_NOALLOC_MAX_COLS); larger returns -20 and launches nothing.
+//   * the first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+//     that first call outside any stream capture.
+//   * every call uses the same array: calls that overlap on the GPU (two streams, two host
+//     threads) race on it.  Calls on the library's one stream are ordered and safe.
+KD_API int keydnn_cuda_sum_axis0_noalloc_f32(const float* x, float* y, int rows, int cols) {
+    if (!x || !y) return -1;
+    if (rows <= 0 || cols <= 0) return -2;
+    if (cols > kNoAllocMaxCols) return kNoAllocTooLarge;
+    unsigned char* base = nullptr;
+    const int st = noalloc_base(&base);
+    if (st != 0) return st;
+    (void)cudaGetLastError();
+    const int V = col_vector_width<float>(x, cols);
+    if (V == 8) return noalloc_sum_cols<8>(x, y, rows, cols, base);
+    if (V == 4) return noalloc_sum_cols<4>(x, y, rows, cols, base);
+    return noalloc_sum_cols<1>(x, y, rows, cols, base);
+}
