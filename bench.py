@@ -260,10 +260,15 @@ def run_ours(args) -> None:
     launches = [0]
 
     def step() -> None:
-        for red, _ in reducers:
-            for op, ax in OPS:
+        # the two matrices are independent: their kernels alternate, so the exchange of one
+        # matrix's partials (second stream) runs under the other matrix's kernel
+        for op, ax in OPS:
+            for red, _ in reducers:
                 red.forward(op, ax)
+            for red, _ in reducers:
                 red.backward(op, ax)
+        for red, _ in reducers:
+            red.finish()                 # the step ends when its collectives have landed
         launches[0] += 2 * len(OPS) * len(reducers)
 
     def barrier() -> None:
@@ -317,6 +322,7 @@ def run_ours(args) -> None:
             for op, ax in OPS:
                 ptr, n = red.forward(op, ax)
                 red.backward(op, ax)
+                red.wait(op, ax)
                 nb = n * red.dt.itemsize
                 lib.call("keydnn_cuda_memcpy_d2h", host_out[id(red)].ctypes.data, ptr, nb)
                 d2h[0] += nb

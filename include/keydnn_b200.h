@@ -57,6 +57,7 @@ int keydnn_cuda_stream_synchronize(void);
 int keydnn_cuda_event_create(uint64_t* out);
 int keydnn_cuda_event_record(uint64_t ev);
 int keydnn_cuda_event_synchronize(uint64_t ev);
+int keydnn_cuda_stream_wait_event(uint64_t ev); /* later work on the library stream waits for ev */
 int keydnn_cuda_event_elapsed_ms(uint64_t start, uint64_t stop, float* out_ms);
 int keydnn_cuda_event_destroy(uint64_t ev);
 int keydnn_cuda_device_count(int* out);
@@ -286,13 +287,16 @@ int keydnn_nccl_allreduce_sum_f32(float* buf, int64_t count);  /* in place */
 int keydnn_nccl_allreduce_sum_f64(double* buf, int64_t count);
 int keydnn_nccl_allgather(const void* send, void* recv, int64_t nbytes);
 int keydnn_nccl_broadcast(void* buf, int64_t nbytes, int root);
-/* Winner per column among `world` per-rank (value, local position) maxima gathered rank-major:
- * greater value, else lower rank; global position = rank*span + local; out_local is the position
- * inside this rank's shard or -1 when another rank owns the maximum. */
+/* Winner per column among `world` per-rank (value, local position) maxima; rank r's n values start at
+ * vals + r*val_stride and its n positions at idx + r*idx_stride (strides in elements, so both can live
+ * in one gathered block per rank): greater value, else lower rank; global position = rank*span + local;
+ * out_local is the position inside this rank's shard or -1 when another rank owns the maximum. */
 int keydnn_cuda_argmax_select_f32(const float* vals, const int64_t* idx, int world, int rank, int64_t span, int64_t n,
-                                  float* out_val, int64_t* out_global, int64_t* out_local);
+                                  int64_t val_stride, int64_t idx_stride, float* out_val, int64_t* out_global,
+                                  int64_t* out_local);
 int keydnn_cuda_argmax_select_f64(const double* vals, const int64_t* idx, int world, int rank, int64_t span, int64_t n,
-                                  double* out_val, int64_t* out_global, int64_t* out_local);
+                                  int64_t val_stride, int64_t idx_stride, double* out_val, int64_t* out_global,
+                                  int64_t* out_local);
 
 #ifdef __cplusplus
 }

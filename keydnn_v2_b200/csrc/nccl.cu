@@ -54,13 +54,15 @@ bool load_api() {
     return true;
 }
 
-// Picks, per column, the winner among `world` per-rank maxima: greater value wins,
+// Picks, per column, the winner among `world` per-rank maxima (rank r's values start at
+// vals + r*val_stride, its positions at idx + r*idx_stride, strides in elements): greater value wins,
 // equal values keep the lower rank (= the smaller global row), and a column whose
 // maximum is -inf keeps global position 0, the single-GPU rule.  `local_idx`
 // receives the position inside this rank's shard, or -1 when another rank owns it.
 template <typename T>
 __global__ void argmax_select_kernel(const T* __restrict__ vals, const long long* __restrict__ idx, int world, int rank,
-                                     long long span, int64_t n, T* __restrict__ out_val,
+                                     long long span, int64_t n, int64_t val_stride, int64_t idx_stride,
+                                     T* __restrict__ out_val,
                                      long long* __restrict__ out_global, long long* __restrict__ out_local) {
     for (int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < n;
          c += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -68,8 +70,8 @@ __global__ void argmax_select_kernel(const T* __restrict__ vals, const long long
         long long g = 0;
         int owner = 0;
         for (int r = 0; r < world; ++r) {
-            const T v = vals[static_cast<int64_t>(r) * n + c];
-            if (v > best) { best = v; g = static_cast<long long>(r) * span + idx[static_cast<int64_t>(r) * n + c]; owner = r; }
+            const T v = vals[r * val_stride + c];
+            if (v > best) { best = v; g = static_cast<long long>(r) * span + idx[r * idx_stride + c]; owner = r; }
         }
         out_val[c] = best;
         out_global[c] = g;
@@ -78,13 +80,14 @@ __global__ void argmax_select_kernel(const T* __restrict__ vals, const long long
 }
 
 template <typename T>
-int argmax_select(const T* vals, const long long* idx, int world, int rank, long long span, int64_t n, T* out_val,
-                  long long* out_global, long long* out_local) {
+int argmax_select(const T* vals, const long long* idx, int world, int rank, long long span, int64_t n,
+                  int64_t val_stride, int64_t idx_stride, T* out_val, long long* out_global, long long* out_local) {
     if (!vals || !idx || !out_val || !out_global || !out_local) return -1;
-    if (world <= 0 || rank < 0 || rank >= world || n <= 0) return -2;
+    if (world <= 0 || rank < 0 || rank >= world || n <= 0 || val_stride < n || idx_stride < n) return -2;
     (void)cudaGetLastError();
     const unsigned grid = kd::grid_for((n + 255) / 256, 8);
-    argmax_select_kernel<T><<<grid, 256, 0, kd::stream()>>>(vals, idx, world, rank, span, n, out_val, out_global, out_local);
+    argmax_select_kernel<T><<<grid, 256, 0, kd::stream()>>>(vals, idx, world, rank, span, n, val_stride, idx_stride, out_val,
+                                                          out_global, out_local);
     return kd::launch_status();
 }
 
@@ -152,12 +155,16 @@ KD_API int keydnn_nccl_broadcast(void* buf, int64_t nbytes, int root) {
 }
 
 KD_API int keydnn_cuda_argmax_select_f32(const float* vals, const int64_t* idx, int world, int rank, int64_t span,
-                                         int64_t n, float* out_val, int64_t* out_global, int64_t* out_local) {
-    return argmax_select<float>(vals, reinterpret_cast<const long long*>(idx), world, rank, span, n, out_val,
+                                         int64_t n, int64_t val_stride, int64_t idx_stride, float* out_val,
+                                         int64_t* out_global, int64_t* out_local) {
+    return argmax_select<float>(vals, reinterpret_cast<const long long*>(idx), world, rank, span, n, val_stride,
+                              idx_stride, out_val,
                                 reinterpret_cast<long long*>(out_global), reinterpret_cast<long long*>(out_local));
 }
 KD_API int keydnn_cuda_argmax_select_f64(const double* vals, const int64_t* idx, int world, int rank, int64_t span,
-                                         int64_t n, double* out_val, int64_t* out_global, int64_t* out_local) {
-    return argmax_select<double>(vals, reinterpret_cast<const long long*>(idx), world, rank, span, n, out_val,
+                                         int64_t n, int64_t val_stride, int64_t idx_stride, double* out_val,
+                                         int64_t* out_global, int64_t* out_local) {
+    return argmax_select<double>(vals, reinterpret_cast<const long long*>(idx), world, rank, span, n, val_stride,
+                              idx_stride, out_val,
                                  reinterpret_cast<long long*>(out_global), reinterpret_cast<long long*>(out_local));
 }

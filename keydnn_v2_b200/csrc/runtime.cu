@@ -334,6 +334,10 @@ KD_API int keydnn_cuda_event_create(std::uint64_t* out) {
 KD_API int keydnn_cuda_event_record(std::uint64_t ev) {
     return kd::status(cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev), g_stream));
 }
+// Work enqueued on the library stream after this call starts only once `ev` has completed.
+KD_API int keydnn_cuda_stream_wait_event(std::uint64_t ev) {
+    return kd::status(cudaStreamWaitEvent(g_stream, reinterpret_cast<cudaEvent_t>(ev), 0));
+}
 KD_API int keydnn_cuda_event_synchronize(std::uint64_t ev) {
     return kd::status(cudaEventSynchronize(reinterpret_cast<cudaEvent_t>(ev)));
 }

@@ -1,0 +1,45 @@
+"""One rank of the row-sharded reduction check (spawned by test_multi_gpu.py).
+
+usage: python _sharded_worker.py RANK WORLD ID_FILE OUT_DIR
+Each rank owns rows [rank*R, (rank+1)*R) of a seeded global matrix, runs every reduction forward +
+backward through ShardedReductions (NCCL inside the library, id exchanged through a file), and writes
+its results; the parent compares them with NumPy on the whole matrix."""
+import sys
+from pathlib import Path
+
+import numpy as np
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+
+def main() -> None:
+    rank, world, id_file, out_dir = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], Path(sys.argv[4])
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import distributed
+    from keydnn_v2_b200.sharded import ShardedReductions
+
+    group = distributed.init_from_file(id_file, rank, world, device=rank, timeout_s=120)
+    res = {}
+    for tag, dt, R, C in (("f32", np.float32, 96, 520), ("f64", np.float64, 40, 264)):
+        full = np.random.default_rng(5).standard_normal((R * world, C))
+        full = (np.round(full * 4) / 4).astype(dt)          # ties across ranks: the lower rank must win
+        full[3, 7] = full[R * world - 2, 7] = 9.0            # same maximum on the first and the last rank
+        shard = np.ascontiguousarray(full[rank * R:(rank + 1) * R])
+        red = ShardedReductions(kd.Tensor.from_numpy(shard), group)
+        for op in ("sum", "mean", "max"):
+            for ax in (0, 1, None):
+                ptr, n = red.forward(op, ax)
+                red.wait(op, ax)
+                out = np.empty(n, dt)
+                red.lib.call("keydnn_cuda_memcpy_d2h", out.ctypes.data, ptr, out.nbytes)
+                gx_ptr = red.backward(op, ax)
+                gx = np.empty((R, C), dt)
+                red.lib.call("keydnn_cuda_memcpy_d2h", gx.ctypes.data, gx_ptr, gx.nbytes)
+                res[f"{tag}/{op}/{ax}/y"] = out
+                res[f"{tag}/{op}/{ax}/gx"] = gx
+    np.savez(out_dir / f"rank{rank}.npz", **res)
+    group.destroy()
+
+
+if __name__ == "__main__":
+    main()

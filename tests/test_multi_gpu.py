@@ -1,0 +1,75 @@
+"""Row-sharded reductions on 2+ GPUs of one box: one process per GPU, NCCL inside the library.
+Skipped on a single-GPU box (the 1-GPU path of the same code is covered by bench.py and smoke)."""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = Path(__file__).resolve().parent
+
+
+def _device_count() -> int:
+    import ctypes
+
+    from keydnn_v2_b200 import load
+
+    n = ctypes.c_int(0)
+    load().call("keydnn_cuda_device_count", ctypes.byref(n))
+    return n.value
+
+
+def test_sharded_reductions_match_numpy_on_the_whole_matrix(tmp_path):
+    world = min(_device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, str(HERE / "_sharded_worker.py"), str(r), str(world),
+                               str(tmp_path / "nccl_id"), str(tmp_path)], env=env) for r in range(world)]
+    try:
+        codes = [p.wait(timeout=300) for p in procs]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+    assert codes == [0] * world
+    res = [dict(np.load(tmp_path / f"rank{r}.npz")) for r in range(world)]
+    for tag, dt, R, C in (("f32", np.float32, 96, 520), ("f64", np.float64, 40, 264)):
+        full = np.random.default_rng(5).standard_normal((R * world, C))
+        full = (np.round(full * 4) / 4).astype(dt)
+        full[3, 7] = full[R * world - 2, 7] = 9.0
+        tol = dict(rtol=1e-5, atol=1e-5) if dt == np.float32 else dict(rtol=1e-12, atol=1e-12)
+        f64 = full.astype(np.float64)
+        for ax in (0, 1, None):
+            for r in range(world):
+                rows = slice(r * R, (r + 1) * R)
+                ys, ym, yx = (res[r][f"{tag}/{op}/{ax}/y"] for op in ("sum", "mean", "max"))
+                gs, gm, gxm = (res[r][f"{tag}/{op}/{ax}/gx"] for op in ("sum", "mean", "max"))
+                if ax == 1:
+                    np.testing.assert_allclose(ys, f64[rows].sum(1), **tol)
+                    np.testing.assert_allclose(ym, f64[rows].mean(1), **tol)
+                    np.testing.assert_array_equal(yx, full[rows].max(1))
+                    want = np.zeros((R, C), dt)
+                    want[np.arange(R), full[rows].argmax(1)] = 1
+                    np.testing.assert_array_equal(gxm, want)
+                    np.testing.assert_allclose(gm, np.full((R, C), 1.0 / C), **tol)
+                else:
+                    axis = 0 if ax == 0 else None
+                    np.testing.assert_allclose(ys, np.atleast_1d(f64.sum(axis)), **tol)
+                    np.testing.assert_allclose(ym, np.atleast_1d(f64.mean(axis)), **tol)
+                    np.testing.assert_array_equal(yx, np.atleast_1d(full.max(axis)))
+                    want = np.zeros_like(full)
+                    if ax == 0:
+                        want[full.argmax(0), np.arange(C)] = 1       # first (lowest-rank) maximum only
+                        n = R * world
+                    else:
+                        want.reshape(-1)[full.argmax()] = 1
+                        n = full.size
+                    np.testing.assert_array_equal(gxm, want[rows])
+                    np.testing.assert_allclose(gm, np.full((R, C), 1.0 / n), **tol)
+                np.testing.assert_array_equal(gs, np.ones((R, C), dt))
