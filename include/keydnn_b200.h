@@ -274,6 +274,27 @@ int keydnn_cuda_transpose2d_f32(const float* x, float* y, int rows, int cols);
 int keydnn_cuda_transpose2d_f64(const double* x, double* y, int rows, int cols);
 
 /* ------------------------------------------------------------------------- */
+/* BatchNorm2d (additive).  The reference composes the layer from ~25 tensor-op launches and
+ * rejects CUDA tensors (src/keydnn/infrastructure/layers/_batchnorm.py:543-544, body :562-700);
+ * these entries run the same formulas in two kernels per direction.  x, y, grad_* are
+ * (N, C, HW) contiguous; gamma/beta (both or neither) may be NULL; mean / invstd receive the
+ * statistics used (saved for backward); training != 0 uses batch statistics and updates
+ * running_mean / running_var (may be NULL) with `momentum`. */
+/* ------------------------------------------------------------------------- */
+int keydnn_cuda_bn2d_forward_f32(const float* x, const float* gamma, const float* beta, float* y, float* mean,
+                                 float* invstd, float* running_mean, float* running_var, int N, int C, int64_t HW,
+                                 float eps, float momentum, int training);
+int keydnn_cuda_bn2d_forward_f64(const double* x, const double* gamma, const double* beta, double* y, double* mean,
+                                 double* invstd, double* running_mean, double* running_var, int N, int C, int64_t HW,
+                                 double eps, double momentum, int training);
+int keydnn_cuda_bn2d_backward_f32(const float* x, const float* gamma, const float* grad_out, const float* mean,
+                                  const float* invstd, float* grad_x, float* grad_gamma, float* grad_beta, int N, int C,
+                                  int64_t HW);
+int keydnn_cuda_bn2d_backward_f64(const double* x, const double* gamma, const double* grad_out, const double* mean,
+                                  const double* invstd, double* grad_x, double* grad_gamma, double* grad_beta, int N,
+                                  int C, int64_t HW);
+
+/* ------------------------------------------------------------------------- */
 /* Multi-GPU (additive; the reference has no distributed code).  One process   */
 /* per GPU; NCCL is opened with dlopen at first use; collectives run on the    */
 /* library stream.  Status: -10 not initialised, -11 NCCL not loadable,        */

@@ -20,6 +20,8 @@ from typing import Callable, Dict, List, Tuple
 PKG_DIR = Path(__file__).resolve().parent
 HEADER_PATH = PKG_DIR.parent / "include" / "keydnn_b200.h"
 DEFAULT_LIB_PATH = PKG_DIR / "lib" / "libkeydnn_b200.so"
+DNN_HEADER_PATH = PKG_DIR.parent / "include" / "keydnn_b200_dnn.h"
+DNN_LIB_PATH = PKG_DIR / "lib" / "libkeydnn_b200_dnn.so"
 
 
 class NativeLibraryError(RuntimeError):
@@ -69,7 +71,7 @@ def parse_header(path: Path = HEADER_PATH) -> Dict[str, Tuple[object, List[objec
 class Native:
     """Handle to the loaded library; ``native.call("keydnn_cuda_add_f32", a, b, y, n)``."""
 
-    def __init__(self, path: Path, strict: bool = True):
+    def __init__(self, path: Path, strict: bool = True, header: Path = HEADER_PATH):
         self.path = Path(path)
         if not self.path.exists():
             raise NativeLibraryError(
@@ -77,7 +79,7 @@ class Native:
                 "(there is no CPU fallback for the CUDA path)"
             )
         self.lib = ctypes.CDLL(str(self.path))
-        self.signatures = parse_header()
+        self.signatures = parse_header(header)
         self._fn: Dict[str, Callable] = {}
         missing = []
         for name, (restype, argtypes, _) in self.signatures.items():
@@ -115,6 +117,12 @@ class Native:
 @lru_cache(maxsize=4)
 def _load(path: str) -> Native:
     return Native(Path(path))
+
+
+@lru_cache(maxsize=1)
+def load_dnn() -> Native:
+    """The cuBLAS / cuDNN wrapper library (Conv2d, Linear); needs libcudnn / libcublas at load time."""
+    return Native(Path(os.environ.get("KEYDNN_B200_DNN_LIB") or DNN_LIB_PATH), header=DNN_HEADER_PATH)
 
 
 def load(path: str | os.PathLike | None = None) -> Native:

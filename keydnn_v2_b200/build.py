@@ -19,6 +19,8 @@ CSRC = PKG_DIR / "csrc"
 OBJ_DIR = PKG_DIR / "build"
 LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libkeydnn_b200.so"
+DNN_SRC = PKG_DIR / "csrc_dnn" / "dnn.cu"
+DNN_LIB_PATH = LIB_DIR / "libkeydnn_b200_dnn.so"
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = [
@@ -88,6 +90,22 @@ def build_native(force: bool = False, verbose: bool = False, ptxas_info: bool = 
     return LIB_PATH
 
 
+def build_dnn(force: bool = False, verbose: bool = False) -> Path:
+    """The cuBLAS / cuDNN wrapper library (Linear and Conv2d stay library calls)."""
+    LIB_DIR.mkdir(exist_ok=True)
+    if not force and _newer(DNN_LIB_PATH, [DNN_SRC, Path(__file__)]):
+        return DNN_LIB_PATH
+    cmd = [_nvcc(), *ARCH_FLAGS, "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler",
+           "-fvisibility=hidden", "-shared", str(DNN_SRC), "-o", str(DNN_LIB_PATH), "-lcudnn", "-lcublas"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {DNN_SRC.name}:\n{r.stdout}\n{r.stderr}")
+    return DNN_LIB_PATH
+
+
 if __name__ == "__main__":
+    print(build_dnn(force="--force" in sys.argv, verbose=True))
     p = build_native(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv)
     print(p)

@@ -1,0 +1,319 @@
+// BatchNorm2d on (N, C, H, W) tensors, training and inference, forward and backward.
+//
+// The reference composes BatchNorm2d from ~25 tensor-op launches (two sum_to_shape, four
+// broadcast_to, sub, mul, add, a host-side sqrt, ...) and refuses CUDA tensors altogether
+// (src/keydnn/infrastructure/layers/_batchnorm.py:543-544; body :562-700).  Here the layer is
+// four kernels with the same formulas:
+//   forward   stats : per-channel sum and sum of squares in double -> mean, biased variance,
+//                     inv_std = 1 / sqrt(var + eps) and the running-average update
+//                     running = running * (1 - momentum) + batch * momentum          (:46-83)
+//             apply : y = gamma * ((x - mean) * inv_std) + beta                      (:590-600)
+//   backward  reduce: sum(g), sum(g * x_hat) per channel  (= dbeta, dgamma)
+//             apply : dx = (1/m) * inv_std * (m*dxhat - sum(dxhat) - x_hat * sum(dxhat*x_hat)),
+//                     dxhat = g * gamma                                               (:640-655)
+// x_hat is recomputed from x, mean and inv_std instead of being stored.
+// No counterpart in the reference's CUDA library (additive entries).
+#include "common.cuh"
+
+namespace {
+
+using kd::Pack4;
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+__device__ __forceinline__ bool bn_take_ticket(unsigned int* counter, unsigned int expected) {
+    __shared__ bool last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = (atomicAdd(counter, 1u) == expected - 1);
+    __syncthreads();
+    if (last) __threadfence();
+    return last;
+}
+
+// Two sums per channel over the (n, hw) extent.  F(v, w) maps an element of the first (and
+// second) tensor to the two summands.  grid = (C, slices); slice s owns images [s*ach, ...).
+// MODE 0: s0 = sum x, s1 = sum x*x.   MODE 1: s0 = sum g, s1 = sum g * x_hat.
+template <typename T, int MODE, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ mean,
+                const T* __restrict__ invstd, int N, int C, int64_t HW, int ach, double* partials,
+                unsigned int* counters, double* sums /* [2][C] */) {
+    __shared__ double sm[kWarps];
+    const int c = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
+    const int n_begin = slice * ach;
+    const int n_end = min(N, n_begin + ach);
+    T mu = T(0), is = T(0);
+    if (MODE == 1) { mu = __ldg(mean + c); is = __ldg(invstd + c); }
+    double a0 = 0.0, a1 = 0.0;
+    for (int n = n_begin; n < n_end; ++n) {
+        const int64_t base = (static_cast<int64_t>(n) * C + c) * HW;
+        T p0 = T(0), p1 = T(0), q0 = T(0), q1 = T(0);      // short per-image partials in T
+        if (VEC) {
+            const int64_t b4 = HW >> 2;
+            for (int64_t p = threadIdx.x; p < b4; p += kThreads) {
+                const Pack4<T> vx = kd::load4_stream(x + base + 4 * p);
+                if (MODE == 0) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (k & 1) { p1 += vx.v[k]; q1 += vx.v[k] * vx.v[k]; }
+                        else { p0 += vx.v[k]; q0 += vx.v[k] * vx.v[k]; }
+                    }
+                } else {
+                    const Pack4<T> vg = kd::load4_stream(g + base + 4 * p);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const T xh = (vx.v[k] - mu) * is;
+                        if (k & 1) { p1 += vg.v[k]; q1 += vg.v[k] * xh; }
+                        else { p0 += vg.v[k]; q0 += vg.v[k] * xh; }
+                    }
+                }
+            }
+        } else {
+            for (int64_t b = threadIdx.x; b < HW; b += kThreads) {
+                const T vx = x[base + b];
+                if (MODE == 0) { p0 += vx; q0 += vx * vx; }
+                else { const T vg = g[base + b]; p0 += vg; q0 += vg * ((vx - mu) * is); }
+            }
+        }
+        a0 += static_cast<double>(p0) + static_cast<double>(p1);
+        a1 += static_cast<double>(q0) + static_cast<double>(q1);
+    }
+    a0 = kd::block_sum(a0, sm);
+    a1 = kd::block_sum(a1, sm);
+    if (threadIdx.x == 0) {
+        partials[(static_cast<int64_t>(slice) * C + c) * 2 + 0] = a0;
+        partials[(static_cast<int64_t>(slice) * C + c) * 2 + 1] = a1;
+    }
+    if (bn_take_ticket(counters + c, nslices)) {
+        double v0 = 0.0, v1 = 0.0;
+        for (int q = threadIdx.x; q < nslices; q += kThreads) {
+            v0 += __ldcg(partials + (static_cast<int64_t>(q) * C + c) * 2 + 0);
+            v1 += __ldcg(partials + (static_cast<int64_t>(q) * C + c) * 2 + 1);
+        }
+        v0 = kd::block_sum(v0, sm);
+        v1 = kd::block_sum(v1, sm);
+        if (threadIdx.x == 0) {
+            sums[c] = v0;
+            sums[C + c] = v1;
+            counters[c] = 0u;
+        }
+    }
+}
+
+// mean, biased variance, inv_std and the running averages, one thread per channel.
+template <typename T>
+__global__ void bn_finalize_stats(const double* __restrict__ sums, int C, double m, T eps, T momentum, T* mean, T* var,
+                                  T* invstd, T* running_mean, T* running_var) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const double mu = sums[c] / m;
+    double v = sums[C + c] / m - mu * mu;
+    if (v < 0.0) v = 0.0;
+    const T mu_t = static_cast<T>(mu), v_t = static_cast<T>(v);
+    mean[c] = mu_t;
+    if (var) var[c] = v_t;
+    invstd[c] = T(1) / sqrt(v_t + eps);
+    if (running_mean) running_mean[c] = running_mean[c] * (T(1) - momentum) + mu_t * momentum;
+    if (running_var) running_var[c] = running_var[c] * (T(1) - momentum) + v_t * momentum;
+}
+
+template <typename T>
+__global__ void bn_invstd_from_var(const T* __restrict__ var, int C, T eps, T* invstd) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < C) invstd[c] = T(1) / sqrt(var[c] + eps);
+}
+
+// y = gamma * ((x - mean) * inv_std) + beta.  blockIdx.x walks (n, c) rows of HW elements,
+// blockIdx.y splits a row.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+bn_apply_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+             const T* __restrict__ mean, const T* __restrict__ invstd, T* __restrict__ y, int64_t rows, int C, int64_t HW) {
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const int c = static_cast<int>(r % C);
+        const T mu = __ldg(mean + c), is = __ldg(invstd + c);
+        const T ga = gamma ? __ldg(gamma + c) : T(1), be = beta ? __ldg(beta + c) : T(0);
+        const bool affine = gamma != nullptr;
+        const T* src = x + r * HW;
+        T* dst = y + r * HW;
+        if (VEC) {
+            const int64_t b4 = HW >> 2;
+            for (int64_t p = static_cast<int64_t>(blockIdx.y) * kThreads + threadIdx.x; p < b4;
+                 p += static_cast<int64_t>(gridDim.y) * kThreads) {
+                Pack4<T> v = kd::load4_stream(src + 4 * p);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const T xh = (v.v[k] - mu) * is;
+                    v.v[k] = affine ? ga * xh + be : xh;
+                }
+                kd::store4(dst + 4 * p, v);
+            }
+        } else {
+            for (int64_t b = static_cast<int64_t>(blockIdx.y) * kThreads + threadIdx.x; b < HW;
+                 b += static_cast<int64_t>(gridDim.y) * kThreads) {
+                const T xh = (src[b] - mu) * is;
+                dst[b] = affine ? ga * xh + be : xh;
+            }
+        }
+    }
+}
+
+// dx = (1/m) * inv_std * (m*dxhat - sum_dxhat - x_hat * sum_dxhat_xhat), dxhat = g * gamma;
+// sums[c] = sum g, sums[C + c] = sum g * x_hat (so sum_dxhat = gamma * sums[c], ...).
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ gamma,
+             const T* __restrict__ mean, const T* __restrict__ invstd, const double* __restrict__ sums,
+             T* __restrict__ dx, int64_t rows, int C, int64_t HW, T m) {
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const int c = static_cast<int>(r % C);
+        const T mu = __ldg(mean + c), is = __ldg(invstd + c);
+        const T ga = gamma ? __ldg(gamma + c) : T(1);
+        const T s1 = static_cast<T>(sums[c]) * ga;
+        const T s2 = static_cast<T>(sums[C + c]) * ga;
+        const T k0 = (T(1) / m) * is;
+        const T* xs = x + r * HW;
+        const T* gs = g + r * HW;
+        T* dst = dx + r * HW;
+        if (VEC) {
+            const int64_t b4 = HW >> 2;
+            for (int64_t p = static_cast<int64_t>(blockIdx.y) * kThreads + threadIdx.x; p < b4;
+                 p += static_cast<int64_t>(gridDim.y) * kThreads) {
+                const Pack4<T> vx = kd::load4_stream(xs + 4 * p);
+                const Pack4<T> vg = kd::load4_stream(gs + 4 * p);
+                Pack4<T> out;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const T xh = (vx.v[k] - mu) * is;
+                    out.v[k] = k0 * (m * (vg.v[k] * ga) - s1 - xh * s2);
+                }
+                kd::store4(dst + 4 * p, out);
+            }
+        } else {
+            for (int64_t b = static_cast<int64_t>(blockIdx.y) * kThreads + threadIdx.x; b < HW;
+                 b += static_cast<int64_t>(gridDim.y) * kThreads) {
+                const T xh = (xs[b] - mu) * is;
+                dst[b] = k0 * (m * (gs[b] * ga) - s1 - xh * s2);
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void bn_param_grads(const double* __restrict__ sums, int C, T* dgamma, T* dbeta) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    if (dbeta) dbeta[c] = static_cast<T>(sums[c]);
+    if (dgamma) dgamma[c] = static_cast<T>(sums[C + c]);
+}
+
+struct SumsPlan {
+    int nslices, ach;
+    double* partials;
+    unsigned int* counters;
+    double* sums;
+};
+
+// scratch layout: [2*C doubles of sums][nslices*C*2 doubles of partials]
+inline bool plan_sums(int N, int C, SumsPlan& p) {
+    int nslices = static_cast<int>((static_cast<int64_t>(kd::sm_count()) * 8 + C - 1) / C);
+    if (nslices > N) nslices = N;
+    if (nslices < 1) nslices = 1;
+    p.ach = (N + nslices - 1) / nslices;
+    p.nslices = (N + p.ach - 1) / p.ach;
+    double* buf = static_cast<double*>(kd::scratch((static_cast<size_t>(p.nslices) + 1) * C * 2 * sizeof(double)));
+    p.counters = kd::counters(C);
+    if (!buf || !p.counters) return false;
+    p.sums = buf;
+    p.partials = buf + 2 * static_cast<size_t>(C);
+    return true;
+}
+
+inline dim3 row_grid(int64_t rows, int64_t HW) {
+    const int64_t cap = static_cast<int64_t>(kd::sm_count()) * 64;
+    const unsigned gx = static_cast<unsigned>(rows < cap ? rows : cap);
+    const int64_t per_row = (HW / 4 + kThreads - 1) / kThreads;
+    int64_t gy = (cap + gx - 1) / gx;
+    if (gy > per_row) gy = per_row;
+    if (gy < 1) gy = 1;
+    if (gy > 65535) gy = 65535;
+    return dim3(gx, static_cast<unsigned>(gy));
+}
+
+template <typename T>
+int bn_forward(const T* x, const T* gamma, const T* beta, T* y, T* mean, T* invstd, T* running_mean, T* running_var,
+               int N, int C, int64_t HW, T eps, T momentum, int training) {
+    if (!x || !y || !mean || !invstd) return -1;
+    if (N <= 0 || C <= 0 || HW <= 0) return -2;
+    if ((gamma == nullptr) != (beta == nullptr)) return -3;
+    if (!training && (!running_mean || !running_var)) return -4;
+    (void)cudaGetLastError();
+    cudaStream_t s = kd::stream();
+    const bool vec = kd::aligned_pack<T>(x) && kd::aligned_pack<T>(y) && (HW % 4 == 0);
+    const T* use_mean = mean;
+    if (training) {
+        SumsPlan p;
+        if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
+        dim3 grid(C, p.nslices);
+        if (vec) bn_channel_sums<T, 0, true><<<grid, kThreads, 0, s>>>(x, nullptr, nullptr, nullptr, N, C, HW, p.ach, p.partials, p.counters, p.sums);
+        else bn_channel_sums<T, 0, false><<<grid, kThreads, 0, s>>>(x, nullptr, nullptr, nullptr, N, C, HW, p.ach, p.partials, p.counters, p.sums);
+        bn_finalize_stats<T><<<(C + 127) / 128, 128, 0, s>>>(p.sums, C, static_cast<double>(N) * static_cast<double>(HW), eps,
+                                                          momentum, mean, static_cast<T*>(nullptr), invstd, running_mean,
+                                                          running_var);
+    } else {
+        bn_invstd_from_var<T><<<(C + 127) / 128, 128, 0, s>>>(running_var, C, eps, invstd);
+        cudaMemcpyAsync(mean, running_mean, C * sizeof(T), cudaMemcpyDeviceToDevice, s);
+    }
+    const int64_t rows = static_cast<int64_t>(N) * C;
+    const dim3 g2 = row_grid(rows, HW);
+    if (vec) bn_apply_fwd<T, true><<<g2, kThreads, 0, s>>>(x, gamma, beta, use_mean, invstd, y, rows, C, HW);
+    else bn_apply_fwd<T, false><<<g2, kThreads, 0, s>>>(x, gamma, beta, use_mean, invstd, y, rows, C, HW);
+    return kd::launch_status();
+}
+
+template <typename T>
+int bn_backward(const T* x, const T* gamma, const T* go, const T* mean, const T* invstd, T* dx, T* dgamma, T* dbeta, int N,
+                int C, int64_t HW) {
+    if (!x || !go || !mean || !invstd || !dx) return -1;
+    if (N <= 0 || C <= 0 || HW <= 0) return -2;
+    (void)cudaGetLastError();
+    cudaStream_t s = kd::stream();
+    const bool vec = kd::aligned_pack<T>(x) && kd::aligned_pack<T>(go) && kd::aligned_pack<T>(dx) && (HW % 4 == 0);
+    SumsPlan p;
+    if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
+    dim3 grid(C, p.nslices);
+    if (vec) bn_channel_sums<T, 1, true><<<grid, kThreads, 0, s>>>(x, go, mean, invstd, N, C, HW, p.ach, p.partials, p.counters, p.sums);
+    else bn_channel_sums<T, 1, false><<<grid, kThreads, 0, s>>>(x, go, mean, invstd, N, C, HW, p.ach, p.partials, p.counters, p.sums);
+    if (dgamma || dbeta) bn_param_grads<T><<<(C + 127) / 128, 128, 0, s>>>(p.sums, C, dgamma, dbeta);
+    const int64_t rows = static_cast<int64_t>(N) * C;
+    const dim3 g2 = row_grid(rows, HW);
+    const T m = static_cast<T>(static_cast<double>(N) * static_cast<double>(HW));
+    if (vec) bn_apply_bwd<T, true><<<g2, kThreads, 0, s>>>(x, go, gamma, mean, invstd, p.sums, dx, rows, C, HW, m);
+    else bn_apply_bwd<T, false><<<g2, kThreads, 0, s>>>(x, go, gamma, mean, invstd, p.sums, dx, rows, C, HW, m);
+    return kd::launch_status();
+}
+
+}  // namespace
+
+KD_API int keydnn_cuda_bn2d_forward_f32(const float* x, const float* gamma, const float* beta, float* y, float* mean,
+                                        float* invstd, float* running_mean, float* running_var, int N, int C, int64_t HW,
+                                        float eps, float momentum, int training) {
+    return bn_forward<float>(x, gamma, beta, y, mean, invstd, running_mean, running_var, N, C, HW, eps, momentum, training);
+}
+KD_API int keydnn_cuda_bn2d_forward_f64(const double* x, const double* gamma, const double* beta, double* y, double* mean,
+                                        double* invstd, double* running_mean, double* running_var, int N, int C,
+                                        int64_t HW, double eps, double momentum, int training) {
+    return bn_forward<double>(x, gamma, beta, y, mean, invstd, running_mean, running_var, N, C, HW, eps, momentum, training);
+}
+KD_API int keydnn_cuda_bn2d_backward_f32(const float* x, const float* gamma, const float* grad_out, const float* mean,
+                                         const float* invstd, float* grad_x, float* grad_gamma, float* grad_beta, int N,
+                                         int C, int64_t HW) {
+    return bn_backward<float>(x, gamma, grad_out, mean, invstd, grad_x, grad_gamma, grad_beta, N, C, HW);
+}
+KD_API int keydnn_cuda_bn2d_backward_f64(const double* x, const double* gamma, const double* grad_out, const double* mean,
+                                         const double* invstd, double* grad_x, double* grad_gamma, double* grad_beta,
+                                         int N, int C, int64_t HW) {
+    return bn_backward<double>(x, gamma, grad_out, mean, invstd, grad_x, grad_gamma, grad_beta, N, C, HW);
+}

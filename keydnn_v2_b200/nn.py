@@ -1,0 +1,346 @@
+"""Layers, loss and optimizer of the small-CNN training step, on CUDA tensors.
+
+Host-side mirror of the reference modules that surround the pool / reduce / elementwise path in a
+CNN layer stack (paths under ``src/keydnn/infrastructure/``):
+  ``convolution/_conv2d_module.py`` + ``_conv2d_function.py``   Conv2d (cuDNN, kept a library call)
+  ``layers/_batchnorm.py:430-700``                              BatchNorm2d (CPU-only in the reference)
+  ``_activations.py`` / ``_function.py:291-293``                ReLU = (x > 0) mask, x * mask
+  ``flatten/``, ``fully_connected/_linear.py:283-291``          Flatten, Linear (cuBLAS + bias_add)
+  ``_losses.py:150-215``                                        MSE = mean((pred - target)^2)
+  ``optimizers/_sgd.py:119-140``                                SGD with coupled weight decay
+  ``models/_sequential.py:130-152``                             Sequential
+
+Same constructor arguments, parameter shapes, initialisers (NumPy global RNG, Kaiming normal =
+randn * sqrt(2 / fan_in), zeros for biases) and formulas.  What differs is where the work runs:
+everything stays on the device (no host round trip around cuDNN, no host sqrt in BatchNorm), the
+optimizer updates all parameters with one fused kernel over a flat buffer, and momentum (absent in
+the reference optimizer) is available.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Iterable, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from ._cuda_storage import CudaStorage
+from ._native import load_dnn
+from .pooling import GlobalAvgPool2d, MaxPool2d, _pair  # noqa: F401  (re-exported for model code)
+from .tensor import Context, Parameter, Tensor, _suffix, no_grad
+
+
+def _cfloat(dtype, v: float):
+    return ctypes.c_float(v) if np.dtype(dtype) == np.float32 else ctypes.c_double(v)
+
+
+class Module:
+    training = True
+
+    def parameters(self) -> List[Parameter]:
+        out: List[Parameter] = []
+        for v in self.__dict__.values():
+            if isinstance(v, Parameter):
+                out.append(v)
+            elif isinstance(v, Module):
+                out.extend(v.parameters())
+            elif isinstance(v, (list, tuple)):
+                for m in v:
+                    if isinstance(m, Module):
+                        out.extend(m.parameters())
+                    elif hasattr(m, "parameters") and not isinstance(m, Tensor):
+                        out.extend(m.parameters())
+        return out
+
+    def train(self, mode: bool = True) -> "Module":
+        self.training = mode
+        for v in self.__dict__.values():
+            if isinstance(v, Module):
+                v.train(mode)
+            elif isinstance(v, (list, tuple)):
+                for m in v:
+                    if isinstance(m, Module):
+                        m.train(mode)
+        return self
+
+    def eval(self) -> "Module":
+        return self.train(False)
+
+    def __call__(self, *a, **k):
+        return self.forward(*a, **k)
+
+
+def kaiming_normal(shape: Sequence[int], dtype=np.float32) -> np.ndarray:
+    """``utils/weight_initializer/_kaiming.py:55-63``: randn(*shape) * sqrt(2 / fan_in) from the global NumPy RNG;
+    fan_in = in_features for (out, in), C_in * K_h * K_w for (C_out, C_in, K_h, K_w)."""
+    fan_in = int(np.prod(shape[1:])) if len(shape) > 1 else int(shape[0])
+    return np.random.randn(*shape).astype(dtype, copy=False) * dtype(math.sqrt(2.0 / float(max(1, fan_in))))
+
+
+class Conv2d(Module):
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, bias: bool = True,
+                 dtype=np.float32, initializer: str = "kaiming") -> None:
+        if initializer != "kaiming":
+            raise ValueError("only the reference default initializer 'kaiming' is implemented")
+        self.in_channels, self.out_channels = int(in_channels), int(out_channels)
+        self.kernel_size, self.stride, self.padding = _pair(kernel_size), _pair(stride), _pair(padding)
+        self.weight = Parameter.from_numpy(kaiming_normal((out_channels, in_channels, *self.kernel_size), np.dtype(dtype).type))
+        self.bias = Parameter.from_numpy(np.zeros(out_channels, dtype)) if bias else None
+
+    def forward(self, x: Tensor) -> Tensor:
+        if x.ndim != 4 or x.shape[1] != self.in_channels:
+            raise ValueError(f"Conv2d expects (N, {self.in_channels}, H, W), got {x.shape}")
+        dnn = load_dnn()
+        N, C, H, W = x.shape
+        (kh, kw), (sh, sw), (ph, pw) = self.kernel_size, self.stride, self.padding
+        Ho, Wo = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+        s = _suffix(x.dtype)
+        y = Tensor.empty((N, self.out_channels, Ho, Wo), x.dtype)
+        dims = (N, C, H, W, self.out_channels, Ho, Wo, kh, kw, sh, sw, ph, pw)
+        dnn.call(f"keydnn_cuda_conv2d_forward_ex_{s}", x.data, self.weight.data, self.bias.data if self.bias else None,
+                 y.data, *dims)
+        w, b = self.weight, self.bias
+        if x._needs_grad(w) or (b is not None and b.requires_grad):
+            y.requires_grad = True
+
+            def backward_fn(g: Tensor):
+                gx = Tensor.empty(x.shape, x.dtype) if x.requires_grad else None
+                gw = Tensor.empty(w.shape, w.dtype)
+                dnn.call(f"keydnn_cuda_conv2d_backward_ex_{s}", x.data, w.data, g.data, gx.data if gx else None, gw.data,
+                         *dims)
+                if b is None:
+                    return (gx, gw)
+                with no_grad():     # the reference sums the bias gradient on the host (ops/conv2d_cuda.py:573-575)
+                    gb = g.sum_to_shape((1, self.out_channels, 1, 1)).reshape(self.out_channels)
+                return (gx, gw, gb)
+
+            y._ctx = Context((x, w) if b is None else (x, w, b), backward_fn)
+        return y
+
+
+class BatchNorm2d(Module):
+    def __init__(self, num_features: int, eps: float = 1e-5, momentum: float = 0.1, affine: bool = True,
+                 dtype=np.float32) -> None:
+        self.num_features, self.eps, self.momentum, self.affine = int(num_features), float(eps), float(momentum), affine
+        self.gamma = Parameter.from_numpy(np.ones(num_features, dtype)) if affine else None
+        self.beta = Parameter.from_numpy(np.zeros(num_features, dtype)) if affine else None
+        self.running_mean = Tensor.zeros((num_features,), dtype)
+        self.running_var = Tensor.ones((num_features,), dtype)
+
+    def parameters(self) -> List[Parameter]:
+        return [self.gamma, self.beta] if self.affine else []
+
+    def forward(self, x: Tensor) -> Tensor:
+        if x.ndim != 4:
+            raise ValueError(f"BatchNorm2d expects 4D input (N, C, H, W), got shape {x.shape}")
+        N, C, H, W = x.shape
+        if C != self.num_features:
+            raise ValueError(f"Expected num_features={self.num_features}, got C={C}")
+        lib, s = x.native, _suffix(x.dtype)
+        y = Tensor.empty(x.shape, x.dtype)
+        mean, invstd = Tensor.empty((C,), x.dtype), Tensor.empty((C,), x.dtype)
+        ga, be = (self.gamma, self.beta) if self.affine else (None, None)
+        lib.call(f"keydnn_cuda_bn2d_forward_{s}", x.data, ga.data if ga else None, be.data if be else None, y.data,
+                 mean.data, invstd.data, self.running_mean.data, self.running_var.data, N, C, H * W,
+                 _cfloat(x.dtype, self.eps), _cfloat(x.dtype, self.momentum), 1 if self.training else 0)
+        if x._needs_grad() or (self.affine and (ga.requires_grad or be.requires_grad)):
+            y.requires_grad = True
+
+            def backward_fn(g: Tensor):
+                dx = Tensor.empty(x.shape, x.dtype)
+                dga = Tensor.empty((C,), x.dtype) if self.affine else None
+                dbe = Tensor.empty((C,), x.dtype) if self.affine else None
+                lib.call(f"keydnn_cuda_bn2d_backward_{s}", x.data, ga.data if ga else None, g.data, mean.data, invstd.data,
+                         dx.data, dga.data if dga else None, dbe.data if dbe else None, N, C, H * W)
+                return (dx, dga, dbe) if self.affine else (dx,)
+
+            y._ctx = Context((x, ga, be) if self.affine else (x,), backward_fn)
+        return y
+
+
+class ReLU(Module):
+    def forward(self, x: Tensor) -> Tensor:
+        with no_grad():
+            mask = x > 0.0                      # float32 1.0 / 0.0 mask (_function.py:291-293)
+            if mask.dtype != x.dtype:
+                raise TypeError("ReLU on CUDA supports float32 tensors (the mask kernels write float32)")
+            y = x * mask
+        if x._needs_grad():
+            y.requires_grad = True
+
+            def backward_fn(g: Tensor):
+                with no_grad():
+                    return (g * mask,)
+
+            y._ctx = Context((x,), backward_fn)
+        return y
+
+
+class Flatten(Module):
+    def forward(self, x: Tensor) -> Tensor:
+        return x.reshape(x.shape[0], -1)
+
+
+class Linear(Module):
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, dtype=np.float32,
+                 initializer: str = "kaiming") -> None:
+        if initializer != "kaiming":
+            raise ValueError("this mirror implements the 'kaiming' initializer (the benchmark's choice)")
+        self.in_features, self.out_features = int(in_features), int(out_features)
+        self.weight = Parameter.from_numpy(kaiming_normal((out_features, in_features), np.dtype(dtype).type))
+        self.bias = Parameter.from_numpy(np.zeros(out_features, dtype)) if bias else None
+
+    def forward(self, x: Tensor) -> Tensor:
+        if x.ndim != 2 or x.shape[1] != self.in_features:
+            raise ValueError(f"Linear expects (batch, {self.in_features}), got {x.shape}")
+        dnn, lib, s = load_dnn(), x.native, _suffix(x.dtype)
+        B, I, O = x.shape[0], self.in_features, self.out_features
+        y = Tensor.empty((B, O), x.dtype)
+        w, b = self.weight, self.bias
+        dnn.call(f"keydnn_cuda_matmul_ex_{s}", x.data, w.data, y.data, B, O, I, 0, 1)          # x @ W.T
+        if b is not None:
+            lib.call(f"keydnn_cuda_bias_add_inplace_{s}", y.data, b.data, B, O)
+        if x._needs_grad(w) or (b is not None and b.requires_grad):
+            y.requires_grad = True
+
+            def backward_fn(g: Tensor):
+                gx = None
+                if x.requires_grad:
+                    gx = Tensor.empty(x.shape, x.dtype)
+                    dnn.call(f"keydnn_cuda_matmul_ex_{s}", g.data, w.data, gx.data, B, I, O, 0, 0)      # g @ W
+                gw = Tensor.empty(w.shape, w.dtype)
+                dnn.call(f"keydnn_cuda_matmul_ex_{s}", g.data, x.data, gw.data, O, I, B, 1, 0)          # g.T @ x
+                if b is None:
+                    return (gx, gw)
+                with no_grad():
+                    gb = g.sum(axis=0)
+                return (gx, gw, gb)
+
+            y._ctx = Context((x, w) if b is None else (x, w, b), backward_fn)
+        return y
+
+
+class Sequential(Module):
+    def __init__(self, *layers) -> None:
+        self.layers = list(layers)
+
+    def forward(self, x: Tensor) -> Tensor:
+        for layer in self.layers:
+            x = layer(x)
+        return x
+
+
+def mse_loss(pred: Tensor, target: Tensor) -> Tensor:
+    """``_losses.py:173-176``: mean((pred - target)^2); gradient 2 * (pred - target) / N times the upstream scalar."""
+    with no_grad():
+        diff = pred - target
+        loss = (diff * diff).mean()
+    if pred.requires_grad:
+        loss.requires_grad = True
+        n = diff.numel
+
+        def backward_fn(g: Tensor):
+            with no_grad():
+                gp = diff * (2.0 / n)
+                if not getattr(g, "_is_unit_seed", False):
+                    gp = gp * g.item()
+            return (gp,)
+
+        loss._ctx = Context((pred,), backward_fn)
+    return loss
+
+
+class _ViewStorage:
+    """A window into a larger allocation; keeps the owner alive, frees nothing itself."""
+
+    __slots__ = ("native", "device_index", "dev_ptr", "nbytes", "dtype", "_owner")
+
+    def __init__(self, owner: CudaStorage, offset: int, nbytes: int, dtype) -> None:
+        self.native, self.device_index = owner.native, owner.device_index
+        self.dev_ptr, self.nbytes, self.dtype, self._owner = owner.dev_ptr + offset, nbytes, np.dtype(dtype), owner
+
+    def incref(self) -> None:
+        pass
+
+    def decref(self) -> None:
+        pass
+
+
+class SGD:
+    """Stochastic gradient descent with coupled L2 weight decay (``optimizers/_sgd.py:119-140``) and
+    optional momentum (an addition: v = momentum * v + g'; p -= lr * v).
+
+    All parameters are moved into one flat device buffer (each at a 256-byte boundary; the
+    ``Parameter`` objects become windows into it), so a step is: gather the gradients into a flat
+    buffer, one in-place NCCL all-reduce over it when ``group.world > 1`` (its 1/world average is
+    folded into the update), one fused kernel over (p, g, v).  The reference runs five tensor passes
+    and four allocations per parameter.
+    """
+
+    def __init__(self, params: Iterable[Parameter], lr: float = 0.01, momentum: float = 0.0, weight_decay: float = 0.0,
+                 group=None) -> None:
+        self.params = [p for p in params]
+        if not self.params:
+            raise ValueError("SGD needs at least one parameter")
+        if lr <= 0.0:
+            raise ValueError(f"lr must be > 0, got {lr}")
+        if weight_decay < 0.0:
+            raise ValueError(f"weight_decay must be >= 0, got {weight_decay}")
+        self.lr, self.momentum, self.weight_decay, self.group = float(lr), float(momentum), float(weight_decay), group
+        self.dtype = self.params[0].dtype
+        if any(p.dtype != self.dtype for p in self.params):
+            raise TypeError("all parameters must share one dtype")
+        isz = self.dtype.itemsize
+        self.offsets: List[int] = []
+        off = 0
+        for p in self.params:
+            self.offsets.append(off)
+            off += (p.nbytes + 255) // 256 * 256
+        self.n = off // isz
+        self.native = self.params[0].native
+        self.flat_p = CudaStorage.allocate(off, self.dtype)
+        self.flat_g = CudaStorage.allocate(off, self.dtype)
+        self.flat_v = CudaStorage.allocate(off, self.dtype) if momentum != 0.0 else None
+        for st in (self.flat_p, self.flat_g, self.flat_v):
+            if st is not None:
+                self.native.call("keydnn_cuda_memset", st.dev_ptr, 0, off)
+        for p, o in zip(self.params, self.offsets):
+            self.native.call("keydnn_cuda_memcpy_d2d", self.flat_p.dev_ptr + o, p.data, p.nbytes)
+            p.storage = _ViewStorage(self.flat_p, o, p.nbytes, self.dtype)
+
+    def zero_grad(self) -> None:
+        for p in self.params:
+            p.zero_grad()
+
+    def step(self) -> None:
+        lib, s = self.native, _suffix(self.dtype)
+        for p, o in zip(self.params, self.offsets):
+            if p.grad is None:
+                lib.call("keydnn_cuda_memset", self.flat_g.dev_ptr + o, 0, p.nbytes)
+            else:
+                lib.call("keydnn_cuda_memcpy_d2d", self.flat_g.dev_ptr + o, p.grad.data, p.nbytes)
+        world = 1 if self.group is None else self.group.world
+        if world > 1:
+            self.group.allreduce_sum(self.flat_g.dev_ptr, self.n, s)
+        lib.call(f"keydnn_cuda_sgd_momentum_step_{s}", self.flat_p.dev_ptr, self.flat_g.dev_ptr,
+                 self.flat_v.dev_ptr if self.flat_v else None, self.n, _cfloat(self.dtype, self.lr),
+                 _cfloat(self.dtype, self.momentum), _cfloat(self.dtype, self.weight_decay),
+                 _cfloat(self.dtype, 1.0 / world))
+
+
+def small_cnn(dtype=np.float32) -> Sequential:
+    """Conv(3->32,3x3,p1)-BN-ReLU-MaxPool(2)-Conv(32->64,3x3,p1)-BN-ReLU-GlobalAvgPool-Flatten-Linear(64->10)."""
+    return Sequential(
+        Conv2d(3, 32, 3, padding=1, dtype=dtype), BatchNorm2d(32, dtype=dtype), ReLU(), MaxPool2d(2),
+        Conv2d(32, 64, 3, padding=1, dtype=dtype), BatchNorm2d(64, dtype=dtype), ReLU(), GlobalAvgPool2d(), Flatten(),
+        Linear(64, 10, dtype=dtype),
+    )
+
+
+def train_step(model: Module, opt: SGD, x: Tensor, target: Tensor) -> Tensor:
+    """zero_grad -> forward -> MSE -> backward -> optimizer step (``models/_models.py:402-513``); returns the loss tensor."""
+    opt.zero_grad()
+    loss = mse_loss(model(x), target)
+    loss.backward()
+    opt.step()
+    return loss

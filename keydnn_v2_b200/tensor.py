@@ -101,7 +101,8 @@ class no_grad:
 
 
 class Tensor:
-    __slots__ = ("storage", "shape", "dtype", "device", "requires_grad", "grad", "_ctx", "native", "__weakref__")
+    __slots__ = ("storage", "shape", "dtype", "device", "requires_grad", "grad", "_ctx", "native", "_is_unit_seed",
+                 "__weakref__")
 
     # ------------------------------------------------------------------ build
     def __init__(self, storage: CudaStorage, shape: Sequence[int], dtype, *, device: Optional[Device] = None,
@@ -113,6 +114,7 @@ class Tensor:
         self.requires_grad = bool(requires_grad)
         self.grad: Optional[Tensor] = None
         self._ctx = ctx
+        self._is_unit_seed = False      # True for the implicit gradient of ones that backward() seeds
         self.native: Native = storage.native
 
     @classmethod
@@ -622,6 +624,7 @@ class Tensor:
             if self.numel != 1:
                 raise ValueError("grad_out must be given for non-scalar tensors")
             grad_out = Tensor.full(self.shape, 1.0, self.dtype)
+            grad_out._is_unit_seed = True
         elif grad_out.shape != self.shape:
             raise ValueError(f"grad_out shape {grad_out.shape} != tensor shape {self.shape}")
 

@@ -32,6 +32,23 @@ sys.path.insert(0, str(REF_ROOT / "src"))
 sys.path.insert(0, str(REPO))
 warnings.simplefilter("ignore")
 
+# The reference's CUDA binding modules resolve symbols through ctypes.windll at import time (they are
+# imported even on the CPU path of Conv2d); give them a stand-in so the CPU path can be imported here.
+import os  # noqa: E402
+
+if not hasattr(ctypes, "windll"):
+    class _Kernel32:
+        @staticmethod
+        def GetProcAddress(handle, name):
+            return None
+
+    class _Windll:
+        kernel32 = _Kernel32()
+
+    ctypes.windll = _Windll()
+if not hasattr(os, "add_dll_directory"):
+    os.add_dll_directory = lambda p: None
+
 from keydnn.domain.device._device import Device  # noqa: E402
 from keydnn.infrastructure.optimizers._sgd import SGD  # noqa: E402
 from keydnn.infrastructure._parameter import Parameter  # noqa: E402
@@ -56,7 +73,7 @@ def tensor(a: np.ndarray, requires_grad: bool = False) -> Tensor:
 
 
 def put(name: str, a) -> None:
-    OUT[name] = np.ascontiguousarray(np.asarray(a))
+    OUT[name] = np.array(a, copy=True, order="C")      # a copy: some to_numpy() results alias live buffers
 
 
 # ---------------------------------------------------------------------------
@@ -233,7 +250,52 @@ def tensor_cases() -> None:
     put("sgd/p2", steps[1])
 
 
+def cnn_case() -> None:
+    """One training step of a scaled-down copy of the benchmark CNN on the reference's CPU path:
+    Conv(3->4,3x3,p1)-BN-ReLU-MaxPool(2)-Conv(4->6,3x3,p1)-BN-ReLU-GlobalAvgPool-Flatten-Linear(6->3), MSE, SGD."""
+    from keydnn.infrastructure._activations import ReLU
+    from keydnn.infrastructure._losses import MSEFn
+    from keydnn.infrastructure.convolution._conv2d_module import Conv2d
+    from keydnn.infrastructure.flatten._flatten_module import Flatten
+    from keydnn.infrastructure.fully_connected._linear import Linear
+    from keydnn.infrastructure.layers._batchnorm import BatchNorm2d
+    from keydnn.infrastructure.models._sequential import Sequential
+    from keydnn.infrastructure.pooling._pooling_module import GlobalAvgPool2d, MaxPool2d
+
+    np.random.seed(5)
+    model = Sequential(
+        Conv2d(3, 4, 3, padding=1, device=CPU), BatchNorm2d(4, device=CPU), ReLU(), MaxPool2d(2),
+        Conv2d(4, 6, 3, padding=1, device=CPU), BatchNorm2d(6, device=CPU), ReLU(), GlobalAvgPool2d(), Flatten(),
+        Linear(6, 3, device=CPU, initializer="kaiming"),
+    )
+    params = list(model.parameters())
+    for i, p in enumerate(params):
+        put(f"cnn/p{i}_init", p.to_numpy())
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((4, 3, 8, 8)).astype(np.float32)
+    t = np.eye(3, dtype=np.float32)[rng.integers(0, 3, 4)]
+    put("cnn/x", x)
+    put("cnn/t", t)
+    pred = model(tensor(x))
+    ctx = Context(parents=(pred,), backward_fn=lambda g: None)
+    tt = tensor(t)
+    loss = MSEFn.forward(ctx, pred, tt)
+    ctx.backward_fn = lambda g: MSEFn.backward(ctx, g)[:1]
+    loss.requires_grad = True
+    loss._set_ctx(ctx)
+    loss.backward()
+    put("cnn/pred", pred.to_numpy())
+    put("cnn/loss", loss.to_numpy())
+    for i, p in enumerate(params):
+        put(f"cnn/p{i}_grad", p.grad.to_numpy())
+    SGD(params, lr=0.01, weight_decay=1e-4).step()
+    for i, p in enumerate(params):
+        put(f"cnn/p{i}_after", p.to_numpy())
+    put("cnn/n_params", np.array([len(params)], np.int64))
+
+
 def main() -> None:
+    cnn_case()
     pool_cases()
     native_pool_cases()
     tensor_cases()

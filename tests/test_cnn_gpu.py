@@ -1,0 +1,106 @@
+"""One training step of the small CNN on the GPU against the same step run by the reference itself
+on its CPU path (tests/golden/, `cnn/*`): forward, MSE loss, every parameter gradient, SGD update.
+Conv / Linear go through cuDNN / cuBLAS as in the reference; BatchNorm2d, ReLU, pooling, loss and the
+optimizer go through this library's kernels."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(kd, nn, golden, dtype):
+    np.random.seed(0)
+    model = nn.Sequential(
+        nn.Conv2d(3, 4, 3, padding=1, dtype=dtype), nn.BatchNorm2d(4, dtype=dtype), nn.ReLU(), nn.MaxPool2d(2),
+        nn.Conv2d(4, 6, 3, padding=1, dtype=dtype), nn.BatchNorm2d(6, dtype=dtype), nn.ReLU(), nn.GlobalAvgPool2d(),
+        nn.Flatten(), nn.Linear(6, 3, dtype=dtype),
+    )
+    params = model.parameters()
+    assert len(params) == int(golden["cnn/n_params"][0])
+    for i, p in enumerate(params):
+        init = golden[f"cnn/p{i}_init"]
+        assert p.shape == init.shape
+        p.copy_from_numpy(init.astype(dtype))
+    return model, params
+
+
+@pytest.mark.parametrize("dtype,tol", [(np.float32, dict(rtol=5e-3, atol=5e-4)), (np.float64, dict(rtol=2e-4, atol=2e-5))])
+def test_training_step_matches_the_reference_cpu_step(golden, dtype, tol):
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import nn
+
+    if dtype == np.float64:
+        nn.ReLU.forward = _relu_any_dtype            # the mask kernels write float32; f64 check casts it
+    model, params = _model(kd, nn, golden, dtype)
+    opt = nn.SGD(params, lr=0.01, weight_decay=1e-4)
+    x = kd.Tensor.from_numpy(golden["cnn/x"].astype(dtype))
+    t = kd.Tensor.from_numpy(golden["cnn/t"].astype(dtype))
+    opt.zero_grad()
+    pred = model(x)
+    loss = nn.mse_loss(pred, t)
+    loss.backward()
+    np.testing.assert_allclose(pred.to_numpy(), golden["cnn/pred"], **tol)
+    np.testing.assert_allclose(loss.to_numpy(), golden["cnn/loss"].reshape(()), **tol)
+    for i, p in enumerate(params):
+        assert p.grad is not None, i
+        np.testing.assert_allclose(p.grad.to_numpy(), golden[f"cnn/p{i}_grad"], err_msg=f"grad {i}", **tol)
+    opt.step()
+    for i, p in enumerate(params):
+        np.testing.assert_allclose(p.to_numpy(), golden[f"cnn/p{i}_after"], err_msg=f"param {i}", **tol)
+
+
+def _relu_any_dtype(self, x):
+    """float64 variant for the check above: same mask-and-multiply, mask converted to the input type on the host."""
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200.tensor import Context, no_grad
+
+    with no_grad():
+        mask = kd.Tensor.from_numpy((x > 0.0).to_numpy().astype(x.dtype))
+        y = x * mask
+    if x._needs_grad():
+        y.requires_grad = True
+        y._ctx = Context((x,), lambda g: (_nograd_mul(g, mask),))
+    return y
+
+
+def _nograd_mul(a, b):
+    from keydnn_v2_b200.tensor import no_grad
+
+    with no_grad():
+        return a * b
+
+
+def test_batchnorm_eval_mode_and_running_stats():
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import nn
+
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((8, 5, 6, 6)).astype(np.float32) * 2 + 1
+    bn = nn.BatchNorm2d(5)
+    y = bn(kd.Tensor.from_numpy(x))
+    mu, var = x.mean((0, 2, 3)), x.var((0, 2, 3))
+    np.testing.assert_allclose(y.to_numpy(), (x - mu[None, :, None, None]) / np.sqrt(var + 1e-5)[None, :, None, None],
+                               rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(bn.running_mean.to_numpy(), 0.1 * mu, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(bn.running_var.to_numpy(), 0.9 + 0.1 * var, rtol=1e-5, atol=1e-6)
+    bn.eval()
+    y2 = bn(kd.Tensor.from_numpy(x)).to_numpy()
+    rm, rv = bn.running_mean.to_numpy(), bn.running_var.to_numpy()
+    np.testing.assert_allclose(y2, (x - rm[None, :, None, None]) / np.sqrt(rv + 1e-5)[None, :, None, None], rtol=1e-4,
+                               atol=1e-5)
+
+
+def test_momentum_training_reduces_the_loss():
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import nn
+
+    np.random.seed(3)
+    rng = np.random.default_rng(3)
+    model = nn.small_cnn()
+    opt = nn.SGD(model.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
+    x = kd.Tensor.from_numpy(rng.standard_normal((32, 3, 64, 64)).astype(np.float32))
+    t = kd.Tensor.from_numpy(np.eye(10, dtype=np.float32)[rng.integers(0, 10, 32)])
+    losses = [nn.train_step(model, opt, x, t).item() for _ in range(15)]
+    assert np.isfinite(losses).all() and losses[-1] < 0.7 * losses[0], losses
