@@ -249,6 +249,28 @@ def run_ours(args) -> None:
     else:
         group = distributed.single(lib)
 
+    if args.workload == "cnn":
+        timer = Timer(lib)
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        cnn = cnn_step_bench(lib, group, dist, args.steps, args.warmup, timer)
+        clocks = sampler.stop() if rank == 0 else None
+        if rank == 0:
+            print(json.dumps({
+                "metric": "CNN training step samples/s (configs[4])", "value": cnn["samples_per_s"], "unit": "samples/s",
+                "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": cnn["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "configs[4]: " + cnn["model"], "global_batch": cnn["batch_per_gpu"] * world,
+                           "parallelism": cnn["parallelism"]},
+                "e2e": {"value": cnn["e2e_samples_per_s"], "unit": "samples/s",
+                        "h2d_bytes_per_step": cnn["h2d_bytes_per_step"], "d2h_bytes_per_step": cnn["d2h_bytes_per_step"]},
+                "clocks": clocks, "cnn_step": cnn}), flush=True)
+        if dist is not None:
+            group.destroy()
+            dist.destroy_process_group()
+        return
+
     rng = np.random.default_rng(1 + rank)
     T = kd.Tensor
     h32 = rng.standard_normal((ROWS32, COLS32), dtype=np.float32)
@@ -349,8 +371,12 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), float(t[1])
 
+    # per-kernel timings run on every rank (the sharded kernels contain collectives); rank 0 reports its own
+    peak, peak_src = measured_peak_gbs()
+    table = kernel_table(lib, reducers, timer, 20, peak) if args.kernels != "none" else None
+    suite = suite_table(lib, timer, peak) if args.kernels == "suite" else None
+    line = None
     if rank == 0:
-        peak, peak_src = measured_peak_gbs()
         bytes_step = algorithmic_bytes_per_step()
         value = bytes_step * world * args.steps / ms / 1e6
         e2e_val = bytes_step * world * e2e_steps / max(e2e_ms, e2e_wall) / 1e6
@@ -366,22 +392,84 @@ def run_ours(args) -> None:
                     "d2h_bytes_per_step": int(d2h[0]), "steps": e2e_steps},
             "gpu_launches": n_launch, "clocks": clocks,
         }
-        if args.kernels != "none":
-            table = kernel_table(lib, reducers, timer, 20, peak)
+        if table is not None:
             top = max(table, key=lambda r: r["us"])
             line["roofline"] = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["gbs"], "peak": peak,
                                 "unit": "GB/s", "frac": top["frac"], "traffic": None, "peak_source": peak_src,
                                 "frac_of_nominal_8000": round(top["gbs"] / 8000.0, 4)}
             line["kernels"] = table
-            if args.kernels == "suite":
-                del r32, r64
-                line["suite"] = suite_table(lib, timer, peak)
+            if suite is not None:
+                line["suite"] = suite
             line["whole_step_frac"] = round(value / world / peak, 4)
         line["cpu_baseline"] = cpu_baseline_sample() if world == 1 or rank == 0 else None
+    cnn = None
+    if args.cnn != "off":
+        del r32, r64, reducers
+        lib.call("keydnn_cuda_empty_cache")
+        cnn = cnn_step_bench(lib, group, dist, max(args.steps, 10), args.warmup, timer)
+    if rank == 0:
+        line["cnn_step"] = cnn
         print(json.dumps(line), flush=True)
     if dist is not None:
         group.destroy()
         dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------
+# configs[4]: small-CNN training step, data parallel
+# ---------------------------------------------------------------------------
+def cnn_step_bench(lib, group, dist, steps: int, warmup: int, timer, batch: int = 256) -> dict:
+    """Conv-BN-ReLU-MaxPool-Conv-BN-ReLU-GlobalAvgPool-Flatten-Linear, MSE, SGD-momentum; batch 256 per GPU,
+    per-shard BatchNorm, one gradient all-reduce per step.  Returns samples/s with inputs resident and
+    end to end (pinned host batch copied in, loss copied out, every step)."""
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import nn
+
+    rank, world = group.rank, group.world
+    np.random.seed(1234)                         # same initial weights on every rank
+    model = nn.small_cnn()
+    opt = nn.SGD(model.parameters(), lr=0.01, momentum=0.9, weight_decay=1e-4, group=group)
+    rng = np.random.default_rng(100 + rank)
+    hx = rng.standard_normal((batch, 3, 64, 64), dtype=np.float32)
+    ht = np.eye(10, dtype=np.float32)[rng.integers(0, 10, batch)]
+    x, t = kd.Tensor.from_numpy(hx), kd.Tensor.from_numpy(ht)
+
+    def sync() -> None:
+        lib.call("keydnn_cuda_synchronize")
+        if dist is not None:
+            dist.barrier()
+
+    for _ in range(max(warmup, 3)):
+        loss = nn.train_step(model, opt, x, t)
+    first = loss.item()
+    sync()
+    timer.start()
+    for _ in range(steps):
+        loss = nn.train_step(model, opt, x, t)
+    ms = timer.stop_ms()
+    sync()
+    last = loss.item()
+    t0 = time.perf_counter()
+    timer.start()
+    for _ in range(steps):
+        x.copy_from_numpy(hx)
+        t.copy_from_numpy(ht)
+        loss = nn.train_step(model, opt, x, t)
+        loss.item()
+    e2e_ms = max(timer.stop_ms(), (time.perf_counter() - t0) * 1e3)
+    sync()
+    if dist is not None:
+        import torch
+
+        tt = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(tt[0]), float(tt[1])
+    return {"samples_per_s": round(batch * world * steps / ms * 1e3, 1), "ms_per_step": round(ms / steps, 4),
+            "e2e_samples_per_s": round(batch * world * steps / e2e_ms * 1e3, 1), "batch_per_gpu": batch, "steps": steps,
+            "h2d_bytes_per_step": int(hx.nbytes + ht.nbytes), "d2h_bytes_per_step": 4,
+            "loss_first": round(first, 6), "loss_last": round(last, 6),
+            "model": "Conv(3-32)-BN-ReLU-MaxPool2-Conv(32-64)-BN-ReLU-GAP-Flatten-Linear(64-10), MSE, SGD momentum 0.9 wd 1e-4",
+            "parallelism": f"dp{world}, per-shard BatchNorm, one NCCL all-reduce of the flat gradient buffer per step"}
 
 
 # ---------------------------------------------------------------------------
@@ -440,6 +528,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kernels", default="all", choices=["all", "none", "suite"])
+    ap.add_argument("--workload", default="reduce", choices=["reduce", "cnn"],
+                    help="reduce: configs[1] (the default line); cnn: only the configs[4] training step, reported as samples/s")
+    ap.add_argument("--cnn", default="on", choices=["on", "off"], help="also time the small-CNN training step (configs[4])")
     ap.add_argument("--once", action="store_true", help="launch every kernel once and exit (profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -279,20 +279,21 @@ int keydnn_cuda_transpose2d_f64(const double* x, double* y, int rows, int cols);
  * these entries run the same formulas in two kernels per direction.  x, y, grad_* are
  * (N, C, HW) contiguous; gamma/beta (both or neither) may be NULL; mean / invstd receive the
  * statistics used (saved for backward); training != 0 uses batch statistics and updates
- * running_mean / running_var (may be NULL) with `momentum`. */
+ * running_mean / running_var (may be NULL) with `momentum`.  relu != 0 fuses the mask-and-multiply
+ * ReLU that follows the layer (src/keydnn/infrastructure/_function.py:291-293) into both directions. */
 /* ------------------------------------------------------------------------- */
 int keydnn_cuda_bn2d_forward_f32(const float* x, const float* gamma, const float* beta, float* y, float* mean,
                                  float* invstd, float* running_mean, float* running_var, int N, int C, int64_t HW,
-                                 float eps, float momentum, int training);
+                                 float eps, float momentum, int training, int relu);
 int keydnn_cuda_bn2d_forward_f64(const double* x, const double* gamma, const double* beta, double* y, double* mean,
                                  double* invstd, double* running_mean, double* running_var, int N, int C, int64_t HW,
-                                 double eps, double momentum, int training);
-int keydnn_cuda_bn2d_backward_f32(const float* x, const float* gamma, const float* grad_out, const float* mean,
-                                  const float* invstd, float* grad_x, float* grad_gamma, float* grad_beta, int N, int C,
-                                  int64_t HW);
-int keydnn_cuda_bn2d_backward_f64(const double* x, const double* gamma, const double* grad_out, const double* mean,
-                                  const double* invstd, double* grad_x, double* grad_gamma, double* grad_beta, int N,
-                                  int C, int64_t HW);
+                                 double eps, double momentum, int training, int relu);
+int keydnn_cuda_bn2d_backward_f32(const float* x, const float* gamma, const float* beta, const float* grad_out,
+                                  const float* mean, const float* invstd, float* grad_x, float* grad_gamma,
+                                  float* grad_beta, int N, int C, int64_t HW, int relu);
+int keydnn_cuda_bn2d_backward_f64(const double* x, const double* gamma, const double* beta, const double* grad_out,
+                                  const double* mean, const double* invstd, double* grad_x, double* grad_gamma,
+                                  double* grad_beta, int N, int C, int64_t HW, int relu);
 
 /* ------------------------------------------------------------------------- */
 /* Multi-GPU (additive; the reference has no distributed code).  One process   */

@@ -35,17 +35,22 @@ __device__ __forceinline__ bool bn_take_ticket(unsigned int* counter, unsigned i
 // Two sums per channel over the (n, hw) extent.  F(v, w) maps an element of the first (and
 // second) tensor to the two summands.  grid = (C, slices); slice s owns images [s*ach, ...).
 // MODE 0: s0 = sum x, s1 = sum x*x.   MODE 1: s0 = sum g, s1 = sum g * x_hat.
-template <typename T, int MODE, bool VEC>
+// RELU: the layer output was relu(gamma * x_hat + beta) computed as z * (z > 0 ? 1 : 0); the
+// upstream gradient is first multiplied by that mask, which is recomputed from x here.
+template <typename T> __device__ __forceinline__ T relu_mask(T z) { return z > T(0) ? T(1) : T(0); }
+
+template <typename T, int MODE, bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ mean,
-                const T* __restrict__ invstd, int N, int C, int64_t HW, int ach, double* partials,
-                unsigned int* counters, double* sums /* [2][C] */) {
+                const T* __restrict__ invstd, const T* __restrict__ gamma, const T* __restrict__ beta, int N, int C,
+                int64_t HW, int ach, double* partials, unsigned int* counters, double* sums /* [2][C] */) {
     __shared__ double sm[kWarps];
     const int c = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
     const int n_begin = slice * ach;
     const int n_end = min(N, n_begin + ach);
-    T mu = T(0), is = T(0);
+    T mu = T(0), is = T(0), ga = T(1), be = T(0);
     if (MODE == 1) { mu = __ldg(mean + c); is = __ldg(invstd + c); }
+    if (RELU) { ga = gamma ? __ldg(gamma + c) : T(1); be = beta ? __ldg(beta + c) : T(0); }
     double a0 = 0.0, a1 = 0.0;
     for (int n = n_begin; n < n_end; ++n) {
         const int64_t base = (static_cast<int64_t>(n) * C + c) * HW;
@@ -65,8 +70,9 @@ bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __res
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const T xh = (vx.v[k] - mu) * is;
-                        if (k & 1) { p1 += vg.v[k]; q1 += vg.v[k] * xh; }
-                        else { p0 += vg.v[k]; q0 += vg.v[k] * xh; }
+                        const T gk = RELU ? vg.v[k] * relu_mask<T>(ga * xh + be) : vg.v[k];
+                        if (k & 1) { p1 += gk; q1 += gk * xh; }
+                        else { p0 += gk; q0 += gk * xh; }
                     }
                 }
             }
@@ -74,7 +80,12 @@ bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __res
             for (int64_t b = threadIdx.x; b < HW; b += kThreads) {
                 const T vx = x[base + b];
                 if (MODE == 0) { p0 += vx; q0 += vx * vx; }
-                else { const T vg = g[base + b]; p0 += vg; q0 += vg * ((vx - mu) * is); }
+                else {
+                    const T xh = (vx - mu) * is;
+                    const T vg = RELU ? g[base + b] * relu_mask<T>(ga * xh + be) : g[base + b];
+                    p0 += vg;
+                    q0 += vg * xh;
+                }
             }
         }
         a0 += static_cast<double>(p0) + static_cast<double>(p1);
@@ -127,7 +138,7 @@ __global__ void bn_invstd_from_var(const T* __restrict__ var, int C, T eps, T* i
 
 // y = gamma * ((x - mean) * inv_std) + beta.  blockIdx.x walks (n, c) rows of HW elements,
 // blockIdx.y splits a row.
-template <typename T, bool VEC>
+template <typename T, bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_apply_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
              const T* __restrict__ mean, const T* __restrict__ invstd, T* __restrict__ y, int64_t rows, int C, int64_t HW) {
@@ -146,7 +157,8 @@ bn_apply_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __re
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const T xh = (v.v[k] - mu) * is;
-                    v.v[k] = affine ? ga * xh + be : xh;
+                    const T z = affine ? ga * xh + be : xh;
+                    v.v[k] = RELU ? z * relu_mask<T>(z) : z;
                 }
                 kd::store4(dst + 4 * p, v);
             }
@@ -154,7 +166,8 @@ bn_apply_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __re
             for (int64_t b = static_cast<int64_t>(blockIdx.y) * kThreads + threadIdx.x; b < HW;
                  b += static_cast<int64_t>(gridDim.y) * kThreads) {
                 const T xh = (src[b] - mu) * is;
-                dst[b] = affine ? ga * xh + be : xh;
+                const T z = affine ? ga * xh + be : xh;
+                dst[b] = RELU ? z * relu_mask<T>(z) : z;
             }
         }
     }
@@ -162,15 +175,16 @@ bn_apply_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __re
 
 // dx = (1/m) * inv_std * (m*dxhat - sum_dxhat - x_hat * sum_dxhat_xhat), dxhat = g * gamma;
 // sums[c] = sum g, sums[C + c] = sum g * x_hat (so sum_dxhat = gamma * sums[c], ...).
-template <typename T, bool VEC>
+template <typename T, bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
-bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ gamma,
+bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ gamma, const T* __restrict__ beta,
              const T* __restrict__ mean, const T* __restrict__ invstd, const double* __restrict__ sums,
              T* __restrict__ dx, int64_t rows, int C, int64_t HW, T m) {
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const int c = static_cast<int>(r % C);
         const T mu = __ldg(mean + c), is = __ldg(invstd + c);
         const T ga = gamma ? __ldg(gamma + c) : T(1);
+        const T be = (RELU && beta) ? __ldg(beta + c) : T(0);
         const T s1 = static_cast<T>(sums[c]) * ga;
         const T s2 = static_cast<T>(sums[C + c]) * ga;
         const T k0 = (T(1) / m) * is;
@@ -187,7 +201,8 @@ bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restri
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const T xh = (vx.v[k] - mu) * is;
-                    out.v[k] = k0 * (m * (vg.v[k] * ga) - s1 - xh * s2);
+                    const T gk = RELU ? vg.v[k] * relu_mask<T>(ga * xh + be) : vg.v[k];
+                    out.v[k] = k0 * (m * (gk * ga) - s1 - xh * s2);
                 }
                 kd::store4(dst + 4 * p, out);
             }
@@ -195,7 +210,8 @@ bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restri
             for (int64_t b = static_cast<int64_t>(blockIdx.y) * kThreads + threadIdx.x; b < HW;
                  b += static_cast<int64_t>(gridDim.y) * kThreads) {
                 const T xh = (xs[b] - mu) * is;
-                dst[b] = k0 * (m * (gs[b] * ga) - s1 - xh * s2);
+                const T gk = RELU ? gs[b] * relu_mask<T>(ga * xh + be) : gs[b];
+                dst[b] = k0 * (m * (gk * ga) - s1 - xh * s2);
             }
         }
     }
@@ -244,7 +260,7 @@ inline dim3 row_grid(int64_t rows, int64_t HW) {
 
 template <typename T>
 int bn_forward(const T* x, const T* gamma, const T* beta, T* y, T* mean, T* invstd, T* running_mean, T* running_var,
-               int N, int C, int64_t HW, T eps, T momentum, int training) {
+               int N, int C, int64_t HW, T eps, T momentum, int training, int relu) {
     if (!x || !y || !mean || !invstd) return -1;
     if (N <= 0 || C <= 0 || HW <= 0) return -2;
     if ((gamma == nullptr) != (beta == nullptr)) return -3;
@@ -252,13 +268,12 @@ int bn_forward(const T* x, const T* gamma, const T* beta, T* y, T* mean, T* invs
     (void)cudaGetLastError();
     cudaStream_t s = kd::stream();
     const bool vec = kd::aligned_pack<T>(x) && kd::aligned_pack<T>(y) && (HW % 4 == 0);
-    const T* use_mean = mean;
     if (training) {
         SumsPlan p;
         if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
         dim3 grid(C, p.nslices);
-        if (vec) bn_channel_sums<T, 0, true><<<grid, kThreads, 0, s>>>(x, nullptr, nullptr, nullptr, N, C, HW, p.ach, p.partials, p.counters, p.sums);
-        else bn_channel_sums<T, 0, false><<<grid, kThreads, 0, s>>>(x, nullptr, nullptr, nullptr, N, C, HW, p.ach, p.partials, p.counters, p.sums);
+        if (vec) bn_channel_sums<T, 0, true, false><<<grid, kThreads, 0, s>>>(x, nullptr, nullptr, nullptr, nullptr, nullptr, N, C, HW, p.ach, p.partials, p.counters, p.sums);
+        else bn_channel_sums<T, 0, false, false><<<grid, kThreads, 0, s>>>(x, nullptr, nullptr, nullptr, nullptr, nullptr, N, C, HW, p.ach, p.partials, p.counters, p.sums);
         bn_finalize_stats<T><<<(C + 127) / 128, 128, 0, s>>>(p.sums, C, static_cast<double>(N) * static_cast<double>(HW), eps,
                                                           momentum, mean, static_cast<T*>(nullptr), invstd, running_mean,
                                                           running_var);
@@ -268,14 +283,19 @@ int bn_forward(const T* x, const T* gamma, const T* beta, T* y, T* mean, T* invs
     }
     const int64_t rows = static_cast<int64_t>(N) * C;
     const dim3 g2 = row_grid(rows, HW);
-    if (vec) bn_apply_fwd<T, true><<<g2, kThreads, 0, s>>>(x, gamma, beta, use_mean, invstd, y, rows, C, HW);
-    else bn_apply_fwd<T, false><<<g2, kThreads, 0, s>>>(x, gamma, beta, use_mean, invstd, y, rows, C, HW);
+    if (relu) {
+        if (vec) bn_apply_fwd<T, true, true><<<g2, kThreads, 0, s>>>(x, gamma, beta, mean, invstd, y, rows, C, HW);
+        else bn_apply_fwd<T, false, true><<<g2, kThreads, 0, s>>>(x, gamma, beta, mean, invstd, y, rows, C, HW);
+    } else {
+        if (vec) bn_apply_fwd<T, true, false><<<g2, kThreads, 0, s>>>(x, gamma, beta, mean, invstd, y, rows, C, HW);
+        else bn_apply_fwd<T, false, false><<<g2, kThreads, 0, s>>>(x, gamma, beta, mean, invstd, y, rows, C, HW);
+    }
     return kd::launch_status();
 }
 
 template <typename T>
-int bn_backward(const T* x, const T* gamma, const T* go, const T* mean, const T* invstd, T* dx, T* dgamma, T* dbeta, int N,
-                int C, int64_t HW) {
+int bn_backward(const T* x, const T* gamma, const T* beta, const T* go, const T* mean, const T* invstd, T* dx, T* dgamma,
+                T* dbeta, int N, int C, int64_t HW, int relu) {
     if (!x || !go || !mean || !invstd || !dx) return -1;
     if (N <= 0 || C <= 0 || HW <= 0) return -2;
     (void)cudaGetLastError();
@@ -284,36 +304,45 @@ int bn_backward(const T* x, const T* gamma, const T* go, const T* mean, const T*
     SumsPlan p;
     if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
     dim3 grid(C, p.nslices);
-    if (vec) bn_channel_sums<T, 1, true><<<grid, kThreads, 0, s>>>(x, go, mean, invstd, N, C, HW, p.ach, p.partials, p.counters, p.sums);
-    else bn_channel_sums<T, 1, false><<<grid, kThreads, 0, s>>>(x, go, mean, invstd, N, C, HW, p.ach, p.partials, p.counters, p.sums);
+#define KD_BN_SUMS(V, R) bn_channel_sums<T, 1, V, R><<<grid, kThreads, 0, s>>>(x, go, mean, invstd, gamma, beta, N, C, HW, p.ach, p.partials, p.counters, p.sums)
+    if (relu) { if (vec) KD_BN_SUMS(true, true); else KD_BN_SUMS(false, true); }
+    else { if (vec) KD_BN_SUMS(true, false); else KD_BN_SUMS(false, false); }
+#undef KD_BN_SUMS
     if (dgamma || dbeta) bn_param_grads<T><<<(C + 127) / 128, 128, 0, s>>>(p.sums, C, dgamma, dbeta);
     const int64_t rows = static_cast<int64_t>(N) * C;
     const dim3 g2 = row_grid(rows, HW);
     const T m = static_cast<T>(static_cast<double>(N) * static_cast<double>(HW));
-    if (vec) bn_apply_bwd<T, true><<<g2, kThreads, 0, s>>>(x, go, gamma, mean, invstd, p.sums, dx, rows, C, HW, m);
-    else bn_apply_bwd<T, false><<<g2, kThreads, 0, s>>>(x, go, gamma, mean, invstd, p.sums, dx, rows, C, HW, m);
+#define KD_BN_APPLY(V, R) bn_apply_bwd<T, V, R><<<g2, kThreads, 0, s>>>(x, go, gamma, beta, mean, invstd, p.sums, dx, rows, C, HW, m)
+    if (relu) { if (vec) KD_BN_APPLY(true, true); else KD_BN_APPLY(false, true); }
+    else { if (vec) KD_BN_APPLY(true, false); else KD_BN_APPLY(false, false); }
+#undef KD_BN_APPLY
     return kd::launch_status();
 }
 
 }  // namespace
 
+// `relu` != 0 fuses the activation that follows the layer in a Conv-BN-ReLU stack: forward writes
+// z * (z > 0 ? 1 : 0) with z = gamma * x_hat + beta (the reference's mask-and-multiply ReLU,
+// _function.py:291-293, bit for bit), backward multiplies grad_out by the same mask, recomputed from x.
 KD_API int keydnn_cuda_bn2d_forward_f32(const float* x, const float* gamma, const float* beta, float* y, float* mean,
                                         float* invstd, float* running_mean, float* running_var, int N, int C, int64_t HW,
-                                        float eps, float momentum, int training) {
-    return bn_forward<float>(x, gamma, beta, y, mean, invstd, running_mean, running_var, N, C, HW, eps, momentum, training);
+                                        float eps, float momentum, int training, int relu) {
+    return bn_forward<float>(x, gamma, beta, y, mean, invstd, running_mean, running_var, N, C, HW, eps, momentum, training,
+                             relu);
 }
 KD_API int keydnn_cuda_bn2d_forward_f64(const double* x, const double* gamma, const double* beta, double* y, double* mean,
                                         double* invstd, double* running_mean, double* running_var, int N, int C,
-                                        int64_t HW, double eps, double momentum, int training) {
-    return bn_forward<double>(x, gamma, beta, y, mean, invstd, running_mean, running_var, N, C, HW, eps, momentum, training);
+                                        int64_t HW, double eps, double momentum, int training, int relu) {
+    return bn_forward<double>(x, gamma, beta, y, mean, invstd, running_mean, running_var, N, C, HW, eps, momentum, training,
+                              relu);
 }
-KD_API int keydnn_cuda_bn2d_backward_f32(const float* x, const float* gamma, const float* grad_out, const float* mean,
-                                         const float* invstd, float* grad_x, float* grad_gamma, float* grad_beta, int N,
-                                         int C, int64_t HW) {
-    return bn_backward<float>(x, gamma, grad_out, mean, invstd, grad_x, grad_gamma, grad_beta, N, C, HW);
+KD_API int keydnn_cuda_bn2d_backward_f32(const float* x, const float* gamma, const float* beta, const float* grad_out,
+                                         const float* mean, const float* invstd, float* grad_x, float* grad_gamma,
+                                         float* grad_beta, int N, int C, int64_t HW, int relu) {
+    return bn_backward<float>(x, gamma, beta, grad_out, mean, invstd, grad_x, grad_gamma, grad_beta, N, C, HW, relu);
 }
-KD_API int keydnn_cuda_bn2d_backward_f64(const double* x, const double* gamma, const double* grad_out, const double* mean,
-                                         const double* invstd, double* grad_x, double* grad_gamma, double* grad_beta,
-                                         int N, int C, int64_t HW) {
-    return bn_backward<double>(x, gamma, grad_out, mean, invstd, grad_x, grad_gamma, grad_beta, N, C, HW);
+KD_API int keydnn_cuda_bn2d_backward_f64(const double* x, const double* gamma, const double* beta, const double* grad_out,
+                                         const double* mean, const double* invstd, double* grad_x, double* grad_gamma,
+                                         double* grad_beta, int N, int C, int64_t HW, int relu) {
+    return bn_backward<double>(x, gamma, beta, grad_out, mean, invstd, grad_x, grad_gamma, grad_beta, N, C, HW, relu);
 }

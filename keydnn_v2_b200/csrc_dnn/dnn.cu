@@ -96,13 +96,23 @@ ConvPlan& conv_plan(int dtype, int N, int Cin, int H, int W, int Cout, int Ho, i
     return p;
 }
 
+// Algorithm choice: measured once per problem shape (cudnnFind*, which times the candidates on the
+// device), falling back to the heuristic the reference uses on every call (cudnnGet*_v7).
 int plan_fwd(ConvPlan& p) {
     if (p.have_fwd) return 0;
-    cudnnConvolutionFwdAlgoPerf_t perf;
+    cudnnConvolutionFwdAlgoPerf_t perf[8];
     int n = 0;
-    cudnnStatus_t s = cudnnGetConvolutionForwardAlgorithm_v7(dnn(), p.x, p.w, p.conv, p.y, 1, &n, &perf);
-    if (s != CUDNN_STATUS_SUCCESS) return cudnn_status(s);
-    p.fwd = perf.algo;
+    cudnnStatus_t s = cudnnFindConvolutionForwardAlgorithm(dnn(), p.x, p.w, p.conv, p.y, 8, &n, perf);
+    int pick = -1;
+    if (s == CUDNN_STATUS_SUCCESS)
+        for (int i = 0; i < n && pick < 0; ++i)
+            if (perf[i].status == CUDNN_STATUS_SUCCESS) pick = i;
+    if (pick < 0) {
+        s = cudnnGetConvolutionForwardAlgorithm_v7(dnn(), p.x, p.w, p.conv, p.y, 1, &n, perf);
+        if (s != CUDNN_STATUS_SUCCESS) return cudnn_status(s);
+        pick = 0;
+    }
+    p.fwd = perf[pick].algo;
     s = cudnnGetConvolutionForwardWorkspaceSize(dnn(), p.x, p.w, p.conv, p.y, p.fwd, &p.ws_fwd);
     if (s != CUDNN_STATUS_SUCCESS) return cudnn_status(s);
     p.have_fwd = true;
@@ -111,17 +121,32 @@ int plan_fwd(ConvPlan& p) {
 
 int plan_bwd(ConvPlan& p) {
     if (p.have_bwd) return 0;
-    int n = 0;
-    cudnnConvolutionBwdDataAlgoPerf_t pd;
-    cudnnStatus_t s = cudnnGetConvolutionBackwardDataAlgorithm_v7(dnn(), p.w, p.y, p.conv, p.x, 1, &n, &pd);
-    if (s != CUDNN_STATUS_SUCCESS) return cudnn_status(s);
-    p.bwd_data = pd.algo;
+    int n = 0, pick = -1;
+    cudnnConvolutionBwdDataAlgoPerf_t pd[8];
+    cudnnStatus_t s = cudnnFindConvolutionBackwardDataAlgorithm(dnn(), p.w, p.y, p.conv, p.x, 8, &n, pd);
+    if (s == CUDNN_STATUS_SUCCESS)
+        for (int i = 0; i < n && pick < 0; ++i)
+            if (pd[i].status == CUDNN_STATUS_SUCCESS) pick = i;
+    if (pick < 0) {
+        s = cudnnGetConvolutionBackwardDataAlgorithm_v7(dnn(), p.w, p.y, p.conv, p.x, 1, &n, pd);
+        if (s != CUDNN_STATUS_SUCCESS) return cudnn_status(s);
+        pick = 0;
+    }
+    p.bwd_data = pd[pick].algo;
     s = cudnnGetConvolutionBackwardDataWorkspaceSize(dnn(), p.w, p.y, p.conv, p.x, p.bwd_data, &p.ws_data);
     if (s != CUDNN_STATUS_SUCCESS) return cudnn_status(s);
-    cudnnConvolutionBwdFilterAlgoPerf_t pf;
-    s = cudnnGetConvolutionBackwardFilterAlgorithm_v7(dnn(), p.x, p.y, p.conv, p.w, 1, &n, &pf);
-    if (s != CUDNN_STATUS_SUCCESS) return cudnn_status(s);
-    p.bwd_filter = pf.algo;
+    cudnnConvolutionBwdFilterAlgoPerf_t pf[8];
+    pick = -1;
+    s = cudnnFindConvolutionBackwardFilterAlgorithm(dnn(), p.x, p.y, p.conv, p.w, 8, &n, pf);
+    if (s == CUDNN_STATUS_SUCCESS)
+        for (int i = 0; i < n && pick < 0; ++i)
+            if (pf[i].status == CUDNN_STATUS_SUCCESS) pick = i;
+    if (pick < 0) {
+        s = cudnnGetConvolutionBackwardFilterAlgorithm_v7(dnn(), p.x, p.y, p.conv, p.w, 1, &n, pf);
+        if (s != CUDNN_STATUS_SUCCESS) return cudnn_status(s);
+        pick = 0;
+    }
+    p.bwd_filter = pf[pick].algo;
     s = cudnnGetConvolutionBackwardFilterWorkspaceSize(dnn(), p.x, p.y, p.conv, p.w, p.bwd_filter, &p.ws_filter);
     if (s != CUDNN_STATUS_SUCCESS) return cudnn_status(s);
     p.have_bwd = true;

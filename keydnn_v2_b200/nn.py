@@ -126,6 +126,7 @@ class BatchNorm2d(Module):
         self.beta = Parameter.from_numpy(np.zeros(num_features, dtype)) if affine else None
         self.running_mean = Tensor.zeros((num_features,), dtype)
         self.running_var = Tensor.ones((num_features,), dtype)
+        self.fused_relu = False     # set by Sequential when a ReLU follows: one kernel pair does both layers
 
     def parameters(self) -> List[Parameter]:
         return [self.gamma, self.beta] if self.affine else []
@@ -142,7 +143,8 @@ class BatchNorm2d(Module):
         ga, be = (self.gamma, self.beta) if self.affine else (None, None)
         lib.call(f"keydnn_cuda_bn2d_forward_{s}", x.data, ga.data if ga else None, be.data if be else None, y.data,
                  mean.data, invstd.data, self.running_mean.data, self.running_var.data, N, C, H * W,
-                 _cfloat(x.dtype, self.eps), _cfloat(x.dtype, self.momentum), 1 if self.training else 0)
+                 _cfloat(x.dtype, self.eps), _cfloat(x.dtype, self.momentum), 1 if self.training else 0,
+                 1 if self.fused_relu else 0)
         if x._needs_grad() or (self.affine and (ga.requires_grad or be.requires_grad)):
             y.requires_grad = True
 
@@ -150,8 +152,9 @@ class BatchNorm2d(Module):
                 dx = Tensor.empty(x.shape, x.dtype)
                 dga = Tensor.empty((C,), x.dtype) if self.affine else None
                 dbe = Tensor.empty((C,), x.dtype) if self.affine else None
-                lib.call(f"keydnn_cuda_bn2d_backward_{s}", x.data, ga.data if ga else None, g.data, mean.data, invstd.data,
-                         dx.data, dga.data if dga else None, dbe.data if dbe else None, N, C, H * W)
+                lib.call(f"keydnn_cuda_bn2d_backward_{s}", x.data, ga.data if ga else None, be.data if be else None, g.data,
+                         mean.data, invstd.data, dx.data, dga.data if dga else None, dbe.data if dbe else None, N, C,
+                         H * W, 1 if self.fused_relu else 0)
                 return (dx, dga, dbe) if self.affine else (dx,)
 
             y._ctx = Context((x, ga, be) if self.affine else (x,), backward_fn)
@@ -221,12 +224,24 @@ class Linear(Module):
 
 
 class Sequential(Module):
-    def __init__(self, *layers) -> None:
+    """Runs its layers in order (``models/_sequential.py:130-152``).  With ``fuse=True`` (default) a ReLU that
+    directly follows a BatchNorm2d is folded into that layer's kernels; results are bit-identical to the
+    two separate layers, three tensor passes forward and one backward disappear."""
+
+    def __init__(self, *layers, fuse: bool = True) -> None:
         self.layers = list(layers)
+        self._skip = set()
+        if fuse:
+            for i in range(len(self.layers) - 1):
+                a, b = self.layers[i], self.layers[i + 1]
+                if isinstance(a, BatchNorm2d) and isinstance(b, ReLU) and a.gamma is not None and a.gamma.dtype == np.float32:
+                    a.fused_relu = True
+                    self._skip.add(i + 1)
 
     def forward(self, x: Tensor) -> Tensor:
-        for layer in self.layers:
-            x = layer(x)
+        for i, layer in enumerate(self.layers):
+            if i not in self._skip:
+                x = layer(x)
         return x
 
 

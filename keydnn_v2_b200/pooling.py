@@ -165,11 +165,17 @@ class GlobalAvgPool2dFn:
 
 
 def _apply(fn, x: Tensor, **kw) -> Tensor:
-    ctx = Context((x,), lambda g: fn.backward(ctx, g))
-    y = fn.forward(ctx, x, **kw)
+    # `saved` is what forward fills and backward reads.  The graph node's closure refers to it, not
+    # to the node itself, so the node is not part of a reference cycle and its activations are
+    # released by reference counting as soon as the graph is dropped (the reference's modules close
+    # over their own Context, pooling/_pooling_module.py:183-198, and wait for the cyclic collector).
+    saved = Context((x,), None)
+    y = fn.forward(saved, x, **kw)
     if x._needs_grad():
         y.requires_grad = True
-        y._set_ctx(ctx)
+        node = Context((x,), lambda g: fn.backward(saved, g))
+        node.saved_meta = saved.saved_meta
+        y._set_ctx(node)
     return y
 
 

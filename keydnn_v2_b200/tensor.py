@@ -614,10 +614,12 @@ class Tensor:
     def _set_ctx(self, ctx: Optional[Context]) -> None:
         self._ctx = ctx
 
-    def backward(self, grad_out: Optional["Tensor"] = None) -> None:
+    def backward(self, grad_out: Optional["Tensor"] = None, *, retain_graph: bool = False) -> None:
         """Reverse topological walk (``tensor/_tensor.py:1601-1861``): seed with ``grad_out``
         (ones for a scalar), call each ``ctx.backward_fn``, add contributions that meet at
-        a tensor, store the result on leaves that require grad."""
+        a tensor, store the result on leaves that require grad.  Unless ``retain_graph`` is
+        set, every visited node drops its Context afterwards, which releases the saved
+        activations to the allocator at once."""
         if not self.requires_grad:
             raise RuntimeError("backward() on a tensor that does not require grad")
         if grad_out is None:
@@ -664,6 +666,8 @@ class Tensor:
                         raise RuntimeError(f"gradient shape {pg.shape} != parent shape {p.shape}")
                     prev = grads.get(id(p))
                     grads[id(p)] = pg if prev is None else prev + pg
+                if not retain_graph:
+                    node._ctx = None
 
 
 class Parameter(Tensor):

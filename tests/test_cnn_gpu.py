@@ -104,3 +104,26 @@ def test_momentum_training_reduces_the_loss():
     t = kd.Tensor.from_numpy(np.eye(10, dtype=np.float32)[rng.integers(0, 10, 32)])
     losses = [nn.train_step(model, opt, x, t).item() for _ in range(15)]
     assert np.isfinite(losses).all() and losses[-1] < 0.7 * losses[0], losses
+
+
+def test_fused_batchnorm_relu_is_bit_identical_to_the_two_layers():
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import nn
+
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((6, 5, 8, 12)).astype(np.float32)
+    g = rng.standard_normal(x.shape).astype(np.float32)
+    outs = []
+    for fuse in (True, False):
+        np.random.seed(0)
+        bn = nn.BatchNorm2d(5)
+        bn.gamma.copy_from_numpy(np.linspace(-1, 1.5, 5).astype(np.float32))
+        bn.beta.copy_from_numpy(np.linspace(0.3, -0.3, 5).astype(np.float32))
+        seq = nn.Sequential(bn, nn.ReLU(), fuse=fuse)
+        assert bn.fused_relu == fuse
+        tx = kd.Tensor.from_numpy(x, requires_grad=True)
+        y = seq(tx)
+        y.backward(kd.Tensor.from_numpy(g))
+        outs.append((y.to_numpy(), tx.grad.to_numpy(), bn.gamma.grad.to_numpy(), bn.beta.grad.to_numpy()))
+    for a, b in zip(*outs):
+        np.testing.assert_array_equal(a.view(np.uint32), b.view(np.uint32))
