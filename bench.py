@@ -215,11 +215,13 @@ def suite_table(lib, timer, peak: float, reps: int = 10, warm: int = 3) -> list[
     for op in ("add", "sub", "mul", "div", "gt"):
         timed(f"{op}_c3_f32", 3.0 * a.nbytes, lambda op=op: lib.call(f"keydnn_cuda_{op}_f32", a.data, b.data, y.data, n))
     timed("neg_c3_f32", 2.0 * a.nbytes, lambda: lib.call("keydnn_cuda_neg_f32", a.data, y.data, n))
-    y2 = T.empty((n,))
-    # mul backward = two products (g*b, g*a): 6 tensor passes; the minimum is 5
-    timed("mul_backward_c3_f32", 5.0 * a.nbytes, lambda: (lib.call("keydnn_cuda_mul_f32", y.data, b.data, y2.data, n),
-                                                         lib.call("keydnn_cuda_mul_f32", y.data, a.data, y2.data, n)))
-    del a, b, y, y2
+    ga, gb = T.empty((n,)), T.empty((n,))
+    # backward of mul / div: read g, a, b, write both gradients (5 tensor passes)
+    timed("mul_backward_c3_f32", 5.0 * a.nbytes, lambda: lib.call("keydnn_cuda_mul_backward_f32", y.data, a.data, b.data,
+                                                                 ga.data, gb.data, n))
+    timed("div_backward_c3_f32", 5.0 * a.nbytes, lambda: lib.call("keydnn_cuda_div_backward_f32", y.data, a.data, b.data,
+                                                                 ga.data, gb.data, n))
+    del a, b, y, ga, gb
     n = 25_165_824
     p = T.from_numpy(rng.standard_normal(n, dtype=np.float32))
     g = T.from_numpy((rng.standard_normal(n, dtype=np.float32) * np.float32(1e-2)))
@@ -430,8 +432,15 @@ def cnn_step_bench(lib, group, dist, steps: int, warmup: int, timer, batch: int 
     model = nn.small_cnn()
     opt = nn.SGD(model.parameters(), lr=0.01, momentum=0.9, weight_decay=1e-4, group=group)
     rng = np.random.default_rng(100 + rank)
-    hx = rng.standard_normal((batch, 3, 64, 64), dtype=np.float32)
-    ht = np.eye(10, dtype=np.float32)[rng.integers(0, 10, batch)]
+    def pinned(a: np.ndarray) -> np.ndarray:
+        p = ctypes.c_void_p(0)
+        lib.call("keydnn_cuda_host_alloc", ctypes.byref(p), a.nbytes)
+        out = np.frombuffer((ctypes.c_char * a.nbytes).from_address(p.value), dtype=a.dtype).reshape(a.shape)
+        out[...] = a
+        return out
+
+    hx = pinned(rng.standard_normal((batch, 3, 64, 64), dtype=np.float32))
+    ht = pinned(np.eye(10, dtype=np.float32)[rng.integers(0, 10, batch)])
     x, t = kd.Tensor.from_numpy(hx), kd.Tensor.from_numpy(ht)
 
     def sync() -> None:

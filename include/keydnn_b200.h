@@ -245,6 +245,14 @@ int keydnn_cuda_mul_scalar_inplace_f64(double* a, double alpha, int numel);
 /* additive: 64-bit element counts for mul */
 int keydnn_cuda_mul64_f32(const float* a, const float* b, float* y, int64_t n);
 int keydnn_cuda_mul64_f64(const double* a, const double* b, double* y, int64_t n);
+/* additive: both gradients of y = a*b (ga = g*b, gb = g*a) or y = a/b (ga = g/b, gb = (-(g*a))/(b*b)) in
+ * one pass, each operation rounded as in the reference closures
+ * (src/keydnn/infrastructure/tensor/mixins/arithmetic/_tensor_multiplication.py:98-103,
+ * _tensor_division.py:104-114); ga or gb may be NULL. */
+int keydnn_cuda_mul_backward_f32(const float* g, const float* a, const float* b, float* ga, float* gb, int64_t n);
+int keydnn_cuda_mul_backward_f64(const double* g, const double* a, const double* b, double* ga, double* gb, int64_t n);
+int keydnn_cuda_div_backward_f32(const float* g, const float* a, const float* b, float* ga, float* gb, int64_t n);
+int keydnn_cuda_div_backward_f64(const double* g, const double* a, const double* b, double* ga, double* gb, int64_t n);
 /* ref: NC/keydnn_fill_cuda.hpp:36-46 */
 int keydnn_cuda_fill_f32(float* y, int64_t numel, float value);
 int keydnn_cuda_fill_f64(double* y, int64_t numel, double value);

@@ -210,6 +210,78 @@ sgd_kernel(T* p, const T* g, T* v, int64_t n, T lr, T mu, T wd, T gscale, bool u
     }
 }
 
+// --- fused backward of mul and div ----------------------------------------------
+// The reference's closures run one kernel per product (tensor/mixins/arithmetic/
+// _tensor_multiplication.py:98-103: g*b, g*a; _tensor_division.py:104-114: g/b, then g*a, neg,
+// b*b, div), re-reading g, a, b for each.  One pass computes both gradients with the same
+// separately rounded operations: DIV == false: ga = g*b, gb = g*a;
+// DIV == true: ga = g/b, gb = (-(g*a)) / (b*b).  Either output may be null.
+template <typename T, bool DIV>
+__global__ void __launch_bounds__(kThreads)
+muldiv_backward_kernel(const T* __restrict__ g, const T* __restrict__ a, const T* __restrict__ b, T* ga, T* gb, int64_t n,
+                       bool vec) {
+    if (vec) {
+        constexpr int UNROLL = 2;
+        const int64_t n4 = n >> 2;
+        const int64_t tile = static_cast<int64_t>(kThreads) * UNROLL;
+        for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < n4;
+             base += static_cast<int64_t>(gridDim.x) * tile) {
+            Pack4<T> vg[UNROLL], va[UNROLL], vb[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int64_t p = base + u * kThreads + threadIdx.x;
+                if (p < n4) {
+                    vg[u] = kd::load4_stream(g + 4 * p);
+                    va[u] = kd::load4_stream(a + 4 * p);
+                    vb[u] = kd::load4_stream(b + 4 * p);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int64_t p = base + u * kThreads + threadIdx.x;
+                if (p < n4) {
+                    Pack4<T> ra, rb;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (DIV) {
+                            ra.v[k] = vg[u].v[k] / vb[u].v[k];
+                            rb.v[k] = (-Rn<T>::mul(vg[u].v[k], va[u].v[k])) / Rn<T>::mul(vb[u].v[k], vb[u].v[k]);
+                        } else {
+                            ra.v[k] = Rn<T>::mul(vg[u].v[k], vb[u].v[k]);
+                            rb.v[k] = Rn<T>::mul(vg[u].v[k], va[u].v[k]);
+                        }
+                    }
+                    if (ga) kd::store4(ga + 4 * p, ra);
+                    if (gb) kd::store4(gb + 4 * p, rb);
+                }
+            }
+        }
+    }
+    const int64_t done = vec ? ((n >> 2) << 2) : 0;
+    for (int64_t i = done + static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * kThreads) {
+        if (DIV) {
+            if (ga) ga[i] = g[i] / b[i];
+            if (gb) gb[i] = (-Rn<T>::mul(g[i], a[i])) / Rn<T>::mul(b[i], b[i]);
+        } else {
+            if (ga) ga[i] = Rn<T>::mul(g[i], b[i]);
+            if (gb) gb[i] = Rn<T>::mul(g[i], a[i]);
+        }
+    }
+}
+
+template <typename T, bool DIV>
+int launch_muldiv_backward(const T* g, const T* a, const T* b, T* ga, T* gb, int64_t n) {
+    if (!g || !a || !b || (!ga && !gb)) return static_cast<int>(cudaErrorInvalidDevicePointer);
+    if (n <= 0) return 0;
+    (void)cudaGetLastError();
+    const bool vec = kd::aligned_pack<T>(g) && kd::aligned_pack<T>(a) && kd::aligned_pack<T>(b) &&
+                     (!ga || kd::aligned_pack<T>(ga)) && (!gb || kd::aligned_pack<T>(gb));
+    const int64_t tiles = vec ? ((n >> 2) + kThreads * 2 - 1) / (kThreads * 2) : (n + kThreads - 1) / kThreads;
+    KD_LAUNCH_W((muldiv_backward_kernel<T, DIV>), 64, tiles, kThreads, 0, g, a, b, ga, gb, n, vec);
+    return kd::launch_status();
+}
+
 template <typename T>
 int launch_sgd(T* p, const T* g, T* v, int64_t n, T lr, T mu, T wd, T gscale) {
     if (!p || !g) return -1;
@@ -409,4 +481,18 @@ KD_API int keydnn_cuda_sgd_momentum_step_f32(float* p, const float* g, float* v,
 KD_API int keydnn_cuda_sgd_momentum_step_f64(double* p, const double* g, double* v, int64_t n, double lr,
                                              double momentum, double weight_decay, double grad_scale) {
     return launch_sgd<double>(p, g, v, n, lr, momentum, weight_decay, grad_scale);
+}
+
+// Additive: both gradients of a product / a quotient in one pass (see muldiv_backward_kernel).
+KD_API int keydnn_cuda_mul_backward_f32(const float* g, const float* a, const float* b, float* ga, float* gb, int64_t n) {
+    return launch_muldiv_backward<float, false>(g, a, b, ga, gb, n);
+}
+KD_API int keydnn_cuda_mul_backward_f64(const double* g, const double* a, const double* b, double* ga, double* gb, int64_t n) {
+    return launch_muldiv_backward<double, false>(g, a, b, ga, gb, n);
+}
+KD_API int keydnn_cuda_div_backward_f32(const float* g, const float* a, const float* b, float* ga, float* gb, int64_t n) {
+    return launch_muldiv_backward<float, true>(g, a, b, ga, gb, n);
+}
+KD_API int keydnn_cuda_div_backward_f64(const double* g, const double* a, const double* b, double* ga, double* gb, int64_t n) {
+    return launch_muldiv_backward<double, true>(g, a, b, ga, gb, n);
 }

@@ -258,6 +258,15 @@ class Tensor:
             self.native.call(f"keydnn_cuda_{name}_{suf}", self.data, arg, out.data, n)
         return out
 
+    @staticmethod
+    def _muldiv_backward(kind: str, g: "Tensor", a: "Tensor", b: "Tensor"):
+        ga = Tensor.empty(a.shape, a.dtype) if a.requires_grad else None
+        gb = Tensor.empty(b.shape, b.dtype) if b.requires_grad else None
+        if a.numel and (ga is not None or gb is not None):
+            a.native.call(f"keydnn_cuda_{kind}_backward_{_suffix(a.dtype)}", g.data, a.data, b.data,
+                          ga.data if ga is not None else None, gb.data if gb is not None else None, a.numel)
+        return (ga, gb)
+
     def _as_tensor_like(self, value: Number) -> "Tensor":
         """Scalar lifted to a filled tensor (``tensor/_tensor.py:722-754``)."""
         return Tensor.full(self.shape, value, self.dtype)
@@ -304,8 +313,8 @@ class Tensor:
                 a, b = self, other
 
                 def backward_fn(g: "Tensor"):
-                    with no_grad():     # _tensor_multiplication.py:98-103
-                        return (g * b if a.requires_grad else None, g * a if b.requires_grad else None)
+                    # (g*b, g*a) as in _tensor_multiplication.py:98-103, both in one pass over g, a, b
+                    return a._muldiv_backward("mul", g, a, b)
 
                 out._ctx = Context((a, b), backward_fn)
             return out
@@ -331,10 +340,8 @@ class Tensor:
                 a, b = self, other
 
                 def backward_fn(g: "Tensor"):
-                    with no_grad():     # _tensor_division.py:104-114
-                        ga = g / b if a.requires_grad else None
-                        gb = (-(g * a)) / (b * b) if b.requires_grad else None
-                    return (ga, gb)
+                    # (g/b, -(g*a)/(b*b)) as in _tensor_division.py:104-114, both in one pass
+                    return a._muldiv_backward("div", g, a, b)
 
                 out._ctx = Context((a, b), backward_fn)
             return out

@@ -153,3 +153,20 @@ def test_same_bits_as_reference_cuda_kernels(op):
         L.call(f"keydnn_cuda_{op}_f32", da.ptr, db.ptr, dy.ptr, n)
         outs.append(dy.get())
     assert_same_bits(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_fused_mul_div_backward_bit_exact(oracle, dtype):
+    """One pass instead of the reference's two (mul) / five (div) kernels, same rounded operations."""
+    lib = native()
+    for n in (3, 1025, (1 << 18) + 5):
+        a, b = _inputs(n, dtype, 21)
+        g = np.random.default_rng(n).standard_normal(n).astype(dtype)
+        dg, da, db = Buf(lib, g), Buf(lib, a), Buf(lib, b)
+        for kind, want in (("mul", oracle.mul_backward(g, a, b)), ("div", oracle.div_backward(g, a, b))):
+            dga, dgb = Buf(lib, shape=(n,), dtype=dtype, fill=0xFF), Buf(lib, shape=(n,), dtype=dtype, fill=0xFF)
+            lib.call(f"keydnn_cuda_{kind}_backward_{suf(dtype)}", dg.ptr, da.ptr, db.ptr, dga.ptr, dgb.ptr, n)
+            assert_same_bits(dga.get(), want[0].astype(dtype), err_msg=kind)
+            assert_same_bits(dgb.get(), want[1].astype(dtype), err_msg=kind)
+            lib.call(f"keydnn_cuda_{kind}_backward_{suf(dtype)}", dg.ptr, da.ptr, db.ptr, None, dgb.ptr, n)   # one side only
+            assert_same_bits(dgb.get(), want[1].astype(dtype), err_msg=kind)
