@@ -33,6 +33,49 @@ OPS = [(op, ax) for op in ("sum", "mean", "max") for ax in (0, 1, None)]
 METRIC = "fwd+bwd HBM GB/s (sum/mean/max reductions over axis 0, axis 1, all axes; fp32 8192^2 + fp64 4096^2)"
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of each kernel of the step, from one
+# `ncu --set full` capture at these sizes (profiles/ncu_full_every_kernel_b200.md).  Writes are under-counted there:
+# lines still dirty in L2 when a kernel ends are not in its DRAM count.
+NCU_TRAFFIC_BYTES = {
+    "sum_axis0_fwd_f32": 272715000,
+    "sum_axis0_fwd_f64": 137865000,
+    "sum_axis0_bwd_f32": 209817000,
+    "sum_axis0_bwd_f64": 75364000,
+    "sum_axis1_fwd_f32": 272213000,
+    "sum_axis1_fwd_f64": 137958000,
+    "sum_axis1_bwd_f32": 211139000,
+    "sum_axis1_bwd_f64": 77029000,
+    "sum_all_fwd_f32": 273015000,
+    "sum_all_fwd_f64": 140446000,
+    "sum_all_bwd_f32": 210100000,
+    "sum_all_bwd_f64": 74301000,
+    "mean_axis0_fwd_f32": 271950000,
+    "mean_axis0_fwd_f64": 138020000,
+    "mean_axis0_bwd_f32": 209788000,
+    "mean_axis0_bwd_f64": 75297000,
+    "mean_axis1_fwd_f32": 272030000,
+    "mean_axis1_fwd_f64": 137968000,
+    "mean_axis1_bwd_f32": 212215000,
+    "mean_axis1_bwd_f64": 76049000,
+    "mean_all_fwd_f32": 271924000,
+    "mean_all_fwd_f64": 137805000,
+    "mean_all_bwd_f32": 209136000,
+    "mean_all_bwd_f64": 75153000,
+    "max_axis0_fwd_f32": 275074000,
+    "max_axis0_fwd_f64": 139061000,
+    "max_axis0_bwd_f32": 209138000,
+    "max_axis0_bwd_f64": 76473000,
+    "max_axis1_fwd_f32": 271911000,
+    "max_axis1_fwd_f64": 138318000,
+    "max_axis1_bwd_f32": 209431000,
+    "max_axis1_bwd_f64": 75042000,
+    "max_all_fwd_f32": 271762000,
+    "max_all_fwd_f64": 138227000,
+    "max_all_bwd_f32": 209150000,
+    "max_all_bwd_f64": 74351000,
+}
+
+
 def _env_int(name: str, default: int) -> int:
     try:
         return int(os.environ.get(name, default))
@@ -339,18 +382,37 @@ def run_ours(args) -> None:
     host_out = {id(r32): np.empty(max(ROWS32, COLS32), np.float32), id(r64): np.empty(max(ROWS64, COLS64), np.float64)}
     d2h = [0]
 
+    # host -> device copies go on their own stream: the second matrix is still arriving while the
+    # kernels of the first one run; results are read back once all kernels of the step are enqueued
+    main_stream, copy_stream = ctypes.c_uint64(0), ctypes.c_uint64(0)
+    lib.call("keydnn_cuda_get_stream", ctypes.byref(main_stream))
+    lib.call("keydnn_cuda_stream_create", ctypes.byref(copy_stream))
+    arrived = []
+    for _ in reducers:
+        e = ctypes.c_uint64(0)
+        lib.call("keydnn_cuda_event_create", ctypes.byref(e))
+        arrived.append(e.value)
+
     def e2e_step() -> None:
         d2h[0] = 0
-        for (red, _), src in zip(reducers, (p32, p64)):
-            red.x.copy_from_numpy(src)
+        lib.call("keydnn_cuda_set_stream", copy_stream.value)
+        for (red, _), src, ev in zip(reducers, (p32, p64), arrived):
+            lib.call("keydnn_cuda_memcpy_h2d_async", red.x.data, src.ctypes.data, src.nbytes)
+            lib.call("keydnn_cuda_event_record", ev)
+        lib.call("keydnn_cuda_set_stream", main_stream.value)
+        results = []
+        for (red, _), ev in zip(reducers, arrived):
+            lib.call("keydnn_cuda_stream_wait_event", ev)
             for op, ax in OPS:
                 ptr, n = red.forward(op, ax)
                 red.backward(op, ax)
-                red.wait(op, ax)
-                nb = n * red.dt.itemsize
-                lib.call("keydnn_cuda_memcpy_d2h", host_out[id(red)].ctypes.data, ptr, nb)
-                d2h[0] += nb
-            # the step's gradient result: first row of the last gradient
+                results.append((red, op, ax, ptr, n))
+        for red, op, ax, ptr, n in results:
+            red.wait(op, ax)
+            nb = n * red.dt.itemsize
+            lib.call("keydnn_cuda_memcpy_d2h", host_out[id(red)].ctypes.data, ptr, nb)
+            d2h[0] += nb
+        for red, _ in reducers:      # the step's gradient result: first row of the last gradient
             lib.call("keydnn_cuda_memcpy_d2h", host_out[id(red)].ctypes.data, red.gx.data, red.cols * red.dt.itemsize)
             d2h[0] += red.cols * red.dt.itemsize
 
@@ -397,7 +459,9 @@ def run_ours(args) -> None:
         if table is not None:
             top = max(table, key=lambda r: r["us"])
             line["roofline"] = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["gbs"], "peak": peak,
-                                "unit": "GB/s", "frac": top["frac"], "traffic": None, "peak_source": peak_src,
+                                "unit": "GB/s", "frac": top["frac"], "traffic": NCU_TRAFFIC_BYTES.get(top["kernel"]),
+                                "traffic_unit": "bytes per launch (ncu dram read+write, captured once; see profiles/)",
+                                "algorithmic_bytes": top["bytes"], "peak_source": peak_src,
                                 "frac_of_nominal_8000": round(top["gbs"] / 8000.0, 4)}
             line["kernels"] = table
             if suite is not None:
