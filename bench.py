@@ -1,4 +1,4 @@
-"""Benchmark of the reduction hot path (BASELINE.json configs[1]) on N GPUs of one node.
+"""Benchmark of the reduction hot path (configuration [1] of the benchmark definition) on N GPUs of one node.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--kernels all|none]
 
@@ -34,7 +34,7 @@ METRIC = "fwd+bwd HBM GB/s (sum/mean/max reductions over axis 0, axis 1, all axe
 
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of each kernel of the step, from one
-# `ncu --set full` capture at these sizes (profiles/ncu_full_every_kernel_b200.md).  Writes are under-counted there:
+# `ncu --set full` capture at these sizes (summary committed under profiles/).  Writes are under-counted there:
 # lines still dirty in L2 when a kernel ends are not in its DRAM count.
 NCU_TRAFFIC_BYTES = {
     "sum_axis0_fwd_f32": 272715000,
@@ -198,7 +198,7 @@ def kernel_table(lib, reducers, timer, reps: int, peak: float) -> list[dict]:
 
 
 def suite_table(lib, timer, peak: float, reps: int = 10, warm: int = 3) -> list[dict]:
-    """Per-kernel device time for the other BASELINE.json configurations (pool, elementwise,
+    """Per-kernel device time for the other benchmark configurations (pool, elementwise,
     optimizer step), each launched `reps` times back to back on inputs larger than L2."""
     import keydnn_v2_b200 as kd
     from keydnn_v2_b200 import pooling
@@ -460,7 +460,7 @@ def run_ours(args) -> None:
             top = max(table, key=lambda r: r["us"])
             line["roofline"] = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["gbs"], "peak": peak,
                                 "unit": "GB/s", "frac": top["frac"], "traffic": NCU_TRAFFIC_BYTES.get(top["kernel"]),
-                                "traffic_unit": "bytes per launch (ncu dram read+write, captured once; see profiles/)",
+                                "traffic_unit": "bytes per launch (ncu dram read+write, captured once; summary under profiles/)",
                                 "algorithmic_bytes": top["bytes"], "peak_source": peak_src,
                                 "frac_of_nominal_8000": round(top["gbs"] / 8000.0, 4)}
             line["kernels"] = table

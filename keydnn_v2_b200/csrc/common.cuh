@@ -1,8 +1,9 @@
 // Shared device/host helpers for the sm_100a KeyDNN operator library.
 //
-// Everything in this library is HBM-bound: kernels are written around 16-byte
-// global accesses, enough independent loads per thread to cover DRAM latency,
-// and grids sized from the SM count of the device the call runs on.
+// Everything in this library is HBM-bound: kernels are written around 16- and
+// 32-byte global accesses, enough independent loads per thread to cover DRAM
+// latency, and grids sized from the SM count and the measured occupancy of the
+// device the call runs on.
 #pragma once
 
 #include <cuda_runtime.h>

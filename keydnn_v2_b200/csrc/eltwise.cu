@@ -6,7 +6,7 @@
 //   thread, 4-byte accesses, launch_1d :65-77), keydnn_mul.cu:8-131 and
 //   keydnn_fill_cuda.cu:19-53,
 // with one streaming kernel template: every thread moves UNROLL independent
-// 4-element packets (16-byte accesses) per trip of a grid-stride loop, all loads
+// 4-element packets (16-byte accesses for float, 32-byte for double) per trip of a grid-stride loop, all loads
 // of a trip issued before the first use.  Arithmetic is one correctly rounded
 // IEEE operation per element exactly as in the reference (no fast-math, no FMA
 // contraction), so results are bit-identical to it.
@@ -32,7 +32,7 @@ struct OpLe { template <typename T> __device__ float operator()(T a, T b) const 
 struct OpEq { template <typename T> __device__ float operator()(T a, T b) const { return a == b ? 1.0f : 0.0f; } };
 struct OpNe { template <typename T> __device__ float operator()(T a, T b) const { return a != b ? 1.0f : 0.0f; } };
 
-// Packet path: all pointers 16-byte aligned. `a` may alias `y` (in-place ops):
+// Packet path: all pointers aligned to one packet (16 bytes for float, 32 for double). `a` may alias `y` (in-place ops):
 // a thread reads its own packets before it writes them and nobody else touches
 // them, and the loads are ordinary coherent loads.
 template <typename TI, typename TO, int MODE, int UNROLL, typename Op>
@@ -97,7 +97,7 @@ int launch_ew(const TI* a, const TI* b, TI alpha, TO* y, int64_t n, Op op) {
 // --- fill -------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(kThreads) fill_kernel(T* y, int64_t n, T value, int head) {
-    // `head` elements bring y up to a 16-byte boundary; packets follow; tail last.
+    // `head` elements bring y up to a packet boundary; packets follow; tail last.
     const int64_t body = n - head;
     const int64_t n4 = body >> 2;
     T* yb = y + head;

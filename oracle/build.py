@@ -13,6 +13,7 @@
 """
 from __future__ import annotations
 
+import os
 import shutil
 import subprocess
 import sys
@@ -40,6 +41,8 @@ REF_CUDA_SOURCES = [
     "keydnn_tensor_bias_add.cu",
     "keydnn_transpose2d.cu",
 ]
+# where a checkout of the reference project is looked for when no path is given
+DEFAULT_REF_ROOT = Path(os.environ.get("KEYDNN_REFERENCE_ROOT", "/root/reference"))
 REF_CUDA_SUBDIR = "src/keydnn/infrastructure/native_cuda/keydnn_v2_cuda_native/KeyDNNV2CudaNative"
 REF_NATIVE_SUBDIR = "src/keydnn/infrastructure/native/src"
 
@@ -59,9 +62,9 @@ def build_oracle(force: bool = False) -> Path:
     return ORACLE_LIB
 
 
-def build_reference(ref_root: str | Path = "/root/reference", force: bool = False) -> dict[str, Path]:
+def build_reference(ref_root: str | Path | None = None, force: bool = False) -> dict[str, Path]:
     """Compile the reference's own pooling .cpp and hot-path .cu files into ``oracle/_ref``."""
-    ref_root = Path(ref_root)
+    ref_root = Path(ref_root) if ref_root is not None else DEFAULT_REF_ROOT
     out: dict[str, Path] = {}
     if not ref_root.exists():
         return out

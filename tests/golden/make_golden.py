@@ -1,7 +1,7 @@
 """Generate ``tests/golden/ref_cpu_golden.npz`` by RUNNING THE REFERENCE ITSELF.
 
 Run from the repository root, on a machine that has a checkout of the reference
-project (default ``/root/reference``):
+project (its path: first argument, else the KEYDNN_REFERENCE_ROOT environment variable):
 
     python tests/golden/make_golden.py [REFERENCE_ROOT]
 
@@ -26,7 +26,10 @@ from pathlib import Path
 import numpy as np
 
 REPO = Path(__file__).resolve().parents[2]
-REF_ROOT = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+sys.path.insert(0, str(REPO))
+from oracle.build import DEFAULT_REF_ROOT  # noqa: E402
+
+REF_ROOT = Path(sys.argv[1]) if len(sys.argv) > 1 else DEFAULT_REF_ROOT
 sys.dont_write_bytecode = True
 sys.path.insert(0, str(REF_ROOT / "src"))
 sys.path.insert(0, str(REPO))
