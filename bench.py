@@ -435,9 +435,12 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), float(t[1])
 
-    # per-kernel timings run on every rank (the sharded kernels contain collectives); rank 0 reports its own
+    # per-kernel timings run on every rank; rank 0 reports its own
     peak, peak_src = measured_peak_gbs()
-    table = kernel_table(lib, reducers, timer, 20, peak) if args.kernels != "none" else None
+    # (at N > 1 the table times the local kernels alone: same shards, no exchange behind them)
+    local = reducers if world == 1 else [(ShardedReductions(red.x, distributed.single(lib)), tag) for red, tag in reducers]
+    table = kernel_table(lib, local, timer, 20, peak) if args.kernels != "none" else None
+    del local
     suite = suite_table(lib, timer, peak) if args.kernels == "suite" else None
     line = None
     if rank == 0:
