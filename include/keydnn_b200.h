@@ -60,6 +60,14 @@ int keydnn_cuda_event_synchronize(uint64_t ev);
 int keydnn_cuda_stream_wait_event(uint64_t ev); /* later work on the library stream waits for ev */
 int keydnn_cuda_event_elapsed_ms(uint64_t start, uint64_t stop, float* out_ms);
 int keydnn_cuda_event_destroy(uint64_t ev);
+/* additive: record what is enqueued on the library stream (a created stream, not the default one) between
+ * begin and end into a CUDA graph; replay with one launch.  Warm the work up eagerly on that stream first.
+ * Blocks allocated during the recording stay reserved for the graph until graph_destroy.
+ * -3: library stream is the default stream; -4: a recording or a graph already exists on this device. */
+int keydnn_cuda_graph_capture_begin(void);
+int keydnn_cuda_graph_capture_end(uint64_t* out_exec);
+int keydnn_cuda_graph_launch(uint64_t exec);
+int keydnn_cuda_graph_destroy(uint64_t exec);
 int keydnn_cuda_device_count(int* out);
 int keydnn_cuda_sm_count(int* out);
 const char* keydnn_cuda_error_string(int code);

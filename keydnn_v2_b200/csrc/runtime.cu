@@ -20,6 +20,7 @@
 #include <map>
 #include <mutex>
 #include <unordered_map>
+#include <unordered_set>
 #include <vector>
 
 namespace {
@@ -35,6 +36,12 @@ struct DevicePool {
     size_t bytes_in_use = 0;
     size_t n_driver_mallocs = 0;
     size_t n_requests = 0;
+    // Stream capture: blocks handed out while a graph is being recorded belong to that graph.
+    // They may be recycled among the tensors of the recording (the graph keeps their order),
+    // but never leave it: a replay writes to these addresses whoever holds them.
+    bool capturing = false;
+    std::multimap<size_t, void*> capture_free;         // freed during the recording, reusable inside it
+    std::unordered_map<void*, size_t> graph_blocks;    // every block owned by a recorded graph
 };
 
 struct DeviceState {
@@ -162,6 +169,18 @@ KD_API int keydnn_cuda_malloc(std::uint64_t* out_ptr, std::size_t nbytes) {
         return 0;
     }
     const size_t want = round_size(nbytes);
+    if (p.capturing) {
+        auto ct = p.capture_free.lower_bound(want);
+        if (ct != p.capture_free.end() && ct->first <= want + want / 2 + kGranule) {
+            void* q = ct->second;
+            size_t sz = ct->first;
+            p.capture_free.erase(ct);
+            p.live.emplace(q, sz);
+            p.bytes_in_use += sz;
+            *out_ptr = reinterpret_cast<std::uint64_t>(q);
+            return 0;
+        }
+    }
     auto it = p.free_blocks.lower_bound(want);
     // Accept a cached block only if it wastes less than half of itself.
     if (it != p.free_blocks.end() && it->first <= want + want / 2 + kGranule) {
@@ -170,6 +189,7 @@ KD_API int keydnn_cuda_malloc(std::uint64_t* out_ptr, std::size_t nbytes) {
         p.free_blocks.erase(it);
         p.live.emplace(q, sz);
         p.bytes_in_use += sz;
+        if (p.capturing) p.graph_blocks.emplace(q, sz);
         *out_ptr = reinterpret_cast<std::uint64_t>(q);
         return 0;
     }
@@ -189,6 +209,7 @@ KD_API int keydnn_cuda_malloc(std::uint64_t* out_ptr, std::size_t nbytes) {
     p.bytes_reserved += want;
     p.bytes_in_use += want;
     p.live.emplace(q, want);
+    if (p.capturing) p.graph_blocks.emplace(q, want);
     *out_ptr = reinterpret_cast<std::uint64_t>(q);
     return 0;
 }
@@ -217,6 +238,11 @@ KD_API int keydnn_cuda_free(std::uint64_t ptr) {
     size_t sz = it->second;
     p.live.erase(it);
     p.bytes_in_use -= sz;
+    if (p.graph_blocks.count(q)) {
+        // owned by a recorded graph: reusable only inside the recording, never by anybody else
+        if (p.capturing) p.capture_free.emplace(sz, q);
+        return 0;
+    }
     p.free_blocks.emplace(sz, q);
     return 0;
 }
@@ -349,6 +375,72 @@ KD_API int keydnn_cuda_event_elapsed_ms(std::uint64_t start, std::uint64_t stop,
 KD_API int keydnn_cuda_event_destroy(std::uint64_t ev) {
     if (!ev) return 0;
     return kd::status(cudaEventDestroy(reinterpret_cast<cudaEvent_t>(ev)));
+}
+
+// Additive: record everything enqueued on the library stream between begin and end into a CUDA
+// graph and replay it with one launch.  The library stream must be a created stream (not the
+// legacy default stream); run the work eagerly on that stream a few times first so that plans,
+// scratch and the allocator are warm: the recording itself must not need cudaMalloc.  Device
+// blocks allocated during the recording stay reserved for the graph until graph_destroy.
+// One recording at a time, one graph alive per device.
+KD_API int keydnn_cuda_graph_capture_begin() {
+    if (!g_stream) return -3;                       // the legacy default stream cannot be captured
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        DevicePool& p = state().pool;
+        if (p.capturing || !p.graph_blocks.empty()) return -4;
+        p.capturing = true;
+    }
+    cudaError_t st = cudaStreamBeginCapture(g_stream, cudaStreamCaptureModeRelaxed);
+    if (st != cudaSuccess) {
+        std::lock_guard<std::mutex> lk(g_mu);
+        state().pool.capturing = false;
+    }
+    return kd::status(st);
+}
+
+KD_API int keydnn_cuda_graph_capture_end(std::uint64_t* out_exec) {
+    if (!out_exec) return -1;
+    *out_exec = 0;
+    cudaGraph_t graph = nullptr;
+    cudaError_t st = cudaStreamEndCapture(g_stream, &graph);
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        DevicePool& p = state().pool;
+        p.capturing = false;
+        p.capture_free.clear();                      // those blocks stay in graph_blocks
+        if (st != cudaSuccess || !graph) {           // failed recording: give its blocks back
+            for (auto& kv : p.graph_blocks)
+                if (!p.live.count(kv.first)) p.free_blocks.emplace(kv.second, kv.first);
+            p.graph_blocks.clear();
+        }
+    }
+    if (st != cudaSuccess) { (void)cudaGetLastError(); return kd::status(st); }
+    cudaGraphExec_t exec = nullptr;
+    st = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (st != cudaSuccess) return kd::status(st);
+    *out_exec = reinterpret_cast<std::uint64_t>(exec);
+    return 0;
+}
+
+KD_API int keydnn_cuda_graph_launch(std::uint64_t exec) {
+    if (!exec) return -1;
+    return kd::status(cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(exec), g_stream));
+}
+
+KD_API int keydnn_cuda_graph_destroy(std::uint64_t exec) {
+    cudaError_t st = cudaSuccess;
+    if (exec) {
+        cudaStreamSynchronize(g_stream);
+        st = cudaGraphExecDestroy(reinterpret_cast<cudaGraphExec_t>(exec));
+    }
+    std::lock_guard<std::mutex> lk(g_mu);
+    DevicePool& p = state().pool;
+    for (auto& kv : p.graph_blocks)
+        if (!p.live.count(kv.first)) p.free_blocks.emplace(kv.second, kv.first);   // live ones return on their free
+    p.graph_blocks.clear();
+    return kd::status(st);
 }
 
 // Additive: device facts for the harness.

@@ -127,3 +127,33 @@ def test_fused_batchnorm_relu_is_bit_identical_to_the_two_layers():
         outs.append((y.to_numpy(), tx.grad.to_numpy(), bn.gamma.grad.to_numpy(), bn.beta.grad.to_numpy()))
     for a, b in zip(*outs):
         np.testing.assert_array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_graphed_training_step_follows_the_eager_one():
+    """A CUDA-graph replay of the step must train exactly like the eager step sequence."""
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import nn
+
+    rng = np.random.default_rng(11)
+    hx = rng.standard_normal((16, 3, 32, 32)).astype(np.float32)
+    ht = np.eye(10, dtype=np.float32)[rng.integers(0, 10, 16)]
+    losses = {}
+    for mode in ("eager", "graph"):
+        np.random.seed(7)
+        model = nn.small_cnn()
+        opt = nn.SGD(model.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
+        x, t = kd.Tensor.from_numpy(hx), kd.Tensor.from_numpy(ht)
+        if mode == "eager":
+            losses[mode] = [nn.train_step(model, opt, x, t).item() for _ in range(8)]
+        else:
+            g = nn.GraphedTrainStep(model, opt, x, t, warmup=3)       # 3 eager + 1 recorded (not executed) step
+            try:
+                seq = [g.run().item() for _ in range(5)]
+            finally:
+                g.close()
+            losses[mode] = seq
+            after = nn.train_step(model, opt, x, t).item()            # eager again after the graph is gone
+            assert np.isfinite(after)
+    # graph replays 1..5 correspond to eager steps 4..8 (three warm-up steps came first)
+    np.testing.assert_allclose(losses["graph"], losses["eager"][3:8], rtol=2e-3, atol=1e-5)
+    assert losses["eager"][-1] < losses["eager"][0]
