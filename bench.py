@@ -272,6 +272,60 @@ def suite_table(lib, timer, peak: float, reps: int = 10, warm: int = 3) -> list[
     timed("sgd_momentum_step_c3_f32", 5.0 * p.nbytes, lambda: lib.call(
         "keydnn_cuda_sgd_momentum_step_f32", p.data, g.data, v.data, n, ctypes.c_float(0.01), ctypes.c_float(0.9),
         ctypes.c_float(1e-4), ctypes.c_float(1.0)))
+    # Adam on the same vector: read p, g, m, v, write p, m, v (7 passes)
+    m = T.zeros((n,))
+    cf = ctypes.c_float
+    timed("adam_step_c3_f32", 7.0 * p.nbytes, lambda: lib.call(
+        "keydnn_cuda_adam_step_f32", p.data, g.data, m.data, v.data, n, cf(1e-3), cf(0.9), cf(0.999), cf(1e-8), cf(1e-4),
+        cf(0.1), cf(0.001), cf(0.1), cf(0.001), cf(1.0)))
+    del p, g, v, m
+    # activations, softmax and losses on 2^27 fp32 elements (537 MB per tensor)
+    n = 1 << 27
+    x = T.from_numpy(rng.standard_normal(n, dtype=np.float32))
+    y, gx = T.empty((n,)), T.empty((n,))
+    for name in ("exp", "log", "sqrt", "sigmoid_forward", "tanh_forward"):
+        count = n if name != "exp" else ctypes.c_int(n)
+        timed(f"{name}_f32", 2.0 * x.nbytes, lambda name=name, count=count: lib.call(f"keydnn_cuda_{name}_f32", x.data, y.data, count))
+    timed("relu_forward_f32", 2.0 * x.nbytes, lambda: lib.call("keydnn_cuda_relu_forward_f32", x.data, y.data, None, n))
+    timed("leaky_relu_forward_f32", 2.0 * x.nbytes, lambda: lib.call("keydnn_cuda_leaky_relu_forward_f32", x.data, y.data, cf(0.1), n))
+    for name in ("sigmoid_backward", "tanh_backward", "relu_backward", "sqrt_backward"):
+        timed(f"{name}_f32", 3.0 * x.nbytes, lambda name=name: lib.call(f"keydnn_cuda_{name}_f32", x.data, y.data, gx.data, n))
+    for rows_, cols_ in ((1 << 17, 1 << 10), (1 << 23, 16), (1 << 13, 1 << 14)):
+        timed(f"softmax_fwd_{rows_}x{cols_}_f32", 2.0 * x.nbytes, lambda r=rows_, c=cols_: lib.call(
+            "keydnn_cuda_softmax_forward_f32", x.data, y.data, r, c, 1))
+        timed(f"softmax_bwd_{rows_}x{cols_}_f32", 3.0 * x.nbytes, lambda r=rows_, c=cols_: lib.call(
+            "keydnn_cuda_softmax_backward_f32", x.data, y.data, gx.data, r, c, 1))
+    loss = T.empty(())
+    pr = T.from_numpy(rng.uniform(0.05, 0.95, n).astype(np.float32))
+    timed("sqdiff_forward_mean_f32", 2.0 * x.nbytes, lambda: lib.call("keydnn_cuda_sqdiff_forward_f32", pr.data, x.data, None,
+                                                                     loss.data, n, 1))
+    timed("bce_forward_f32", 2.0 * x.nbytes, lambda: lib.call("keydnn_cuda_bce_forward_f32", pr.data, y.data, loss.data, n))
+    timed("bce_backward_f32", 3.0 * x.nbytes, lambda: lib.call("keydnn_cuda_bce_backward_f32", pr.data, y.data, None, gx.data, n))
+    timed("cce_forward_f32", 2.0 * x.nbytes, lambda: lib.call("keydnn_cuda_cce_forward_f32", pr.data, y.data, loss.data, n, 1 << 17))
+    timed("cce_backward_f32", 3.0 * x.nbytes, lambda: lib.call("keydnn_cuda_cce_backward_f32", pr.data, y.data, None, gx.data, n,
+                                                             1 << 17))
+    del x, y, gx, pr
+    # layer glue: bias add, broadcast, un-broadcast, transpose on the CNN's activation shape
+    N_, C_, HW_ = 256, 32, 64 * 64
+    act = T.from_numpy(rng.standard_normal((N_, C_, HW_), dtype=np.float32))
+    out = T.empty(act.shape)
+    bias = T.from_numpy(rng.standard_normal(C_, dtype=np.float32))
+    i64 = ctypes.c_int64
+    in_shape, out_shape = (i64 * 3)(N_, C_, HW_), (i64 * 3)(1, C_, 1)
+    chan = T.empty((C_,))
+    timed("sum_to_shape_NCHW_to_C_f32", float(act.nbytes), lambda: lib.call(
+        "keydnn_cuda_sum_to_shape_f32", act.data, chan.data, in_shape, out_shape, 3))
+    timed("broadcast_to_C_to_NCHW_f32", float(act.nbytes), lambda: lib.call(
+        "keydnn_cuda_broadcast_to_f32", bias.data, out.data, out_shape, 3, in_shape, 3))
+    xb = T.from_numpy(rng.standard_normal((1 << 16, 1024), dtype=np.float32))
+    yb = T.empty(xb.shape)
+    b1k = T.from_numpy(rng.standard_normal(1024, dtype=np.float32))
+    timed("bias_add_65536x1024_f32", 2.0 * xb.nbytes, lambda: lib.call("keydnn_cuda_bias_add_f32", xb.data, b1k.data, yb.data,
+                                                                      1 << 16, 1024))
+    del xb, yb
+    mat = T.from_numpy(rng.standard_normal((8192, 4096), dtype=np.float32))
+    matT = T.empty((4096, 8192))
+    timed("transpose2d_8192x4096_f32", 2.0 * mat.nbytes, lambda: lib.call("keydnn_cuda_transpose2d_f32", mat.data, matT.data, 8192, 4096))
     return rows
 
 

@@ -312,6 +312,78 @@ int keydnn_cuda_bn2d_backward_f64(const double* x, const double* gamma, const do
                                   double* grad_beta, int N, int C, int64_t HW, int relu);
 
 /* ------------------------------------------------------------------------- */
+/* exp / log / sqrt, activations, losses, Adam.                                 */
+/* ref: NC/keydnn_cuda_ops.hpp (keydnn_cuda_exp_*; kernel keydnn_cuda_exp.cu:5-40) is the only unary
+ * export of the reference.  Everything else here is additive: the reference builds these from chains of
+ * one-op tensor kernels (src/keydnn/infrastructure/_function.py:54-612, _losses.py:44-408,
+ * optimizers/_adam.py:170-220) or on the host (tensor/mixins/unary/_tensor_log.py:77,
+ * _tensor_sqrt.py:81-91); each entry is one pass with the same separately rounded operations.        */
+/* ------------------------------------------------------------------------- */
+/* status as in the reference: 1 numel < 0, 2 null pointer, 3 launch failure */
+int keydnn_cuda_exp_f32(const float* x, float* y, int numel);
+int keydnn_cuda_exp_f64(const double* x, double* y, int numel);
+/* additive */
+int keydnn_cuda_log_f32(const float* x, float* y, int64_t n);
+int keydnn_cuda_sqrt_f32(const float* x, float* y, int64_t n);
+int keydnn_cuda_sqrt_backward_f32(const float* grad_out, const float* y, float* grad_x, int64_t n);          /* g * (0.5 / y) */
+int keydnn_cuda_sigmoid_forward_f32(const float* x, float* y, int64_t n);                                  /* 1 / (exp(-x) + 1) */
+int keydnn_cuda_sigmoid_backward_f32(const float* grad_out, const float* y, float* grad_x, int64_t n);        /* (g*y) * ((-y) + 1) */
+int keydnn_cuda_tanh_forward_f32(const float* x, float* y, int64_t n);                                     /* (e^x - e^-x) / (e^x + e^-x) */
+int keydnn_cuda_tanh_backward_f32(const float* grad_out, const float* y, float* grad_x, int64_t n);           /* g - (y*y)*g */
+int keydnn_cuda_relu_forward_f32(const float* x, float* y, float* mask_or_null, int64_t n);                   /* mask = x > 0; y = x*mask */
+int keydnn_cuda_relu_backward_f32(const float* grad_out, const float* x, float* grad_x, int64_t n);           /* g * (x > 0) */
+int keydnn_cuda_leaky_relu_forward_f32(const float* x, float* y, float alpha, int64_t n);
+int keydnn_cuda_leaky_relu_backward_f32(const float* grad_out, const float* x, float* grad_x, float alpha, int64_t n);
+int keydnn_cuda_log_f64(const double* x, double* y, int64_t n);
+int keydnn_cuda_sqrt_f64(const double* x, double* y, int64_t n);
+int keydnn_cuda_sqrt_backward_f64(const double* grad_out, const double* y, double* grad_x, int64_t n);          /* g * (0.5 / y) */
+int keydnn_cuda_sigmoid_forward_f64(const double* x, double* y, int64_t n);                                  /* 1 / (exp(-x) + 1) */
+int keydnn_cuda_sigmoid_backward_f64(const double* grad_out, const double* y, double* grad_x, int64_t n);        /* (g*y) * ((-y) + 1) */
+int keydnn_cuda_tanh_forward_f64(const double* x, double* y, int64_t n);                                     /* (e^x - e^-x) / (e^x + e^-x) */
+int keydnn_cuda_tanh_backward_f64(const double* grad_out, const double* y, double* grad_x, int64_t n);           /* g - (y*y)*g */
+int keydnn_cuda_relu_forward_f64(const double* x, double* y, double* mask_or_null, int64_t n);                   /* mask = x > 0; y = x*mask */
+int keydnn_cuda_relu_backward_f64(const double* grad_out, const double* x, double* grad_x, int64_t n);           /* g * (x > 0) */
+int keydnn_cuda_leaky_relu_forward_f64(const double* x, double* y, double alpha, int64_t n);
+int keydnn_cuda_leaky_relu_backward_f64(const double* grad_out, const double* x, double* grad_x, double alpha, int64_t n);
+/* softmax along the middle axis of a dense (outer, len, inner) view; inner = 1 for the last axis */
+int keydnn_cuda_softmax_forward_f32(const float* x, float* y, int64_t outer, int64_t len, int64_t inner);
+int keydnn_cuda_softmax_backward_f32(const float* grad_out, const float* y, float* grad_x, int64_t outer, int64_t len,
+                                     int64_t inner);
+int keydnn_cuda_softmax_forward_f64(const double* x, double* y, int64_t outer, int64_t len, int64_t inner);
+int keydnn_cuda_softmax_backward_f64(const double* grad_out, const double* y, double* grad_x, int64_t outer, int64_t len,
+                                     int64_t inner);
+/* Adam with coupled L2 decay, in place on p, m, v.  one_minus_beta* = 1 - beta*, bias* = 1 - beta*^t, all
+ * computed by the caller in double and narrowed here, as the reference's Python scalars are at its call
+ * boundary; grad_scale multiplies g first (1 skips it). */
+int keydnn_cuda_adam_step_f32(float* p, const float* g, float* m, float* v, int64_t n, float lr, float beta1, float beta2, float eps,
+                              float weight_decay, float one_minus_beta1, float one_minus_beta2, float bias1, float bias2,
+                              float grad_scale);
+int keydnn_cuda_adam_step_f64(double* p, const double* g, double* m, double* v, int64_t n, double lr, double beta1, double beta2, double eps,
+                              double weight_decay, double one_minus_beta1, double one_minus_beta2, double bias1, double bias2,
+                              double grad_scale);
+/* Losses.  loss is one device scalar.  sqdiff: diff = pred - target (written when diff is not null), loss =
+ * sum(diff*diff), times 1/n when mean.  In the backward entries g is the upstream gradient as a DEVICE
+ * scalar (null = 1); it is combined with the host factor in double on the device, where the reference reads
+ * it to the host first: sqdiff grad_pred = diff * (scale*g), grad_target (nullable) = grad_pred * -1;
+ * bce grad_pred = ((p - t) / (p*(1 - p))) * (g/n); cce grad_pred = (t/p) * -(g/batch). */
+int keydnn_cuda_sqdiff_forward_f32(const float* pred, const float* target, float* diff, float* loss, int64_t n, int mean);
+int keydnn_cuda_sqdiff_backward_f32(const float* diff, const float* g, double scale, float* grad_pred, float* grad_target,
+                                    int64_t n);
+int keydnn_cuda_bce_forward_f32(const float* pred, const float* target, float* loss, int64_t n);
+int keydnn_cuda_bce_backward_f32(const float* pred, const float* target, const float* g, float* grad_pred, int64_t n);
+int keydnn_cuda_cce_forward_f32(const float* pred, const float* target, float* loss, int64_t n, int64_t batch);
+int keydnn_cuda_cce_backward_f32(const float* pred, const float* target, const float* g, float* grad_pred, int64_t n,
+                                 int64_t batch);
+int keydnn_cuda_sqdiff_forward_f64(const double* pred, const double* target, double* diff, double* loss, int64_t n, int mean);
+int keydnn_cuda_sqdiff_backward_f64(const double* diff, const double* g, double scale, double* grad_pred, double* grad_target,
+                                    int64_t n);
+int keydnn_cuda_bce_forward_f64(const double* pred, const double* target, double* loss, int64_t n);
+int keydnn_cuda_bce_backward_f64(const double* pred, const double* target, const double* g, double* grad_pred, int64_t n);
+int keydnn_cuda_cce_forward_f64(const double* pred, const double* target, double* loss, int64_t n, int64_t batch);
+int keydnn_cuda_cce_backward_f64(const double* pred, const double* target, const double* g, double* grad_pred, int64_t n,
+                                 int64_t batch);
+
+/* ------------------------------------------------------------------------- */
 /* Multi-GPU (additive; the reference has no distributed code).  One process   */
 /* per GPU; NCCL is opened with dlopen at first use; collectives run on the    */
 /* library stream.  Status: -10 not initialised, -11 NCCL not loadable,        */

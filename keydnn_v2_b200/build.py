@@ -52,12 +52,18 @@ def _newer(target: Path, deps: list[Path]) -> bool:
     return all(d.stat().st_mtime <= t for d in deps)
 
 
+# translation units that keep nvcc's default FMA contraction: their transcendental functions must
+# expand exactly as in the reference build; their own arithmetic uses explicitly rounded intrinsics
+DEFAULT_FMAD = {"activation.cu", "softmax.cu"}
+
+
 def _compile(src: Path, verbose: bool, extra: list[str]) -> Path:
     obj = OBJ_DIR / (src.stem + ".o")
     headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
     if _newer(obj, [src, *headers, Path(__file__)]):
         return obj
-    cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    flags = [f for f in NVCC_FLAGS if not (src.name in DEFAULT_FMAD and f == "-fmad=false")]
+    cmd = [_nvcc(), *ARCH_FLAGS, *flags, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     if verbose:
         print(" ".join(cmd), flush=True)
     r = subprocess.run(cmd, capture_output=True, text=True)

@@ -96,6 +96,19 @@ inline unsigned grid_fit(K kernel, int threads, int64_t work_ctas, size_t smem =
         kd_fn_<<<kd::grid_fit(kd_fn_, (THREADS), (WORK), (SMEM), 1), (THREADS), (SMEM), kd::stream()>>>(__VA_ARGS__); \
     } while (0)
 
+// Separately rounded IEEE operations: never contracted into an FMA, whatever -fmad says.
+template <typename T> struct Rn;
+template <> struct Rn<float> {
+    static __device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
+    static __device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
+    static __device__ __forceinline__ float sub(float a, float b) { return __fsub_rn(a, b); }
+};
+template <> struct Rn<double> {
+    static __device__ __forceinline__ double mul(double a, double b) { return __dmul_rn(a, b); }
+    static __device__ __forceinline__ double add(double a, double b) { return __dadd_rn(a, b); }
+    static __device__ __forceinline__ double sub(double a, double b) { return __dsub_rn(a, b); }
+};
+
 // ---------------------------------------------------------------------------
 // 4-element packets: one 16-byte access for float, one 32-byte access (256-bit
 // ld/st, sm_100) for double and int64, so that a warp always touches whole,

@@ -133,17 +133,7 @@ int launch_fill(T* y, int64_t n, T value) {
 // product and sum rounded on its own:
 //   t1 = p * wd ; g2 = g + t1 ; [v = v * mu + g2] ; t2 = (v or g2) * lr ; p = p - t2
 // `gscale` pre-multiplies g (1/world after a gradient all-reduce); 1 skips it.
-template <typename T> struct Rn;
-template <> struct Rn<float> {
-    static __device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
-    static __device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
-    static __device__ __forceinline__ float sub(float a, float b) { return __fsub_rn(a, b); }
-};
-template <> struct Rn<double> {
-    static __device__ __forceinline__ double mul(double a, double b) { return __dmul_rn(a, b); }
-    static __device__ __forceinline__ double add(double a, double b) { return __dadd_rn(a, b); }
-    static __device__ __forceinline__ double sub(double a, double b) { return __dsub_rn(a, b); }
-};
+using kd::Rn;
 
 template <typename T>
 __device__ __forceinline__ void sgd_one(T& p, T g, T* v, T lr, T mu, T wd, T gscale, bool use_scale, bool use_wd) {

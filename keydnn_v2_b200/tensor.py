@@ -618,6 +618,25 @@ class Tensor:
         return out
 
     # ---------------------------------------------------------------- autograd
+    # ------------------------------------------------------------------ unary
+    def exp(self) -> "Tensor":
+        """``tensor/mixins/unary/_tensor_exp.py:40-80``."""
+        from . import functional as F
+
+        return F.exp(self)
+
+    def log(self) -> "Tensor":
+        """``tensor/mixins/unary/_tensor_log.py:60-123`` (on the device here)."""
+        from . import functional as F
+
+        return F.log(self)
+
+    def sqrt(self) -> "Tensor":
+        """``tensor/mixins/unary/_tensor_sqrt.py:60-125`` (on the device here)."""
+        from . import functional as F
+
+        return F.sqrt(self)
+
     def _set_ctx(self, ctx: Optional[Context]) -> None:
         self._ctx = ctx
 

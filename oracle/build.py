@@ -40,6 +40,7 @@ REF_CUDA_SOURCES = [
     "keydnn_cuda_broadcast_to.cu",
     "keydnn_tensor_bias_add.cu",
     "keydnn_transpose2d.cu",
+    "keydnn_cuda_exp.cu",
 ]
 # where a checkout of the reference project is looked for when no path is given
 DEFAULT_REF_ROOT = Path(os.environ.get("KEYDNN_REFERENCE_ROOT", "/root/reference"))

@@ -297,11 +297,89 @@ def cnn_case() -> None:
     put("cnn/n_params", np.array([len(params)], np.int64))
 
 
+def _run_fn(fn, arrays, go, **kw):
+    """forward + backward of a reference Function on its CPU path; returns (y, grads of the inputs that get one)."""
+    ts = [tensor(a) for a in arrays]
+    ctx = Context(parents=tuple(ts), backward_fn=lambda g: None)
+    y = fn.forward(ctx, *ts, **kw)
+    g = fn.backward(ctx, tensor(go))
+    if not isinstance(g, (tuple, list)):
+        g = (g,)
+    return y.to_numpy(), [None if t is None else t.to_numpy() for t in g]
+
+
+def activation_cases() -> None:
+    """Activations (_function.py), unary ops, losses (_losses.py) and Adam (optimizers/_adam.py) on the CPU path."""
+    from keydnn.infrastructure._function import ExpFn, LeakyReLUFn, ReLUFn, SigmoidFn, SoftmaxFn, TanhFn
+    from keydnn.infrastructure._losses import BinaryCrossEntropyFn, CategoricalCrossEntropyFn, MSEFn, SSEFn
+    from keydnn.infrastructure.optimizers._adam import Adam
+
+    rng = np.random.default_rng(31)
+    x = (rng.standard_normal((13, 37)) * 2.0).astype(np.float32)
+    x.flat[:4] = [0.0, -0.0, 1e-3, -1e-3]
+    go = rng.standard_normal(x.shape).astype(np.float32)
+    put("act/x", x)
+    put("act/go", go)
+    for name, fn, kw in (("exp", ExpFn, {}), ("sigmoid", SigmoidFn, {}), ("relu", ReLUFn, {}), ("tanh", TanhFn, {}),
+                         ("leaky", LeakyReLUFn, {"alpha": 0.1}), ("softmax1", SoftmaxFn, {"axis": -1}),
+                         ("softmax0", SoftmaxFn, {"axis": 0})):
+        y, g = _run_fn(fn, [x], go, **kw)
+        put(f"act/{name}_y", y)
+        put(f"act/{name}_gx", g[0])
+    xp = rng.uniform(0.05, 4.0, x.shape).astype(np.float32)
+    put("act/xpos", xp)
+    for name in ("log", "sqrt"):
+        t = tensor(xp, True)
+        y = getattr(t, name)()
+        y.backward(tensor(go))
+        put(f"act/{name}_y", y.to_numpy())
+        put(f"act/{name}_gx", t.grad.to_numpy())
+
+    pred = rng.uniform(0.05, 0.95, (16, 10)).astype(np.float32)
+    pred /= pred.sum(1, keepdims=True)
+    onehot = np.eye(10, dtype=np.float32)[rng.integers(0, 10, 16)]
+    binary = (rng.uniform(size=pred.shape) > 0.5).astype(np.float32)
+    target = rng.standard_normal(pred.shape).astype(np.float32)
+    g_up = np.array(0.7, np.float32)                                   # upstream gradient of the scalar loss
+    put("loss/pred", pred)
+    put("loss/onehot", onehot)
+    put("loss/binary", binary)
+    put("loss/target", target)
+    put("loss/g", g_up)
+    for name, fn, tgt in (("sse", SSEFn, target), ("mse", MSEFn, target), ("bce", BinaryCrossEntropyFn, binary),
+                          ("cce", CategoricalCrossEntropyFn, onehot)):
+        y, g = _run_fn(fn, [pred, tgt], g_up)
+        put(f"loss/{name}_y", y)
+        put(f"loss/{name}_gpred", g[0])
+        if g[1] is not None:
+            put(f"loss/{name}_gtarget", g[1])
+
+    # Adam with coupled weight decay, three steps
+    p0 = rng.standard_normal(53).astype(np.float32)
+    grads = [(rng.standard_normal(53) * 1e-1).astype(np.float32) for _ in range(3)]
+    for tag, wd in (("adam", 0.0), ("adam_wd", 1e-2)):
+        par = Parameter(shape=p0.shape, device=CPU, requires_grad=True)
+        par.copy_from_numpy(p0)
+        opt = Adam([par], lr=1e-2, betas=(0.9, 0.999), eps=1e-8, weight_decay=wd)
+        for k, gi in enumerate(grads):
+            par.zero_grad()
+            par._set_grad(tensor(gi)) if hasattr(par, "_set_grad") else setattr(par, "_grad", tensor(gi))
+            opt.step()
+            put(f"{tag}/p{k + 1}", par.to_numpy())
+        st = next(iter(opt._state.values()))
+        put(f"{tag}/m3", st["m"].to_numpy())
+        put(f"{tag}/v3", st["v"].to_numpy())
+    put("adam/p0", p0)
+    for k, gi in enumerate(grads):
+        put(f"adam/g{k + 1}", gi)
+
+
 def main() -> None:
     cnn_case()
     pool_cases()
     native_pool_cases()
     tensor_cases()
+    activation_cases()
     out = REPO / "tests" / "golden" / "ref_cpu_golden.npz"
     np.savez_compressed(out, **OUT)
     print(f"wrote {out} ({out.stat().st_size} bytes, {len(OUT)} arrays)")

@@ -148,3 +148,56 @@ def test_max_selection_rule_edge_cases(oracle):
     xp = np.full((1, 1, 2, 2), np.nan, np.float32)
     y, pidx = oracle.maxpool2d_forward(xp, 2, 2, 0)
     assert np.isneginf(y).all() and pidx.reshape(-1)[0] == 0
+
+
+# --- activations, unary ops, losses, Adam: the reference's own CPU path ran these ---------------
+def test_activations_match_reference_cpu(golden, oracle):
+    x, go = golden["act/x"], golden["act/go"]
+    cases = {
+        "exp": (oracle.exp(x), lambda y: oracle.exp_backward(go, y)),
+        "sigmoid": (oracle.sigmoid(x), lambda y: oracle.sigmoid_backward(go, y)),
+        "tanh": (oracle.tanh(x), lambda y: oracle.tanh_backward(go, y)),
+        "relu": (oracle.relu(x)[0], lambda y: oracle.relu_backward(go, x)),
+        "leaky": (oracle.leaky_relu(x, x, 0.1), lambda y: oracle.leaky_relu(go, x, 0.1)),
+    }
+    for name, (y, bwd) in cases.items():
+        np.testing.assert_array_equal(y, golden[f"act/{name}_y"], err_msg=name)
+        np.testing.assert_array_equal(bwd(y), golden[f"act/{name}_gx"], err_msg=name)
+    for axis, name in ((-1, "softmax1"), (0, "softmax0")):
+        y = oracle.softmax(x, axis)
+        np.testing.assert_allclose(y, golden[f"act/{name}_y"], rtol=1e-6, atol=1e-8)
+        np.testing.assert_allclose(oracle.softmax_backward(go, y, axis), golden[f"act/{name}_gx"], rtol=1e-5, atol=1e-7)
+        np.testing.assert_allclose(y.sum(axis), 1.0, rtol=1e-6)
+
+
+def test_log_sqrt_match_reference_cpu(golden, oracle):
+    xp, go = golden["act/xpos"], golden["act/go"]
+    np.testing.assert_array_equal(oracle.log(xp), golden["act/log_y"])
+    np.testing.assert_array_equal(oracle.log_backward(go, xp), golden["act/log_gx"])
+    np.testing.assert_array_equal(oracle.sqrt(xp), golden["act/sqrt_y"])
+    np.testing.assert_array_equal(oracle.sqrt_backward(go, oracle.sqrt(xp)), golden["act/sqrt_gx"])
+
+
+def test_losses_match_reference_cpu(golden, oracle):
+    pred, g = golden["loss/pred"], float(golden["loss/g"])
+    for name, mean in (("sse", False), ("mse", True)):
+        loss, diff = oracle.sqdiff(pred, golden["loss/target"], mean)
+        np.testing.assert_allclose(loss, golden[f"loss/{name}_y"], rtol=1e-6)
+        gp, gt = oracle.sqdiff_backward(diff, g, mean)
+        np.testing.assert_array_equal(gp, golden[f"loss/{name}_gpred"])
+        np.testing.assert_array_equal(gt, golden[f"loss/{name}_gtarget"])
+    np.testing.assert_allclose(oracle.bce(pred, golden["loss/binary"]), golden["loss/bce_y"], rtol=1e-6)
+    np.testing.assert_array_equal(oracle.bce_backward(pred, golden["loss/binary"], g), golden["loss/bce_gpred"])
+    np.testing.assert_allclose(oracle.cce(pred, golden["loss/onehot"]), golden["loss/cce_y"], rtol=1e-6)
+    np.testing.assert_array_equal(oracle.cce_backward(pred, golden["loss/onehot"], g), golden["loss/cce_gpred"])
+
+
+@pytest.mark.parametrize("tag,wd", [("adam", 0.0), ("adam_wd", 1e-2)])
+def test_adam_matches_reference_cpu_bitwise(golden, oracle, tag, wd):
+    p = golden["adam/p0"]
+    m, v = np.zeros_like(p), np.zeros_like(p)
+    for k in range(3):
+        p, m, v = oracle.adam_step(p, golden[f"adam/g{k + 1}"], m, v, k + 1, 1e-2, (0.9, 0.999), 1e-8, wd)
+        np.testing.assert_array_equal(p, golden[f"{tag}/p{k + 1}"])
+    np.testing.assert_array_equal(m, golden[f"{tag}/m3"])
+    np.testing.assert_array_equal(v, golden[f"{tag}/v3"])
