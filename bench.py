@@ -273,7 +273,7 @@ def suite_table(lib, timer, peak: float, reps: int = 10, warm: int = 3) -> list[
         "keydnn_cuda_sgd_momentum_step_f32", p.data, g.data, v.data, n, ctypes.c_float(0.01), ctypes.c_float(0.9),
         ctypes.c_float(1e-4), ctypes.c_float(1.0)))
     # Adam on the same vector: read p, g, m, v, write p, m, v (7 passes)
-    m = T.zeros((n,))
+    m, v = T.zeros((n,)), T.zeros((n,))          # a fresh second moment: the SGD velocity above has negative entries
     cf = ctypes.c_float
     timed("adam_step_c3_f32", 7.0 * p.nbytes, lambda: lib.call(
         "keydnn_cuda_adam_step_f32", p.data, g.data, m.data, v.data, n, cf(1e-3), cf(0.9), cf(0.999), cf(1e-8), cf(1e-4),
@@ -283,9 +283,13 @@ def suite_table(lib, timer, peak: float, reps: int = 10, warm: int = 3) -> list[
     n = 1 << 27
     x = T.from_numpy(rng.standard_normal(n, dtype=np.float32))
     y, gx = T.empty((n,)), T.empty((n,))
+    xpos = T.from_numpy(np.abs(x.to_numpy()) + np.float32(0.01))      # log / sqrt of positive values (NaN results take a slow path)
     for name in ("exp", "log", "sqrt", "sigmoid_forward", "tanh_forward"):
         count = n if name != "exp" else ctypes.c_int(n)
-        timed(f"{name}_f32", 2.0 * x.nbytes, lambda name=name, count=count: lib.call(f"keydnn_cuda_{name}_f32", x.data, y.data, count))
+        src = xpos if name in ("log", "sqrt") else x
+        timed(f"{name}_f32", 2.0 * x.nbytes, lambda name=name, count=count, src=src: lib.call(
+            f"keydnn_cuda_{name}_f32", src.data, y.data, count))
+    del xpos
     timed("relu_forward_f32", 2.0 * x.nbytes, lambda: lib.call("keydnn_cuda_relu_forward_f32", x.data, y.data, None, n))
     timed("leaky_relu_forward_f32", 2.0 * x.nbytes, lambda: lib.call("keydnn_cuda_leaky_relu_forward_f32", x.data, y.data, cf(0.1), n))
     for name in ("sigmoid_backward", "tanh_backward", "relu_backward", "sqrt_backward"):

@@ -203,7 +203,10 @@ int adam_step(T* p, const T* g, T* m, T* v, int64_t n, T lr, T b1, T b2, T eps, 
     if (n == 0) return 0;
     MapArgs<T, 4, 3> a{{p, g, m, v}, {p, m, v}};
     FAdam<T> f{lr, b1, b2, eps, wd, c1, c2, bias1, bias2, gscale, wd != T(0), gscale != T(1)};
-    return kd::launch_map<T, 4, 3>(a, n, f);
+    // one packet per tensor in flight per thread: the update's long dependent chain (three divisions, a square
+    // root) wants resident warps more than it wants loads per thread (measured on B200: 107 us against 186 us
+    // with two packets for 25 M parameters)
+    return kd::launch_map<T, 4, 3, 1>(a, n, f, 16);
 }
 
 template <typename T, typename F>

@@ -93,11 +93,13 @@ inline bool map_aligned(const MapArgs<T, NIN, NOUT>& a) {
 }
 
 // Launches the map; inputs must be non-null, outputs may be null (skipped).  Returns a cudaError_t.
-template <typename T, int NIN, int NOUT, typename F>
-inline int launch_map(const MapArgs<T, NIN, NOUT>& a, int64_t n, F f) {
+// UNROLL_ = 0 picks the packets in flight per thread from the number of inputs; compute-heavy maps pass a
+// smaller value to trade registers for resident warps.
+template <typename T, int NIN, int NOUT, int UNROLL_ = 0, typename F>
+inline int launch_map(const MapArgs<T, NIN, NOUT>& a, int64_t n, F f, int waves = 0) {
     (void)cudaGetLastError();
-    constexpr int UNROLL = (NIN <= 1) ? 8 : (NIN == 2 ? 4 : 2);
-    constexpr int WAVES = (NIN + NOUT <= 3) ? 64 : 16;
+    constexpr int UNROLL = UNROLL_ > 0 ? UNROLL_ : ((NIN <= 1) ? 8 : (NIN == 2 ? 4 : 2));
+    const int WAVES = waves > 0 ? waves : ((NIN + NOUT <= 3) ? 64 : 16);
     if (map_aligned(a)) {
         const int64_t tiles = ((n >> 2) + kMapThreads * UNROLL - 1) / (kMapThreads * UNROLL);
         KD_LAUNCH_W((map_kernel<T, NIN, NOUT, UNROLL, true, F>), WAVES, tiles > 0 ? tiles : 1, kMapThreads, 0, a, n, f);

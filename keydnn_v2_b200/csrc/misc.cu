@@ -163,6 +163,35 @@ bias_add_kernel(const T* x, const T* __restrict__ b, T* y, int64_t out, int64_t 
         y[i] = x[i] + __ldg(b + (i % out));
 }
 
+// Packet path: `out` a multiple of 4 and every pointer packet-aligned, so a 4-element packet never straddles a
+// row and its bias packet is b[4*(p % (out/4)) ...]; the row of packet p comes from a multiply-high division.
+template <typename T, int UNROLL>
+__global__ void __launch_bounds__(kThreads)
+bias_add_packet_kernel(const T* x, const T* __restrict__ b, T* y, kd::FastDiv per_row, int64_t n4) {
+    const int64_t tile = static_cast<int64_t>(kThreads) * UNROLL;
+    for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < n4; base += static_cast<int64_t>(gridDim.x) * tile) {
+        kd::Pack4<T> vx[UNROLL], vb[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t p = base + u * kThreads + threadIdx.x;
+            if (p < n4) {
+                vx[u] = kd::load4_stream(x + 4 * p);
+                const unsigned q = static_cast<unsigned>(p);
+                vb[u] = kd::load4(b + 4 * static_cast<int64_t>(q - per_row.div(q) * per_row.d));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t p = base + u * kThreads + threadIdx.x;
+            if (p < n4) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) vx[u].v[k] = vx[u].v[k] + vb[u].v[k];
+                kd::store4(y + 4 * p, vx[u]);
+            }
+        }
+    }
+}
+
 template <typename T>
 int bias_add(const T* x, const T* b, T* y, int64_t batch, int64_t out) {
     if (!x || !b || !y) return static_cast<int>(cudaErrorInvalidDevicePointer);
@@ -170,6 +199,13 @@ int bias_add(const T* x, const T* b, T* y, int64_t batch, int64_t out) {
     const int64_t n = batch * out;
     if (n <= 0) return 0;
     (void)cudaGetLastError();
+    if (out % 4 == 0 && (n >> 2) < (1ll << 31) && kd::aligned_pack<T>(x) && kd::aligned_pack<T>(y) && kd::aligned_pack<T>(b)) {
+        constexpr int UNROLL = 4;
+        const int64_t n4 = n >> 2;
+        KD_LAUNCH_W((bias_add_packet_kernel<T, UNROLL>), 64, (n4 + kThreads * UNROLL - 1) / (kThreads * UNROLL), kThreads, 0, x, b,
+                    y, kd::FastDiv(static_cast<unsigned>(out >> 2)), n4);
+        return kd::launch_status();
+    }
     const unsigned grid = kd::grid_for((n + kThreads - 1) / kThreads, 8);
     bias_add_kernel<T><<<grid, kThreads, 0, kd::stream()>>>(x, b, y, out, n);
     return kd::launch_status();
@@ -199,14 +235,57 @@ transpose_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int cols)
     }
 }
 
+// 64x64 tiles, one packet (4 elements) per access on both sides: rows and cols multiples of 4, both pointers
+// packet-aligned.  A thread reads 4 packets along the input rows and writes 4 packets along the output rows,
+// gathering each output packet from one tile column (row stride 65 words: at most 2-way bank conflicts).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+transpose_packet_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int cols) {
+    __shared__ T tile[64][65];
+    const int tiles_c = (cols + 63) / 64, tiles_r = (rows + 63) / 64;
+    for (int64_t t = blockIdx.x; t < static_cast<int64_t>(tiles_c) * tiles_r; t += gridDim.x) {
+        const int r0 = static_cast<int>(t / tiles_c) * 64, c0 = static_cast<int>(t % tiles_c) * 64;
+        kd::Pack4<T> v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int idx = threadIdx.x + kThreads * k, r = r0 + (idx >> 4), c = c0 + 4 * (idx & 15);
+            if (r < rows && c < cols) v[k] = kd::load4_stream(x + static_cast<int64_t>(r) * cols + c);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int idx = threadIdx.x + kThreads * k;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tile[idx >> 4][4 * (idx & 15) + j] = v[k].v[j];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int idx = threadIdx.x + kThreads * k, oc = idx >> 4, r4 = 4 * (idx & 15);
+            const int c = c0 + oc, r = r0 + r4;
+            if (c < cols && r < rows) {
+                kd::Pack4<T> o;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) o.v[j] = tile[r4 + j][oc];
+                kd::store4(y + static_cast<int64_t>(c) * rows + r, o);
+            }
+        }
+        __syncthreads();
+    }
+}
+
 template <typename T>
 int transpose2d(const T* x, T* y, int rows, int cols) {
     if (rows < 0 || cols < 0) return 1;
     if (rows == 0 || cols == 0) return 0;
     if (!x || !y) return 2;
     (void)cudaGetLastError();
-    const int64_t tiles = static_cast<int64_t>((cols + 31) / 32) * ((rows + 31) / 32);
-    transpose_kernel<T><<<kd::grid_for(tiles, 8), kThreads, 0, kd::stream()>>>(x, y, rows, cols);
+    if (rows % 4 == 0 && cols % 4 == 0 && kd::aligned_pack<T>(x) && kd::aligned_pack<T>(y)) {
+        const int64_t tiles = static_cast<int64_t>((cols + 63) / 64) * ((rows + 63) / 64);
+        KD_LAUNCH_W(transpose_packet_kernel<T>, 8, tiles, kThreads, 0, x, y, rows, cols);
+    } else {
+        const int64_t tiles = static_cast<int64_t>((cols + 31) / 32) * ((rows + 31) / 32);
+        transpose_kernel<T><<<kd::grid_for(tiles, 8), kThreads, 0, kd::stream()>>>(x, y, rows, cols);
+    }
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 

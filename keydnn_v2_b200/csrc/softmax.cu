@@ -5,9 +5,11 @@
 // and five kernels with as many temporaries.  Here each direction is one kernel: one HBM read of
 // every operand, one write.  Element arithmetic is the reference's, separately rounded:
 //   forward   m = max over the axis (strict >, from -inf; a NaN never wins)
-//             e = exp(x - m);  y = e / sum(e)
+//             e = exp(x - m);  y = e * (1 / sum(e))
 //   backward  gy = g * y;  dx = y * (g - sum(gy))
-// The sums are tree sums (the reference adds serially), hence equal only to rounding.
+// The sums are tree sums (the reference adds serially), so results equal the reference's only to
+// rounding in any case; the forward therefore multiplies by the correctly rounded reciprocal of the
+// sum (one division per row) instead of dividing every element, which halves its instruction count.
 //
 // Compiled with nvcc's default FMA contraction so that exp expands as in the reference build; all
 // arithmetic written here uses explicitly rounded intrinsics.
@@ -25,133 +27,190 @@ template <> __device__ __forceinline__ float t_div<float>(float a, float b) { re
 template <> __device__ __forceinline__ double t_div<double>(double a, double b) { return __ddiv_rn(a, b); }
 template <typename T> __device__ __forceinline__ T neg_inf() { return -std::numeric_limits<T>::infinity(); }
 
-template <typename T> __device__ __forceinline__ T warp_max(T v) {
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+// Reductions inside groups of G neighbouring lanes (G a power of two).
+template <typename T, int G> __device__ __forceinline__ T group_max(T v) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
+    for (int o = G / 2; o > 0; o >>= 1) {
         const T w = __shfl_xor_sync(0xffffffffu, v, o);
         v = w > v ? w : v;
     }
     return v;
 }
-template <typename T> __device__ __forceinline__ T warp_add(T v) {
+template <typename T, int G> __device__ __forceinline__ T group_add(T v) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = Rn<T>::add(v, __shfl_xor_sync(0xffffffffu, v, o));
+    for (int o = G / 2; o > 0; o >>= 1) v = Rn<T>::add(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
 
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
-
-// ---- rows that fit in the registers of one warp: len <= 32 * R -----------------------------------
-// A warp owns a row; lane l holds elements l, l+32, ...  Loads of the R elements are independent.
-template <typename T, int R, bool BWD>
-__global__ void __launch_bounds__(kThreads)
+// ---- rows of up to G*R elements: G lanes own a row, lane l of the group holds elements l, l+G, ...;
+// a warp works on K groups of 32/G rows at once so that K*R independent loads are in flight per lane.
+template <typename T, int G, int R, int K, bool BWD>
+__global__ void __launch_bounds__(kThreads, (R * sizeof(T) * (BWD ? 2 : 1) >= 128 ? 3 : 1))
 softmax_warp_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t rows, int len) {
+    constexpr int RPG = 32 / G;                 // rows per group of a warp
+    constexpr int RPW = RPG * K;                // rows per warp and trip
     const int lane = threadIdx.x & 31;
+    const int sub = lane / G, col0 = lane % G;
     const int64_t warp0 = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps;
-    for (int64_t row = warp0; row < rows; row += stride) {
-        const T* pa = a + row * len;
-        T va[R], vb[R];
+    const int64_t trips = (rows + RPW - 1) / RPW;
+    for (int64_t trip = warp0; trip < trips; trip += stride) {
+        T va[K][R], vb[K][R];
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int c = lane + 32 * r;
-            if (BWD) {
-                va[r] = c < len ? __ldcs(pa + c) : T(0);                  // g
-                vb[r] = c < len ? __ldcs(b + row * len + c) : T(0);       // y
-            } else {
-                va[r] = c < len ? __ldcs(pa + c) : neg_inf<T>();
+        for (int k = 0; k < K; ++k) {
+            const int64_t row = trip * RPW + k * RPG + sub;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int c = col0 + G * r;
+                const bool ok = row < rows && c < len;
+                if (BWD) {
+                    va[k][r] = ok ? __ldcs(a + row * len + c) : T(0);                  // g
+                    vb[k][r] = ok ? __ldcs(b + row * len + c) : T(0);                  // y
+                } else {
+                    va[k][r] = ok ? __ldcs(a + row * len + c) : neg_inf<T>();
+                }
             }
         }
-        if (BWD) {
-            T dot = T(0);
 #pragma unroll
-            for (int r = 0; r < R; ++r) dot = Rn<T>::add(dot, Rn<T>::mul(va[r], vb[r]));
-            dot = warp_add(dot);
+        for (int k = 0; k < K; ++k) {
+            const int64_t row = trip * RPW + k * RPG + sub;
+            if (BWD) {
+                T dot = T(0);
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int c = lane + 32 * r;
-                if (c < len) __stcs(out + row * len + c, Rn<T>::mul(vb[r], Rn<T>::sub(va[r], dot)));
-            }
-        } else {
-            T m = neg_inf<T>();
+                for (int r = 0; r < R; ++r) dot = Rn<T>::add(dot, Rn<T>::mul(va[k][r], vb[k][r]));
+                dot = group_add<T, G>(dot);
 #pragma unroll
-            for (int r = 0; r < R; ++r) m = va[r] > m ? va[r] : m;
-            m = warp_max(m);
-            T s = T(0);
+                for (int r = 0; r < R; ++r) {
+                    const int c = col0 + G * r;
+                    if (row < rows && c < len)
+                        __stcs(out + row * len + c, Rn<T>::mul(vb[k][r], Rn<T>::sub(va[k][r], dot)));
+                }
+            } else {
+                T m = neg_inf<T>();
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int c = lane + 32 * r;
-                va[r] = c < len ? t_exp(Rn<T>::sub(va[r], m)) : T(0);
-                s = Rn<T>::add(s, va[r]);
-            }
-            s = warp_add(s);
+                for (int r = 0; r < R; ++r) m = va[k][r] > m ? va[k][r] : m;
+                m = group_max<T, G>(m);
+                T s = T(0);
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int c = lane + 32 * r;
-                if (c < len) __stcs(out + row * len + c, t_div(va[r], s));
+                for (int r = 0; r < R; ++r) {
+                    const int c = col0 + G * r;
+                    va[k][r] = (row < rows && c < len) ? t_exp(Rn<T>::sub(va[k][r], m)) : T(0);
+                    s = Rn<T>::add(s, va[k][r]);
+                }
+                const T inv = t_div(T(1), group_add<T, G>(s));
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int c = col0 + G * r;
+                    if (row < rows && c < len) __stcs(out + row * len + c, Rn<T>::mul(va[k][r], inv));
+                }
             }
         }
     }
 }
 
-// ---- long rows: one CTA per row, the row staged in shared memory (or re-read from L2 when it
-// does not fit: `staged` false) -------------------------------------------------------------------
-template <typename T> __device__ __forceinline__ T block_max(T v, T* sm) {
-    v = warp_max(v);
+// ---- long rows: one CTA per row, operands staged in shared memory while they stream in (or re-read
+// through L2 when they do not fit: `staged` false).  VEC: rows start on packet boundaries and len % 4 == 0.
+template <typename T, int kBlockWarps> __device__ __forceinline__ T block_max(T v, T* sm) {
+    v = group_max<T, 32>(v);
     __syncthreads();
     if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
     __syncthreads();
     T r = sm[0];
 #pragma unroll
-    for (int w = 1; w < kWarps; ++w) r = sm[w] > r ? sm[w] : r;
+    for (int w = 1; w < kBlockWarps; ++w) r = sm[w] > r ? sm[w] : r;
     return r;
 }
-template <typename T> __device__ __forceinline__ T block_add(T v, T* sm) {
-    v = warp_add(v);
+template <typename T, int kBlockWarps> __device__ __forceinline__ T block_add(T v, T* sm) {
+    v = group_add<T, 32>(v);
     __syncthreads();
     if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
     __syncthreads();
     T r = sm[0];
 #pragma unroll
-    for (int w = 1; w < kWarps; ++w) r = Rn<T>::add(r, sm[w]);
+    for (int w = 1; w < kBlockWarps; ++w) r = Rn<T>::add(r, sm[w]);
     return r;
 }
 
-template <typename T, bool BWD>
-__global__ void __launch_bounds__(kThreads)
+template <typename T, bool BWD, bool VEC, int kBlockThreads>
+__global__ void __launch_bounds__(kBlockThreads)
 softmax_block_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t rows, int len,
                      bool staged) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    T* buf = reinterpret_cast<T*>(smem_raw);          // forward: e;  backward: g*y
-    __shared__ T red[kWarps];
+    extern __shared__ __align__(32) unsigned char smem_raw[];
+    T* buf = reinterpret_cast<T*>(smem_raw);          // forward: x then e;  backward: g
+    T* buf2 = buf + len;                              // backward: y
+    constexpr int kBlockWarps = kBlockThreads / 32;
+    __shared__ T red[kBlockWarps];
+    constexpr int V = VEC ? 4 : 1;
+    const int step = kBlockThreads * V;
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const T* pa = a + row * len;
         const T* pb = BWD ? b + row * len : nullptr;
         T* po = out + row * len;
         if (BWD) {
-            T dot = T(0);
-            for (int c = threadIdx.x; c < len; c += kThreads) dot = Rn<T>::add(dot, Rn<T>::mul(pa[c], pb[c]));
-            dot = block_add(dot, red);
-            for (int c = threadIdx.x; c < len; c += kThreads)
-                __stcs(po + c, Rn<T>::mul(pb[c], Rn<T>::sub(pa[c], dot)));
+            T dot[V];
+#pragma unroll
+            for (int k = 0; k < V; ++k) dot[k] = T(0);
+#pragma unroll 2
+            for (int c = threadIdx.x * V; c < len; c += step) {
+                kd::Pack4<T> g, y;
+                if (VEC) { g = kd::load4_stream(pa + c); y = kd::load4_stream(pb + c); }
+                else { g.v[0] = pa[c]; y.v[0] = pb[c]; }
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    dot[k] = Rn<T>::add(dot[k], Rn<T>::mul(g.v[k], y.v[k]));
+                    if (staged) { buf[c + k] = g.v[k]; buf2[c + k] = y.v[k]; }
+                }
+            }
+            T d = dot[0];
+#pragma unroll
+            for (int k = 1; k < V; ++k) d = Rn<T>::add(d, dot[k]);
+            d = block_add<T, kBlockWarps>(d, red);
+#pragma unroll 2
+            for (int c = threadIdx.x * V; c < len; c += step) {
+                kd::Pack4<T> r;
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    const T g = staged ? buf[c + k] : pa[c + k], y = staged ? buf2[c + k] : pb[c + k];
+                    r.v[k] = Rn<T>::mul(y, Rn<T>::sub(g, d));
+                }
+                if (VEC) kd::store4(po + c, r);
+                else po[c] = r.v[0];
+            }
         } else {
             T m = neg_inf<T>();
-            for (int c = threadIdx.x; c < len; c += kThreads) {
-                const T v = pa[c];
-                if (staged) buf[c] = v;
-                m = v > m ? v : m;
+#pragma unroll 2
+            for (int c = threadIdx.x * V; c < len; c += step) {
+                kd::Pack4<T> x;
+                if (VEC) x = kd::load4_stream(pa + c);
+                else x.v[0] = pa[c];
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    if (staged) buf[c + k] = x.v[k];
+                    m = x.v[k] > m ? x.v[k] : m;
+                }
             }
-            m = block_max(m, red);
+            m = block_max<T, kBlockWarps>(m, red);
             T s = T(0);
-            for (int c = threadIdx.x; c < len; c += kThreads) {
-                const T e = t_exp(Rn<T>::sub(staged ? buf[c] : pa[c], m));
-                if (staged) buf[c] = e;
-                s = Rn<T>::add(s, e);
+            for (int c = threadIdx.x * V; c < len; c += step) {
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    const T e = t_exp(Rn<T>::sub(staged ? buf[c + k] : pa[c + k], m));
+                    if (staged) buf[c + k] = e;
+                    s = Rn<T>::add(s, e);
+                }
             }
-            s = block_add(s, red);
-            for (int c = threadIdx.x; c < len; c += kThreads)
-                __stcs(po + c, t_div(staged ? buf[c] : t_exp(Rn<T>::sub(pa[c], m)), s));
+            const T inv = t_div(T(1), block_add<T, kBlockWarps>(s, red));
+            for (int c = threadIdx.x * V; c < len; c += step) {
+                kd::Pack4<T> r;
+#pragma unroll
+                for (int k = 0; k < V; ++k)
+                    r.v[k] = Rn<T>::mul(staged ? buf[c + k] : t_exp(Rn<T>::sub(pa[c + k], m)), inv);
+                if (VEC) kd::store4(po + c, r);
+                else po[c] = r.v[0];
+            }
         }
         __syncthreads();
     }
@@ -181,14 +240,67 @@ softmax_strided_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __re
             }
             T s = T(0);
             for (int k = 0; k < len; ++k) s = Rn<T>::add(s, t_exp(Rn<T>::sub(a[base + k * inner], m)));
-            for (int k = 0; k < len; ++k) out[base + k * inner] = t_div(t_exp(Rn<T>::sub(a[base + k * inner], m)), s);
+            const T inv = t_div(T(1), s);
+            for (int k = 0; k < len; ++k) out[base + k * inner] = Rn<T>::mul(t_exp(Rn<T>::sub(a[base + k * inner], m)), inv);
         }
     }
 }
 
-template <typename T, int R, bool BWD>
+template <typename T, int G, int R, int K, bool BWD>
 void launch_warp(const T* a, const T* b, T* out, int64_t rows, int len) {
-    KD_LAUNCH_W((softmax_warp_kernel<T, R, BWD>), 8, (rows + kWarps - 1) / kWarps, kThreads, 0, a, b, out, rows, len);
+    constexpr int RPW = (32 / G) * K;
+    const int64_t trips = (rows + RPW - 1) / RPW;
+    KD_LAUNCH_W((softmax_warp_kernel<T, G, R, K, BWD>), 8, (trips + kWarps - 1) / kWarps, kThreads, 0, a, b, out, rows, len);
+}
+
+// Rows are staged while at least two CTAs stay resident per SM; longer rows are re-read through L2.
+template <typename T, bool BWD, bool VEC, int THREADS>
+int launch_block(const T* a, const T* b, T* out, int64_t rows, int len) {
+    auto kernel = softmax_block_kernel<T, BWD, VEC, THREADS>;
+    constexpr size_t kMaxSmem = 100 * 1024;
+    size_t smem = static_cast<size_t>(len) * sizeof(T) * (BWD ? 2 : 1);
+    bool staged = smem <= kMaxSmem;
+    if (staged && smem > 48 * 1024) {
+        static bool opted = false;                    // per template instance
+        if (!opted) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kMaxSmem)) !=
+                cudaSuccess) {
+                (void)cudaGetLastError();
+                staged = false;
+            } else {
+                opted = true;
+            }
+        }
+    }
+    if (!staged) smem = 0;
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, smem) != cudaSuccess || per_sm < 1)
+        per_sm = 1;
+    const int64_t cap = static_cast<int64_t>(kd::sm_count()) * per_sm * 4;
+    const unsigned grid = static_cast<unsigned>(rows < cap ? rows : cap);
+    kernel<<<grid, THREADS, smem, kd::stream()>>>(a, b, out, rows, len, staged);
+    return kd::launch_status();
+}
+
+// CTA width: wide enough that a row gives every thread work and that the staged bytes per thread stay near
+// what lets 1,536-2,048 threads share an SM's shared memory (about 112 bytes each).
+template <typename T, bool BWD, bool VEC>
+int launch_block_for(const T* a, const T* b, T* out, int64_t rows, int len) {
+    const size_t bytes = static_cast<size_t>(len) * sizeof(T) * (BWD ? 2 : 1);
+    int threads = len <= 256 ? 32 : (len <= 512 ? 64 : 128);
+    if (bytes <= 100 * 1024) {
+        while (threads < 512 && static_cast<size_t>(threads) * 112 < bytes) threads *= 2;
+    } else {
+        threads = 1024;                                 // not staged: re-read through L2
+    }
+    switch (threads) {
+        case 32: return launch_block<T, BWD, VEC, 32>(a, b, out, rows, len);
+        case 64: return launch_block<T, BWD, VEC, 64>(a, b, out, rows, len);
+        case 128: return launch_block<T, BWD, VEC, 128>(a, b, out, rows, len);
+        case 256: return launch_block<T, BWD, VEC, 256>(a, b, out, rows, len);
+        case 512: return launch_block<T, BWD, VEC, 512>(a, b, out, rows, len);
+        default: return launch_block<T, BWD, VEC, 1024>(a, b, out, rows, len);
+    }
 }
 
 template <typename T, bool BWD>
@@ -203,37 +315,25 @@ int softmax(const T* a, const T* b, T* out, int64_t outer, int64_t len, int64_t 
                     outer, n, inner);
         return kd::launch_status();
     }
-    if (n <= 32) launch_warp<T, 1, BWD>(a, b, out, outer, n);
-    else if (n <= 64) launch_warp<T, 2, BWD>(a, b, out, outer, n);
-    else if (n <= 128) launch_warp<T, 4, BWD>(a, b, out, outer, n);
-    else if (n <= 256) launch_warp<T, 8, BWD>(a, b, out, outer, n);
-    else if (n <= 512) launch_warp<T, 16, BWD>(a, b, out, outer, n);
-    else if (n <= 1024 && (!BWD || sizeof(T) == 4)) launch_warp<T, 32, BWD>(a, b, out, outer, n);
-    else {
-        // stage the row when it fits the opt-in shared memory of one CTA (two CTAs per SM stay resident up to 96 KiB)
-        size_t smem = BWD ? 0 : static_cast<size_t>(n) * sizeof(T);
-        bool staged = !BWD && smem <= 200 * 1024;
-        if (!staged) smem = 0;
-        auto kernel = softmax_block_kernel<T, BWD>;
-        if (smem > 48 * 1024) {
-            static size_t granted = 0;      // per template instance
-            if (smem > granted) {
-                if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
-                    (void)cudaGetLastError();
-                    staged = false;
-                    smem = 0;
-                } else {
-                    granted = 200 * 1024;
-                }
-            }
-        }
-        int per_sm = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem) != cudaSuccess || per_sm < 1)
-            per_sm = 1;
-        const int64_t cap = static_cast<int64_t>(kd::sm_count()) * per_sm * 4;
-        const unsigned grid = static_cast<unsigned>(outer < cap ? outer : cap);
-        kernel<<<grid, kThreads, smem, kd::stream()>>>(a, b, out, outer, n, staged);
+    // Measured on B200 (2^27 elements): the forward pass (an exp per element between two reductions) runs faster
+    // from shared memory with many small CTAs once a row has 256 elements; the backward pass stays in registers
+    // up to 1024 (float) / 512 (double) elements.
+    const int block_min = BWD ? (sizeof(T) == 4 ? 1025 : 513) : 256;
+    if (n >= block_min) {
+        const bool vec = (n % 4 == 0) && kd::aligned_pack<T>(a) && kd::aligned_pack<T>(out) && (!BWD || kd::aligned_pack<T>(b));
+        return vec ? launch_block_for<T, BWD, true>(a, b, out, outer, n) : launch_block_for<T, BWD, false>(a, b, out, outer, n);
     }
+    if (n <= 1) launch_warp<T, 1, 1, 8, BWD>(a, b, out, outer, n);
+    else if (n <= 2) launch_warp<T, 2, 1, 8, BWD>(a, b, out, outer, n);
+    else if (n <= 4) launch_warp<T, 4, 1, 8, BWD>(a, b, out, outer, n);
+    else if (n <= 8) launch_warp<T, 8, 1, 8, BWD>(a, b, out, outer, n);
+    else if (n <= 16) launch_warp<T, 16, 1, 8, BWD>(a, b, out, outer, n);
+    else if (n <= 32) launch_warp<T, 32, 1, 8, BWD>(a, b, out, outer, n);
+    else if (n <= 64) launch_warp<T, 32, 2, 4, BWD>(a, b, out, outer, n);
+    else if (n <= 128) launch_warp<T, 32, 4, 2, BWD>(a, b, out, outer, n);
+    else if (n <= 256) launch_warp<T, 32, 8, 1, BWD>(a, b, out, outer, n);
+    else if (n <= 512) launch_warp<T, 32, 16, 1, BWD>(a, b, out, outer, n);
+    else if constexpr (sizeof(T) == 4) launch_warp<T, 32, 32, 1, BWD>(a, b, out, outer, n);
     return kd::launch_status();
 }
 

@@ -162,21 +162,12 @@ class BatchNorm2d(Module):
 
 
 class ReLU(Module):
+    """``_activations.py:97-140`` over ``ReLUFn``: y = x * (x > 0), gradient g * (x > 0); one fused kernel each way."""
+
     def forward(self, x: Tensor) -> Tensor:
-        with no_grad():
-            mask = x > 0.0                      # float32 1.0 / 0.0 mask (_function.py:291-293)
-            if mask.dtype != x.dtype:
-                raise TypeError("ReLU on CUDA supports float32 tensors (the mask kernels write float32)")
-            y = x * mask
-        if x._needs_grad():
-            y.requires_grad = True
+        from . import functional as F
 
-            def backward_fn(g: Tensor):
-                with no_grad():
-                    return (g * mask,)
-
-            y._ctx = Context((x,), backward_fn)
-        return y
+        return F.relu(x)
 
 
 class Flatten(Module):
@@ -246,23 +237,11 @@ class Sequential(Module):
 
 
 def mse_loss(pred: Tensor, target: Tensor) -> Tensor:
-    """``_losses.py:173-176``: mean((pred - target)^2); gradient 2 * (pred - target) / N times the upstream scalar."""
-    with no_grad():
-        diff = pred - target
-        loss = (diff * diff).mean()
-    if pred.requires_grad:
-        loss.requires_grad = True
-        n = diff.numel
+    """``_losses.py:130-216``: mean((pred - target)^2) with the fused kernels of ``functional.MSEFn``; the backward takes
+    the upstream scalar from the device, so a training step never waits for the host."""
+    from . import functional as F
 
-        def backward_fn(g: Tensor):
-            with no_grad():
-                gp = diff * (2.0 / n)
-                if not getattr(g, "_is_unit_seed", False):
-                    gp = gp * g.item()
-            return (gp,)
-
-        loss._ctx = Context((pred,), backward_fn)
-    return loss
+    return F.mse_loss(pred, target)
 
 
 class _ViewStorage:

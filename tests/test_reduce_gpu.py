@@ -170,6 +170,26 @@ def test_bias_add_and_transpose(oracle):
         np.testing.assert_array_equal(dt.get(), m.T)
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_bias_add_and_transpose_packet_paths(oracle, dtype):
+    """Shapes that take the 4-element packet kernels (extents multiples of 4) next to ragged ones."""
+    lib = native()
+    s = "f32" if dtype == np.float32 else "f64"
+    rng = np.random.default_rng(18)
+    for batch, out in ((1, 4), (5, 8), (257, 12), (300, 1000), (4096, 64), (3, 4096), (7, 6)):
+        x, b = rng.standard_normal((batch, out)).astype(dtype), rng.standard_normal(out).astype(dtype)
+        dx, db, dy = Buf(lib, x), Buf(lib, b), Buf(lib, shape=x.shape, dtype=dtype, fill=0xFF)
+        lib.call(f"keydnn_cuda_bias_add_{s}", dx.ptr, db.ptr, dy.ptr, batch, out)
+        assert_same_bits(dy.get(), oracle.bias_add(x, b))
+        lib.call(f"keydnn_cuda_bias_add_inplace_{s}", dx.ptr, db.ptr, batch, out)
+        assert_same_bits(dx.get(), oracle.bias_add(x, b))
+    for shape in ((4, 4), (64, 64), (128, 60), (60, 128), (68, 132), (1000, 36), (512, 2048), (4, 1000), (64, 66)):
+        m = rng.standard_normal(shape).astype(dtype)
+        dm, dt = Buf(lib, m), Buf(lib, shape=shape[::-1], dtype=dtype, fill=0xFF)
+        lib.call(f"keydnn_cuda_transpose2d_{s}", dm.ptr, dt.ptr, shape[0], shape[1])
+        np.testing.assert_array_equal(dt.get(), m.T, err_msg=str(shape))
+
+
 def test_guards_follow_the_reference():
     lib = native()
     d = Buf(lib, np.zeros(16, np.float32))
