@@ -156,7 +156,10 @@ softmax_block_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __rest
 #pragma unroll 2
             for (int c = threadIdx.x * V; c < len; c += step) {
                 kd::Pack4<T> g, y;
-                if (VEC) { g = kd::load4_stream(pa + c); y = kd::load4_stream(pb + c); }
+                if (VEC) {          // rows that are not staged are read again below: keep them in L2
+                    g = staged ? kd::load4_stream(pa + c) : kd::load4(pa + c);
+                    y = staged ? kd::load4_stream(pb + c) : kd::load4(pb + c);
+                }
                 else { g.v[0] = pa[c]; y.v[0] = pb[c]; }
 #pragma unroll
                 for (int k = 0; k < V; ++k) {
@@ -184,7 +187,7 @@ softmax_block_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __rest
 #pragma unroll 2
             for (int c = threadIdx.x * V; c < len; c += step) {
                 kd::Pack4<T> x;
-                if (VEC) x = kd::load4_stream(pa + c);
+                if (VEC) x = staged ? kd::load4_stream(pa + c) : kd::load4(pa + c);
                 else x.v[0] = pa[c];
 #pragma unroll
                 for (int k = 0; k < V; ++k) {

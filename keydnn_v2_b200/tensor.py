@@ -643,7 +643,8 @@ class Tensor:
     def backward(self, grad_out: Optional["Tensor"] = None, *, retain_graph: bool = False) -> None:
         """Reverse topological walk (``tensor/_tensor.py:1601-1861``): seed with ``grad_out``
         (ones for a scalar), call each ``ctx.backward_fn``, add contributions that meet at
-        a tensor, store the result on leaves that require grad.  Unless ``retain_graph`` is
+        a tensor (the first two out of place, later ones in place into that private sum),
+        store the result on leaves that require grad.  Unless ``retain_graph`` is
         set, every visited node drops its Context afterwards, which releases the saved
         activations to the allocator at once."""
         if not self.requires_grad:
@@ -674,6 +675,7 @@ class Tensor:
                         stack.append((p, False))
 
         grads: Dict[int, Tensor] = {id(self): grad_out}
+        owned = set()       # ids of sums made here: nobody else sees them, so further terms are added in place
         with no_grad():
             for node in reversed(topo):
                 g = grads.pop(id(node), None)
@@ -691,7 +693,14 @@ class Tensor:
                     if pg.shape != p.shape:
                         raise RuntimeError(f"gradient shape {pg.shape} != parent shape {p.shape}")
                     prev = grads.get(id(p))
-                    grads[id(p)] = pg if prev is None else prev + pg
+                    if prev is None:
+                        grads[id(p)] = pg
+                    elif id(prev) in owned:
+                        prev += pg              # third and later terms: no new tensor (tensor/_tensor.py:2487 wishes for this)
+                    else:
+                        total = prev + pg       # first meeting: either term may be shared with another branch
+                        owned.add(id(total))
+                        grads[id(p)] = total
                 if not retain_graph:
                     node._ctx = None
 

@@ -122,6 +122,27 @@ def test_graph_with_shared_nodes_and_inplace_rules(kd):
         T.from_numpy(rng.standard_normal((2, 3, 4))).sum(axis=1)
 
 
+def test_fan_in_of_four_accumulates_without_touching_shared_gradients(kd):
+    """u = a + a + a + a: four contributions meet at `a`, all the very same upstream tensor (add's backward
+    returns grad_out itself).  The third and fourth are added in place into a private sum; the shared upstream
+    gradient must come out unchanged."""
+    T = kd.Tensor
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((5, 7)).astype(np.float32)
+    g = rng.standard_normal((5, 7)).astype(np.float32)
+    ta = T.from_numpy(a, requires_grad=True)
+    tg = T.from_numpy(g)
+    u = ta + ta + ta + ta
+    u.backward(tg)
+    np.testing.assert_array_equal(tg.to_numpy(), g)
+    np.testing.assert_array_equal(ta.grad.to_numpy(), ((g + g) + g) + g)
+    # a second backward on a fresh graph adds to .grad out of place: the old .grad object keeps its values
+    old = ta.grad
+    (ta * 2.0).backward(tg)
+    np.testing.assert_array_equal(old.to_numpy(), ((g + g) + g) + g)
+    np.testing.assert_array_equal(ta.grad.to_numpy(), (((g + g) + g) + g) + g * np.float32(2.0))
+
+
 def test_allocator_reuses_blocks(kd):
     import ctypes
 
