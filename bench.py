@@ -599,11 +599,22 @@ def cnn_step_bench(lib, group, dist, steps: int, warmup: int, timer, batch: int 
     last = loss.item()
     t0 = time.perf_counter()
     timer.start()
-    for _ in range(steps):
-        lib.call("keydnn_cuda_memcpy_h2d_async", x.data, hx.ctypes.data, hx.nbytes)
-        lib.call("keydnn_cuda_memcpy_h2d_async", t.data, ht.ctypes.data, ht.nbytes)
-        loss = run_step()
-        loss.item()
+    if graph is not None:
+        # the public pipelined call: batch i+1 crosses PCIe on a copy stream while step i replays; every step's
+        # loss is copied to the host and read there one step later
+        pending = None
+        for _ in range(steps):
+            ticket = graph.step_async(hx, ht)
+            if pending is not None:
+                graph.loss_of(pending)
+            pending = ticket
+        graph.loss_of(pending)
+    else:
+        for _ in range(steps):
+            lib.call("keydnn_cuda_memcpy_h2d_async", x.data, hx.ctypes.data, hx.nbytes)
+            lib.call("keydnn_cuda_memcpy_h2d_async", t.data, ht.ctypes.data, ht.nbytes)
+            loss = run_step()
+            loss.item()
     e2e_ms = max(timer.stop_ms(), (time.perf_counter() - t0) * 1e3)
     sync()
     if graph is not None:

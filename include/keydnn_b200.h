@@ -43,6 +43,7 @@ int keydnn_cuda_memset(uint64_t dev_ptr, int value, size_t nbytes);
 int keydnn_cuda_synchronize(void);
 /* additive */
 int keydnn_cuda_memcpy_h2d_async(uint64_t dst_dev_ptr, const void* src_host_ptr, size_t nbytes);
+int keydnn_cuda_memcpy_d2h_async(void* dst_host_ptr, uint64_t src_dev_ptr, size_t nbytes);
 int keydnn_cuda_empty_cache(void);
 int keydnn_cuda_pool_stats(uint64_t* out4); /* reserved, in use, driver mallocs, requests */
 int keydnn_cuda_host_alloc(void** out, size_t nbytes); /* pinned host memory */

@@ -294,6 +294,14 @@ KD_API int keydnn_cuda_memcpy_h2d_async(std::uint64_t dst_dev, const void* src_h
                                       cudaMemcpyHostToDevice, g_stream));
 }
 
+// Additive: device->host copy that returns as soon as it is enqueued; the destination (pinned, to be
+// asynchronous) may be read after an event recorded behind the copy has completed.
+KD_API int keydnn_cuda_memcpy_d2h_async(void* dst_host, std::uint64_t src_dev, std::size_t nbytes) {
+    if (nbytes == 0) return 0;
+    return kd::status(cudaMemcpyAsync(dst_host, reinterpret_cast<const void*>(src_dev), nbytes,
+                                      cudaMemcpyDeviceToHost, g_stream));
+}
+
 KD_API int keydnn_cuda_memcpy_d2d(void* dst, const void* src, std::size_t nbytes) {
     if (nbytes == 0) return 0;
     if (!dst || !src) return 1;

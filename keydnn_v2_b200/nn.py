@@ -382,7 +382,67 @@ class GraphedTrainStep:
         self.lib.call("keydnn_cuda_graph_launch", self.exec.value)
         return self.loss
 
+    # -- pipelined feeding: batch i+1 crosses PCIe while step i runs ---------------------------------
+    def _pipeline(self):
+        if getattr(self, "_pipe", None) is None:
+            lib = self.lib
+            _, _, x, t = self._keep
+            copy = ctypes.c_uint64(0)
+            lib.call("keydnn_cuda_stream_create", ctypes.byref(copy))
+            slots = []
+            for _ in range(2):
+                ev_in, ev_done, host = ctypes.c_uint64(0), ctypes.c_uint64(0), ctypes.c_void_p(0)
+                lib.call("keydnn_cuda_event_create", ctypes.byref(ev_in))
+                lib.call("keydnn_cuda_event_create", ctypes.byref(ev_done))
+                lib.call("keydnn_cuda_host_alloc", ctypes.byref(host), 16)
+                slots.append({"x": Tensor.empty(x.shape, x.dtype), "t": Tensor.empty(t.shape, t.dtype), "arrived": ev_in.value,
+                              "done": ev_done.value, "host": host.value,
+                              "loss": np.frombuffer((ctypes.c_char * 16).from_address(host.value), dtype=self.loss.dtype, count=1)})
+            self._pipe = {"copy": copy.value, "slots": slots, "n": 0}
+        return self._pipe
+
+    def step_async(self, host_x: np.ndarray, host_target: np.ndarray) -> int:
+        """Enqueue one step on a batch in (pinned) host memory and return a ticket for ``loss_of``.
+
+        The batch goes to one of two staging buffers on a copy stream, so it overlaps the step that is
+        still running; the training stream then waits for it, moves it into the recorded step's input
+        buffers (a device copy, microseconds), replays the step and copies its loss to pinned host memory.
+        Nothing here waits for the GPU."""
+        lib, pipe = self.lib, self._pipeline()
+        _, _, x, t = self._keep
+        k = pipe["n"] % 2
+        slot = pipe["slots"][k]
+        pipe["n"] += 1
+        lib.call("keydnn_cuda_set_stream", pipe["copy"])
+        lib.call("keydnn_cuda_stream_wait_event", slot["done"])          # the step that last read this slot is over
+        lib.call("keydnn_cuda_memcpy_h2d_async", slot["x"].data, host_x.ctypes.data, host_x.nbytes)
+        lib.call("keydnn_cuda_memcpy_h2d_async", slot["t"].data, host_target.ctypes.data, host_target.nbytes)
+        lib.call("keydnn_cuda_event_record", slot["arrived"])
+        lib.call("keydnn_cuda_set_stream", self.stream.value)
+        lib.call("keydnn_cuda_stream_wait_event", slot["arrived"])
+        lib.call("keydnn_cuda_memcpy_d2d", x.data, slot["x"].data, x.nbytes)
+        lib.call("keydnn_cuda_memcpy_d2d", t.data, slot["t"].data, t.nbytes)
+        lib.call("keydnn_cuda_graph_launch", self.exec.value)
+        lib.call("keydnn_cuda_memcpy_d2h_async", slot["host"], self.loss.data, self.loss.nbytes)
+        lib.call("keydnn_cuda_event_record", slot["done"])
+        return k
+
+    def loss_of(self, ticket: int) -> float:
+        """The loss of the step ``step_async`` returned ``ticket`` for (waits for that step only)."""
+        slot = self._pipe["slots"][ticket]
+        self.lib.call("keydnn_cuda_event_synchronize", slot["done"])
+        return float(slot["loss"][0])
+
     def close(self) -> None:
+        pipe = getattr(self, "_pipe", None)
+        if pipe is not None:
+            self.lib.call("keydnn_cuda_synchronize")
+            for slot in pipe["slots"]:
+                self.lib.call("keydnn_cuda_event_destroy", slot["arrived"])
+                self.lib.call("keydnn_cuda_event_destroy", slot["done"])
+                self.lib.call("keydnn_cuda_host_free", slot["host"])
+            self.lib.call("keydnn_cuda_stream_destroy", pipe["copy"])
+            self._pipe = None
         if self.exec.value:
             self.lib.call("keydnn_cuda_graph_destroy", self.exec.value)
             self.exec = ctypes.c_uint64(0)

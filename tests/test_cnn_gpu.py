@@ -157,3 +157,57 @@ def test_graphed_training_step_follows_the_eager_one():
     # graph replays 1..5 correspond to eager steps 4..8 (three warm-up steps came first)
     np.testing.assert_allclose(losses["graph"], losses["eager"][3:8], rtol=2e-3, atol=1e-5)
     assert losses["eager"][-1] < losses["eager"][0]
+
+
+def test_pipelined_feeding_trains_on_the_batches_it_is_given():
+    """step_async / loss_of: two alternating batches fed from pinned host memory through the staging
+    buffers must give the losses of the same sequence run with plain copies and graph launches."""
+    import ctypes
+
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import nn
+
+    lib = kd.load()
+    rng = np.random.default_rng(12)
+
+    def pinned(a):
+        p = ctypes.c_void_p(0)
+        lib.call("keydnn_cuda_host_alloc", ctypes.byref(p), a.nbytes)
+        out = np.frombuffer((ctypes.c_char * a.nbytes).from_address(p.value), dtype=a.dtype).reshape(a.shape)
+        out[...] = a
+        return out, p
+
+    batches = []
+    for _ in range(2):
+        hx, px = pinned(rng.standard_normal((16, 3, 32, 32)).astype(np.float32))
+        ht, pt = pinned(np.eye(10, dtype=np.float32)[rng.integers(0, 10, 16)])
+        batches.append((hx, ht, px, pt))
+    losses = {}
+    for mode in ("plain", "pipelined"):
+        np.random.seed(3)
+        model = nn.small_cnn()
+        opt = nn.SGD(model.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
+        x, t = kd.Tensor.from_numpy(batches[0][0]), kd.Tensor.from_numpy(batches[0][1])
+        g = nn.GraphedTrainStep(model, opt, x, t, warmup=2)
+        try:
+            seq = []
+            if mode == "plain":
+                for i in range(6):
+                    x.copy_from_numpy(batches[i % 2][0])
+                    t.copy_from_numpy(batches[i % 2][1])
+                    seq.append(g.run().item())
+            else:
+                tickets = []
+                for i in range(6):
+                    tickets.append(g.step_async(batches[i % 2][0], batches[i % 2][1]))
+                    if i >= 1:
+                        seq.append(g.loss_of(tickets[i - 1]))
+                seq.append(g.loss_of(tickets[-1]))
+        finally:
+            g.close()
+        losses[mode] = seq
+    # same batches in the same order; the convolution's weight-gradient algorithm is free to add in any order
+    np.testing.assert_allclose(losses["pipelined"], losses["plain"], rtol=1e-5)
+    for _, _, px, pt in batches:
+        lib.call("keydnn_cuda_host_free", px)
+        lib.call("keydnn_cuda_host_free", pt)
