@@ -260,27 +260,22 @@ class _ViewStorage:
         pass
 
 
-class SGD:
-    """Stochastic gradient descent with coupled L2 weight decay (``optimizers/_sgd.py:119-140``) and
-    optional momentum (an addition: v = momentum * v + g'; p -= lr * v).
+class _FlatOptimizer:
+    """Parameters, gradients and optimizer state in flat device buffers.
 
-    All parameters are moved into one flat device buffer (each at a 256-byte boundary; the
-    ``Parameter`` objects become windows into it), so a step is: gather the gradients into a flat
-    buffer, one in-place NCCL all-reduce over it when ``group.world > 1`` (its 1/world average is
-    folded into the update), one fused kernel over (p, g, v).  The reference runs five tensor passes
-    and four allocations per parameter.
+    All parameters are moved into one allocation (each at a 256-byte boundary; the ``Parameter`` objects
+    become windows into it), so a step is: gather the gradients into a flat buffer, one in-place NCCL
+    all-reduce over it when ``group.world > 1`` (its 1/world average is folded into the update kernel),
+    one fused update kernel over the whole buffer.
     """
 
-    def __init__(self, params: Iterable[Parameter], lr: float = 0.01, momentum: float = 0.0, weight_decay: float = 0.0,
-                 group=None) -> None:
+    graph_safe = True          # the launches of a step depend on nothing the host changes between steps
+
+    def __init__(self, params: Iterable[Parameter], n_state: int, group=None) -> None:
         self.params = [p for p in params]
         if not self.params:
-            raise ValueError("SGD needs at least one parameter")
-        if lr <= 0.0:
-            raise ValueError(f"lr must be > 0, got {lr}")
-        if weight_decay < 0.0:
-            raise ValueError(f"weight_decay must be >= 0, got {weight_decay}")
-        self.lr, self.momentum, self.weight_decay, self.group = float(lr), float(momentum), float(weight_decay), group
+            raise ValueError(f"{type(self).__name__} needs at least one parameter")
+        self.group = group
         self.dtype = self.params[0].dtype
         if any(p.dtype != self.dtype for p in self.params):
             raise TypeError("all parameters must share one dtype")
@@ -294,10 +289,9 @@ class SGD:
         self.native = self.params[0].native
         self.flat_p = CudaStorage.allocate(off, self.dtype)
         self.flat_g = CudaStorage.allocate(off, self.dtype)
-        self.flat_v = CudaStorage.allocate(off, self.dtype) if momentum != 0.0 else None
-        for st in (self.flat_p, self.flat_g, self.flat_v):
-            if st is not None:
-                self.native.call("keydnn_cuda_memset", st.dev_ptr, 0, off)
+        self.state = [CudaStorage.allocate(off, self.dtype) for _ in range(n_state)]
+        for st in (self.flat_p, self.flat_g, *self.state):
+            self.native.call("keydnn_cuda_memset", st.dev_ptr, 0, off)
         for p, o in zip(self.params, self.offsets):
             self.native.call("keydnn_cuda_memcpy_d2d", self.flat_p.dev_ptr + o, p.data, p.nbytes)
             p.storage = _ViewStorage(self.flat_p, o, p.nbytes, self.dtype)
@@ -306,8 +300,9 @@ class SGD:
         for p in self.params:
             p.zero_grad()
 
-    def step(self) -> None:
-        lib, s = self.native, _suffix(self.dtype)
+    def _gather_grads(self) -> int:
+        """Copies every gradient into the flat buffer, sums it over the ranks; returns the world size."""
+        lib = self.native
         for p, o in zip(self.params, self.offsets):
             if p.grad is None:
                 lib.call("keydnn_cuda_memset", self.flat_g.dev_ptr + o, 0, p.nbytes)
@@ -315,11 +310,68 @@ class SGD:
                 lib.call("keydnn_cuda_memcpy_d2d", self.flat_g.dev_ptr + o, p.grad.data, p.nbytes)
         world = 1 if self.group is None else self.group.world
         if world > 1:
-            self.group.allreduce_sum(self.flat_g.dev_ptr, self.n, s)
-        lib.call(f"keydnn_cuda_sgd_momentum_step_{s}", self.flat_p.dev_ptr, self.flat_g.dev_ptr,
-                 self.flat_v.dev_ptr if self.flat_v else None, self.n, _cfloat(self.dtype, self.lr),
-                 _cfloat(self.dtype, self.momentum), _cfloat(self.dtype, self.weight_decay),
-                 _cfloat(self.dtype, 1.0 / world))
+            self.group.allreduce_sum(self.flat_g.dev_ptr, self.n, _suffix(self.dtype))
+        return world
+
+
+class SGD(_FlatOptimizer):
+    """Stochastic gradient descent with coupled L2 weight decay (``optimizers/_sgd.py:119-140``) and
+    optional momentum (an addition: v = momentum * v + g'; p -= lr * v), over flat buffers: one fused
+    kernel over (p, g, v) where the reference runs five tensor passes and four allocations per parameter.
+    """
+
+    def __init__(self, params: Iterable[Parameter], lr: float = 0.01, momentum: float = 0.0, weight_decay: float = 0.0,
+                 group=None) -> None:
+        if lr <= 0.0:
+            raise ValueError(f"lr must be > 0, got {lr}")
+        if weight_decay < 0.0:
+            raise ValueError(f"weight_decay must be >= 0, got {weight_decay}")
+        super().__init__(params, 1 if momentum != 0.0 else 0, group)
+        self.lr, self.momentum, self.weight_decay = float(lr), float(momentum), float(weight_decay)
+        self.flat_v = self.state[0] if self.state else None
+
+    def step(self) -> None:
+        world = self._gather_grads()
+        self.native.call(f"keydnn_cuda_sgd_momentum_step_{_suffix(self.dtype)}", self.flat_p.dev_ptr, self.flat_g.dev_ptr,
+                         self.flat_v.dev_ptr if self.flat_v else None, self.n, _cfloat(self.dtype, self.lr),
+                         _cfloat(self.dtype, self.momentum), _cfloat(self.dtype, self.weight_decay),
+                         _cfloat(self.dtype, 1.0 / world))
+
+
+class Adam(_FlatOptimizer):
+    """Adam with coupled L2 weight decay (``optimizers/_adam.py:120-219``; there CPU-only, eleven tensor passes
+    per parameter) over flat buffers: one fused kernel over (p, g, m, v) per step, the gradient all-reduce of
+    ``group`` in front of it.  Every parameter shares the step count, as all of them get a gradient each step.
+    The bias corrections 1 - beta^t change every step and are passed by value, so a step cannot be replayed
+    from a CUDA graph (``graph_safe`` is False)."""
+
+    graph_safe = False
+
+    def __init__(self, params: Iterable[Parameter], lr: float = 1e-3, betas: Tuple[float, float] = (0.9, 0.999),
+                 eps: float = 1e-8, weight_decay: float = 0.0, group=None) -> None:
+        self.lr, self.betas, self.eps, self.weight_decay = float(lr), (float(betas[0]), float(betas[1])), float(eps), float(weight_decay)
+        b1, b2 = self.betas
+        if self.lr <= 0.0:
+            raise ValueError(f"lr must be > 0, got {self.lr}")
+        if not (0.0 < b1 < 1.0) or not (0.0 < b2 < 1.0):
+            raise ValueError(f"betas must be in (0,1), got {self.betas}")
+        if self.eps <= 0.0:
+            raise ValueError(f"eps must be > 0, got {self.eps}")
+        if self.weight_decay < 0.0:
+            raise ValueError(f"weight_decay must be >= 0, got {self.weight_decay}")
+        super().__init__(params, 2, group)
+        self.flat_m, self.flat_v = self.state
+        self.t = 0
+
+    def step(self) -> None:
+        world = self._gather_grads()
+        self.t += 1
+        b1, b2 = self.betas
+        c = lambda v: _cfloat(self.dtype, v)   # noqa: E731
+        self.native.call(f"keydnn_cuda_adam_step_{_suffix(self.dtype)}", self.flat_p.dev_ptr, self.flat_g.dev_ptr,
+                         self.flat_m.dev_ptr, self.flat_v.dev_ptr, self.n, c(self.lr), c(b1), c(b2), c(self.eps),
+                         c(self.weight_decay), c(1.0 - b1), c(1.0 - b2), c(1.0 - b1 ** self.t), c(1.0 - b2 ** self.t),
+                         c(1.0 / world))
 
 
 def small_cnn(dtype=np.float32) -> Sequential:
@@ -352,6 +404,8 @@ class GraphedTrainStep:
     """
 
     def __init__(self, model: Module, opt: SGD, x: Tensor, target: Tensor, warmup: int = 3) -> None:
+        if not getattr(opt, "graph_safe", False):
+            raise TypeError(f"{type(opt).__name__} passes per-step values from the host; its step cannot be recorded")
         self.lib, self.dnn = x.native, load_dnn()
         self._keep = (model, opt, x, target)
         self._prev = ctypes.c_uint64(0)

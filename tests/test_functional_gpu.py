@@ -149,3 +149,32 @@ def test_softmax_classifier_trains_with_adam():
         opt.step()
         losses.append(loss.item())
     assert losses[-1] < 0.35 * losses[0], losses[::8]
+
+
+def test_flat_buffer_adam_equals_the_per_parameter_one(golden):
+    """nn.Adam keeps all parameters in one buffer and updates them with one launch: same bits as the
+    reference-pinned per-parameter optimizer; a recorded step refuses it (per-step host scalars)."""
+    Tensor, Parameter, _, F = _mods()
+    from keydnn_v2_b200 import nn
+
+    rng = np.random.default_rng(4)
+    extra = rng.standard_normal((7, 5)).astype(np.float32)
+    ps = [Parameter.from_numpy(golden["adam/p0"]), Parameter.from_numpy(extra)]
+    qs = [Parameter.from_numpy(golden["adam/p0"]), Parameter.from_numpy(extra)]
+    flat = nn.Adam(ps, lr=1e-2, weight_decay=1e-2)
+    each = F.Adam(qs, lr=1e-2, weight_decay=1e-2)
+    for k in range(3):
+        g_extra = rng.standard_normal(extra.shape).astype(np.float32)
+        for group in (ps, qs):
+            group[0].grad = Tensor.from_numpy(golden[f"adam/g{k + 1}"])
+            group[1].grad = Tensor.from_numpy(g_extra)
+        flat.step()
+        each.step()
+        assert_same_bits(ps[0].to_numpy(), golden[f"adam_wd/p{k + 1}"])
+        for a, b in zip(ps, qs):
+            assert_same_bits(a.to_numpy(), b.to_numpy())
+    model = nn.Linear(4, 2)
+    x = Tensor.from_numpy(rng.standard_normal((3, 4)).astype(np.float32))
+    t = Tensor.from_numpy(rng.standard_normal((3, 2)).astype(np.float32))
+    with pytest.raises(TypeError):
+        nn.GraphedTrainStep(model, nn.Adam(model.parameters()), x, t)
