@@ -73,3 +73,35 @@ def test_sharded_reductions_match_numpy_on_the_whole_matrix(tmp_path):
                     np.testing.assert_array_equal(gxm, want[rows])
                     np.testing.assert_allclose(gm, np.full((R, C), 1.0 / n), **tol)
                 np.testing.assert_array_equal(gs, np.ones((R, C), dt))
+
+
+def test_data_parallel_steps_equal_one_process_on_the_whole_batch(tmp_path):
+    """SGD-momentum and Adam over the flat gradient buffer with an NCCL all-reduce: after three steps every
+    rank holds the same parameters, and they equal a one-process run on the concatenated batch (the mean
+    loss makes the averaged shard gradients the full-batch gradient)."""
+    world = min(_device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    worker = str(HERE / "_dp_worker.py")
+    procs = [subprocess.Popen([sys.executable, worker, str(r), str(world), str(tmp_path / "nccl_id_dp"), str(tmp_path)], env=env)
+             for r in range(world)]
+    try:
+        codes = [p.wait(timeout=300) for p in procs]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+    assert codes == [0] * world
+    one = subprocess.run([sys.executable, worker, "0", "1", str(tmp_path / "unused"), str(tmp_path), str(world)], env=env, timeout=300)
+    assert one.returncode == 0
+    whole = dict(np.load(tmp_path / "dp_rank0_of1.npz"))
+    ranks = [dict(np.load(tmp_path / f"dp_rank{r}_of{world}.npz")) for r in range(world)]
+    for key in whole:
+        if key.endswith("/loss"):
+            # each rank reports the loss of its own slice; their mean is the whole-batch loss
+            np.testing.assert_allclose(np.mean([r[key] for r in ranks], axis=0), whole[key], rtol=1e-4)
+            continue
+        for r in ranks[1:]:
+            np.testing.assert_array_equal(r[key], ranks[0][key], err_msg=key)       # replicas stay identical
+        np.testing.assert_allclose(ranks[0][key], whole[key], rtol=2e-3, atol=2e-5, err_msg=key)
