@@ -44,6 +44,7 @@ __global__ void __launch_bounds__(kThreads)
 bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ mean,
                 const T* __restrict__ invstd, const T* __restrict__ gamma, const T* __restrict__ beta, int N, int C,
                 int64_t HW, int ach, double* partials, unsigned int* counters, double* sums /* [2][C] */) {
+    kd::pdl_prologue();
     __shared__ double sm[kWarps];
     const int c = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
     const int n_begin = slice * ach;
@@ -117,6 +118,7 @@ bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __res
 template <typename T>
 __global__ void bn_finalize_stats(const double* __restrict__ sums, int C, double m, T eps, T momentum, T* mean, T* var,
                                   T* invstd, T* running_mean, T* running_var) {
+    kd::pdl_prologue();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
     const double mu = sums[c] / m;
@@ -132,6 +134,7 @@ __global__ void bn_finalize_stats(const double* __restrict__ sums, int C, double
 
 template <typename T>
 __global__ void bn_invstd_from_var(const T* __restrict__ var, int C, T eps, T* invstd) {
+    kd::pdl_prologue();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c < C) invstd[c] = T(1) / sqrt(var[c] + eps);
 }
@@ -142,6 +145,7 @@ template <typename T, bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_apply_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
              const T* __restrict__ mean, const T* __restrict__ invstd, T* __restrict__ y, int64_t rows, int C, int64_t HW) {
+    kd::pdl_prologue();
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const int c = static_cast<int>(r % C);
         const T mu = __ldg(mean + c), is = __ldg(invstd + c);
@@ -180,6 +184,7 @@ __global__ void __launch_bounds__(kThreads)
 bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ gamma, const T* __restrict__ beta,
              const T* __restrict__ mean, const T* __restrict__ invstd, const double* __restrict__ sums,
              T* __restrict__ dx, int64_t rows, int C, int64_t HW, T m) {
+    kd::pdl_prologue();
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const int c = static_cast<int>(r % C);
         const T mu = __ldg(mean + c), is = __ldg(invstd + c);
@@ -219,6 +224,7 @@ bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restri
 
 template <typename T>
 __global__ void bn_param_grads(const double* __restrict__ sums, int C, T* dgamma, T* dbeta) {
+    kd::pdl_prologue();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
     if (dbeta) dbeta[c] = static_cast<T>(sums[c]);
@@ -272,23 +278,23 @@ int bn_forward(const T* x, const T* gamma, const T* beta, T* y, T* mean, T* invs
         SumsPlan p;
         if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
         dim3 grid(C, p.nslices);
-        if (vec) bn_channel_sums<T, 0, true, false><<<grid, kThreads, 0, s>>>(x, nullptr, nullptr, nullptr, nullptr, nullptr, N, C, HW, p.ach, p.partials, p.counters, p.sums);
-        else bn_channel_sums<T, 0, false, false><<<grid, kThreads, 0, s>>>(x, nullptr, nullptr, nullptr, nullptr, nullptr, N, C, HW, p.ach, p.partials, p.counters, p.sums);
-        bn_finalize_stats<T><<<(C + 127) / 128, 128, 0, s>>>(p.sums, C, static_cast<double>(N) * static_cast<double>(HW), eps,
+        if (vec) (void)kd::launch(bn_channel_sums<T, 0, true, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, N, C, HW, p.ach, p.partials, p.counters, p.sums);
+        else (void)kd::launch(bn_channel_sums<T, 0, false, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, N, C, HW, p.ach, p.partials, p.counters, p.sums);
+        (void)kd::launch(bn_finalize_stats<T>, dim3((C + 127) / 128), 128, 0, p.sums, C, static_cast<double>(N) * static_cast<double>(HW), eps,
                                                           momentum, mean, static_cast<T*>(nullptr), invstd, running_mean,
                                                           running_var);
     } else {
-        bn_invstd_from_var<T><<<(C + 127) / 128, 128, 0, s>>>(running_var, C, eps, invstd);
+        (void)kd::launch(bn_invstd_from_var<T>, dim3((C + 127) / 128), 128, 0, running_var, C, eps, invstd);
         cudaMemcpyAsync(mean, running_mean, C * sizeof(T), cudaMemcpyDeviceToDevice, s);
     }
     const int64_t rows = static_cast<int64_t>(N) * C;
     const dim3 g2 = row_grid(rows, HW);
     if (relu) {
-        if (vec) bn_apply_fwd<T, true, true><<<g2, kThreads, 0, s>>>(x, gamma, beta, mean, invstd, y, rows, C, HW);
-        else bn_apply_fwd<T, false, true><<<g2, kThreads, 0, s>>>(x, gamma, beta, mean, invstd, y, rows, C, HW);
+        if (vec) (void)kd::launch(bn_apply_fwd<T, true, true>, dim3(g2), kThreads, 0, x, gamma, beta, mean, invstd, y, rows, C, HW);
+        else (void)kd::launch(bn_apply_fwd<T, false, true>, dim3(g2), kThreads, 0, x, gamma, beta, mean, invstd, y, rows, C, HW);
     } else {
-        if (vec) bn_apply_fwd<T, true, false><<<g2, kThreads, 0, s>>>(x, gamma, beta, mean, invstd, y, rows, C, HW);
-        else bn_apply_fwd<T, false, false><<<g2, kThreads, 0, s>>>(x, gamma, beta, mean, invstd, y, rows, C, HW);
+        if (vec) (void)kd::launch(bn_apply_fwd<T, true, false>, dim3(g2), kThreads, 0, x, gamma, beta, mean, invstd, y, rows, C, HW);
+        else (void)kd::launch(bn_apply_fwd<T, false, false>, dim3(g2), kThreads, 0, x, gamma, beta, mean, invstd, y, rows, C, HW);
     }
     return kd::launch_status();
 }
@@ -304,15 +310,15 @@ int bn_backward(const T* x, const T* gamma, const T* beta, const T* go, const T*
     SumsPlan p;
     if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
     dim3 grid(C, p.nslices);
-#define KD_BN_SUMS(V, R) bn_channel_sums<T, 1, V, R><<<grid, kThreads, 0, s>>>(x, go, mean, invstd, gamma, beta, N, C, HW, p.ach, p.partials, p.counters, p.sums)
+#define KD_BN_SUMS(V, R) (void)kd::launch(bn_channel_sums<T, 1, V, R>, dim3(grid), kThreads, 0, x, go, mean, invstd, gamma, beta, N, C, HW, p.ach, p.partials, p.counters, p.sums)
     if (relu) { if (vec) KD_BN_SUMS(true, true); else KD_BN_SUMS(false, true); }
     else { if (vec) KD_BN_SUMS(true, false); else KD_BN_SUMS(false, false); }
 #undef KD_BN_SUMS
-    if (dgamma || dbeta) bn_param_grads<T><<<(C + 127) / 128, 128, 0, s>>>(p.sums, C, dgamma, dbeta);
+    if (dgamma || dbeta) (void)kd::launch(bn_param_grads<T>, dim3((C + 127) / 128), 128, 0, p.sums, C, dgamma, dbeta);
     const int64_t rows = static_cast<int64_t>(N) * C;
     const dim3 g2 = row_grid(rows, HW);
     const T m = static_cast<T>(static_cast<double>(N) * static_cast<double>(HW));
-#define KD_BN_APPLY(V, R) bn_apply_bwd<T, V, R><<<g2, kThreads, 0, s>>>(x, go, gamma, beta, mean, invstd, p.sums, dx, rows, C, HW, m)
+#define KD_BN_APPLY(V, R) (void)kd::launch(bn_apply_bwd<T, V, R>, dim3(g2), kThreads, 0, x, go, gamma, beta, mean, invstd, p.sums, dx, rows, C, HW, m)
     if (relu) { if (vec) KD_BN_APPLY(true, true); else KD_BN_APPLY(false, true); }
     else { if (vec) KD_BN_APPLY(true, false); else KD_BN_APPLY(false, false); }
 #undef KD_BN_APPLY

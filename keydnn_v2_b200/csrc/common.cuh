@@ -75,25 +75,55 @@ inline unsigned grid_fit(K kernel, int threads, int64_t work_ctas, size_t smem =
     return static_cast<unsigned>(g < 1 ? 1 : g);
 }
 
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of the library opens with pdl_prologue(): it lets the next
+// kernel of the stream be scheduled while this one is still running, then waits until everything the stream
+// holds in front of this kernel has completed and its writes are visible.  A dependent kernel's CTAs are
+// therefore already resident, parked at the wait, when the last CTA of its predecessor retires: launch latency
+// and the ramp-up of a grid are hidden behind the tail of the kernel before it (the short reductions of this
+// library spend 2-4 us of a 20-45 us run in ramp and tail).  Nothing is read or written before the wait, so
+// stream order is kept exactly.  Launched without the attribute both instructions do nothing.
+// ---------------------------------------------------------------------------
+bool pdl_enabled();             // runtime.cu: on unless the environment sets KEYDNN_PDL=0
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, unsigned threads, size_t smem, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define KD_LAUNCH(KERNEL, WORK, THREADS, SMEM, ...)                                                           \
     do {                                                                                                      \
         auto kd_fn_ = (KERNEL);                                                                               \
-        kd_fn_<<<kd::grid_fit(kd_fn_, (THREADS), (WORK), (SMEM), kd::stream_waves()), (THREADS), (SMEM),        \
-                 kd::stream()>>>(__VA_ARGS__);                                                                \
+        (void)kd::launch(kd_fn_, dim3(kd::grid_fit(kd_fn_, (THREADS), (WORK), (SMEM), kd::stream_waves())), (THREADS), \
+                         (SMEM), __VA_ARGS__);                                                                \
     } while (0)
 
 // Same with an explicit number of waves.
 #define KD_LAUNCH_W(KERNEL, WAVES, WORK, THREADS, SMEM, ...)                                                  \
     do {                                                                                                      \
         auto kd_fn_ = (KERNEL);                                                                               \
-        kd_fn_<<<kd::grid_fit(kd_fn_, (THREADS), (WORK), (SMEM), (WAVES)), (THREADS), (SMEM), kd::stream()>>>(__VA_ARGS__); \
+        (void)kd::launch(kd_fn_, dim3(kd::grid_fit(kd_fn_, (THREADS), (WORK), (SMEM), (WAVES))), (THREADS), (SMEM), __VA_ARGS__); \
     } while (0)
 
 // Same with exactly one resident wave.
 #define KD_LAUNCH1(KERNEL, WORK, THREADS, SMEM, ...)                                                          \
     do {                                                                                                      \
         auto kd_fn_ = (KERNEL);                                                                               \
-        kd_fn_<<<kd::grid_fit(kd_fn_, (THREADS), (WORK), (SMEM), 1), (THREADS), (SMEM), kd::stream()>>>(__VA_ARGS__); \
+        (void)kd::launch(kd_fn_, dim3(kd::grid_fit(kd_fn_, (THREADS), (WORK), (SMEM), 1)), (THREADS), (SMEM), __VA_ARGS__); \
     } while (0)
 
 // Separately rounded IEEE operations: never contracted into an FMA, whatever -fmad says.

@@ -38,6 +38,7 @@ struct OpNe { template <typename T> __device__ float operator()(T a, T b) const 
 template <typename TI, typename TO, int MODE, int UNROLL, typename Op>
 __global__ void __launch_bounds__(kThreads)
 ew_packet_kernel(const TI* a, const TI* b, TI alpha, TO* y, int64_t n, Op op) {
+    kd::pdl_prologue();
     const int64_t n4 = n >> 2;
     const int64_t tile = static_cast<int64_t>(kThreads) * UNROLL;
     for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < n4;
@@ -74,6 +75,7 @@ ew_packet_kernel(const TI* a, const TI* b, TI alpha, TO* y, int64_t n, Op op) {
 template <typename TI, typename TO, int MODE, typename Op>
 __global__ void __launch_bounds__(kThreads)
 ew_scalar_kernel(const TI* a, const TI* b, TI alpha, TO* y, int64_t n, Op op) {
+    kd::pdl_prologue();
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
          i += static_cast<int64_t>(gridDim.x) * kThreads)
         y[i] = op(a[i], MODE == kBinary ? b[i] : alpha);
@@ -89,7 +91,7 @@ int launch_ew(const TI* a, const TI* b, TI alpha, TO* y, int64_t n, Op op) {
         KD_LAUNCH_W((ew_packet_kernel<TI, TO, MODE, UNROLL, Op>), 64, tiles, kThreads, 0, a, b, alpha, y, n, op);
     } else {
         const unsigned grid = kd::grid_for((n + kThreads - 1) / kThreads, 16);
-        ew_scalar_kernel<TI, TO, MODE, Op><<<grid, kThreads, 0, kd::stream()>>>(a, b, alpha, y, n, op);
+        (void)kd::launch(ew_scalar_kernel<TI, TO, MODE, Op>, dim3(grid), kThreads, 0, a, b, alpha, y, n, op);
     }
     return kd::launch_status();
 }
@@ -97,6 +99,7 @@ int launch_ew(const TI* a, const TI* b, TI alpha, TO* y, int64_t n, Op op) {
 // --- fill -------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(kThreads) fill_kernel(T* y, int64_t n, T value, int head) {
+    kd::pdl_prologue();
     // `head` elements bring y up to a packet boundary; packets follow; tail last.
     const int64_t body = n - head;
     const int64_t n4 = body >> 2;
@@ -149,6 +152,7 @@ __device__ __forceinline__ void sgd_one(T& p, T g, T* v, T lr, T mu, T wd, T gsc
 template <typename T, bool MOMENTUM, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 sgd_kernel(T* p, const T* g, T* v, int64_t n, T lr, T mu, T wd, T gscale, bool use_scale, bool use_wd) {
+    kd::pdl_prologue();
     if (VEC) {
         constexpr int UNROLL = 2;
         const int64_t n4 = n >> 2;
@@ -210,6 +214,7 @@ template <typename T, bool DIV>
 __global__ void __launch_bounds__(kThreads)
 muldiv_backward_kernel(const T* __restrict__ g, const T* __restrict__ a, const T* __restrict__ b, T* ga, T* gb, int64_t n,
                        bool vec) {
+    kd::pdl_prologue();
     if (vec) {
         constexpr int UNROLL = 2;
         const int64_t n4 = n >> 2;

@@ -22,6 +22,7 @@ struct MapArgs {
 template <typename T, int NIN, int NOUT, int UNROLL, bool VEC, typename F>
 __global__ void __launch_bounds__(kMapThreads)
 map_kernel(MapArgs<T, NIN, NOUT> a, int64_t n, F f) {
+    kd::pdl_prologue();
     if (VEC) {
         const int64_t n4 = n >> 2;
         const int64_t tile = static_cast<int64_t>(kMapThreads) * UNROLL;
@@ -119,6 +120,7 @@ inline int launch_map(const MapArgs<T, NIN, NOUT>& a, int64_t n, F f, int waves 
 template <typename T, int NIN, bool VEC, typename F>
 __global__ void __launch_bounds__(kMapThreads)
 map_sum_kernel(MapArgs<T, NIN, 1> a, int64_t n, double* partials, unsigned int* counter, T scale, int finish, F f) {
+    kd::pdl_prologue();
     __shared__ double sm[kMapThreads / 32];
     __shared__ bool last;
     constexpr int U = (NIN == 1) ? 8 : 4;
@@ -209,8 +211,8 @@ inline int launch_map_sum(const MapArgs<T, NIN, 1>& a, int64_t n, T scale, int f
     double* partials = static_cast<double*>(scratch(grid * sizeof(double)));
     unsigned int* counter = counters(1);
     if (!partials || !counter) return static_cast<int>(cudaErrorMemoryAllocation);
-    if (vec) map_sum_kernel<T, NIN, true, F><<<grid, kMapThreads, 0, stream()>>>(a, n, partials, counter, scale, finish, f);
-    else map_sum_kernel<T, NIN, false, F><<<grid, kMapThreads, 0, stream()>>>(a, n, partials, counter, scale, finish, f);
+    if (vec) (void)kd::launch(map_sum_kernel<T, NIN, true, F>, dim3(grid), kMapThreads, 0, a, n, partials, counter, scale, finish, f);
+    else (void)kd::launch(map_sum_kernel<T, NIN, false, F>, dim3(grid), kMapThreads, 0, a, n, partials, counter, scale, finish, f);
     return launch_status();
 }
 

@@ -27,6 +27,7 @@ struct GatherMeta {
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 broadcast_gather_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n, GatherMeta m) {
+    kd::pdl_prologue();
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
          i += static_cast<int64_t>(gridDim.x) * kThreads) {
         int64_t rem = i, off = 0;
@@ -45,6 +46,7 @@ broadcast_gather_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n, G
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 broadcast_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int K, int64_t B) {
+    kd::pdl_prologue();
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const T v = __ldg(x + (r % K));
         T* dst = y + r * B;
@@ -67,6 +69,7 @@ broadcast_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, 
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 broadcast_cols_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t A, int64_t K) {
+    kd::pdl_prologue();
     for (int64_t k = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; k < K;
          k += static_cast<int64_t>(gridDim.x) * kThreads) {
         const T v = __ldg(x + k);
@@ -123,7 +126,7 @@ int broadcast_to(const T* x, T* y, const int64_t* in_shape, int in_ndim, const i
             if (gy > A) gy = A;
             if (gy > 65535) gy = 65535;
             dim3 grid(gx, static_cast<unsigned>(gy));
-            broadcast_cols_kernel<T><<<grid, kThreads, 0, s>>>(x, y, A, K);
+            (void)kd::launch(broadcast_cols_kernel<T>, dim3(grid), kThreads, 0, x, y, A, K);
         } else {
             const int64_t rows = A * K;
             // few long rows: split each row over blockIdx.y so the machine stays full
@@ -135,8 +138,8 @@ int broadcast_to(const T* x, T* y, const int64_t* in_shape, int in_ndim, const i
             if (gy > 65535) gy = 65535;
             const dim3 grid(gx, static_cast<unsigned>(gy));
             const bool vec = kd::aligned_pack<T>(y) && (B % 4 == 0);
-            if (vec) broadcast_rows_kernel<T, true><<<grid, kThreads, 0, s>>>(x, y, rows, static_cast<int>(K), B);
-            else broadcast_rows_kernel<T, false><<<grid, kThreads, 0, s>>>(x, y, rows, static_cast<int>(K), B);
+            if (vec) (void)kd::launch(broadcast_rows_kernel<T, true>, dim3(grid), kThreads, 0, x, y, rows, static_cast<int>(K), B);
+            else (void)kd::launch(broadcast_rows_kernel<T, false>, dim3(grid), kThreads, 0, x, y, rows, static_cast<int>(K), B);
         }
         return cudaGetLastError() == cudaSuccess ? ST_OK : ST_CUDA_ERR;
     }
@@ -150,7 +153,7 @@ int broadcast_to(const T* x, T* y, const int64_t* in_shape, int in_ndim, const i
         si *= in_p[d];
     }
     const unsigned grid = kd::grid_for((n + kThreads - 1) / kThreads, 8);
-    broadcast_gather_kernel<T><<<grid, kThreads, 0, s>>>(x, y, n, m);
+    (void)kd::launch(broadcast_gather_kernel<T>, dim3(grid), kThreads, 0, x, y, n, m);
     return cudaGetLastError() == cudaSuccess ? ST_OK : ST_CUDA_ERR;
 }
 
@@ -158,6 +161,7 @@ int broadcast_to(const T* x, T* y, const int64_t* in_shape, int in_ndim, const i
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 bias_add_kernel(const T* x, const T* __restrict__ b, T* y, int64_t out, int64_t n) {
+    kd::pdl_prologue();
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
          i += static_cast<int64_t>(gridDim.x) * kThreads)
         y[i] = x[i] + __ldg(b + (i % out));
@@ -168,6 +172,7 @@ bias_add_kernel(const T* x, const T* __restrict__ b, T* y, int64_t out, int64_t 
 template <typename T, int UNROLL>
 __global__ void __launch_bounds__(kThreads)
 bias_add_packet_kernel(const T* x, const T* __restrict__ b, T* y, kd::FastDiv per_row, int64_t n4) {
+    kd::pdl_prologue();
     const int64_t tile = static_cast<int64_t>(kThreads) * UNROLL;
     for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < n4; base += static_cast<int64_t>(gridDim.x) * tile) {
         kd::Pack4<T> vx[UNROLL], vb[UNROLL];
@@ -207,7 +212,7 @@ int bias_add(const T* x, const T* b, T* y, int64_t batch, int64_t out) {
         return kd::launch_status();
     }
     const unsigned grid = kd::grid_for((n + kThreads - 1) / kThreads, 8);
-    bias_add_kernel<T><<<grid, kThreads, 0, kd::stream()>>>(x, b, y, out, n);
+    (void)kd::launch(bias_add_kernel<T>, dim3(grid), kThreads, 0, x, b, y, out, n);
     return kd::launch_status();
 }
 
@@ -215,6 +220,7 @@ int bias_add(const T* x, const T* b, T* y, int64_t batch, int64_t out) {
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 transpose_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int cols) {
+    kd::pdl_prologue();
     __shared__ T tile[32][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
     const int tiles_c = (cols + 31) / 32, tiles_r = (rows + 31) / 32;
@@ -241,6 +247,7 @@ transpose_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int cols)
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 transpose_packet_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int cols) {
+    kd::pdl_prologue();
     __shared__ T tile[64][65];
     const int tiles_c = (cols + 63) / 64, tiles_r = (rows + 63) / 64;
     for (int64_t t = blockIdx.x; t < static_cast<int64_t>(tiles_c) * tiles_r; t += gridDim.x) {
@@ -284,7 +291,7 @@ int transpose2d(const T* x, T* y, int rows, int cols) {
         KD_LAUNCH_W(transpose_packet_kernel<T>, 8, tiles, kThreads, 0, x, y, rows, cols);
     } else {
         const int64_t tiles = static_cast<int64_t>((cols + 31) / 32) * ((rows + 31) / 32);
-        transpose_kernel<T><<<kd::grid_for(tiles, 8), kThreads, 0, kd::stream()>>>(x, y, rows, cols);
+        (void)kd::launch(transpose_kernel<T>, dim3(kd::grid_for(tiles, 8)), kThreads, 0, x, y, rows, cols);
     }
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }

@@ -64,6 +64,7 @@ __global__ void argmax_select_kernel(const T* __restrict__ vals, const long long
                                      long long span, int64_t n, int64_t val_stride, int64_t idx_stride,
                                      T* __restrict__ out_val,
                                      long long* __restrict__ out_global, long long* __restrict__ out_local) {
+    kd::pdl_prologue();
     for (int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < n;
          c += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         T best = kd::neg_inf<T>();
@@ -86,7 +87,7 @@ int argmax_select(const T* vals, const long long* idx, int world, int rank, long
     if (world <= 0 || rank < 0 || rank >= world || n <= 0 || val_stride < n || idx_stride < n) return -2;
     (void)cudaGetLastError();
     const unsigned grid = kd::grid_for((n + 255) / 256, 8);
-    argmax_select_kernel<T><<<grid, 256, 0, kd::stream()>>>(vals, idx, world, rank, span, n, val_stride, idx_stride, out_val,
+    (void)kd::launch(argmax_select_kernel<T>, dim3(grid), 256, 0, vals, idx, world, rank, span, n, val_stride, idx_stride, out_val,
                                                           out_global, out_local);
     return kd::launch_status();
 }

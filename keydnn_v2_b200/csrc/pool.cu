@@ -46,6 +46,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 maxpool_fwd_generic(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, PoolGeom g,
                     int64_t total) {
+    kd::pdl_prologue();
     const int Wp = g.W + 2 * g.pw;
     for (int64_t o = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; o < total;
          o += static_cast<int64_t>(gridDim.x) * kThreads) {
@@ -79,6 +80,7 @@ template <typename T, int U>
 __global__ void __launch_bounds__(kThreads)
 maxpool2x2_fwd(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, int H, int W, int Ho, int Wo,
                int64_t groups, kd::FastDiv by_gpr, kd::FastDiv by_ho) {
+    kd::pdl_prologue();
     const int64_t tile = static_cast<int64_t>(kThreads) * U;
     for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < groups;
          base += static_cast<int64_t>(gridDim.x) * tile) {
@@ -139,6 +141,7 @@ template <typename T, int U>
 __global__ void __launch_bounds__(kThreads)
 maxpool2x2_bwd(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, int H, int W, int Ho,
                int Wo, int64_t blocks, kd::FastDiv by_bpr, kd::FastDiv by_h) {
+    kd::pdl_prologue();
     const int64_t tile = static_cast<int64_t>(kThreads) * U;
     for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < blocks;
          base += static_cast<int64_t>(gridDim.x) * tile) {
@@ -185,6 +188,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 maxpool_bwd_gather(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, PoolGeom g,
                    int64_t total) {
+    kd::pdl_prologue();
     const int Wp = g.W + 2 * g.pw;
     for (int64_t e = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; e < total;
          e += static_cast<int64_t>(gridDim.x) * kThreads) {
@@ -216,6 +220,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 maxpool_bwd_scatter(const T* __restrict__ go, const long long* __restrict__ idx, T* gx_pad, int Ho, int Wo, int Hp,
                     int Wp, int64_t total) {
+    kd::pdl_prologue();
     const int64_t plane_o = static_cast<int64_t>(Ho) * Wo;
     const int64_t plane_i = static_cast<int64_t>(Hp) * Wp;
     for (int64_t o = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; o < total;
@@ -238,6 +243,7 @@ maxpool_bwd_scatter(const T* __restrict__ go, const long long* __restrict__ idx,
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 avgpool_fwd_generic(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int64_t total) {
+    kd::pdl_prologue();
     const T denom = static_cast<T>(g.kh * g.kw);
     for (int64_t o = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; o < total;
          o += static_cast<int64_t>(gridDim.x) * kThreads) {
@@ -286,6 +292,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 avgpool3x3s2p1_fwd(const T* __restrict__ x, T* __restrict__ y, int H, int W, int Ho, int Wo, int64_t groups,
                    kd::FastDiv by_gpr, kd::FastDiv by_ho) {
+    kd::pdl_prologue();
     for (int64_t gi = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; gi < groups;
          gi += static_cast<int64_t>(gridDim.x) * kThreads) {
         unsigned row, ujg, nc, ui;
@@ -332,6 +339,7 @@ avgpool3x3s2p1_fwd(const T* __restrict__ x, T* __restrict__ y, int H, int W, int
 template <typename T, bool ACCUM>
 __global__ void __launch_bounds__(kThreads)
 avgpool_bwd_gather(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int64_t total) {
+    kd::pdl_prologue();
     const T denom = static_cast<T>(g.kh * g.kw);
     for (int64_t e = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; e < total;
          e += static_cast<int64_t>(gridDim.x) * kThreads) {
@@ -365,6 +373,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 avgpool3x3s2p1_bwd(const T* __restrict__ go, T* __restrict__ gx, int H, int W, int Ho, int Wo, int64_t blocks,
                    kd::FastDiv by_bpr, kd::FastDiv by_hh) {
+    kd::pdl_prologue();
     for (int64_t bi = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; bi < blocks;
          bi += static_cast<int64_t>(gridDim.x) * kThreads) {
         unsigned rowp, ujg, nc, um;                    // rowp = nc * ceil(H/2) + m
@@ -432,6 +441,7 @@ avgpool3x3s2p1_bwd(const T* __restrict__ go, T* __restrict__ gx, int H, int W, i
 template <typename T, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 gap_fwd_short(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int L, int Ls) {
+    kd::pdl_prologue();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T* sm = reinterpret_cast<T*>(smem_raw) + static_cast<size_t>(threadIdx.x >> 5) * 32 * Ls;
     const int lane = threadIdx.x & 31;
@@ -496,6 +506,7 @@ gap_fwd_short(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int L, i
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 gap_fwd_long(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int L) {
+    kd::pdl_prologue();
     const int lane = threadIdx.x & 31;
     const int64_t nwarps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
     for (int64_t r = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5); r < rows; r += nwarps) {
@@ -522,6 +533,7 @@ gap_fwd_long(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int L) {
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 gap_bwd(const T* __restrict__ go, T* __restrict__ gx, int64_t total, int L, bool vec) {
+    kd::pdl_prologue();
     const T scale = T(1) / static_cast<T>(L);
     if (vec) {
         const int64_t n4 = total >> 2;
@@ -575,6 +587,7 @@ gap_bwd(const T* __restrict__ go, T* __restrict__ gx, int64_t total, int L, bool
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 pad2d_kernel(const T* __restrict__ x, T* __restrict__ y, int H, int W, int ph, int pw, T value, int64_t total) {
+    kd::pdl_prologue();
     const int Hp = H + 2 * ph, Wp = W + 2 * pw;
     for (int64_t o = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; o < total;
          o += static_cast<int64_t>(gridDim.x) * kThreads) {
@@ -591,6 +604,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 crop2d_kernel(const T* __restrict__ xp, T* __restrict__ y, int Hp, int Wp, int ph, int pw, int H, int W,
               int64_t total) {
+    kd::pdl_prologue();
     for (int64_t o = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; o < total;
          o += static_cast<int64_t>(gridDim.x) * kThreads) {
         const int w = static_cast<int>(o % W);
@@ -634,7 +648,7 @@ int maxpool_forward(const T* x, T* y, long long* idx, int N, int C, PoolGeom g) 
         KD_LAUNCH((maxpool2x2_fwd<T, U>), (groups + kThreads * U - 1) / (kThreads * U), kThreads, 0, x, y, idx, g.H, g.W,
                   g.Ho, g.Wo, groups, kd::FastDiv(g.Wo / 4), kd::FastDiv(g.Ho));
     } else {
-        maxpool_fwd_generic<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(x, y, idx, g, total);
+        (void)kd::launch(maxpool_fwd_generic<T>, dim3(flat_grid(total)), kThreads, 0, x, y, idx, g, total);
     }
     return kd::launch_status();
 }
@@ -659,7 +673,7 @@ int maxpool_backward_ex(const T* go, const long long* idx, T* gx, int N, int C, 
                   g.W, g.Ho, g.Wo, blocks, kd::FastDiv(g.W / 8), kd::FastDiv(g.H));
     } else {
         const int64_t total = nc * g.H * g.W;
-        maxpool_bwd_gather<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(go, idx, gx, g, total);
+        (void)kd::launch(maxpool_bwd_gather<T>, dim3(flat_grid(total)), kThreads, 0, go, idx, gx, g, total);
     }
     return kd::launch_status();
 }
@@ -672,7 +686,7 @@ int maxpool_backward_legacy(const T* go, const long long* idx, T* gx_pad, int N,
     if (Ho <= 0 || Wo <= 0 || Hp <= 0 || Wp <= 0) return -3;
     (void)cudaGetLastError();
     const int64_t total = static_cast<int64_t>(N) * C * Ho * Wo;
-    maxpool_bwd_scatter<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(go, idx, gx_pad, Ho, Wo, Hp, Wp, total);
+    (void)kd::launch(maxpool_bwd_scatter<T>, dim3(flat_grid(total)), kThreads, 0, go, idx, gx_pad, Ho, Wo, Hp, Wp, total);
     return kd::launch_status();
 }
 
@@ -694,7 +708,7 @@ int avgpool_forward(const T* x, T* y, int N, int C, PoolGeom g) {
         KD_LAUNCH1(avgpool3x3s2p1_fwd<T>, (groups + kThreads - 1) / kThreads, kThreads, 0, x, y, g.H, g.W, g.Ho, g.Wo, groups,
                    kd::FastDiv(g.Wo / 4), kd::FastDiv(g.Ho));
     } else {
-        avgpool_fwd_generic<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(x, y, g, total);
+        (void)kd::launch(avgpool_fwd_generic<T>, dim3(flat_grid(total)), kThreads, 0, x, y, g, total);
     }
     return kd::launch_status();
 }
@@ -717,9 +731,9 @@ int avgpool_backward(const T* go, T* gx, int N, int C, PoolGeom g, bool accumula
         KD_LAUNCH(avgpool3x3s2p1_bwd<T>, (blocks + kThreads - 1) / kThreads, kThreads, 0, go, gx, g.H, g.W, g.Ho, g.Wo, blocks,
                   kd::FastDiv(g.W / 8), kd::FastDiv((g.H + 1) / 2));
     } else if (accumulate) {
-        avgpool_bwd_gather<T, true><<<flat_grid(total), kThreads, 0, kd::stream()>>>(go, gx, g, total);
+        (void)kd::launch(avgpool_bwd_gather<T, true>, dim3(flat_grid(total)), kThreads, 0, go, gx, g, total);
     } else {
-        avgpool_bwd_gather<T, false><<<flat_grid(total), kThreads, 0, kd::stream()>>>(go, gx, g, total);
+        (void)kd::launch(avgpool_bwd_gather<T, false>, dim3(flat_grid(total)), kThreads, 0, go, gx, g, total);
     }
     return kd::launch_status();
 }
@@ -744,8 +758,8 @@ int gap_forward(const T* x, T* y, int N, int C, int H, int W) {
     } else {
         const unsigned grid = kd::grid_for((rows + 7) / 8, 8);
         const bool vec = kd::aligned_pack<T>(x) && (L % 4 == 0);
-        if (vec) gap_fwd_long<T, true><<<grid, kThreads, 0, kd::stream()>>>(x, y, rows, L);
-        else gap_fwd_long<T, false><<<grid, kThreads, 0, kd::stream()>>>(x, y, rows, L);
+        if (vec) (void)kd::launch(gap_fwd_long<T, true>, dim3(grid), kThreads, 0, x, y, rows, L);
+        else (void)kd::launch(gap_fwd_long<T, false>, dim3(grid), kThreads, 0, x, y, rows, L);
     }
     return kd::launch_status();
 }
@@ -771,7 +785,7 @@ int pad2d(const T* x, T* y, int N, int C, int H, int W, int ph, int pw, T value)
     if (ph < 0 || pw < 0) return -3;
     (void)cudaGetLastError();
     const int64_t total = static_cast<int64_t>(N) * C * (H + 2 * ph) * (W + 2 * pw);
-    pad2d_kernel<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(x, y, H, W, ph, pw, value, total);
+    (void)kd::launch(pad2d_kernel<T>, dim3(flat_grid(total)), kThreads, 0, x, y, H, W, ph, pw, value, total);
     return kd::launch_status();
 }
 
@@ -783,7 +797,7 @@ int crop2d(const T* xp, T* y, int N, int C, int Hp, int Wp, int ph, int pw, int 
     if (ph < 0 || pw < 0) return -4;
     (void)cudaGetLastError();
     const int64_t total = static_cast<int64_t>(N) * C * H * W;
-    crop2d_kernel<T><<<flat_grid(total), kThreads, 0, kd::stream()>>>(xp, y, Hp, Wp, ph, pw, H, W, total);
+    (void)kd::launch(crop2d_kernel<T>, dim3(flat_grid(total)), kThreads, 0, xp, y, Hp, Wp, ph, pw, H, W, total);
     return kd::launch_status();
 }
 

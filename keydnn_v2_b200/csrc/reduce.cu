@@ -51,6 +51,7 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 sum_all_kernel(const T* __restrict__ x, int64_t n, double* partials, unsigned int* counter, T* out, T scale,
                bool apply_scale) {
+    kd::pdl_prologue();
     __shared__ double sm[kWarps];
     constexpr int U = 8;     // packets in flight per thread and trip
     constexpr int A = 8;     // independent accumulators
@@ -108,6 +109,7 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 max_all_kernel(const T* __restrict__ x, int64_t n, T* pval, long long* pidx, unsigned int* counter, T* out,
                long long* out_idx) {
+    kd::pdl_prologue();
     __shared__ T smv[kWarps];
     __shared__ long long smi[kWarps];
     ArgMax<T> a = kd::argmax_init<T>();
@@ -177,6 +179,7 @@ max_all_kernel(const T* __restrict__ x, int64_t n, T* pval, long long* pidx, uns
 template <typename T, int TPR, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 sum_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int cols, T scale, bool apply_scale) {
+    kd::pdl_prologue();
     __shared__ double sm[kWarps];
     constexpr int RPB = kThreads / TPR;              // rows per CTA trip
     const int t = threadIdx.x % TPR;
@@ -225,6 +228,7 @@ sum_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int co
 template <typename T, int TPR, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 max_rows_kernel(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, int64_t rows, int cols) {
+    kd::pdl_prologue();
     __shared__ T smv[kWarps];
     __shared__ long long smi[kWarps];
     constexpr int RPB = kThreads / TPR;
@@ -312,6 +316,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
 sum_cols_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int cols, int rch, T* partials,
                 unsigned int* counters, T scale, bool apply_scale) {
+    kd::pdl_prologue();
     __shared__ T sm[kWarps][32 * V + 1];
     const int lane = threadIdx.x & 31, phase = threadIdx.x >> 5;
     const int stripe = blockIdx.x;                    // column stripe
@@ -382,6 +387,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
 max_cols_kernel(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, int rows, int cols, int rch,
                 T* pval, int* pidx, unsigned int* counters) {
+    kd::pdl_prologue();
     __shared__ T smv[kWarps][32 * V + 1];
     __shared__ int smi[kWarps][32 * V + 1];
     constexpr int kNone = std::numeric_limits<int>::max();
@@ -466,6 +472,7 @@ max_cols_kernel(const T* __restrict__ x, T* __restrict__ y, long long* __restric
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 bcast_scalar_kernel(const T* __restrict__ go, T* __restrict__ gx, int64_t n, T scale, int head) {
+    kd::pdl_prologue();
     const T v = __ldg(go) * scale;
     const int64_t body = n - head;
     const int64_t n4 = body >> 2;
@@ -486,6 +493,7 @@ bcast_scalar_kernel(const T* __restrict__ go, T* __restrict__ gx, int64_t n, T s
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 onehot_kernel(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, int64_t n, int head) {
+    kd::pdl_prologue();
     const T g = T(0) + __ldg(go);
     const long long target = __ldg(idx);
     const int64_t body = n - head;
@@ -519,6 +527,7 @@ template <typename T, int MODE, int V>
 __global__ void __launch_bounds__(kThreads)
 grad_matrix_kernel(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, int rows, int cols,
                    T scale, bool apply_scale) {
+    kd::pdl_prologue();
     const int ppr = (cols + V - 1) / V;
     for (int p = blockIdx.x * kThreads + threadIdx.x; p < ppr; p += gridDim.x * kThreads) {
         const int c0 = p * V;
@@ -573,6 +582,7 @@ grad_matrix_kernel(const T* __restrict__ go, const long long* __restrict__ idx, 
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 max_scatter_kernel(const T* __restrict__ go, const long long* __restrict__ idx, T* gx, int rows, int cols, int axis) {
+    kd::pdl_prologue();
     const int n = axis == 1 ? rows : cols;
     for (int i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
         const long long k = idx[i];
@@ -593,6 +603,7 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 sum_akb_kernel(const T* __restrict__ x, T* __restrict__ y, int A, int K, int64_t B, int ach, double* partials,
                unsigned int* counters) {
+    kd::pdl_prologue();
     __shared__ double sm[kWarps];
     const int k = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
     const int a_begin = slice * ach;
@@ -637,6 +648,7 @@ struct ShapeMeta {
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 sum_to_shape_atomic_kernel(const T* __restrict__ x, T* y, int64_t n, ShapeMeta m) {
+    kd::pdl_prologue();
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
          i += static_cast<int64_t>(gridDim.x) * kThreads) {
         int64_t rem = i, off = 0;
@@ -667,8 +679,8 @@ int sum_all(const T* x, T* y, int64_t n, bool mean) {
     unsigned int* counter = kd::counters(1);
     if (!partials || !counter) return static_cast<int>(cudaErrorMemoryAllocation);
     const T scale = T(1) / static_cast<T>(n);
-    if (vec) sum_all_kernel<T, true><<<grid, kThreads, 0, kd::stream()>>>(x, n, partials, counter, y, scale, mean);
-    else sum_all_kernel<T, false><<<grid, kThreads, 0, kd::stream()>>>(x, n, partials, counter, y, scale, mean);
+    if (vec) (void)kd::launch(sum_all_kernel<T, true>, dim3(grid), kThreads, 0, x, n, partials, counter, y, scale, mean);
+    else (void)kd::launch(sum_all_kernel<T, false>, dim3(grid), kThreads, 0, x, n, partials, counter, y, scale, mean);
     return kd::launch_status();
 }
 
@@ -686,8 +698,8 @@ int max_all(const T* x, T* y, long long* idx, int64_t n) {
     if (!buf || !counter) return static_cast<int>(cudaErrorMemoryAllocation);
     long long* pidx = reinterpret_cast<long long*>(buf);
     T* pval = reinterpret_cast<T*>(buf + static_cast<size_t>(grid) * 8);
-    if (vec) max_all_kernel<T, true><<<grid, kThreads, 0, kd::stream()>>>(x, n, pval, pidx, counter, y, idx);
-    else max_all_kernel<T, false><<<grid, kThreads, 0, kd::stream()>>>(x, n, pval, pidx, counter, y, idx);
+    if (vec) (void)kd::launch(max_all_kernel<T, true>, dim3(grid), kThreads, 0, x, n, pval, pidx, counter, y, idx);
+    else (void)kd::launch(max_all_kernel<T, false>, dim3(grid), kThreads, 0, x, n, pval, pidx, counter, y, idx);
     return kd::launch_status();
 }
 
@@ -747,7 +759,7 @@ int sum_cols_v(const T* x, T* y, int rows, int cols, T scale, bool apply_scale) 
         counters = kd::counters(stripes);
         if (!partials || !counters) return static_cast<int>(cudaErrorMemoryAllocation);
     }
-    sum_cols_kernel<T, V><<<dim3(stripes, nchunks), kThreads, 0, kd::stream()>>>(x, y, rows, cols, rch, partials, counters,
+    (void)kd::launch(sum_cols_kernel<T, V>, dim3(stripes, nchunks), kThreads, 0, x, y, rows, cols, rch, partials, counters,
                                                                                scale, apply_scale);
     return kd::launch_status();
 }
@@ -777,7 +789,7 @@ int max_cols_v(const T* x, T* y, long long* idx, int rows, int cols) {
         pval = reinterpret_cast<T*>(buf);
         pidx = reinterpret_cast<int*>(buf + cells * sizeof(T));
     }
-    max_cols_kernel<T, V><<<dim3(stripes, nchunks), kThreads, 0, kd::stream()>>>(x, y, idx, rows, cols, rch, pval, pidx,
+    (void)kd::launch(max_cols_kernel<T, V>, dim3(stripes, nchunks), kThreads, 0, x, y, idx, rows, cols, rch, pval, pidx,
                                                                                counters);
     return kd::launch_status();
 }
@@ -837,8 +849,8 @@ int grad_matrix(const T* go, const long long* idx, T* gx, int rows, int cols, T 
     if (gy < 1) gy = 1;
     dim3 grid(gx_dim, gy);
     cudaStream_t s = kd::stream();
-    if (vec) grad_matrix_kernel<T, MODE, 4><<<grid, kThreads, 0, s>>>(go, idx, gx, rows, cols, scale, apply_scale);
-    else grad_matrix_kernel<T, MODE, 1><<<grid, kThreads, 0, s>>>(go, idx, gx, rows, cols, scale, apply_scale);
+    if (vec) (void)kd::launch(grad_matrix_kernel<T, MODE, 4>, dim3(grid), kThreads, 0, go, idx, gx, rows, cols, scale, apply_scale);
+    else (void)kd::launch(grad_matrix_kernel<T, MODE, 1>, dim3(grid), kThreads, 0, go, idx, gx, rows, cols, scale, apply_scale);
     return kd::launch_status();
 }
 
@@ -871,7 +883,7 @@ int max_axis2d_backward_legacy(const T* go, const long long* idx, T* gx, int row
     (void)cudaGetLastError();
     const int n = axis == 1 ? rows : cols;
     const unsigned grid = kd::grid_for((n + kThreads - 1) / kThreads, 8);
-    max_scatter_kernel<T><<<grid, kThreads, 0, kd::stream()>>>(go, idx, gx, rows, cols, axis);
+    (void)kd::launch(max_scatter_kernel<T>, dim3(grid), kThreads, 0, go, idx, gx, rows, cols, axis);
     return kd::launch_status();
 }
 
@@ -943,8 +955,8 @@ int sum_to_shape(const T* x, T* y, const int64_t* in_shape, const int64_t* out_s
         }
         dim3 grid(K, nslices);
         const bool vec = kd::aligned_pack<T>(x) && (B % 4 == 0);
-        if (vec) sum_akb_kernel<T, true><<<grid, kThreads, 0, s>>>(x, y, A, K, B, ach, partials, counters);
-        else sum_akb_kernel<T, false><<<grid, kThreads, 0, s>>>(x, y, A, K, B, ach, partials, counters);
+        if (vec) (void)kd::launch(sum_akb_kernel<T, true>, dim3(grid), kThreads, 0, x, y, A, K, B, ach, partials, counters);
+        else (void)kd::launch(sum_akb_kernel<T, false>, dim3(grid), kThreads, 0, x, y, A, K, B, ach, partials, counters);
         return kd::launch_status();
     }
     // general interleaving
@@ -960,7 +972,7 @@ int sum_to_shape(const T* x, T* y, const int64_t* in_shape, const int64_t* out_s
     cudaError_t st = cudaMemsetAsync(y, 0, numel_out * sizeof(T), s);
     if (st != cudaSuccess) return kd::status(st);
     const unsigned grid = kd::grid_for((numel_in + kThreads - 1) / kThreads, 8);
-    sum_to_shape_atomic_kernel<T><<<grid, kThreads, 0, s>>>(x, y, numel_in, m);
+    (void)kd::launch(sum_to_shape_atomic_kernel<T>, dim3(grid), kThreads, 0, x, y, numel_in, m);
     return kd::launch_status();
 }
 
@@ -1088,7 +1100,7 @@ int noalloc_sum_cols(const float* x, float* y, int rows, int cols, unsigned char
     // the array keeps whatever the previous call left: tickets must start at zero
     cudaError_t st = cudaMemsetAsync(counters, 0, static_cast<size_t>(stripes) * sizeof(unsigned int), s);
     if (st != cudaSuccess) return static_cast<int>(st);
-    sum_cols_kernel<float, V><<<dim3(stripes, nchunks), kThreads, 0, s>>>(x, y, rows, cols, rch, partials, counters, 1.0f,
+    (void)kd::launch(sum_cols_kernel<float, V>, dim3(stripes, nchunks), kThreads, 0, x, y, rows, cols, rch, partials, counters, 1.0f,
                                                                        false);
     return kd::launch_status();
 }

@@ -104,6 +104,14 @@ namespace kd {
 
 cudaStream_t stream() { return g_stream; }
 
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("KEYDNN_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 int sm_count() {
     std::lock_guard<std::mutex> lk(g_mu);
     return state().sm_count;

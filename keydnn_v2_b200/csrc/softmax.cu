@@ -50,6 +50,7 @@ template <typename T, int G> __device__ __forceinline__ T group_add(T v) {
 template <typename T, int G, int R, int K, bool BWD>
 __global__ void __launch_bounds__(kThreads, (R * sizeof(T) * (BWD ? 2 : 1) >= 128 ? 3 : 1))
 softmax_warp_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t rows, int len) {
+    kd::pdl_prologue();
     constexpr int RPG = 32 / G;                 // rows per group of a warp
     constexpr int RPW = RPG * K;                // rows per warp and trip
     const int lane = threadIdx.x & 31;
@@ -138,6 +139,7 @@ template <typename T, bool BWD, bool VEC, int kBlockThreads>
 __global__ void __launch_bounds__(kBlockThreads)
 softmax_block_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t rows, int len,
                      bool staged) {
+    kd::pdl_prologue();
     extern __shared__ __align__(32) unsigned char smem_raw[];
     T* buf = reinterpret_cast<T*>(smem_raw);          // forward: x then e;  backward: g
     T* buf2 = buf + len;                              // backward: y
@@ -225,6 +227,7 @@ template <typename T, bool BWD>
 __global__ void __launch_bounds__(kThreads)
 softmax_strided_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t outer, int len,
                        int64_t inner) {
+    kd::pdl_prologue();
     const int64_t lines = outer * inner;
     for (int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; t < lines;
          t += static_cast<int64_t>(gridDim.x) * kThreads) {
@@ -281,7 +284,7 @@ int launch_block(const T* a, const T* b, T* out, int64_t rows, int len) {
         per_sm = 1;
     const int64_t cap = static_cast<int64_t>(kd::sm_count()) * per_sm * 4;
     const unsigned grid = static_cast<unsigned>(rows < cap ? rows : cap);
-    kernel<<<grid, THREADS, smem, kd::stream()>>>(a, b, out, rows, len, staged);
+    (void)kd::launch(kernel, dim3(grid), THREADS, smem, a, b, out, rows, len, staged);
     return kd::launch_status();
 }
 
