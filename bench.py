@@ -385,11 +385,14 @@ def run_ours(args) -> None:
     launches = [0]
 
     def step() -> None:
-        # the two matrices are independent: their kernels alternate, so the exchange of one
-        # matrix's partials (second stream) runs under the other matrix's kernel
+        # all forward reductions, then all backward passes (the order of a graph with eighteen reduction heads);
+        # the forward partials cross ranks in one bucket per matrix once the forward kernels are enqueued
         for op, ax in OPS:
             for red, _ in reducers:
-                red.forward(op, ax)
+                red.forward(op, ax, defer=True)
+        for red, _ in reducers:
+            red.flush()                  # one all-reduce + one all-gather per matrix, under the backward kernels
+        for op, ax in OPS:
             for red, _ in reducers:
                 red.backward(op, ax)
         for red, _ in reducers:

@@ -15,6 +15,13 @@ straight on to the next kernel.  Only a consumer of the reduced value (the max b
 the host, ``finish()``) waits for it.  Every (op, axis) has its own result buffers, so nothing on the
 compute stream overwrites an operand that is still in flight.  With world == 1 the same calls run
 without any collective or second stream.  Buffers are allocated once; a call enqueues work and returns.
+
+``forward(..., defer=True)`` postpones the exchange to ``flush()``, which moves everything postponed with
+ONE all-reduce (the sum / mean partials of axis 0 and of all axes lie side by side in one buffer) and ONE
+all-gather (both max candidate blocks lie side by side): two latency-bound collectives per step and matrix
+instead of six, issued where the caller chooses - e.g. after the last forward kernel, so that they run
+under the streaming backward kernels and not next to the one-wave reduction kernels whose grids fill
+every SM exactly.
 """
 from __future__ import annotations
 
@@ -52,21 +59,39 @@ class ShardedReductions:
         n_max = max(self.rows, self.cols)
         self._out: Dict[Key, object] = {}
         self._idx: Dict[Key, "_View"] = {}
-        self._blk: Dict[Key, Tuple[CudaStorage, int, int]] = {}
-        for op in ("sum", "mean", "max"):
-            for ax in (0, 1, None):
-                n = self.cols if ax == 0 else self.rows if ax == 1 else 1
-                if op == "max":
-                    # value block and position block side by side: one all-gather moves both
-                    voff = (n * isz + 7) // 8 * 8
-                    blk = CudaStorage.allocate(voff + n * 8, np.uint8)
-                    self._blk[(op, ax)] = (blk, voff, voff + n * 8)
-                    self._out[(op, ax)] = _View(blk.dev_ptr)
-                    self._idx[(op, ax)] = _View(blk.dev_ptr + voff)
-                else:
-                    self._out[(op, ax)] = Tensor.empty((n,), self.dt)
-        # cross-rank max: gathered candidates and the selection, per axis
+        self._blk: Dict[Key, Tuple[object, int, int]] = {}
+        # the four partials that cross ranks share one buffer: [sum ax0 | mean ax0 | sum all | mean all]
+        cpad = (self.cols + 3) // 4 * 4
+        self._sumblk = Tensor.empty((2 * cpad + 2,), self.dt)
+        self._sum_count = 2 * cpad + 2
+        for i, key in enumerate((("sum", 0), ("mean", 0))):
+            self._out[key] = _View(self._sumblk.data + i * cpad * isz)
+        for i, key in enumerate((("sum", None), ("mean", None))):
+            self._out[key] = _View(self._sumblk.data + (2 * cpad + i) * isz)
+        self.lib.call("keydnn_cuda_memset", self._sumblk.data, 0, self._sum_count * isz)
+        for op in ("sum", "mean"):
+            self._out[(op, 1)] = Tensor.empty((self.rows,), self.dt)
+        # max: value block and position block side by side, and the two blocks that cross ranks (axis 0, all
+        # axes) side by side as well: one all-gather moves everything
+        sizes = {}
+        for ax in (0, None, 1):
+            n = self.cols if ax == 0 else self.rows if ax == 1 else 1
+            voff = (n * isz + 7) // 8 * 8
+            sizes[ax] = (voff, voff + n * 8)
+        self._maxblk = CudaStorage.allocate(sizes[0][1] + sizes[None][1], np.uint8)
+        self.lib.call("keydnn_cuda_memset", self._maxblk.dev_ptr, 0, sizes[0][1] + sizes[None][1])
+        self._maxblk_bytes = sizes[0][1] + sizes[None][1]
+        own1 = CudaStorage.allocate(sizes[1][1], np.uint8)
+        for ax, base, owner in ((0, self._maxblk.dev_ptr, self._maxblk), (None, self._maxblk.dev_ptr + sizes[0][1], self._maxblk),
+                                (1, own1.dev_ptr, own1)):
+            voff, nbytes = sizes[ax]
+            self._blk[("max", ax)] = (owner, voff, nbytes)
+            self._out[("max", ax)] = _View(base)
+            self._idx[("max", ax)] = _View(base + voff)
+        # cross-rank max: gathered candidates (per axis, and of both blocks at once) and the selection
         self._gathered = {ax: CudaStorage.allocate(w * self._blk[("max", ax)][2], np.uint8) for ax in (0, None)}
+        self._gathered_all = CudaStorage.allocate(w * self._maxblk_bytes, np.uint8)
+        self._deferred: list = []
         self._sel = {ax: Tensor.empty((n,), self.dt) for ax, n in ((0, self.cols), (None, 1))}
         self._iglobal = {ax: CudaStorage.allocate(n * 8, np.int64) for ax, n in ((0, self.cols), (None, 1))}
         self._ilocal = {ax: CudaStorage.allocate(n * 8, np.int64) for ax, n in ((0, self.cols), (None, 1))}
@@ -83,45 +108,90 @@ class ShardedReductions:
         if w > 1:
             self.lib.call("keydnn_cuda_stream_create", ctypes.byref(self._comm))
             self.lib.call("keydnn_cuda_event_create", ctypes.byref(self._ready))
-            for key in self._out:
+            for key in list(self._out) + [("bucket", None)]:
                 e = ctypes.c_uint64(0)
                 self.lib.call("keydnn_cuda_event_create", ctypes.byref(e))
                 self._done[key] = e.value
+        self._wait_for: Dict[Key, int] = {}      # pending key -> the event that completes it
 
     def _c(self, v: float):
         return ctypes.c_float(v) if self.dt == np.float32 else ctypes.c_double(v)
 
     # -------------------------------------------------------------- stream hops
-    def _on_comm_stream(self, key: Key, fn) -> None:
+    def _on_comm_stream(self, keys, fn, event_key: Optional[Key] = None) -> None:
         """Run `fn` (collective + its small follow-up kernels) on the second stream, after
-        everything enqueued so far on the compute stream."""
+        everything enqueued so far on the compute stream; `keys` complete with it."""
         lib = self.lib
+        event = self._done[event_key if event_key is not None else keys[0]]
         lib.call("keydnn_cuda_event_record", self._ready.value)
         lib.call("keydnn_cuda_set_stream", self._comm.value)
         try:
             lib.call("keydnn_cuda_stream_wait_event", self._ready.value)
             fn()
-            lib.call("keydnn_cuda_event_record", self._done[key])
+            lib.call("keydnn_cuda_event_record", event)
         finally:
             lib.call("keydnn_cuda_set_stream", self._main.value)
-        self._pending.add(key)
+        for key in keys:
+            self._pending.add(key)
+            self._wait_for[key] = event
 
     def wait(self, op: str, axis: Optional[int]) -> None:
         """Later work on the compute stream sees the reduced value of (op, axis)."""
         key = (op, axis)
+        if any(k == key for k, _ in self._deferred):
+            self.flush()
         if key in self._pending:
-            self.lib.call("keydnn_cuda_stream_wait_event", self._done[key])
+            event = self._wait_for.pop(key)
+            self.lib.call("keydnn_cuda_stream_wait_event", event)
             self._pending.discard(key)
+            for other in [k for k, e in self._wait_for.items() if e == event]:      # same collective: done as well
+                self._pending.discard(other)
+                del self._wait_for[other]
 
     def finish(self) -> None:
         """Order everything outstanding on the second stream before later compute-stream work."""
+        self.flush()
         for key in list(self._pending):
             self.wait(*key)
 
+    def flush(self) -> None:
+        """Exchange everything ``forward(..., defer=True)`` postponed: one all-reduce over the shared sum buffer,
+        one all-gather over the shared max block, the mean scales and the selections behind them."""
+        if not self._deferred:
+            return
+        todo, self._deferred = self._deferred, []
+        lib, s, g, w = self.lib, self.suf, self.g, self.g.world
+        isz = self.dt.itemsize
+
+        def exchange() -> None:
+            sums = [(k, meta) for k, meta in todo if k[0] != "max"]
+            maxes = [(k, meta) for k, meta in todo if k[0] == "max"]
+            if len(sums) == 4:
+                g.allreduce_sum(self._sumblk.data, self._sum_count, s)      # all four partials at once
+            else:
+                for (op, ax), (n, _) in sums:                               # never re-reduce a finished neighbour
+                    g.allreduce_sum(self._out[(op, ax)].data, n, s)
+            if sums:
+                for (op, ax), (n, count) in sums:
+                    if op == "mean":
+                        lib.call(f"keydnn_cuda_mul_scalar_inplace_{s}", self._out[(op, ax)].data, self._c(1.0 / count), n)
+            if maxes:
+                total = self._maxblk_bytes
+                gathered = self._gathered_all.dev_ptr
+                g.allgather(self._maxblk.dev_ptr, gathered, total)
+                for (op, ax), (n, span) in maxes:
+                    base = gathered + (self._out[(op, ax)].data - self._maxblk.dev_ptr)
+                    voff = self._blk[(op, ax)][1]
+                    lib.call(f"keydnn_cuda_argmax_select_{s}", base, base + voff, w, g.rank, span, n, total // isz, total // 8,
+                             self._sel[ax].data, self._iglobal[ax].dev_ptr, self._ilocal[ax].dev_ptr)
+
+        self._on_comm_stream([k for k, _ in todo], exchange, ("bucket", None))
+
     # ------------------------------------------------------------------ forward
-    def forward(self, op: str, axis: Optional[int]) -> Tuple[int, int]:
+    def forward(self, op: str, axis: Optional[int], defer: bool = False) -> Tuple[int, int]:
         """Runs one reduction; returns (device pointer, element count) of the result.  At
-        world > 1 the value of an axis-0 / all-axes result is complete after ``wait(op, axis)``."""
+        world > 1 the value of an axis-0 / all-axes result is complete after ``wait(op, axis)``;
+        with ``defer`` its exchange is postponed to the next ``flush()`` (or the first ``wait`` for it)."""
         lib, x, s, g = self.lib, self.x, self.suf, self.g
         rows, cols, w = self.rows, self.cols, self.g.world
         key = (op, axis)
@@ -144,13 +214,15 @@ class ShardedReductions:
                     return out, 1
                 lib.call(f"keydnn_cuda_sum_all_{s}", x.data, out, rows * cols)
                 n, count = 1, rows * cols * w
-            if w > 1:
+            if w > 1 and defer:
+                self._deferred.append((key, (n, count)))
+            elif w > 1:
                 def exchange() -> None:
                     g.allreduce_sum(out, n, s)
                     if op == "mean":
                         lib.call(f"keydnn_cuda_mul_scalar_inplace_{s}", out, self._c(1.0 / count), n)
 
-                self._on_comm_stream(key, exchange)
+                self._on_comm_stream([key], exchange)
             return out, n
         if op != "max":
             raise ValueError(op)
@@ -167,6 +239,9 @@ class ShardedReductions:
         if w == 1:
             return out, n
 
+        if defer:
+            self._deferred.append((key, (n, span)))
+            return self._sel[axis].data, n
         _, voff, blk_bytes = self._blk[key]
         gathered = self._gathered[axis].dev_ptr
 
@@ -176,7 +251,7 @@ class ShardedReductions:
                      blk_bytes // self.dt.itemsize, blk_bytes // 8, self._sel[axis].data,
                      self._iglobal[axis].dev_ptr, self._ilocal[axis].dev_ptr)
 
-        self._on_comm_stream(key, exchange_max)
+        self._on_comm_stream([key], exchange_max)
         return self._sel[axis].data, n
 
     # ----------------------------------------------------------------- backward

@@ -26,17 +26,34 @@ def main() -> None:
         full[3, 7] = full[R * world - 2, 7] = 9.0            # same maximum on the first and the last rank
         shard = np.ascontiguousarray(full[rank * R:(rank + 1) * R])
         red = ShardedReductions(kd.Tensor.from_numpy(shard), group)
-        for op in ("sum", "mean", "max"):
-            for ax in (0, 1, None):
-                ptr, n = red.forward(op, ax)
-                red.wait(op, ax)
-                out = np.empty(n, dt)
-                red.lib.call("keydnn_cuda_memcpy_d2h", out.ctypes.data, ptr, out.nbytes)
-                gx_ptr = red.backward(op, ax)
-                gx = np.empty((R, C), dt)
-                red.lib.call("keydnn_cuda_memcpy_d2h", gx.ctypes.data, gx_ptr, gx.nbytes)
-                res[f"{tag}/{op}/{ax}/y"] = out
-                res[f"{tag}/{op}/{ax}/gx"] = gx
+
+        def read(ptr, n, shape=None):
+            out = np.empty(n if shape is None else shape, dt)
+            red.lib.call("keydnn_cuda_memcpy_d2h", out.ctypes.data, ptr, out.nbytes)
+            return out
+
+        keys = [(op, ax) for op in ("sum", "mean", "max") for ax in (0, 1, None)]
+        # one exchange per reduction, right behind its kernel
+        for op, ax in keys:
+            ptr, n = red.forward(op, ax)
+            red.wait(op, ax)
+            res[f"{tag}/{op}/{ax}/y"] = read(ptr, n)
+            res[f"{tag}/{op}/{ax}/gx"] = read(red.backward(op, ax), 0, (R, C))
+        # all exchanges postponed to one bucket (one all-reduce, one all-gather), then every backward
+        outs = {k: red.forward(*k, defer=True) for k in keys}
+        red.flush()
+        for op, ax in keys:
+            res[f"{tag}/bucket/{op}/{ax}/gx"] = read(red.backward(op, ax), 0, (R, C))
+        red.finish()
+        for (op, ax), (ptr, n) in outs.items():
+            res[f"{tag}/bucket/{op}/{ax}/y"] = read(ptr, n)
+        # a partial bucket next to finished neighbours: they must keep their values
+        part = {k: red.forward(*k, defer=True) for k in (("mean", 0), ("max", None))}
+        red.finish()
+        for (op, ax), (ptr, n) in part.items():
+            res[f"{tag}/partial/{op}/{ax}/y"] = read(ptr, n)
+        ptr, n = outs[("sum", 0)]
+        res[f"{tag}/partial/sum/0/y"] = read(ptr, n)
     np.savez(out_dir / f"rank{rank}.npz", **res)
     group.destroy()
 

@@ -50,6 +50,16 @@ def test_sharded_reductions_match_numpy_on_the_whole_matrix(tmp_path):
                 rows = slice(r * R, (r + 1) * R)
                 ys, ym, yx = (res[r][f"{tag}/{op}/{ax}/y"] for op in ("sum", "mean", "max"))
                 gs, gm, gxm = (res[r][f"{tag}/{op}/{ax}/gx"] for op in ("sum", "mean", "max"))
+                # the bucketed exchange (one all-reduce + one all-gather for everything) gives the same bits
+                for op in ("sum", "mean", "max"):
+                    for what in ("y", "gx"):
+                        np.testing.assert_array_equal(res[r][f"{tag}/bucket/{op}/{ax}/{what}"], res[r][f"{tag}/{op}/{ax}/{what}"],
+                                                      err_msg=f"bucket {tag} {op} {ax} {what}")
+                if ax == 0:
+                    np.testing.assert_array_equal(res[r][f"{tag}/partial/mean/0/y"], ym)
+                    np.testing.assert_array_equal(res[r][f"{tag}/partial/sum/0/y"], ys)     # untouched by the partial bucket
+                if ax is None:
+                    np.testing.assert_array_equal(res[r][f"{tag}/partial/max/None/y"], yx)
                 if ax == 1:
                     np.testing.assert_allclose(ys, f64[rows].sum(1), **tol)
                     np.testing.assert_allclose(ym, f64[rows].mean(1), **tol)
