@@ -16,11 +16,11 @@ host (the reference calls ``item()``): the device scalar is passed to the kernel
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Iterable, List, Optional, Sequence, Tuple
 
 import numpy as np
 
-from ._cuda_storage import CudaStorage
 from .tensor import Context, Parameter, Tensor, _suffix, no_grad
 
 
@@ -29,8 +29,6 @@ def _call(x: Tensor, name: str, *args) -> None:
 
 
 def _scalar_arg(x: Tensor, v: float):
-    import ctypes
-
     return ctypes.c_float(v) if x.dtype == np.float32 else ctypes.c_double(v)
 
 
@@ -289,8 +287,6 @@ class _SqDiffFn:
 
     @classmethod
     def forward(cls, ctx: Context, pred: Tensor, target: Tensor) -> Tensor:
-        import ctypes  # noqa: F401
-
         _check_pair(pred, target, cls.__name__)
         diff = Tensor.empty(pred.shape, pred.dtype)
         loss = Tensor.empty((), pred.dtype)
@@ -301,8 +297,6 @@ class _SqDiffFn:
 
     @classmethod
     def backward(cls, ctx: Context, grad_out: Optional[Tensor], *, need_target_grad: bool = True):
-        import ctypes
-
         (diff,) = ctx.saved_tensors
         n = int(ctx.saved_meta["n"])
         scale = (2.0 / n) if cls.MEAN else 2.0

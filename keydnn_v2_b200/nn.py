@@ -20,7 +20,7 @@ from __future__ import annotations
 
 import ctypes
 import math
-from typing import Iterable, List, Optional, Sequence, Tuple
+from typing import Iterable, List, Sequence, Tuple
 
 import numpy as np
 

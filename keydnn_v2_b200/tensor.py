@@ -22,7 +22,7 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple, Union
 import numpy as np
 
 from ._cuda_storage import CudaStorage
-from ._native import Native, load
+from ._native import Native
 
 Number = Union[int, float]
 _INT32_MAX = 2**31 - 1

@@ -19,7 +19,7 @@ expressions of the same form (np.sum(x, axis) / extent; np.max(x) with an equali
 from __future__ import annotations
 
 import time
-from typing import Callable, Dict, List, Tuple
+from typing import Dict, List, Tuple
 
 import numpy as np
 

@@ -12,7 +12,7 @@ import ctypes
 import numpy as np
 import pytest
 
-from _gpu_util import Buf, assert_same_bits, bits, cfloat, native, ref_cuda, suf
+from _gpu_util import Buf, assert_same_bits, cfloat, native, ref_cuda, suf
 
 pytestmark = pytest.mark.gpu
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 import numpy as np
 import pytest
 
-from _gpu_util import TOL, Buf, assert_same_bits, native, ref_cuda, suf
+from _gpu_util import Buf, assert_same_bits, native, ref_cuda, suf
 
 pytestmark = pytest.mark.gpu
 
