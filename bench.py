@@ -650,7 +650,7 @@ def cpu_baseline_sample(rows32: int = ROWS32 // 4, rows64: int = ROWS64 // 4, bu
     cpu_baseline.time_reduce_workload(x32[:64], x64[:64])
     nbytes = seconds = 0.0
     passes = 0
-    while seconds < budget_s and passes < 16:
+    while seconds < budget_s and passes < 48:
         r = cpu_baseline.time_reduce_workload(x32, x64)
         nbytes += r["bytes"]
         seconds += r["seconds"]
