@@ -531,7 +531,8 @@ def run_ours(args) -> None:
             if suite is not None:
                 line["suite"] = suite
             line["whole_step_frac"] = round(value / world / peak, 4)
-        line["cpu_baseline"] = cpu_baseline_sample() if world == 1 or rank == 0 else None
+        # timed at N = 1 only: at N > 1 the other ranks would sit in the next collective while rank 0 computes
+        line["cpu_baseline"] = cpu_baseline_sample() if world == 1 else None
     cnn = None
     if args.cnn != "off":
         del r32, r64, reducers

@@ -7,9 +7,11 @@
 //   forward   m = max over the axis (strict >, from -inf; a NaN never wins)
 //             e = exp(x - m);  y = e * (1 / sum(e))
 //   backward  gy = g * y;  dx = y * (g - sum(gy))
-// The sums are tree sums (the reference adds serially), so results equal the reference's only to
-// rounding in any case; the forward therefore multiplies by the correctly rounded reciprocal of the
-// sum (one division per row) instead of dividing every element, which halves its instruction count.
+// Rows of at most 32 elements are walked serially by one thread, in the reference's order and with its
+// division: bit-identical to the reference chain.  Longer rows use tree sums (the reference adds serially),
+// so their results equal the reference's only to rounding in any case; their forward therefore multiplies
+// by the correctly rounded reciprocal of the sum (one division per row) instead of dividing every element,
+// which halves its instruction count.
 //
 // Compiled with nvcc's default FMA contraction so that exp expands as in the reference build; all
 // arithmetic written here uses explicitly rounded intrinsics.
@@ -108,6 +110,87 @@ softmax_warp_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restr
                     if (row < rows && c < len) __stcs(out + row * len + c, Rn<T>::mul(va[k][r], inv));
                 }
             }
+        }
+    }
+}
+
+// ---- rows of at most 32 elements (classifier heads): one thread owns a row and walks it in index order,
+// which is the reference's own order for the row maximum and the row sums (keydnn_reduce_cuda.cu:301-306,
+// :167-179 are serial loops), and the forward divides every element by the sum as the reference does: the
+// result equals the reference's kernel chain bit for bit.  LEN is the row length rounded up to 4, 8, 16 or 32;
+// VEC: len % 4 == 0 and packet-aligned pointers.  Neighbouring lanes read neighbouring rows, so the 16-byte
+// pieces a warp asks for in one instruction lie len*sizeof(T) apart; the other pieces of the same sectors
+// follow in the next instructions and are served by L1.
+template <typename T, int LEN, bool VEC, bool BWD>
+__global__ void __launch_bounds__(kThreads)
+softmax_thread_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t rows, int len) {
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; row < rows;
+         row += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const T* pa = a + row * len;
+        const T* pb = BWD ? b + row * len : nullptr;
+        T* po = out + row * len;
+        T va[LEN], vb[LEN];
+        if (VEC) {
+#pragma unroll
+            for (int j = 0; j < LEN; j += 4) {
+                if (j < len) {
+                    const kd::Pack4<T> p = kd::load4(pa + j);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) va[j + k] = p.v[k];
+                    if (BWD) {
+                        const kd::Pack4<T> q = kd::load4(pb + j);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) vb[j + k] = q.v[k];
+                    }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < LEN; ++j) {
+                if (j < len) {
+                    va[j] = __ldg(pa + j);
+                    if (BWD) vb[j] = __ldg(pb + j);
+                }
+            }
+        }
+        if (BWD) {
+            T dot = T(0);
+#pragma unroll
+            for (int j = 0; j < LEN; ++j)
+                if (j < len) dot = Rn<T>::add(dot, Rn<T>::mul(va[j], vb[j]));
+#pragma unroll
+            for (int j = 0; j < LEN; ++j)
+                if (j < len) va[j] = Rn<T>::mul(vb[j], Rn<T>::sub(va[j], dot));
+        } else {
+            T m = neg_inf<T>();
+#pragma unroll
+            for (int j = 0; j < LEN; ++j)
+                if (j < len) m = va[j] > m ? va[j] : m;
+            T s = T(0);
+#pragma unroll
+            for (int j = 0; j < LEN; ++j)
+                if (j < len) {
+                    va[j] = t_exp(Rn<T>::sub(va[j], m));
+                    s = Rn<T>::add(s, va[j]);
+                }
+#pragma unroll
+            for (int j = 0; j < LEN; ++j)
+                if (j < len) va[j] = t_div(va[j], s);
+        }
+        if (VEC) {
+#pragma unroll
+            for (int j = 0; j < LEN; j += 4) {
+                if (j < len) {
+                    kd::Pack4<T> p;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) p.v[k] = va[j + k];
+                    kd::store4(po + j, p);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < LEN; ++j)
+                if (j < len) po[j] = va[j];
         }
     }
 }
@@ -329,13 +412,20 @@ int softmax(const T* a, const T* b, T* out, int64_t outer, int64_t len, int64_t 
         const bool vec = (n % 4 == 0) && kd::aligned_pack<T>(a) && kd::aligned_pack<T>(out) && (!BWD || kd::aligned_pack<T>(b));
         return vec ? launch_block_for<T, BWD, true>(a, b, out, outer, n) : launch_block_for<T, BWD, false>(a, b, out, outer, n);
     }
-    if (n <= 1) launch_warp<T, 1, 1, 8, BWD>(a, b, out, outer, n);
-    else if (n <= 2) launch_warp<T, 2, 1, 8, BWD>(a, b, out, outer, n);
-    else if (n <= 4) launch_warp<T, 4, 1, 8, BWD>(a, b, out, outer, n);
-    else if (n <= 8) launch_warp<T, 8, 1, 8, BWD>(a, b, out, outer, n);
-    else if (n <= 16) launch_warp<T, 16, 1, 8, BWD>(a, b, out, outer, n);
-    else if (n <= 32) launch_warp<T, 32, 1, 8, BWD>(a, b, out, outer, n);
-    else if (n <= 64) launch_warp<T, 32, 2, 4, BWD>(a, b, out, outer, n);
+    if (n <= 32) {
+        const bool vec = (n % 4 == 0) && kd::aligned_pack<T>(a) && kd::aligned_pack<T>(out) && (!BWD || kd::aligned_pack<T>(b));
+        const int64_t ctas = (outer + kThreads - 1) / kThreads;
+#define KD_SOFTMAX_THREAD(LEN)                                                                                            \
+    do {                                                                                                                  \
+        if (vec) KD_LAUNCH_W((softmax_thread_kernel<T, LEN, true, BWD>), 8, ctas, kThreads, 0, a, b, out, outer, n);      \
+        else KD_LAUNCH_W((softmax_thread_kernel<T, LEN, false, BWD>), 8, ctas, kThreads, 0, a, b, out, outer, n);         \
+    } while (0)
+        if (n <= 4) KD_SOFTMAX_THREAD(4);
+        else if (n <= 8) KD_SOFTMAX_THREAD(8);
+        else if (n <= 16) KD_SOFTMAX_THREAD(16);
+        else KD_SOFTMAX_THREAD(32);
+#undef KD_SOFTMAX_THREAD
+    } else if (n <= 64) launch_warp<T, 32, 2, 4, BWD>(a, b, out, outer, n);
     else if (n <= 128) launch_warp<T, 32, 4, 2, BWD>(a, b, out, outer, n);
     else if (n <= 256) launch_warp<T, 32, 8, 1, BWD>(a, b, out, outer, n);
     else if (n <= 512) launch_warp<T, 32, 16, 1, BWD>(a, b, out, outer, n);

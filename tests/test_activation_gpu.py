@@ -346,3 +346,56 @@ def test_adam_matches_reference_cpu_outputs_bitwise(golden, tag, wd):
         assert_same_bits(dp.get(), golden[f"{tag}/p{k + 1}"])
     assert_same_bits(dm.get(), golden[f"{tag}/m3"])
     assert_same_bits(dv.get(), golden[f"{tag}/v3"])
+
+
+def _ref_chain_softmax(ref, x, g):
+    """SoftmaxFn forward / backward exactly as the reference runs them on a CUDA (rows, cols) tensor, axis = 1:
+    max -> broadcast_to -> sub -> exp -> sum -> broadcast_to -> div;  mul -> sum -> broadcast_to -> sub -> mul."""
+    rows, cols = x.shape
+    s, dt = suf(x.dtype), x.dtype
+    mk = lambda shape=x.shape: Buf(ref, shape=shape, dtype=dt)   # noqa: E731
+    small, full = (ctypes.c_int64 * 2)(rows, 1), (ctypes.c_int64 * 2)(rows, cols)
+
+    def bcast(src):
+        dst = mk()
+        ref.call(f"keydnn_cuda_broadcast_to_{s}", src.ptr, dst.ptr, small, 2, full, 2)
+        return dst
+
+    dx, dg = Buf(ref, x), Buf(ref, g)
+    m, idx = mk((rows,)), Buf(ref, shape=(rows,), dtype=np.int64)
+    ref.call(f"keydnn_cuda_max_axis2d_forward_{s}", dx.ptr, m.ptr, idx.ptr, rows, cols, 1)
+    shift, e, den, y = mk(), mk(), mk((rows,)), mk()
+    ref.call(f"keydnn_cuda_sub_{s}", dx.ptr, bcast(m).ptr, shift.ptr, x.size)
+    ref.call(f"keydnn_cuda_exp_{s}", shift.ptr, e.ptr, x.size)
+    ref.call(f"keydnn_cuda_sum_axis2d_forward_{s}", e.ptr, den.ptr, rows, cols, 1)
+    ref.call(f"keydnn_cuda_div_{s}", e.ptr, bcast(den).ptr, y.ptr, x.size)
+    gy, dot, t, gx = mk(), mk((rows,)), mk(), mk()
+    ref.call(f"keydnn_cuda_mul_{s}", dg.ptr, y.ptr, gy.ptr, x.size)
+    ref.call(f"keydnn_cuda_sum_axis2d_forward_{s}", gy.ptr, dot.ptr, rows, cols, 1)
+    ref.call(f"keydnn_cuda_sub_{s}", dg.ptr, bcast(dot).ptr, t.ptr, x.size)
+    ref.call(f"keydnn_cuda_mul_{s}", y.ptr, t.ptr, gx.ptr, x.size)
+    return y.get(), gx.get()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_softmax_rows_up_to_32_same_bits_as_the_reference_kernel_chain(dtype):
+    """Classifier-head rows are reduced in the reference's serial order and divided, not scaled: bit-identical."""
+    ref = ref_cuda()
+    if ref is None:
+        pytest.skip("reference CUDA library not built")
+    lib = native()
+    for rows, cols in ((1, 1), (5, 2), (300, 3), (256, 10), (1000, 16), (777, 17), (513, 31), (2048, 32)):
+        rng = np.random.default_rng(rows + cols)
+        x = (rng.standard_normal((rows, cols)) * 3).astype(dtype)
+        g = rng.standard_normal((rows, cols)).astype(dtype)
+        if rows > 4:
+            x[1, 0] = np.nan
+            x[2, :] = -np.inf
+            x[3, cols - 1] = np.inf
+        want_y, want_gx = _ref_chain_softmax(ref, x, g)
+        dx, dg = Buf(lib, x), Buf(lib, g)
+        dy, dgx = Buf(lib, shape=x.shape, dtype=dtype, fill=0xFF), Buf(lib, shape=x.shape, dtype=dtype, fill=0xFF)
+        lib.call(f"keydnn_cuda_softmax_forward_{suf(dtype)}", dx.ptr, dy.ptr, rows, cols, 1)
+        lib.call(f"keydnn_cuda_softmax_backward_{suf(dtype)}", dg.ptr, dy.ptr, dgx.ptr, rows, cols, 1)
+        assert_same_bits(dy.get(), want_y, err_msg=f"forward {rows}x{cols}")
+        assert_same_bits(dgx.get(), want_gx, err_msg=f"backward {rows}x{cols}")
