@@ -312,6 +312,24 @@ int keydnn_cuda_bn2d_backward_f64(const double* x, const double* gamma, const do
                                   const double* mean, const double* invstd, double* grad_x, double* grad_gamma,
                                   double* grad_beta, int N, int C, int64_t HW, int relu);
 
+/* The layer in front adds a per-channel bias (a convolution's): pre_bias (C values) is added to every element of x as
+ * it is read, one rounded addition, so the separate bias pass over the activation disappears; statistics, output and
+ * gradients are those of x + pre_bias. */
+int keydnn_cuda_bn2d_forward_bias_f32(const float* x, const float* pre_bias, const float* gamma, const float* beta,
+                                      float* y, float* mean, float* invstd, float* running_mean, float* running_var,
+                                      int N, int C, int64_t HW, float eps, float momentum, int training, int relu);
+int keydnn_cuda_bn2d_forward_bias_f64(const double* x, const double* pre_bias, const double* gamma, const double* beta,
+                                      double* y, double* mean, double* invstd, double* running_mean,
+                                      double* running_var, int N, int C, int64_t HW, double eps, double momentum,
+                                      int training, int relu);
+int keydnn_cuda_bn2d_backward_bias_f32(const float* x, const float* pre_bias, const float* gamma, const float* beta,
+                                       const float* grad_out, const float* mean, const float* invstd, float* grad_x,
+                                       float* grad_gamma, float* grad_beta, int N, int C, int64_t HW, int relu);
+int keydnn_cuda_bn2d_backward_bias_f64(const double* x, const double* pre_bias, const double* gamma, const double* beta,
+                                       const double* grad_out, const double* mean, const double* invstd,
+                                       double* grad_x, double* grad_gamma, double* grad_beta, int N, int C, int64_t HW,
+                                       int relu);
+
 /* ------------------------------------------------------------------------- */
 /* exp / log / sqrt, activations, losses, Adam.                                 */
 /* ref: NC/keydnn_cuda_ops.hpp (keydnn_cuda_exp_*; kernel keydnn_cuda_exp.cu:5-40) is the only unary

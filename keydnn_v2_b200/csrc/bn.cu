@@ -42,14 +42,17 @@ template <typename T> __device__ __forceinline__ T relu_mask(T z) { return z > T
 template <typename T, int MODE, bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ mean,
-                const T* __restrict__ invstd, const T* __restrict__ gamma, const T* __restrict__ beta, int N, int C,
-                int64_t HW, int ach, double* partials, unsigned int* counters, double* sums /* [2][C] */) {
+                const T* __restrict__ invstd, const T* __restrict__ gamma, const T* __restrict__ beta,
+                const T* __restrict__ pre_bias, int N, int C, int64_t HW, int ach, double* partials,
+                unsigned int* counters, double* sums /* [2][C] */) {
     kd::pdl_prologue();
     __shared__ double sm[kWarps];
     const int c = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
     const int n_begin = slice * ach;
     const int n_end = min(N, n_begin + ach);
     T mu = T(0), is = T(0), ga = T(1), be = T(0);
+    const bool biased = pre_bias != nullptr;            // the layer input is x + pre_bias[c], rounded once
+    const T pb = biased ? __ldg(pre_bias + c) : T(0);
     if (MODE == 1) { mu = __ldg(mean + c); is = __ldg(invstd + c); }
     if (RELU) { ga = gamma ? __ldg(gamma + c) : T(1); be = beta ? __ldg(beta + c) : T(0); }
     double a0 = 0.0, a1 = 0.0;
@@ -59,7 +62,11 @@ bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __res
         if (VEC) {
             const int64_t b4 = HW >> 2;
             for (int64_t p = threadIdx.x; p < b4; p += kThreads) {
-                const Pack4<T> vx = kd::load4_stream(x + base + 4 * p);
+                Pack4<T> vx = kd::load4_stream(x + base + 4 * p);
+                if (biased) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) vx.v[k] = vx.v[k] + pb;
+                }
                 if (MODE == 0) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
@@ -79,7 +86,7 @@ bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __res
             }
         } else {
             for (int64_t b = threadIdx.x; b < HW; b += kThreads) {
-                const T vx = x[base + b];
+                const T vx = biased ? x[base + b] + pb : x[base + b];
                 if (MODE == 0) { p0 += vx; q0 += vx * vx; }
                 else {
                     const T xh = (vx - mu) * is;
@@ -144,11 +151,14 @@ __global__ void bn_invstd_from_var(const T* __restrict__ var, int C, T eps, T* i
 template <typename T, bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_apply_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
-             const T* __restrict__ mean, const T* __restrict__ invstd, T* __restrict__ y, int64_t rows, int C, int64_t HW) {
+             const T* __restrict__ mean, const T* __restrict__ invstd, const T* __restrict__ pre_bias, T* __restrict__ y,
+             int64_t rows, int C, int64_t HW) {
     kd::pdl_prologue();
+    const bool biased = pre_bias != nullptr;
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const int c = static_cast<int>(r % C);
         const T mu = __ldg(mean + c), is = __ldg(invstd + c);
+        const T pb = biased ? __ldg(pre_bias + c) : T(0);
         const T ga = gamma ? __ldg(gamma + c) : T(1), be = beta ? __ldg(beta + c) : T(0);
         const bool affine = gamma != nullptr;
         const T* src = x + r * HW;
@@ -160,7 +170,8 @@ bn_apply_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __re
                 Pack4<T> v = kd::load4_stream(src + 4 * p);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const T xh = (v.v[k] - mu) * is;
+                    const T xv = biased ? v.v[k] + pb : v.v[k];
+                    const T xh = (xv - mu) * is;
                     const T z = affine ? ga * xh + be : xh;
                     v.v[k] = RELU ? z * relu_mask<T>(z) : z;
                 }
@@ -169,7 +180,8 @@ bn_apply_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __re
         } else {
             for (int64_t b = static_cast<int64_t>(blockIdx.y) * kThreads + threadIdx.x; b < HW;
                  b += static_cast<int64_t>(gridDim.y) * kThreads) {
-                const T xh = (src[b] - mu) * is;
+                const T xv = biased ? src[b] + pb : src[b];
+                const T xh = (xv - mu) * is;
                 const T z = affine ? ga * xh + be : xh;
                 dst[b] = RELU ? z * relu_mask<T>(z) : z;
             }
@@ -182,12 +194,14 @@ bn_apply_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __re
 template <typename T, bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ gamma, const T* __restrict__ beta,
-             const T* __restrict__ mean, const T* __restrict__ invstd, const double* __restrict__ sums,
-             T* __restrict__ dx, int64_t rows, int C, int64_t HW, T m) {
+             const T* __restrict__ mean, const T* __restrict__ invstd, const T* __restrict__ pre_bias,
+             const double* __restrict__ sums, T* __restrict__ dx, int64_t rows, int C, int64_t HW, T m) {
     kd::pdl_prologue();
+    const bool biased = pre_bias != nullptr;
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const int c = static_cast<int>(r % C);
         const T mu = __ldg(mean + c), is = __ldg(invstd + c);
+        const T pb = biased ? __ldg(pre_bias + c) : T(0);
         const T ga = gamma ? __ldg(gamma + c) : T(1);
         const T be = (RELU && beta) ? __ldg(beta + c) : T(0);
         const T s1 = static_cast<T>(sums[c]) * ga;
@@ -205,7 +219,8 @@ bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restri
                 Pack4<T> out;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const T xh = (vx.v[k] - mu) * is;
+                    const T xv = biased ? vx.v[k] + pb : vx.v[k];
+                    const T xh = (xv - mu) * is;
                     const T gk = RELU ? vg.v[k] * relu_mask<T>(ga * xh + be) : vg.v[k];
                     out.v[k] = k0 * (m * (gk * ga) - s1 - xh * s2);
                 }
@@ -214,7 +229,8 @@ bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restri
         } else {
             for (int64_t b = static_cast<int64_t>(blockIdx.y) * kThreads + threadIdx.x; b < HW;
                  b += static_cast<int64_t>(gridDim.y) * kThreads) {
-                const T xh = (xs[b] - mu) * is;
+                const T xv = biased ? xs[b] + pb : xs[b];
+                const T xh = (xv - mu) * is;
                 const T gk = RELU ? gs[b] * relu_mask<T>(ga * xh + be) : gs[b];
                 dst[b] = k0 * (m * (gk * ga) - s1 - xh * s2);
             }
@@ -266,7 +282,7 @@ inline dim3 row_grid(int64_t rows, int64_t HW) {
 
 template <typename T>
 int bn_forward(const T* x, const T* gamma, const T* beta, T* y, T* mean, T* invstd, T* running_mean, T* running_var,
-               int N, int C, int64_t HW, T eps, T momentum, int training, int relu) {
+               int N, int C, int64_t HW, T eps, T momentum, int training, int relu, const T* pre_bias) {
     if (!x || !y || !mean || !invstd) return -1;
     if (N <= 0 || C <= 0 || HW <= 0) return -2;
     if ((gamma == nullptr) != (beta == nullptr)) return -3;
@@ -278,8 +294,8 @@ int bn_forward(const T* x, const T* gamma, const T* beta, T* y, T* mean, T* invs
         SumsPlan p;
         if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
         dim3 grid(C, p.nslices);
-        if (vec) (void)kd::launch(bn_channel_sums<T, 0, true, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, N, C, HW, p.ach, p.partials, p.counters, p.sums);
-        else (void)kd::launch(bn_channel_sums<T, 0, false, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, N, C, HW, p.ach, p.partials, p.counters, p.sums);
+        if (vec) (void)kd::launch(bn_channel_sums<T, 0, true, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums);
+        else (void)kd::launch(bn_channel_sums<T, 0, false, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums);
         (void)kd::launch(bn_finalize_stats<T>, dim3((C + 127) / 128), 128, 0, p.sums, C, static_cast<double>(N) * static_cast<double>(HW), eps,
                                                           momentum, mean, static_cast<T*>(nullptr), invstd, running_mean,
                                                           running_var);
@@ -290,18 +306,18 @@ int bn_forward(const T* x, const T* gamma, const T* beta, T* y, T* mean, T* invs
     const int64_t rows = static_cast<int64_t>(N) * C;
     const dim3 g2 = row_grid(rows, HW);
     if (relu) {
-        if (vec) (void)kd::launch(bn_apply_fwd<T, true, true>, dim3(g2), kThreads, 0, x, gamma, beta, mean, invstd, y, rows, C, HW);
-        else (void)kd::launch(bn_apply_fwd<T, false, true>, dim3(g2), kThreads, 0, x, gamma, beta, mean, invstd, y, rows, C, HW);
+        if (vec) (void)kd::launch(bn_apply_fwd<T, true, true>, dim3(g2), kThreads, 0, x, gamma, beta, mean, invstd, pre_bias, y, rows, C, HW);
+        else (void)kd::launch(bn_apply_fwd<T, false, true>, dim3(g2), kThreads, 0, x, gamma, beta, mean, invstd, pre_bias, y, rows, C, HW);
     } else {
-        if (vec) (void)kd::launch(bn_apply_fwd<T, true, false>, dim3(g2), kThreads, 0, x, gamma, beta, mean, invstd, y, rows, C, HW);
-        else (void)kd::launch(bn_apply_fwd<T, false, false>, dim3(g2), kThreads, 0, x, gamma, beta, mean, invstd, y, rows, C, HW);
+        if (vec) (void)kd::launch(bn_apply_fwd<T, true, false>, dim3(g2), kThreads, 0, x, gamma, beta, mean, invstd, pre_bias, y, rows, C, HW);
+        else (void)kd::launch(bn_apply_fwd<T, false, false>, dim3(g2), kThreads, 0, x, gamma, beta, mean, invstd, pre_bias, y, rows, C, HW);
     }
     return kd::launch_status();
 }
 
 template <typename T>
 int bn_backward(const T* x, const T* gamma, const T* beta, const T* go, const T* mean, const T* invstd, T* dx, T* dgamma,
-                T* dbeta, int N, int C, int64_t HW, int relu) {
+                T* dbeta, int N, int C, int64_t HW, int relu, const T* pre_bias) {
     if (!x || !go || !mean || !invstd || !dx) return -1;
     if (N <= 0 || C <= 0 || HW <= 0) return -2;
     (void)cudaGetLastError();
@@ -310,7 +326,7 @@ int bn_backward(const T* x, const T* gamma, const T* beta, const T* go, const T*
     SumsPlan p;
     if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
     dim3 grid(C, p.nslices);
-#define KD_BN_SUMS(V, R) (void)kd::launch(bn_channel_sums<T, 1, V, R>, dim3(grid), kThreads, 0, x, go, mean, invstd, gamma, beta, N, C, HW, p.ach, p.partials, p.counters, p.sums)
+#define KD_BN_SUMS(V, R) (void)kd::launch(bn_channel_sums<T, 1, V, R>, dim3(grid), kThreads, 0, x, go, mean, invstd, gamma, beta, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums)
     if (relu) { if (vec) KD_BN_SUMS(true, true); else KD_BN_SUMS(false, true); }
     else { if (vec) KD_BN_SUMS(true, false); else KD_BN_SUMS(false, false); }
 #undef KD_BN_SUMS
@@ -318,7 +334,7 @@ int bn_backward(const T* x, const T* gamma, const T* beta, const T* go, const T*
     const int64_t rows = static_cast<int64_t>(N) * C;
     const dim3 g2 = row_grid(rows, HW);
     const T m = static_cast<T>(static_cast<double>(N) * static_cast<double>(HW));
-#define KD_BN_APPLY(V, R) (void)kd::launch(bn_apply_bwd<T, V, R>, dim3(g2), kThreads, 0, x, go, gamma, beta, mean, invstd, p.sums, dx, rows, C, HW, m)
+#define KD_BN_APPLY(V, R) (void)kd::launch(bn_apply_bwd<T, V, R>, dim3(g2), kThreads, 0, x, go, gamma, beta, mean, invstd, pre_bias, p.sums, dx, rows, C, HW, m)
     if (relu) { if (vec) KD_BN_APPLY(true, true); else KD_BN_APPLY(false, true); }
     else { if (vec) KD_BN_APPLY(true, false); else KD_BN_APPLY(false, false); }
 #undef KD_BN_APPLY
@@ -334,21 +350,40 @@ KD_API int keydnn_cuda_bn2d_forward_f32(const float* x, const float* gamma, cons
                                         float* invstd, float* running_mean, float* running_var, int N, int C, int64_t HW,
                                         float eps, float momentum, int training, int relu) {
     return bn_forward<float>(x, gamma, beta, y, mean, invstd, running_mean, running_var, N, C, HW, eps, momentum, training,
-                             relu);
+                             relu, nullptr);
 }
 KD_API int keydnn_cuda_bn2d_forward_f64(const double* x, const double* gamma, const double* beta, double* y, double* mean,
                                         double* invstd, double* running_mean, double* running_var, int N, int C,
                                         int64_t HW, double eps, double momentum, int training, int relu) {
     return bn_forward<double>(x, gamma, beta, y, mean, invstd, running_mean, running_var, N, C, HW, eps, momentum, training,
-                              relu);
+                              relu, nullptr);
 }
 KD_API int keydnn_cuda_bn2d_backward_f32(const float* x, const float* gamma, const float* beta, const float* grad_out,
                                          const float* mean, const float* invstd, float* grad_x, float* grad_gamma,
                                          float* grad_beta, int N, int C, int64_t HW, int relu) {
-    return bn_backward<float>(x, gamma, beta, grad_out, mean, invstd, grad_x, grad_gamma, grad_beta, N, C, HW, relu);
+    return bn_backward<float>(x, gamma, beta, grad_out, mean, invstd, grad_x, grad_gamma, grad_beta, N, C, HW, relu, nullptr);
 }
 KD_API int keydnn_cuda_bn2d_backward_f64(const double* x, const double* gamma, const double* beta, const double* grad_out,
                                          const double* mean, const double* invstd, double* grad_x, double* grad_gamma,
                                          double* grad_beta, int N, int C, int64_t HW, int relu) {
-    return bn_backward<double>(x, gamma, beta, grad_out, mean, invstd, grad_x, grad_gamma, grad_beta, N, C, HW, relu);
+    return bn_backward<double>(x, gamma, beta, grad_out, mean, invstd, grad_x, grad_gamma, grad_beta, N, C, HW, relu, nullptr);
 }
+
+// The layer in front adds a per-channel bias (a convolution's): `pre_bias` (C values) is added to every element of x
+// as it is read - one rounded addition, what the separate bias pass would have stored - so that pass and its
+// read + write of the whole activation disappear.  Statistics, output and gradients are those of x + pre_bias.
+#define KD_BN_BIAS_EXPORTS(T, SUF)                                                                                      \
+    KD_API int keydnn_cuda_bn2d_forward_bias_##SUF(const T* x, const T* pre_bias, const T* gamma, const T* beta, T* y,   \
+                                                   T* mean, T* invstd, T* running_mean, T* running_var, int N, int C,    \
+                                                   int64_t HW, T eps, T momentum, int training, int relu) {              \
+        return bn_forward<T>(x, gamma, beta, y, mean, invstd, running_mean, running_var, N, C, HW, eps, momentum,        \
+                             training, relu, pre_bias);                                                                  \
+    }                                                                                                                    \
+    KD_API int keydnn_cuda_bn2d_backward_bias_##SUF(const T* x, const T* pre_bias, const T* gamma, const T* beta,        \
+                                                    const T* grad_out, const T* mean, const T* invstd, T* grad_x,        \
+                                                    T* grad_gamma, T* grad_beta, int N, int C, int64_t HW, int relu) {   \
+        return bn_backward<T>(x, gamma, beta, grad_out, mean, invstd, grad_x, grad_gamma, grad_beta, N, C, HW, relu,     \
+                              pre_bias);                                                                                 \
+    }
+KD_BN_BIAS_EXPORTS(float, f32)
+KD_BN_BIAS_EXPORTS(double, f64)

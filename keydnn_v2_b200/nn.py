@@ -86,6 +86,7 @@ class Conv2d(Module):
         self.kernel_size, self.stride, self.padding = _pair(kernel_size), _pair(stride), _pair(padding)
         self.weight = Parameter.from_numpy(kaiming_normal((out_channels, in_channels, *self.kernel_size), np.dtype(dtype).type))
         self.bias = Parameter.from_numpy(np.zeros(out_channels, dtype)) if bias else None
+        self.bias_deferred = False      # set by Sequential when a BatchNorm2d follows: that layer adds the bias as it reads
 
     def forward(self, x: Tensor) -> Tensor:
         if x.ndim != 4 or x.shape[1] != self.in_channels:
@@ -97,8 +98,8 @@ class Conv2d(Module):
         s = _suffix(x.dtype)
         y = Tensor.empty((N, self.out_channels, Ho, Wo), x.dtype)
         dims = (N, C, H, W, self.out_channels, Ho, Wo, kh, kw, sh, sw, ph, pw)
-        dnn.call(f"keydnn_cuda_conv2d_forward_ex_{s}", x.data, self.weight.data, self.bias.data if self.bias else None,
-                 y.data, *dims)
+        dnn.call(f"keydnn_cuda_conv2d_forward_ex_{s}", x.data, self.weight.data,
+                 self.bias.data if self.bias and not self.bias_deferred else None, y.data, *dims)
         w, b = self.weight, self.bias
         if x._needs_grad(w) or (b is not None and b.requires_grad):
             y.requires_grad = True
@@ -127,6 +128,7 @@ class BatchNorm2d(Module):
         self.running_mean = Tensor.zeros((num_features,), dtype)
         self.running_var = Tensor.ones((num_features,), dtype)
         self.fused_relu = False     # set by Sequential when a ReLU follows: one kernel pair does both layers
+        self.pre_bias = None        # set by Sequential when a Conv2d precedes: its bias, added while x is read
 
     def parameters(self) -> List[Parameter]:
         return [self.gamma, self.beta] if self.affine else []
@@ -141,9 +143,10 @@ class BatchNorm2d(Module):
         y = Tensor.empty(x.shape, x.dtype)
         mean, invstd = Tensor.empty((C,), x.dtype), Tensor.empty((C,), x.dtype)
         ga, be = (self.gamma, self.beta) if self.affine else (None, None)
-        lib.call(f"keydnn_cuda_bn2d_forward_{s}", x.data, ga.data if ga else None, be.data if be else None, y.data,
-                 mean.data, invstd.data, self.running_mean.data, self.running_var.data, N, C, H * W,
-                 _cfloat(x.dtype, self.eps), _cfloat(x.dtype, self.momentum), 1 if self.training else 0,
+        pb = self.pre_bias
+        lib.call(f"keydnn_cuda_bn2d_forward_bias_{s}", x.data, pb.data if pb is not None else None, ga.data if ga else None,
+                 be.data if be else None, y.data, mean.data, invstd.data, self.running_mean.data, self.running_var.data,
+                 N, C, H * W, _cfloat(x.dtype, self.eps), _cfloat(x.dtype, self.momentum), 1 if self.training else 0,
                  1 if self.fused_relu else 0)
         if x._needs_grad() or (self.affine and (ga.requires_grad or be.requires_grad)):
             y.requires_grad = True
@@ -152,9 +155,9 @@ class BatchNorm2d(Module):
                 dx = Tensor.empty(x.shape, x.dtype)
                 dga = Tensor.empty((C,), x.dtype) if self.affine else None
                 dbe = Tensor.empty((C,), x.dtype) if self.affine else None
-                lib.call(f"keydnn_cuda_bn2d_backward_{s}", x.data, ga.data if ga else None, be.data if be else None, g.data,
-                         mean.data, invstd.data, dx.data, dga.data if dga else None, dbe.data if dbe else None, N, C,
-                         H * W, 1 if self.fused_relu else 0)
+                lib.call(f"keydnn_cuda_bn2d_backward_bias_{s}", x.data, pb.data if pb is not None else None,
+                         ga.data if ga else None, be.data if be else None, g.data, mean.data, invstd.data, dx.data,
+                         dga.data if dga else None, dbe.data if dbe else None, N, C, H * W, 1 if self.fused_relu else 0)
                 return (dx, dga, dbe) if self.affine else (dx,)
 
             y._ctx = Context((x, ga, be) if self.affine else (x,), backward_fn)
@@ -216,8 +219,10 @@ class Linear(Module):
 
 class Sequential(Module):
     """Runs its layers in order (``models/_sequential.py:130-152``).  With ``fuse=True`` (default) a ReLU that
-    directly follows a BatchNorm2d is folded into that layer's kernels; results are bit-identical to the
-    two separate layers, three tensor passes forward and one backward disappear."""
+    directly follows a BatchNorm2d is folded into that layer's kernels, and the bias of a Conv2d that directly
+    precedes a BatchNorm2d is added by the BatchNorm kernels as they read the activation (the convolution then
+    skips its bias pass).  Results are bit-identical to the separate layers; three tensor passes forward and one
+    backward (ReLU) and a read + write of the activation (bias) disappear."""
 
     def __init__(self, *layers, fuse: bool = True) -> None:
         self.layers = list(layers)
@@ -228,6 +233,9 @@ class Sequential(Module):
                 if isinstance(a, BatchNorm2d) and isinstance(b, ReLU) and a.gamma is not None and a.gamma.dtype == np.float32:
                     a.fused_relu = True
                     self._skip.add(i + 1)
+                if isinstance(a, Conv2d) and isinstance(b, BatchNorm2d) and a.bias is not None and a.bias.dtype == b.running_mean.dtype:
+                    a.bias_deferred = True
+                    b.pre_bias = a.bias
 
     def forward(self, x: Tensor) -> Tensor:
         for i, layer in enumerate(self.layers):

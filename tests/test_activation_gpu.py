@@ -356,8 +356,11 @@ def _ref_chain_softmax(ref, x, g):
     mk = lambda shape=x.shape: Buf(ref, shape=shape, dtype=dt)   # noqa: E731
     small, full = (ctypes.c_int64 * 2)(rows, 1), (ctypes.c_int64 * 2)(rows, cols)
 
+    keep = []                   # every temporary stays allocated until the results are read back
+
     def bcast(src):
         dst = mk()
+        keep.append(dst)
         ref.call(f"keydnn_cuda_broadcast_to_{s}", src.ptr, dst.ptr, small, 2, full, 2)
         return dst
 
@@ -374,7 +377,9 @@ def _ref_chain_softmax(ref, x, g):
     ref.call(f"keydnn_cuda_sum_axis2d_forward_{s}", gy.ptr, dot.ptr, rows, cols, 1)
     ref.call(f"keydnn_cuda_sub_{s}", dg.ptr, bcast(dot).ptr, t.ptr, x.size)
     ref.call(f"keydnn_cuda_mul_{s}", y.ptr, t.ptr, gx.ptr, x.size)
-    return y.get(), gx.get()
+    out = (y.get(), gx.get())
+    del keep
+    return out
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -129,6 +129,39 @@ def test_fused_batchnorm_relu_is_bit_identical_to_the_two_layers():
         np.testing.assert_array_equal(a.view(np.uint32), b.view(np.uint32))
 
 
+@pytest.mark.parametrize("training", [True, False])
+def test_conv_bias_added_by_batchnorm_is_bit_identical_to_the_bias_pass(training):
+    """Conv2d -> BatchNorm2d -> ReLU with the convolution's bias added inside the BatchNorm kernels, against the same
+    stack with a separate bias pass: outputs, running statistics and every gradient must have the same bits."""
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import nn
+
+    rng = np.random.default_rng(16)
+    x = rng.standard_normal((5, 3, 10, 12)).astype(np.float32)
+    g = rng.standard_normal((5, 6, 10, 12)).astype(np.float32)
+    bias = rng.standard_normal(6).astype(np.float32)
+    outs = []
+    for fuse in (True, False):
+        np.random.seed(2)
+        conv, bn = nn.Conv2d(3, 6, 3, padding=1), nn.BatchNorm2d(6)
+        conv.bias.copy_from_numpy(bias)
+        bn.gamma.copy_from_numpy(np.linspace(0.5, 1.5, 6).astype(np.float32))
+        bn.beta.copy_from_numpy(np.linspace(0.2, -0.2, 6).astype(np.float32))
+        seq = nn.Sequential(conv, bn, nn.ReLU(), fuse=fuse)
+        assert conv.bias_deferred == fuse and (bn.pre_bias is conv.bias) == fuse
+        seq.train(training)
+        tx = kd.Tensor.from_numpy(x, requires_grad=True)
+        y = seq(tx)
+        y.backward(kd.Tensor.from_numpy(g))
+        outs.append((y.to_numpy(), tx.grad.to_numpy(), conv.weight.grad.to_numpy(), conv.bias.grad.to_numpy(),
+                     bn.gamma.grad.to_numpy(), bn.beta.grad.to_numpy(), bn.running_mean.to_numpy(), bn.running_var.to_numpy()))
+    for i, (a, b) in enumerate(zip(*outs)):
+        if i in (1, 2):      # input / weight gradients come from cuDNN, whose reduction order is its own
+            np.testing.assert_allclose(a, b, rtol=1e-5, atol=1e-6)
+        else:
+            np.testing.assert_array_equal(a.view(np.uint32), b.view(np.uint32), err_msg=str(i))
+
+
 def test_graphed_training_step_follows_the_eager_one():
     """A CUDA-graph replay of the step must train exactly like the eager step sequence."""
     import keydnn_v2_b200 as kd
