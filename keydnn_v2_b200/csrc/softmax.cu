@@ -195,6 +195,75 @@ softmax_thread_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __res
     }
 }
 
+// Same walk for rows whose pieces do not line up with 16-byte packets (len % 4 != 0, unaligned base) or are long
+// enough to thrash L1 when every lane strides by a whole row (len > 16): a CTA copies TPB consecutive rows - one
+// contiguous piece of memory - into shared memory with coalesced accesses, every thread then walks its own row there
+// (row pitch len | 1 words: odd, so the lanes of a warp hit 32 different banks), and the results go back the same way.
+template <typename T, int LEN, int TPB, bool BWD>
+__global__ void __launch_bounds__(TPB)
+softmax_thread_staged_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t rows, int len,
+                             kd::FastDiv by_len) {
+    kd::pdl_prologue();
+    extern __shared__ __align__(32) unsigned char smem_raw[];
+    const int pitch = len | 1;
+    T* sa = reinterpret_cast<T*>(smem_raw);
+    T* sb = sa + TPB * pitch;
+    const int64_t tiles = (rows + TPB - 1) / TPB;
+    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int64_t row0 = tile * TPB;
+        const int nrows = static_cast<int>(rows - row0 < TPB ? rows - row0 : TPB);
+        const int count = nrows * len;
+        const T* pa = a + row0 * len;
+        const T* pb = BWD ? b + row0 * len : nullptr;
+        for (int i = threadIdx.x; i < count; i += TPB) {
+            const unsigned r = by_len.div(static_cast<unsigned>(i));
+            const int at = static_cast<int>(r) * pitch + (i - static_cast<int>(r) * len);
+            sa[at] = __ldcs(pa + i);
+            if (BWD) sb[at] = __ldcs(pb + i);
+        }
+        __syncthreads();
+        if (static_cast<int>(threadIdx.x) < nrows) {
+            T* ra = sa + threadIdx.x * pitch;
+            const T* rb = sb + threadIdx.x * pitch;
+            T va[LEN];
+#pragma unroll
+            for (int j = 0; j < LEN; ++j)
+                if (j < len) va[j] = ra[j];
+            if (BWD) {
+                T dot = T(0);
+#pragma unroll
+                for (int j = 0; j < LEN; ++j)
+                    if (j < len) dot = Rn<T>::add(dot, Rn<T>::mul(va[j], rb[j]));
+#pragma unroll
+                for (int j = 0; j < LEN; ++j)
+                    if (j < len) ra[j] = Rn<T>::mul(rb[j], Rn<T>::sub(va[j], dot));
+            } else {
+                T m = neg_inf<T>();
+#pragma unroll
+                for (int j = 0; j < LEN; ++j)
+                    if (j < len) m = va[j] > m ? va[j] : m;
+                T s = T(0);
+#pragma unroll
+                for (int j = 0; j < LEN; ++j)
+                    if (j < len) {
+                        va[j] = t_exp(Rn<T>::sub(va[j], m));
+                        s = Rn<T>::add(s, va[j]);
+                    }
+#pragma unroll
+                for (int j = 0; j < LEN; ++j)
+                    if (j < len) ra[j] = t_div(va[j], s);
+            }
+        }
+        __syncthreads();
+        T* po = out + row0 * len;
+        for (int i = threadIdx.x; i < count; i += TPB) {
+            const unsigned r = by_len.div(static_cast<unsigned>(i));
+            __stcs(po + i, sa[static_cast<int>(r) * pitch + (i - static_cast<int>(r) * len)]);
+        }
+        __syncthreads();
+    }
+}
+
 // ---- long rows: one CTA per row, operands staged in shared memory while they stream in (or re-read
 // through L2 when they do not fit: `staged` false).  VEC: rows start on packet boundaries and len % 4 == 0.
 template <typename T, int kBlockWarps> __device__ __forceinline__ T block_max(T v, T* sm) {
@@ -420,10 +489,22 @@ int softmax(const T* a, const T* b, T* out, int64_t outer, int64_t len, int64_t 
         if (vec) KD_LAUNCH_W((softmax_thread_kernel<T, LEN, true, BWD>), 8, ctas, kThreads, 0, a, b, out, outer, n);      \
         else KD_LAUNCH_W((softmax_thread_kernel<T, LEN, false, BWD>), 8, ctas, kThreads, 0, a, b, out, outer, n);         \
     } while (0)
-        if (n <= 4) KD_SOFTMAX_THREAD(4);
-        else if (n <= 8) KD_SOFTMAX_THREAD(8);
-        else if (n <= 16) KD_SOFTMAX_THREAD(16);
-        else KD_SOFTMAX_THREAD(32);
+#define KD_SOFTMAX_STAGED(LEN)                                                                                            \
+    do {                                                                                                                  \
+        constexpr int TPB = (BWD && sizeof(T) == 8) ? 64 : 128;                                                           \
+        const size_t smem = static_cast<size_t>(TPB) * (n | 1) * sizeof(T) * (BWD ? 2 : 1);                               \
+        KD_LAUNCH_W((softmax_thread_staged_kernel<T, LEN, TPB, BWD>), 8, (outer + TPB - 1) / TPB, TPB, smem, a, b, out,   \
+                    outer, n, kd::FastDiv(static_cast<unsigned>(n)));                                                     \
+    } while (0)
+        if (vec && n <= 16) {
+            if (n <= 4) KD_SOFTMAX_THREAD(4);
+            else if (n <= 8) KD_SOFTMAX_THREAD(8);
+            else KD_SOFTMAX_THREAD(16);
+        } else if (n <= 4) KD_SOFTMAX_STAGED(4);
+        else if (n <= 8) KD_SOFTMAX_STAGED(8);
+        else if (n <= 16) KD_SOFTMAX_STAGED(16);
+        else KD_SOFTMAX_STAGED(32);
+#undef KD_SOFTMAX_STAGED
 #undef KD_SOFTMAX_THREAD
     } else if (n <= 64) launch_warp<T, 32, 2, 4, BWD>(a, b, out, outer, n);
     else if (n <= 128) launch_warp<T, 32, 4, 2, BWD>(a, b, out, outer, n);
