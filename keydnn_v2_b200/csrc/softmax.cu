@@ -195,8 +195,8 @@ softmax_thread_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __res
     }
 }
 
-// Same walk for rows whose pieces do not line up with 16-byte packets (len % 4 != 0, unaligned base) or are long
-// enough to thrash L1 when every lane strides by a whole row (len > 16): a CTA copies TPB consecutive rows - one
+// Same walk for rows whose pieces do not line up with 16-byte packets (len % 4 != 0 or an unaligned base): a CTA
+// copies TPB consecutive rows - one
 // contiguous piece of memory - into shared memory with coalesced accesses, every thread then walks its own row there
 // (row pitch len | 1 words: odd, so the lanes of a warp hit 32 different banks), and the results go back the same way.
 template <typename T, int LEN, int TPB, bool BWD>
@@ -486,8 +486,7 @@ int softmax(const T* a, const T* b, T* out, int64_t outer, int64_t len, int64_t 
         const int64_t ctas = (outer + kThreads - 1) / kThreads;
 #define KD_SOFTMAX_THREAD(LEN)                                                                                            \
     do {                                                                                                                  \
-        if (vec) KD_LAUNCH_W((softmax_thread_kernel<T, LEN, true, BWD>), 8, ctas, kThreads, 0, a, b, out, outer, n);      \
-        else KD_LAUNCH_W((softmax_thread_kernel<T, LEN, false, BWD>), 8, ctas, kThreads, 0, a, b, out, outer, n);         \
+        KD_LAUNCH_W((softmax_thread_kernel<T, LEN, true, BWD>), 8, ctas, kThreads, 0, a, b, out, outer, n);                \
     } while (0)
 #define KD_SOFTMAX_STAGED(LEN)                                                                                            \
     do {                                                                                                                  \
@@ -496,10 +495,11 @@ int softmax(const T* a, const T* b, T* out, int64_t outer, int64_t len, int64_t 
         KD_LAUNCH_W((softmax_thread_staged_kernel<T, LEN, TPB, BWD>), 8, (outer + TPB - 1) / TPB, TPB, smem, a, b, out,   \
                     outer, n, kd::FastDiv(static_cast<unsigned>(n)));                                                     \
     } while (0)
-        if (vec && n <= 16) {
+        if (vec) {                   // measured: packet-aligned rows are faster straight from global memory, up to 32
             if (n <= 4) KD_SOFTMAX_THREAD(4);
             else if (n <= 8) KD_SOFTMAX_THREAD(8);
-            else KD_SOFTMAX_THREAD(16);
+            else if (n <= 16) KD_SOFTMAX_THREAD(16);
+            else KD_SOFTMAX_THREAD(32);
         } else if (n <= 4) KD_SOFTMAX_STAGED(4);
         else if (n <= 8) KD_SOFTMAX_STAGED(8);
         else if (n <= 16) KD_SOFTMAX_STAGED(16);
