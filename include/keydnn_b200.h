@@ -380,6 +380,18 @@ int keydnn_cuda_adam_step_f32(float* p, const float* g, float* m, float* v, int6
 int keydnn_cuda_adam_step_f64(double* p, const double* g, double* m, double* v, int64_t n, double lr, double beta1, double beta2, double eps,
                               double weight_decay, double one_minus_beta1, double one_minus_beta2, double bias1, double bias2,
                               double grad_scale);
+/* Adam whose step count lives on the device (step_counter: one int64, zero before the first step): entry i of
+ * bias_table holds {1 - beta1^(i+1), 1 - beta2^(i+1)} as the caller computed them, table_len entries, the last one
+ * used for every later step (build the table until both values are exactly 1).  bias_now: 2 elements of scratch.
+ * No argument changes between steps, so a step recorded in a CUDA graph can be replayed. */
+int keydnn_cuda_adam_step_counted_f32(float* p, const float* g, float* m, float* v, int64_t n, float lr, float beta1,
+                                      float beta2, float eps, float weight_decay, float one_minus_beta1,
+                                      float one_minus_beta2, const float* bias_table, int64_t table_len,
+                                      int64_t* step_counter, float* bias_now, float grad_scale);
+int keydnn_cuda_adam_step_counted_f64(double* p, const double* g, double* m, double* v, int64_t n, double lr,
+                                      double beta1, double beta2, double eps, double weight_decay,
+                                      double one_minus_beta1, double one_minus_beta2, const double* bias_table,
+                                      int64_t table_len, int64_t* step_counter, double* bias_now, double grad_scale);
 /* Losses.  loss is one device scalar.  sqdiff: diff = pred - target (written when diff is not null), loss =
  * sum(diff*diff), times 1/n when mean.  In the backward entries g is the upstream gradient as a DEVICE
  * scalar (null = 1); it is combined with the host factor in double on the device, where the reference reads

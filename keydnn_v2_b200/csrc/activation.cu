@@ -96,6 +96,13 @@ template <typename T> struct FLeaky1 {       // forward: v == x, one load
 template <typename T> struct FAdam {         // in: p, g, m, v   out: p, m, v
     T lr, b1, b2, eps, wd, c1, c2, bias1, bias2, gscale;
     bool use_wd, use_scale;
+    const T* dev_bias;                       // when set: {bias1, bias2} of this step, left there by adam_tick_kernel
+    __device__ void prepare() {
+        if (dev_bias) {
+            bias1 = __ldg(dev_bias);
+            bias2 = __ldg(dev_bias + 1);
+        }
+    }
     __device__ void operator()(const T (&in)[4], T (&o)[3]) const {
         const T p = in[0];
         T g = in[1];
@@ -195,14 +202,30 @@ int exp_reference_abi(const T* x, T* y, int numel) {
     return kd::launch_map<T, 1, 1>(a, numel, FExp<T>{}) == 0 ? 0 : 3;
 }
 
+// The step count lives on the device: entry i of `table` holds {1 - beta1^(i+1), 1 - beta2^(i+1)} as the caller
+// computed them (clamped to the last entry, where both have reached 1); this kernel hands the entry of the current
+// step to the update kernel behind it and advances the count.  No launch argument changes from step to step, so a
+// recorded step can be replayed.
+template <typename T>
+__global__ void adam_tick_kernel(const T* __restrict__ table, long long table_len, long long* step, T* bias_now) {
+    kd::pdl_prologue();
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        const long long t = *step;
+        const long long i = t < table_len ? t : table_len - 1;
+        bias_now[0] = table[2 * i];
+        bias_now[1] = table[2 * i + 1];
+        *step = t + 1;
+    }
+}
+
 template <typename T>
 int adam_step(T* p, const T* g, T* m, T* v, int64_t n, T lr, T b1, T b2, T eps, T wd, T c1, T c2, T bias1, T bias2,
-              T gscale) {
+              T gscale, const T* dev_bias = nullptr) {
     if (!p || !g || !m || !v) return -1;
     if (n < 0) return -2;
     if (n == 0) return 0;
     MapArgs<T, 4, 3> a{{p, g, m, v}, {p, m, v}};
-    FAdam<T> f{lr, b1, b2, eps, wd, c1, c2, bias1, bias2, gscale, wd != T(0), gscale != T(1)};
+    FAdam<T> f{lr, b1, b2, eps, wd, c1, c2, bias1, bias2, gscale, wd != T(0), gscale != T(1), dev_bias};
     // one packet per tensor in flight per thread: the update's long dependent chain (three divisions, a square
     // root) wants resident warps more than it wants loads per thread (measured on B200: 107 us against 186 us
     // with two packets for 25 M parameters)
@@ -255,6 +278,19 @@ int loss_sum(const T* pred, const T* target, T* loss, int64_t n, T scale, int fi
                                            T grad_scale) {                                                             \
         return adam_step<T>(p, g, m, v, n, lr, beta1, beta2, eps, weight_decay, one_minus_beta1, one_minus_beta2,      \
                             bias1, bias2, grad_scale);                                                                 \
+    }                                                                                                                  \
+    KD_API int keydnn_cuda_adam_step_counted_##SUF(T* p, const T* g, T* m, T* v, int64_t n, T lr, T beta1, T beta2,    \
+                                                   T eps, T weight_decay, T one_minus_beta1, T one_minus_beta2,        \
+                                                   const T* bias_table, int64_t table_len, int64_t* step_counter,      \
+                                                   T* bias_now, T grad_scale) {                                        \
+        if (!bias_table || !step_counter || !bias_now) return -1;                                                      \
+        if (table_len <= 0) return -2;                                                                                 \
+        (void)cudaGetLastError();                                                                                      \
+        (void)kd::launch(adam_tick_kernel<T>, dim3(1), 32, 0, bias_table, static_cast<long long>(table_len),           \
+                         reinterpret_cast<long long*>(step_counter), bias_now);                                        \
+        if (int st = kd::launch_status()) return st;                                                                   \
+        return adam_step<T>(p, g, m, v, n, lr, beta1, beta2, eps, weight_decay, one_minus_beta1, one_minus_beta2,      \
+                            T(1), T(1), grad_scale, bias_now);                                                         \
     }                                                                                                                  \
     KD_API int keydnn_cuda_sqdiff_forward_##SUF(const T* pred, const T* target, T* diff, T* loss, int64_t n, int mean) { \
         if (diff) {                                                                                                    \

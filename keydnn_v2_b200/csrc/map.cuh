@@ -19,10 +19,16 @@ struct MapArgs {
     T* out[NOUT];
 };
 
+// A functor may define prepare(): it runs once per thread behind the dependency wait and before the first
+// element, e.g. to fetch launch-invariant scalars that an earlier kernel of the stream left in device memory.
+template <typename F> __device__ __forceinline__ auto map_prepare(F& f, int) -> decltype(f.prepare(), void()) { f.prepare(); }
+template <typename F> __device__ __forceinline__ void map_prepare(F&, long) {}
+
 template <typename T, int NIN, int NOUT, int UNROLL, bool VEC, typename F>
 __global__ void __launch_bounds__(kMapThreads)
 map_kernel(MapArgs<T, NIN, NOUT> a, int64_t n, F f) {
     kd::pdl_prologue();
+    map_prepare(f, 0);
     if (VEC) {
         const int64_t n4 = n >> 2;
         const int64_t tile = static_cast<int64_t>(kMapThreads) * UNROLL;

@@ -350,13 +350,17 @@ class Adam(_FlatOptimizer):
     """Adam with coupled L2 weight decay (``optimizers/_adam.py:120-219``; there CPU-only, eleven tensor passes
     per parameter) over flat buffers: one fused kernel over (p, g, m, v) per step, the gradient all-reduce of
     ``group`` in front of it.  Every parameter shares the step count, as all of them get a gradient each step.
-    The bias corrections 1 - beta^t change every step and are passed by value, so a step cannot be replayed
-    from a CUDA graph (``graph_safe`` is False)."""
+    The bias corrections 1 - beta^t change every step.  By default they are passed by value, so a step cannot be
+    replayed from a CUDA graph (``graph_safe`` is False).  With ``device_step=True`` the step count lives on the
+    device and the corrections come from a table built here in Python doubles (one entry per step until both are
+    exactly 1 in the element type, a few ten thousand entries for the usual betas): same bits, and the step can
+    be recorded."""
 
     graph_safe = False
+    _MAX_TABLE = 1 << 21
 
     def __init__(self, params: Iterable[Parameter], lr: float = 1e-3, betas: Tuple[float, float] = (0.9, 0.999),
-                 eps: float = 1e-8, weight_decay: float = 0.0, group=None) -> None:
+                 eps: float = 1e-8, weight_decay: float = 0.0, group=None, device_step: bool = False) -> None:
         self.lr, self.betas, self.eps, self.weight_decay = float(lr), (float(betas[0]), float(betas[1])), float(eps), float(weight_decay)
         b1, b2 = self.betas
         if self.lr <= 0.0:
@@ -370,12 +374,36 @@ class Adam(_FlatOptimizer):
         super().__init__(params, 2, group)
         self.flat_m, self.flat_v = self.state
         self.t = 0
+        self._table = None
+        if device_step:
+            t_ = self.dtype.type
+            rows, k = [], 1
+            while True:
+                a, b = t_(1.0 - b1 ** k), t_(1.0 - b2 ** k)
+                rows.append((a, b))
+                if a == 1 and b == 1:
+                    break
+                if len(rows) >= self._MAX_TABLE:
+                    raise ValueError("betas too close to 1 for device_step: the correction table would not end")
+                k += 1
+            self._table = Tensor.from_numpy(np.asarray(rows, self.dtype))
+            self._table_len = len(rows)
+            self._count = CudaStorage.allocate(8, np.int64)
+            self.native.call("keydnn_cuda_memset", self._count.dev_ptr, 0, 8)
+            self._bias_now = Tensor.zeros((2,), self.dtype)
+            self.graph_safe = True
 
     def step(self) -> None:
         world = self._gather_grads()
         self.t += 1
         b1, b2 = self.betas
         c = lambda v: _cfloat(self.dtype, v)   # noqa: E731
+        if self._table is not None:
+            self.native.call(f"keydnn_cuda_adam_step_counted_{_suffix(self.dtype)}", self.flat_p.dev_ptr, self.flat_g.dev_ptr,
+                             self.flat_m.dev_ptr, self.flat_v.dev_ptr, self.n, c(self.lr), c(b1), c(b2), c(self.eps),
+                             c(self.weight_decay), c(1.0 - b1), c(1.0 - b2), self._table.data, self._table_len,
+                             self._count.dev_ptr, self._bias_now.data, c(1.0 / world))
+            return
         self.native.call(f"keydnn_cuda_adam_step_{_suffix(self.dtype)}", self.flat_p.dev_ptr, self.flat_g.dev_ptr,
                          self.flat_m.dev_ptr, self.flat_v.dev_ptr, self.n, c(self.lr), c(b1), c(b2), c(self.eps),
                          c(self.weight_decay), c(1.0 - b1), c(1.0 - b2), c(1.0 - b1 ** self.t), c(1.0 - b2 ** self.t),

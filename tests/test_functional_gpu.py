@@ -178,3 +178,43 @@ def test_flat_buffer_adam_equals_the_per_parameter_one(golden):
     t = Tensor.from_numpy(rng.standard_normal((3, 2)).astype(np.float32))
     with pytest.raises(TypeError):
         nn.GraphedTrainStep(model, nn.Adam(model.parameters()), x, t)
+
+
+def test_adam_with_the_step_count_on_the_device_same_bits_and_recordable(golden):
+    """device_step=True: the bias corrections come from a table indexed by a device counter; same bits as passing
+    them by value, and a training step with it can be recorded in a CUDA graph and replayed."""
+    Tensor, Parameter, _, _ = _mods()
+    from keydnn_v2_b200 import nn
+
+    rng = np.random.default_rng(14)
+    p0 = golden["adam/p0"]
+    a, b = Parameter.from_numpy(p0), Parameter.from_numpy(p0)
+    by_value = nn.Adam([a], lr=1e-2, weight_decay=1e-2)
+    counted = nn.Adam([b], lr=1e-2, weight_decay=1e-2, device_step=True)
+    assert counted.graph_safe and not by_value.graph_safe
+    for k in range(6):
+        g = golden[f"adam/g{k + 1}"] if k < 3 else (rng.standard_normal(p0.shape) * 0.1).astype(np.float32)
+        a.grad, b.grad = Tensor.from_numpy(g), Tensor.from_numpy(g)
+        by_value.step()
+        counted.step()
+        assert_same_bits(b.to_numpy(), a.to_numpy())
+        if k < 3:
+            assert_same_bits(b.to_numpy(), golden[f"adam_wd/p{k + 1}"])
+    # recorded: Linear -> MSE with Adam, replays against eager steps of a twin
+    x = Tensor.from_numpy(rng.standard_normal((32, 12)).astype(np.float32))
+    t = Tensor.from_numpy(rng.standard_normal((32, 3)).astype(np.float32))
+    losses = {}
+    for mode in ("eager", "graph"):
+        np.random.seed(9)
+        model = nn.Linear(12, 3)
+        opt = nn.Adam(model.parameters(), lr=5e-2, device_step=True)
+        if mode == "eager":
+            losses[mode] = [nn.train_step(model, opt, x, t).item() for _ in range(7)]
+        else:
+            g = nn.GraphedTrainStep(model, opt, x, t, warmup=2)
+            try:
+                losses[mode] = [g.run().item() for _ in range(5)]
+            finally:
+                g.close()
+    np.testing.assert_allclose(losses["graph"], losses["eager"][2:7], rtol=1e-5)
+    assert losses["eager"][-1] < losses["eager"][0]
