@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import argparse
 import ctypes
+import gc
 import json
 import os
 import subprocess
@@ -104,6 +105,7 @@ class ClockSampler:
         self.gpu = gpu_index
         self.proc = None
         self.lines: list[str] = []
+        self.first = 0
 
     def start(self) -> None:
         try:
@@ -113,6 +115,10 @@ class ClockSampler:
             threading.Thread(target=self._pump, daemon=True).start()
         except Exception:
             self.proc = None
+
+    def mark(self) -> None:
+        """Samples from here on are the ones reported (all of them if none arrives afterwards)."""
+        self.first = len(self.lines)
 
     def _pump(self) -> None:
         assert self.proc and self.proc.stdout
@@ -129,7 +135,7 @@ class ClockSampler:
             pass
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for ln in (self.lines[self.first:] or self.lines):
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 6:
                 continue
@@ -415,13 +421,20 @@ def run_ours(args) -> None:
         print("once: every kernel launched one time", flush=True)
         return
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
+    # the clock sampler (one nvidia-smi process) is started before the warm-up: its start-up talks to the driver
+    # for tens of ms and must not fall into the K timed steps; its samples are kept from the end of the warm-up on
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler.mark()
     launches[0] = 0
+    # the host only enqueues; a cyclic-collector pass of the interpreter (tens of ms once torch is imported at N > 1)
+    # inside K steps of ~1 ms would starve the GPU, so the collector is paused for the timed regions
+    gc.collect()
+    gc.disable()
     timer.start()
     for _ in range(args.steps):
         step()
@@ -479,6 +492,7 @@ def run_ours(args) -> None:
 
     e2e_step()
     barrier()
+    gc.collect()
     e2e_steps = max(2, min(args.steps, 5))
     t0 = time.perf_counter()
     timer.start()
@@ -595,6 +609,8 @@ def cnn_step_bench(lib, group, dist, steps: int, warmup: int, timer, batch: int 
     for _ in range(3):
         loss = run_step()
     sync()
+    gc.collect()
+    gc.disable()            # see run_ours: no collector pass inside the timed steps
     timer.start()
     for _ in range(steps):
         loss = run_step()
