@@ -380,6 +380,10 @@ def run_ours(args) -> None:
             dist.destroy_process_group()
         return
 
+    # everything below runs on a created stream (the legacy default stream cannot be recorded into a graph)
+    work_stream = ctypes.c_uint64(0)
+    lib.call("keydnn_cuda_stream_create", ctypes.byref(work_stream))
+    lib.call("keydnn_cuda_set_stream", work_stream.value)
     rng = np.random.default_rng(1 + rank)
     T = kd.Tensor
     h32 = rng.standard_normal((ROWS32, COLS32), dtype=np.float32)
@@ -429,6 +433,37 @@ def run_ours(args) -> None:
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    # At N > 1 the step (kernels, the second stream's collectives, the events between them) is recorded once and
+    # replayed with one launch per step: the ranks meet in four collectives per step, so a rank whose host thread
+    # is late with its ~120 enqueue calls holds all of them up; a replay takes the host out of the loop.
+    # (At N = 1 nothing waits on another process and the eager enqueue is far ahead of the GPU.)
+    run_step, stepping, step_graph = step, "eager", ctypes.c_uint64(0)
+    if world > 1:
+        try:
+            lib.call("keydnn_cuda_graph_capture_begin")
+            try:
+                step()
+            finally:
+                lib.call("keydnn_cuda_graph_capture_end", ctypes.byref(step_graph))
+            per_step = 2 * len(OPS) * len(reducers)
+
+            def run_step() -> None:
+                lib.call("keydnn_cuda_graph_launch", step_graph.value)
+                launches[0] += per_step
+
+            stepping = "cuda graph replay"
+            for _ in range(2):
+                run_step()
+        except Exception as exc:  # noqa: BLE001
+            run_step, stepping = step, f"eager (graph capture failed: {type(exc).__name__})"
+        flags = [stepping]
+        if dist is not None:
+            gathered = [None] * world
+            dist.all_gather_object(gathered, stepping)
+            flags = gathered
+        if any(f != "cuda graph replay" for f in flags):        # all ranks replay, or none does
+            run_step, stepping = step, "eager"
+        barrier()
     sampler.mark()
     launches[0] = 0
     # the host only enqueues; a cyclic-collector pass of the interpreter (tens of ms once torch is imported at N > 1)
@@ -437,10 +472,12 @@ def run_ours(args) -> None:
     gc.disable()
     timer.start()
     for _ in range(args.steps):
-        step()
+        run_step()
     ms = timer.stop_ms()
     barrier()
     n_launch = launches[0]
+    if step_graph.value:
+        lib.call("keydnn_cuda_graph_destroy", step_graph.value)
 
     # ---- end to end: pinned host inputs in, results out, through the public Tensor API ----
     def pinned_like(a: np.ndarray) -> np.ndarray:
@@ -529,7 +566,9 @@ def run_ours(args) -> None:
             "config": {"workload": "configs[1]: sum/mean/max over axis 0, axis 1, all axes, fwd + bwd (grad of ones), "
                                    "fp32 (8192,8192) N(0,1) + fp64 (4096,4096) N(0,1) per GPU, rows sharded across GPUs",
                        "l2": "inputs larger than L2 (268 MB and 134 MB vs 126 MB); no flush",
-                       "collectives": "none" if world == 1 else "NCCL all-reduce / all-gather of axis-0 and all-axes partials"},
+                       "collectives": "none" if world == 1 else "NCCL all-reduce / all-gather of axis-0 and all-axes partials, "
+                                                                 "one bucket of each per matrix and step",
+                       "stepping": stepping},
             "e2e": {"value": round(e2e_val, 1), "unit": "GB/s", "h2d_bytes_per_step": int(p32.nbytes + p64.nbytes),
                     "d2h_bytes_per_step": int(d2h[0]), "steps": e2e_steps},
             "gpu_launches": n_launch, "clocks": clocks,
