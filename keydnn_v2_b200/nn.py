@@ -321,6 +321,16 @@ class _FlatOptimizer:
             self.group.allreduce_sum(self.flat_g.dev_ptr, self.n, _suffix(self.dtype))
         return world
 
+    def _segments(self):
+        """(element offset, element count) pieces to update: the whole buffer when every parameter has a gradient;
+        otherwise one piece per parameter that has one - a parameter without a gradient is skipped entirely, weight
+        decay and state included, as the reference optimizers do (``optimizers/_sgd.py:127-129``, ``_adam.py:172-175``).
+        With a process group every rank must see the same parameters without gradients."""
+        if all(p.grad is not None for p in self.params):
+            return [(0, self.n)]
+        isz = self.dtype.itemsize
+        return [(o // isz, p.numel) for p, o in zip(self.params, self.offsets) if p.grad is not None]
+
 
 class SGD(_FlatOptimizer):
     """Stochastic gradient descent with coupled L2 weight decay (``optimizers/_sgd.py:119-140``) and
@@ -340,10 +350,12 @@ class SGD(_FlatOptimizer):
 
     def step(self) -> None:
         world = self._gather_grads()
-        self.native.call(f"keydnn_cuda_sgd_momentum_step_{_suffix(self.dtype)}", self.flat_p.dev_ptr, self.flat_g.dev_ptr,
-                         self.flat_v.dev_ptr if self.flat_v else None, self.n, _cfloat(self.dtype, self.lr),
-                         _cfloat(self.dtype, self.momentum), _cfloat(self.dtype, self.weight_decay),
-                         _cfloat(self.dtype, 1.0 / world))
+        isz = self.dtype.itemsize
+        for off, count in self._segments():
+            self.native.call(f"keydnn_cuda_sgd_momentum_step_{_suffix(self.dtype)}", self.flat_p.dev_ptr + off * isz,
+                             self.flat_g.dev_ptr + off * isz, self.flat_v.dev_ptr + off * isz if self.flat_v else None, count,
+                             _cfloat(self.dtype, self.lr), _cfloat(self.dtype, self.momentum),
+                             _cfloat(self.dtype, self.weight_decay), _cfloat(self.dtype, 1.0 / world))
 
 
 class Adam(_FlatOptimizer):
@@ -399,15 +411,20 @@ class Adam(_FlatOptimizer):
         b1, b2 = self.betas
         c = lambda v: _cfloat(self.dtype, v)   # noqa: E731
         if self._table is not None:
+            if any(p.grad is None for p in self.params):
+                raise RuntimeError("Adam(device_step=True) shares one device-side step count: every parameter needs a gradient")
             self.native.call(f"keydnn_cuda_adam_step_counted_{_suffix(self.dtype)}", self.flat_p.dev_ptr, self.flat_g.dev_ptr,
                              self.flat_m.dev_ptr, self.flat_v.dev_ptr, self.n, c(self.lr), c(b1), c(b2), c(self.eps),
                              c(self.weight_decay), c(1.0 - b1), c(1.0 - b2), self._table.data, self._table_len,
                              self._count.dev_ptr, self._bias_now.data, c(1.0 / world))
             return
-        self.native.call(f"keydnn_cuda_adam_step_{_suffix(self.dtype)}", self.flat_p.dev_ptr, self.flat_g.dev_ptr,
-                         self.flat_m.dev_ptr, self.flat_v.dev_ptr, self.n, c(self.lr), c(b1), c(b2), c(self.eps),
-                         c(self.weight_decay), c(1.0 - b1), c(1.0 - b2), c(1.0 - b1 ** self.t), c(1.0 - b2 ** self.t),
-                         c(1.0 / world))
+        isz = self.dtype.itemsize
+        for off, count in self._segments():
+            b = off * isz
+            self.native.call(f"keydnn_cuda_adam_step_{_suffix(self.dtype)}", self.flat_p.dev_ptr + b, self.flat_g.dev_ptr + b,
+                             self.flat_m.dev_ptr + b, self.flat_v.dev_ptr + b, count, c(self.lr), c(b1), c(b2), c(self.eps),
+                             c(self.weight_decay), c(1.0 - b1), c(1.0 - b2), c(1.0 - b1 ** self.t), c(1.0 - b2 ** self.t),
+                             c(1.0 / world))
 
 
 def small_cnn(dtype=np.float32) -> Sequential:

@@ -25,6 +25,11 @@ GEOMS = [
     (1, 3, 8, 9, (3, 2), (1, 2), (1, 0)),        # rectangular, overlapping rows
     (1, 2, 10, 10, (2, 2), (3, 3), (0, 0)),      # gaps between windows
     (3, 1, 5, 5, (5, 5), (1, 1), (2, 2)),        # window as large as the plane
+    # the reference's own shape matrix (tests/infrastructure/pool2d/test_pool2d_stride_padding_shape_matrix.py)
+    (2, 3, 8, 8, (2, 2), (2, 2), (0, 0)),
+    (1, 1, 7, 6, (3, 2), (1, 2), (1, 0)),
+    (1, 4, 9, 5, (2, 3), (2, 1), (0, 1)),
+    (1, 2, 5, 5, (3, 3), (1, 1), (1, 1)),
 ]
 
 
@@ -232,3 +237,23 @@ def test_same_results_as_reference_cuda_kernels(oracle):
     assert_same_bits(g0, g1)
     assert_same_bits(a0, a1)
     np.testing.assert_allclose(p0, p1, rtol=1e-5, atol=1e-6)
+
+
+def test_maxpool_padding_never_wins_and_gradient_stays_in_bounds():
+    """The reference's padding trap (tests/infrastructure/pool2d/test_maxpool2d_padding_trap.py): strictly negative
+    input, windows that reach into the padding; padding must behave as -inf, so every output is a real (negative)
+    input and every upstream gradient lands on a real input."""
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import pooling
+
+    x = np.array([[[[-1.0, -2.0], [-3.0, -4.0]]]], dtype=np.float32)
+    tx = kd.Tensor.from_numpy(x, requires_grad=True)
+    y = pooling.MaxPool2d(kernel_size=(2, 2), stride=(1, 1), padding=(1, 1))(tx)
+    assert y.shape == (1, 1, 3, 3)
+    yv = y.to_numpy()
+    assert (yv < 0).all(), yv
+    np.testing.assert_array_equal(yv[0, 0], [[-1, -1, -2], [-1, -1, -2], [-3, -3, -4]])
+    y.backward(kd.Tensor.ones(y.shape))
+    gx = tx.grad.to_numpy()
+    assert np.isfinite(gx).all() and gx.sum() == 9.0
+    np.testing.assert_array_equal(gx[0, 0], [[4, 2], [2, 1]])
