@@ -330,6 +330,27 @@ int keydnn_cuda_bn2d_backward_bias_f64(const double* x, const double* pre_bias, 
                                        double* grad_x, double* grad_gamma, double* grad_beta, int N, int C, int64_t HW,
                                        int relu);
 
+/* BatchNorm2d (+ ReLU) followed by MaxPool2d(2): forward writes only the pooled tensor and its int64 positions
+ * (h * W + w, as keydnn_cuda_maxpool2d_forward_ex_* records them); backward takes the gradient of the pooled tensor
+ * and derives each element's gradient on the fly.  Same bits as the separate entries; the (N, C, H, W) activation
+ * and its gradient are never stored.  H even, W a multiple of 8, else -6 (use the separate entries). */
+int keydnn_cuda_bn2d_maxpool2x2_forward_f32(const float* x, const float* pre_bias, const float* gamma, const float* beta,
+                                            float* y_pool, int64_t* argmax_idx, float* mean, float* invstd,
+                                            float* running_mean, float* running_var, int N, int C, int H, int W,
+                                            float eps, float momentum, int training, int relu);
+int keydnn_cuda_bn2d_maxpool2x2_forward_f64(const double* x, const double* pre_bias, const double* gamma,
+                                            const double* beta, double* y_pool, int64_t* argmax_idx, double* mean,
+                                            double* invstd, double* running_mean, double* running_var, int N, int C,
+                                            int H, int W, double eps, double momentum, int training, int relu);
+int keydnn_cuda_bn2d_maxpool2x2_backward_f32(const float* x, const float* pre_bias, const float* gamma, const float* beta,
+                                             const float* grad_pool, const int64_t* argmax_idx, const float* mean,
+                                             const float* invstd, float* grad_x, float* grad_gamma, float* grad_beta,
+                                             int N, int C, int H, int W, int relu);
+int keydnn_cuda_bn2d_maxpool2x2_backward_f64(const double* x, const double* pre_bias, const double* gamma,
+                                             const double* beta, const double* grad_pool, const int64_t* argmax_idx,
+                                             const double* mean, const double* invstd, double* grad_x,
+                                             double* grad_gamma, double* grad_beta, int N, int C, int H, int W, int relu);
+
 /* ------------------------------------------------------------------------- */
 /* exp / log / sqrt, activations, losses, Adam.                                 */
 /* ref: NC/keydnn_cuda_ops.hpp (keydnn_cuda_exp_*; kernel keydnn_cuda_exp.cu:5-40) is the only unary

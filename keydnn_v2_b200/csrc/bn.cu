@@ -39,12 +39,34 @@ __device__ __forceinline__ bool bn_take_ticket(unsigned int* counter, unsigned i
 // upstream gradient is first multiplied by that mask, which is recomputed from x here.
 template <typename T> __device__ __forceinline__ T relu_mask(T z) { return z > T(0) ? T(1) : T(0); }
 
+// Gradient of four neighbouring elements (e .. e+3 of one input row, e % 4 == 0) of a plane that went through a
+// 2x2 / stride 2 max pooling: the pooled gradient where the recorded position says so, zero elsewhere - exactly
+// the values the separate pooling backward writes (`0 + go`: it accumulates onto a zeroed buffer).  `pool_go` /
+// `pool_idx` are the (H/2, W/2) planes of this (n, c); positions are h * W + w.
+template <typename T>
+__device__ __forceinline__ Pack4<T> pooled_grad4(const T* __restrict__ pool_go, const long long* __restrict__ pool_idx,
+                                                 int64_t pooled_plane_base, unsigned e, kd::FastDiv by_w) {
+    const unsigned h = by_w.div(e), w0 = e - h * by_w.d;
+    const int64_t at = pooled_plane_base + static_cast<int64_t>(h >> 1) * (by_w.d >> 1) + (w0 >> 1);
+    const T g0 = __ldg(pool_go + at), g1 = __ldg(pool_go + at + 1);
+    const long long i0 = __ldg(pool_idx + at), i1 = __ldg(pool_idx + at + 1);
+    Pack4<T> r;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const long long want = (k < 2) ? i0 : i1;
+        const T go = (k < 2) ? g0 : g1;
+        r.v[k] = (want == static_cast<long long>(e + k)) ? T(0) + go : T(0);
+    }
+    return r;
+}
+
 template <typename T, int MODE, bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ mean,
                 const T* __restrict__ invstd, const T* __restrict__ gamma, const T* __restrict__ beta,
                 const T* __restrict__ pre_bias, int N, int C, int64_t HW, int ach, double* partials,
-                unsigned int* counters, double* sums /* [2][C] */) {
+                unsigned int* counters, double* sums /* [2][C] */, const long long* __restrict__ pool_idx,
+                kd::FastDiv by_w) {
     kd::pdl_prologue();
     __shared__ double sm[kWarps];
     const int c = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
@@ -74,7 +96,9 @@ bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __res
                         else { p0 += vx.v[k]; q0 += vx.v[k] * vx.v[k]; }
                     }
                 } else {
-                    const Pack4<T> vg = kd::load4_stream(g + base + 4 * p);
+                    const Pack4<T> vg = pool_idx ? pooled_grad4<T>(g, pool_idx, (static_cast<int64_t>(n) * C + c) * (HW >> 2),
+                                                                   static_cast<unsigned>(4 * p), by_w)
+                                                 : kd::load4_stream(g + base + 4 * p);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const T xh = (vx.v[k] - mu) * is;
@@ -189,13 +213,90 @@ bn_apply_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __re
     }
 }
 
+// BatchNorm apply (+ ReLU) and the 2x2 / stride 2 max pooling that follows it, in one pass: the normalised
+// activation is never written.  A thread owns four adjacent windows of one output row: two rows of eight inputs
+// come in as 32-byte loads, each is normalised exactly as bn_apply_fwd does, and the four maxima leave with
+// their int64 positions (h * W + w; strict `>` from -inf in (0,0), (0,1), (1,0), (1,1) order, as the pooling
+// kernel scans).  Needs H even, W % 8 == 0.
+template <typename T, int U, bool RELU>
+__global__ void __launch_bounds__(kThreads)
+bn_relu_maxpool2x2_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                       const T* __restrict__ mean, const T* __restrict__ invstd, const T* __restrict__ pre_bias,
+                       T* __restrict__ y, long long* __restrict__ idx, int H, int W, int Wo, int64_t groups,
+                       kd::FastDiv by_gpr, kd::FastDiv by_ho, kd::FastDiv by_c) {
+    kd::pdl_prologue();
+    const bool affine = gamma != nullptr, biased = pre_bias != nullptr;
+    const int64_t tile = static_cast<int64_t>(kThreads) * U;
+    for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < groups;
+         base += static_cast<int64_t>(gridDim.x) * tile) {
+        kd::Row8<T> top8[U], bot8[U];
+        int64_t row[U];
+        int jg[U], i2[U], ch[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t gi = base + u * kThreads + threadIdx.x;
+            if (gi < groups) {
+                unsigned rw, j4, nc, i, n_;
+                by_gpr.divmod(static_cast<unsigned>(gi), rw, j4);
+                by_ho.divmod(rw, nc, i);
+                n_ = by_c.div(nc);
+                row[u] = rw;
+                jg[u] = static_cast<int>(j4);
+                i2[u] = 2 * static_cast<int>(i);
+                ch[u] = static_cast<int>(nc - n_ * by_c.d);
+                const T* r0 = x + (static_cast<int64_t>(nc) * H + i2[u]) * W + 8 * jg[u];
+                top8[u] = kd::load8_stream(r0);
+                bot8[u] = kd::load8_stream(r0 + W);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t gi = base + u * kThreads + threadIdx.x;
+            if (gi < groups) {
+                const int c = ch[u];
+                const T mu = __ldg(mean + c), is = __ldg(invstd + c);
+                const T ga = affine ? __ldg(gamma + c) : T(1), be = affine ? __ldg(beta + c) : T(0);
+                const T pb = biased ? __ldg(pre_bias + c) : T(0);
+                T top[8], bot[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const T a = biased ? top8[u].v[k] + pb : top8[u].v[k];
+                    const T b = biased ? bot8[u].v[k] + pb : bot8[u].v[k];
+                    const T xa = (a - mu) * is, xb = (b - mu) * is;
+                    const T za = affine ? ga * xa + be : xa, zb = affine ? ga * xb + be : xb;
+                    top[k] = RELU ? za * relu_mask<T>(za) : za;
+                    bot[k] = RELU ? zb * relu_mask<T>(zb) : zb;
+                }
+                Pack4<T> out;
+                Pack4<long long> pos;
+                const long long origin = static_cast<long long>(i2[u]) * W + 8 * jg[u];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    T best = -std::numeric_limits<T>::infinity();
+                    long long off = 0;
+                    if (top[2 * q] > best) { best = top[2 * q]; off = 0; }
+                    if (top[2 * q + 1] > best) { best = top[2 * q + 1]; off = 1; }
+                    if (bot[2 * q] > best) { best = bot[2 * q]; off = W; }
+                    if (bot[2 * q + 1] > best) { best = bot[2 * q + 1]; off = W + 1; }
+                    out.v[q] = best;
+                    pos.v[q] = origin + 2 * q + off;
+                }
+                const int64_t o = row[u] * Wo + 4 * jg[u];
+                kd::store4(y + o, out);
+                kd::store4(idx + o, pos);
+            }
+        }
+    }
+}
+
 // dx = (1/m) * inv_std * (m*dxhat - sum_dxhat - x_hat * sum_dxhat_xhat), dxhat = g * gamma;
 // sums[c] = sum g, sums[C + c] = sum g * x_hat (so sum_dxhat = gamma * sums[c], ...).
 template <typename T, bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ gamma, const T* __restrict__ beta,
              const T* __restrict__ mean, const T* __restrict__ invstd, const T* __restrict__ pre_bias,
-             const double* __restrict__ sums, T* __restrict__ dx, int64_t rows, int C, int64_t HW, T m) {
+             const double* __restrict__ sums, T* __restrict__ dx, int64_t rows, int C, int64_t HW, T m,
+             const long long* __restrict__ pool_idx, kd::FastDiv by_w) {
     kd::pdl_prologue();
     const bool biased = pre_bias != nullptr;
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -215,7 +316,8 @@ bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restri
             for (int64_t p = static_cast<int64_t>(blockIdx.y) * kThreads + threadIdx.x; p < b4;
                  p += static_cast<int64_t>(gridDim.y) * kThreads) {
                 const Pack4<T> vx = kd::load4_stream(xs + 4 * p);
-                const Pack4<T> vg = kd::load4_stream(gs + 4 * p);
+                const Pack4<T> vg = pool_idx ? pooled_grad4<T>(g, pool_idx, r * (HW >> 2), static_cast<unsigned>(4 * p), by_w)
+                                             : kd::load4_stream(gs + 4 * p);
                 Pack4<T> out;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
@@ -294,8 +396,8 @@ int bn_forward(const T* x, const T* gamma, const T* beta, T* y, T* mean, T* invs
         SumsPlan p;
         if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
         dim3 grid(C, p.nslices);
-        if (vec) (void)kd::launch(bn_channel_sums<T, 0, true, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums);
-        else (void)kd::launch(bn_channel_sums<T, 0, false, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums);
+        if (vec) (void)kd::launch(bn_channel_sums<T, 0, true, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, nullptr, kd::FastDiv());
+        else (void)kd::launch(bn_channel_sums<T, 0, false, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, nullptr, kd::FastDiv());
         (void)kd::launch(bn_finalize_stats<T>, dim3((C + 127) / 128), 128, 0, p.sums, C, static_cast<double>(N) * static_cast<double>(HW), eps,
                                                           momentum, mean, static_cast<T*>(nullptr), invstd, running_mean,
                                                           running_var);
@@ -315,18 +417,67 @@ int bn_forward(const T* x, const T* gamma, const T* beta, T* y, T* mean, T* invs
     return kd::launch_status();
 }
 
+// Statistics as bn_forward, then the fused apply + ReLU + pooling kernel.  -6: geometry the fused kernel does not take.
+template <typename T>
+int bn_pool_forward(const T* x, const T* gamma, const T* beta, T* y_pool, long long* idx, T* mean, T* invstd,
+                    T* running_mean, T* running_var, int N, int C, int H, int W, T eps, T momentum, int training, int relu,
+                    const T* pre_bias) {
+    if (!x || !y_pool || !idx || !mean || !invstd) return -1;
+    if (N <= 0 || C <= 0 || H <= 0 || W <= 0) return -2;
+    if ((gamma == nullptr) != (beta == nullptr)) return -3;
+    if (!training && (!running_mean || !running_var)) return -4;
+    const int64_t HW = static_cast<int64_t>(H) * W;
+    const int64_t total = static_cast<int64_t>(N) * C * (HW / 4);
+    if ((H & 1) || (W % 8) || !kd::aligned_row8<T>(x) || !kd::aligned_pack<T>(y_pool) || !kd::aligned_pack<long long>(idx) ||
+        total >= (int64_t(1) << 32))
+        return -6;
+    (void)cudaGetLastError();
+    cudaStream_t s = kd::stream();
+    if (training) {
+        SumsPlan p;
+        if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
+        dim3 grid(C, p.nslices);
+        (void)kd::launch(bn_channel_sums<T, 0, true, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr,
+                         pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, nullptr, kd::FastDiv());
+        (void)kd::launch(bn_finalize_stats<T>, dim3((C + 127) / 128), 128, 0, p.sums, C, static_cast<double>(N) * static_cast<double>(HW),
+                         eps, momentum, mean, static_cast<T*>(nullptr), invstd, running_mean, running_var);
+    } else {
+        (void)kd::launch(bn_invstd_from_var<T>, dim3((C + 127) / 128), 128, 0, running_var, C, eps, invstd);
+        cudaMemcpyAsync(mean, running_mean, C * sizeof(T), cudaMemcpyDeviceToDevice, s);
+    }
+    constexpr int U = 2;
+    const int Ho = H / 2, Wo = W / 2;
+    const int64_t groups = total >> 2;
+    const int64_t work = (groups + kThreads * U - 1) / (kThreads * U);
+    if (relu) KD_LAUNCH((bn_relu_maxpool2x2_fwd<T, U, true>), work, kThreads, 0, x, gamma, beta, mean, invstd, pre_bias, y_pool, idx,
+                        H, W, Wo, groups, kd::FastDiv(Wo / 4), kd::FastDiv(Ho), kd::FastDiv(C));
+    else KD_LAUNCH((bn_relu_maxpool2x2_fwd<T, U, false>), work, kThreads, 0, x, gamma, beta, mean, invstd, pre_bias, y_pool, idx,
+                   H, W, Wo, groups, kd::FastDiv(Wo / 4), kd::FastDiv(Ho), kd::FastDiv(C));
+    return kd::launch_status();
+}
+
 template <typename T>
 int bn_backward(const T* x, const T* gamma, const T* beta, const T* go, const T* mean, const T* invstd, T* dx, T* dgamma,
-                T* dbeta, int N, int C, int64_t HW, int relu, const T* pre_bias) {
+                T* dbeta, int N, int C, int64_t HW, int relu, const T* pre_bias, const long long* pool_idx = nullptr,
+                int W = 0) {
     if (!x || !go || !mean || !invstd || !dx) return -1;
     if (N <= 0 || C <= 0 || HW <= 0) return -2;
     (void)cudaGetLastError();
     cudaStream_t s = kd::stream();
-    const bool vec = kd::aligned_pack<T>(x) && kd::aligned_pack<T>(go) && kd::aligned_pack<T>(dx) && (HW % 4 == 0);
+    bool vec = kd::aligned_pack<T>(x) && kd::aligned_pack<T>(dx) && (HW % 4 == 0);
+    kd::FastDiv by_w;
+    if (pool_idx) {
+        // `go` and `pool_idx` are the (H/2, W/2) planes behind a 2x2 / stride 2 max pooling of this layer's output
+        if (W <= 0 || W % 4 != 0 || HW % W != 0 || ((HW / W) & 1) || HW >= (int64_t(1) << 32) || !vec) return -6;
+        if ((reinterpret_cast<uintptr_t>(go) & 7u) || (reinterpret_cast<uintptr_t>(pool_idx) & 15u)) return -6;
+        by_w = kd::FastDiv(static_cast<unsigned>(W));
+    } else {
+        vec = vec && kd::aligned_pack<T>(go);
+    }
     SumsPlan p;
     if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
     dim3 grid(C, p.nslices);
-#define KD_BN_SUMS(V, R) (void)kd::launch(bn_channel_sums<T, 1, V, R>, dim3(grid), kThreads, 0, x, go, mean, invstd, gamma, beta, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums)
+#define KD_BN_SUMS(V, R) (void)kd::launch(bn_channel_sums<T, 1, V, R>, dim3(grid), kThreads, 0, x, go, mean, invstd, gamma, beta, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, pool_idx, by_w)
     if (relu) { if (vec) KD_BN_SUMS(true, true); else KD_BN_SUMS(false, true); }
     else { if (vec) KD_BN_SUMS(true, false); else KD_BN_SUMS(false, false); }
 #undef KD_BN_SUMS
@@ -334,7 +485,7 @@ int bn_backward(const T* x, const T* gamma, const T* beta, const T* go, const T*
     const int64_t rows = static_cast<int64_t>(N) * C;
     const dim3 g2 = row_grid(rows, HW);
     const T m = static_cast<T>(static_cast<double>(N) * static_cast<double>(HW));
-#define KD_BN_APPLY(V, R) (void)kd::launch(bn_apply_bwd<T, V, R>, dim3(g2), kThreads, 0, x, go, gamma, beta, mean, invstd, pre_bias, p.sums, dx, rows, C, HW, m)
+#define KD_BN_APPLY(V, R) (void)kd::launch(bn_apply_bwd<T, V, R>, dim3(g2), kThreads, 0, x, go, gamma, beta, mean, invstd, pre_bias, p.sums, dx, rows, C, HW, m, pool_idx, by_w)
     if (relu) { if (vec) KD_BN_APPLY(true, true); else KD_BN_APPLY(false, true); }
     else { if (vec) KD_BN_APPLY(true, false); else KD_BN_APPLY(false, false); }
 #undef KD_BN_APPLY
@@ -387,3 +538,28 @@ KD_API int keydnn_cuda_bn2d_backward_f64(const double* x, const double* gamma, c
     }
 KD_BN_BIAS_EXPORTS(float, f32)
 KD_BN_BIAS_EXPORTS(double, f64)
+
+// BatchNorm2d (+ ReLU) followed by MaxPool2d(2): forward writes only the pooled tensor and its int64 positions
+// (h * W + w, the pooling kernels' encoding); backward takes the gradient of the pooled tensor and those positions
+// and derives each element's gradient on the fly.  Same bits as the separate layers; the (N, C, H, W) activation and
+// its gradient are never stored.  H even, W a multiple of 8 (else -6: use the separate entries).
+#define KD_BN_POOL_EXPORTS(T, SUF)                                                                                      \
+    KD_API int keydnn_cuda_bn2d_maxpool2x2_forward_##SUF(const T* x, const T* pre_bias, const T* gamma, const T* beta,   \
+                                                         T* y_pool, int64_t* argmax_idx, T* mean, T* invstd,             \
+                                                         T* running_mean, T* running_var, int N, int C, int H, int W,    \
+                                                         T eps, T momentum, int training, int relu) {                    \
+        return bn_pool_forward<T>(x, gamma, beta, y_pool, reinterpret_cast<long long*>(argmax_idx), mean, invstd,        \
+                                  running_mean, running_var, N, C, H, W, eps, momentum, training, relu, pre_bias);       \
+    }                                                                                                                    \
+    KD_API int keydnn_cuda_bn2d_maxpool2x2_backward_##SUF(const T* x, const T* pre_bias, const T* gamma, const T* beta,  \
+                                                          const T* grad_pool, const int64_t* argmax_idx, const T* mean,  \
+                                                          const T* invstd, T* grad_x, T* grad_gamma, T* grad_beta,       \
+                                                          int N, int C, int H, int W, int relu) {                        \
+        if (!argmax_idx) return -1;                                                                                      \
+        if (H <= 0 || W <= 0 || (H & 1)) return -6;                                                                      \
+        return bn_backward<T>(x, gamma, beta, grad_pool, mean, invstd, grad_x, grad_gamma, grad_beta, N, C,              \
+                              static_cast<int64_t>(H) * W, relu, pre_bias,                                               \
+                              reinterpret_cast<const long long*>(argmax_idx), W);                                        \
+    }
+KD_BN_POOL_EXPORTS(float, f32)
+KD_BN_POOL_EXPORTS(double, f64)

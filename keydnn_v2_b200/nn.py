@@ -129,6 +129,7 @@ class BatchNorm2d(Module):
         self.running_var = Tensor.ones((num_features,), dtype)
         self.fused_relu = False     # set by Sequential when a ReLU follows: one kernel pair does both layers
         self.pre_bias = None        # set by Sequential when a Conv2d precedes: its bias, added while x is read
+        self.fused_pool = None      # set by Sequential when a MaxPool2d(2) follows: pooled in the same pass
 
     def parameters(self) -> List[Parameter]:
         return [self.gamma, self.beta] if self.affine else []
@@ -140,10 +141,12 @@ class BatchNorm2d(Module):
         if C != self.num_features:
             raise ValueError(f"Expected num_features={self.num_features}, got C={C}")
         lib, s = x.native, _suffix(x.dtype)
-        y = Tensor.empty(x.shape, x.dtype)
         mean, invstd = Tensor.empty((C,), x.dtype), Tensor.empty((C,), x.dtype)
         ga, be = (self.gamma, self.beta) if self.affine else (None, None)
         pb = self.pre_bias
+        if self.fused_pool is not None and H % 2 == 0 and W % 8 == 0 and N * C * H * W < (1 << 34):
+            return self._forward_pooled(x, mean, invstd, ga, be, pb)
+        y = Tensor.empty(x.shape, x.dtype)
         lib.call(f"keydnn_cuda_bn2d_forward_bias_{s}", x.data, pb.data if pb is not None else None, ga.data if ga else None,
                  be.data if be else None, y.data, mean.data, invstd.data, self.running_mean.data, self.running_var.data,
                  N, C, H * W, _cfloat(x.dtype, self.eps), _cfloat(x.dtype, self.momentum), 1 if self.training else 0,
@@ -158,6 +161,33 @@ class BatchNorm2d(Module):
                 lib.call(f"keydnn_cuda_bn2d_backward_bias_{s}", x.data, pb.data if pb is not None else None,
                          ga.data if ga else None, be.data if be else None, g.data, mean.data, invstd.data, dx.data,
                          dga.data if dga else None, dbe.data if dbe else None, N, C, H * W, 1 if self.fused_relu else 0)
+                return (dx, dga, dbe) if self.affine else (dx,)
+
+            y._ctx = Context((x, ga, be) if self.affine else (x,), backward_fn)
+        return y if self.fused_pool is None else self.fused_pool(y)
+
+    def _forward_pooled(self, x: Tensor, mean: Tensor, invstd: Tensor, ga, be, pb) -> Tensor:
+        """BatchNorm (+ ReLU) and the MaxPool2d(2) behind it in one pass each way: only the pooled tensor and its
+        argmax positions are written; backward derives every element's gradient from them."""
+        N, C, H, W = x.shape
+        lib, s = x.native, _suffix(x.dtype)
+        y = Tensor.empty((N, C, H // 2, W // 2), x.dtype)
+        idx = CudaStorage.allocate(y.numel * 8, np.int64)
+        relu = 1 if self.fused_relu else 0
+        lib.call(f"keydnn_cuda_bn2d_maxpool2x2_forward_{s}", x.data, pb.data if pb is not None else None,
+                 ga.data if ga else None, be.data if be else None, y.data, idx.dev_ptr, mean.data, invstd.data,
+                 self.running_mean.data, self.running_var.data, N, C, H, W, _cfloat(x.dtype, self.eps),
+                 _cfloat(x.dtype, self.momentum), 1 if self.training else 0, relu)
+        if x._needs_grad() or (self.affine and (ga.requires_grad or be.requires_grad)):
+            y.requires_grad = True
+
+            def backward_fn(g: Tensor):
+                dx = Tensor.empty(x.shape, x.dtype)
+                dga = Tensor.empty((C,), x.dtype) if self.affine else None
+                dbe = Tensor.empty((C,), x.dtype) if self.affine else None
+                lib.call(f"keydnn_cuda_bn2d_maxpool2x2_backward_{s}", x.data, pb.data if pb is not None else None,
+                         ga.data if ga else None, be.data if be else None, g.data, idx.dev_ptr, mean.data, invstd.data,
+                         dx.data, dga.data if dga else None, dbe.data if dbe else None, N, C, H, W, relu)
                 return (dx, dga, dbe) if self.affine else (dx,)
 
             y._ctx = Context((x, ga, be) if self.affine else (x,), backward_fn)
@@ -221,8 +251,9 @@ class Sequential(Module):
     """Runs its layers in order (``models/_sequential.py:130-152``).  With ``fuse=True`` (default) a ReLU that
     directly follows a BatchNorm2d is folded into that layer's kernels, and the bias of a Conv2d that directly
     precedes a BatchNorm2d is added by the BatchNorm kernels as they read the activation (the convolution then
-    skips its bias pass).  Results are bit-identical to the separate layers; three tensor passes forward and one
-    backward (ReLU) and a read + write of the activation (bias) disappear."""
+    skips its bias pass), and a MaxPool2d(2) that follows a BatchNorm2d (+ ReLU) is computed by the BatchNorm
+    kernels as well (the normalised activation and its gradient are never stored).  Results are bit-identical to
+    the separate layers."""
 
     def __init__(self, *layers, fuse: bool = True) -> None:
         self.layers = list(layers)
@@ -230,12 +261,21 @@ class Sequential(Module):
         if fuse:
             for i in range(len(self.layers) - 1):
                 a, b = self.layers[i], self.layers[i + 1]
-                if isinstance(a, BatchNorm2d) and isinstance(b, ReLU) and a.gamma is not None and a.gamma.dtype == np.float32:
+                if isinstance(a, BatchNorm2d) and isinstance(b, ReLU) and a.gamma is not None:
                     a.fused_relu = True
                     self._skip.add(i + 1)
                 if isinstance(a, Conv2d) and isinstance(b, BatchNorm2d) and a.bias is not None and a.bias.dtype == b.running_mean.dtype:
                     a.bias_deferred = True
                     b.pre_bias = a.bias
+            for i, a in enumerate(self.layers):
+                j = i + 1
+                while j in self._skip:
+                    j += 1
+                nxt = self.layers[j] if j < len(self.layers) else None
+                if (isinstance(a, BatchNorm2d) and isinstance(nxt, MaxPool2d) and nxt.kernel_size == (2, 2)
+                        and nxt.stride == (2, 2) and nxt.padding == (0, 0)):
+                    a.fused_pool = nxt         # pooled by the BatchNorm kernels; shapes they do not take go through nxt
+                    self._skip.add(j)
 
     def forward(self, x: Tensor) -> Tensor:
         for i, layer in enumerate(self.layers):
