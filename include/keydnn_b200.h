@@ -351,6 +351,26 @@ int keydnn_cuda_bn2d_maxpool2x2_backward_f64(const double* x, const double* pre_
                                              const double* mean, const double* invstd, double* grad_x,
                                              double* grad_gamma, double* grad_beta, int N, int C, int H, int W, int relu);
 
+/* BatchNorm2d (+ ReLU) followed by GlobalAvgPool2d: forward writes only the (N, C) plane means, backward takes their
+ * gradient (every element of plane (n, c) receives grad_mean[n, c] * (1 / HW)).  Same bits as the separate entries.
+ * HW a multiple of 4 and above 64, else -6. */
+int keydnn_cuda_bn2d_global_avgpool_forward_f32(const float* x, const float* pre_bias, const float* gamma,
+                                                const float* beta, float* y_mean, float* mean, float* invstd,
+                                                float* running_mean, float* running_var, int N, int C, int64_t HW,
+                                                float eps, float momentum, int training, int relu);
+int keydnn_cuda_bn2d_global_avgpool_forward_f64(const double* x, const double* pre_bias, const double* gamma,
+                                                const double* beta, double* y_mean, double* mean, double* invstd,
+                                                double* running_mean, double* running_var, int N, int C, int64_t HW,
+                                                double eps, double momentum, int training, int relu);
+int keydnn_cuda_bn2d_global_avgpool_backward_f32(const float* x, const float* pre_bias, const float* gamma,
+                                                 const float* beta, const float* grad_mean, const float* mean,
+                                                 const float* invstd, float* grad_x, float* grad_gamma,
+                                                 float* grad_beta, int N, int C, int64_t HW, int relu);
+int keydnn_cuda_bn2d_global_avgpool_backward_f64(const double* x, const double* pre_bias, const double* gamma,
+                                                 const double* beta, const double* grad_mean, const double* mean,
+                                                 const double* invstd, double* grad_x, double* grad_gamma,
+                                                 double* grad_beta, int N, int C, int64_t HW, int relu);
+
 /* ------------------------------------------------------------------------- */
 /* exp / log / sqrt, activations, losses, Adam.                                 */
 /* ref: NC/keydnn_cuda_ops.hpp (keydnn_cuda_exp_*; kernel keydnn_cuda_exp.cu:5-40) is the only unary

@@ -60,13 +60,38 @@ __device__ __forceinline__ Pack4<T> pooled_grad4(const T* __restrict__ pool_go, 
     return r;
 }
 
+// Where the upstream gradient of the layer output comes from:
+//   0  a dense (N, C, H, W) tensor;
+//   1  the (N, C, H/2, W/2) gradient and positions of a 2x2 / stride 2 max pooling of the output (pooled_grad4);
+//   2  the (N, C) gradient of a global average pooling of the output: every element of plane (n, c) gets
+//      g[n, c] * (1 / HW), the product the pooling backward stores (its reciprocal is rounded first).
+template <typename T>
+struct GradSrc {
+    int mode;
+    const long long* pool_idx;
+    kd::FastDiv by_w;
+    T gap_scale;
+};
+
+template <typename T>
+__device__ __forceinline__ Pack4<T> grad4(const GradSrc<T>& gs, const T* __restrict__ g, int64_t dense_off, int64_t plane,
+                                          int64_t HW, unsigned e) {
+    if (gs.mode == 1) return pooled_grad4<T>(g, gs.pool_idx, plane * (HW >> 2), e, gs.by_w);
+    if (gs.mode == 2) {
+        const T v = __ldg(g + plane) * gs.gap_scale;
+        Pack4<T> r;
+        r.v[0] = r.v[1] = r.v[2] = r.v[3] = v;
+        return r;
+    }
+    return kd::load4_stream(g + dense_off);
+}
+
 template <typename T, int MODE, bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ mean,
                 const T* __restrict__ invstd, const T* __restrict__ gamma, const T* __restrict__ beta,
                 const T* __restrict__ pre_bias, int N, int C, int64_t HW, int ach, double* partials,
-                unsigned int* counters, double* sums /* [2][C] */, const long long* __restrict__ pool_idx,
-                kd::FastDiv by_w) {
+                unsigned int* counters, double* sums /* [2][C] */, GradSrc<T> gsrc) {
     kd::pdl_prologue();
     __shared__ double sm[kWarps];
     const int c = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
@@ -96,9 +121,8 @@ bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __res
                         else { p0 += vx.v[k]; q0 += vx.v[k] * vx.v[k]; }
                     }
                 } else {
-                    const Pack4<T> vg = pool_idx ? pooled_grad4<T>(g, pool_idx, (static_cast<int64_t>(n) * C + c) * (HW >> 2),
-                                                                   static_cast<unsigned>(4 * p), by_w)
-                                                 : kd::load4_stream(g + base + 4 * p);
+                    const Pack4<T> vg = grad4<T>(gsrc, g, base + 4 * p, static_cast<int64_t>(n) * C + c, HW,
+                                                 static_cast<unsigned>(4 * p));
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const T xh = (vx.v[k] - mu) * is;
@@ -289,14 +313,50 @@ bn_relu_maxpool2x2_fwd(const T* __restrict__ x, const T* __restrict__ gamma, con
     }
 }
 
+// BatchNorm apply (+ ReLU) and the global average pooling that follows it, in one pass: a warp owns a plane, every
+// lane normalises its packets as bn_apply_fwd does and adds them up exactly as the pooling kernel for long planes
+// does (four running sums per lane in T, combined in double, a shuffle tree, one division by HW), so the mean has
+// the bits of the two separate layers and the normalised activation is never written.  HW % 4 == 0, HW > 64.
+template <typename T, bool RELU>
+__global__ void __launch_bounds__(kThreads)
+bn_relu_gap_fwd(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                const T* __restrict__ mean, const T* __restrict__ invstd, const T* __restrict__ pre_bias,
+                T* __restrict__ y, int64_t rows, int C, int L) {
+    kd::pdl_prologue();
+    const bool affine = gamma != nullptr, biased = pre_bias != nullptr;
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5); r < rows; r += nwarps) {
+        const int c = static_cast<int>(r % C);
+        const T mu = __ldg(mean + c), is = __ldg(invstd + c);
+        const T ga = affine ? __ldg(gamma + c) : T(1), be = affine ? __ldg(beta + c) : T(0);
+        const T pb = biased ? __ldg(pre_bias + c) : T(0);
+        const T* src = x + r * L;
+        T s[4] = {T(0), T(0), T(0), T(0)};
+        const int c4 = L >> 2;
+        for (int p = lane; p < c4; p += 32) {
+            const Pack4<T> v = kd::load4_stream(src + 4 * p);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const T xv = biased ? v.v[k] + pb : v.v[k];
+                const T xh = (xv - mu) * is;
+                const T z = affine ? ga * xh + be : xh;
+                s[k] += RELU ? z * relu_mask<T>(z) : z;
+            }
+        }
+        double t = (static_cast<double>(s[0]) + static_cast<double>(s[1])) + (static_cast<double>(s[2]) + static_cast<double>(s[3]));
+        t = kd::warp_sum(t);
+        if (lane == 0) y[r] = static_cast<T>(t) / static_cast<T>(L);
+    }
+}
+
 // dx = (1/m) * inv_std * (m*dxhat - sum_dxhat - x_hat * sum_dxhat_xhat), dxhat = g * gamma;
 // sums[c] = sum g, sums[C + c] = sum g * x_hat (so sum_dxhat = gamma * sums[c], ...).
 template <typename T, bool VEC, bool RELU>
 __global__ void __launch_bounds__(kThreads)
 bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ gamma, const T* __restrict__ beta,
              const T* __restrict__ mean, const T* __restrict__ invstd, const T* __restrict__ pre_bias,
-             const double* __restrict__ sums, T* __restrict__ dx, int64_t rows, int C, int64_t HW, T m,
-             const long long* __restrict__ pool_idx, kd::FastDiv by_w) {
+             const double* __restrict__ sums, T* __restrict__ dx, int64_t rows, int C, int64_t HW, T m, GradSrc<T> gsrc) {
     kd::pdl_prologue();
     const bool biased = pre_bias != nullptr;
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -316,8 +376,7 @@ bn_apply_bwd(const T* __restrict__ x, const T* __restrict__ g, const T* __restri
             for (int64_t p = static_cast<int64_t>(blockIdx.y) * kThreads + threadIdx.x; p < b4;
                  p += static_cast<int64_t>(gridDim.y) * kThreads) {
                 const Pack4<T> vx = kd::load4_stream(xs + 4 * p);
-                const Pack4<T> vg = pool_idx ? pooled_grad4<T>(g, pool_idx, r * (HW >> 2), static_cast<unsigned>(4 * p), by_w)
-                                             : kd::load4_stream(gs + 4 * p);
+                const Pack4<T> vg = grad4<T>(gsrc, g, r * HW + 4 * p, r, HW, static_cast<unsigned>(4 * p));
                 Pack4<T> out;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
@@ -396,8 +455,8 @@ int bn_forward(const T* x, const T* gamma, const T* beta, T* y, T* mean, T* invs
         SumsPlan p;
         if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
         dim3 grid(C, p.nslices);
-        if (vec) (void)kd::launch(bn_channel_sums<T, 0, true, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, nullptr, kd::FastDiv());
-        else (void)kd::launch(bn_channel_sums<T, 0, false, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, nullptr, kd::FastDiv());
+        if (vec) (void)kd::launch(bn_channel_sums<T, 0, true, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, GradSrc<T>{0, nullptr, kd::FastDiv(), T(0)});
+        else (void)kd::launch(bn_channel_sums<T, 0, false, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, GradSrc<T>{0, nullptr, kd::FastDiv(), T(0)});
         (void)kd::launch(bn_finalize_stats<T>, dim3((C + 127) / 128), 128, 0, p.sums, C, static_cast<double>(N) * static_cast<double>(HW), eps,
                                                           momentum, mean, static_cast<T*>(nullptr), invstd, running_mean,
                                                           running_var);
@@ -438,7 +497,7 @@ int bn_pool_forward(const T* x, const T* gamma, const T* beta, T* y_pool, long l
         if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
         dim3 grid(C, p.nslices);
         (void)kd::launch(bn_channel_sums<T, 0, true, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr,
-                         pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, nullptr, kd::FastDiv());
+                         pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, GradSrc<T>{0, nullptr, kd::FastDiv(), T(0)});
         (void)kd::launch(bn_finalize_stats<T>, dim3((C + 127) / 128), 128, 0, p.sums, C, static_cast<double>(N) * static_cast<double>(HW),
                          eps, momentum, mean, static_cast<T*>(nullptr), invstd, running_mean, running_var);
     } else {
@@ -456,10 +515,42 @@ int bn_pool_forward(const T* x, const T* gamma, const T* beta, T* y_pool, long l
     return kd::launch_status();
 }
 
+// Statistics as bn_forward, then the fused apply + ReLU + global average pooling kernel.
+template <typename T>
+int bn_gap_forward(const T* x, const T* gamma, const T* beta, T* y_gap, T* mean, T* invstd, T* running_mean, T* running_var,
+                   int N, int C, int64_t HW, T eps, T momentum, int training, int relu, const T* pre_bias) {
+    if (!x || !y_gap || !mean || !invstd) return -1;
+    if (N <= 0 || C <= 0 || HW <= 0) return -2;
+    if ((gamma == nullptr) != (beta == nullptr)) return -3;
+    if (!training && (!running_mean || !running_var)) return -4;
+    if (HW % 4 != 0 || HW <= 64 || HW > std::numeric_limits<int>::max() || !kd::aligned_pack<T>(x)) return -6;
+    (void)cudaGetLastError();
+    cudaStream_t s = kd::stream();
+    if (training) {
+        SumsPlan p;
+        if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
+        dim3 grid(C, p.nslices);
+        (void)kd::launch(bn_channel_sums<T, 0, true, false>, dim3(grid), kThreads, 0, x, nullptr, nullptr, nullptr, nullptr, nullptr,
+                         pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, GradSrc<T>{0, nullptr, kd::FastDiv(), T(0)});
+        (void)kd::launch(bn_finalize_stats<T>, dim3((C + 127) / 128), 128, 0, p.sums, C, static_cast<double>(N) * static_cast<double>(HW),
+                         eps, momentum, mean, static_cast<T*>(nullptr), invstd, running_mean, running_var);
+    } else {
+        (void)kd::launch(bn_invstd_from_var<T>, dim3((C + 127) / 128), 128, 0, running_var, C, eps, invstd);
+        cudaMemcpyAsync(mean, running_mean, C * sizeof(T), cudaMemcpyDeviceToDevice, s);
+    }
+    const int64_t rows = static_cast<int64_t>(N) * C;
+    const unsigned grid = kd::grid_for((rows + 7) / 8, 8);
+    if (relu) (void)kd::launch(bn_relu_gap_fwd<T, true>, dim3(grid), kThreads, 0, x, gamma, beta, mean, invstd, pre_bias, y_gap, rows, C,
+                               static_cast<int>(HW));
+    else (void)kd::launch(bn_relu_gap_fwd<T, false>, dim3(grid), kThreads, 0, x, gamma, beta, mean, invstd, pre_bias, y_gap, rows, C,
+                          static_cast<int>(HW));
+    return kd::launch_status();
+}
+
 template <typename T>
 int bn_backward(const T* x, const T* gamma, const T* beta, const T* go, const T* mean, const T* invstd, T* dx, T* dgamma,
                 T* dbeta, int N, int C, int64_t HW, int relu, const T* pre_bias, const long long* pool_idx = nullptr,
-                int W = 0) {
+                int W = 0, bool gap = false) {
     if (!x || !go || !mean || !invstd || !dx) return -1;
     if (N <= 0 || C <= 0 || HW <= 0) return -2;
     (void)cudaGetLastError();
@@ -471,13 +562,16 @@ int bn_backward(const T* x, const T* gamma, const T* beta, const T* go, const T*
         if (W <= 0 || W % 4 != 0 || HW % W != 0 || ((HW / W) & 1) || HW >= (int64_t(1) << 32) || !vec) return -6;
         if ((reinterpret_cast<uintptr_t>(go) & 7u) || (reinterpret_cast<uintptr_t>(pool_idx) & 15u)) return -6;
         by_w = kd::FastDiv(static_cast<unsigned>(W));
+    } else if (gap) {
+        if (!vec || HW >= (int64_t(1) << 32)) return -6;        // `go` is the (N, C) gradient behind a global average pooling
     } else {
         vec = vec && kd::aligned_pack<T>(go);
     }
+    const GradSrc<T> gsrc{pool_idx ? 1 : (gap ? 2 : 0), pool_idx, by_w, T(1) / static_cast<T>(HW)};
     SumsPlan p;
     if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
     dim3 grid(C, p.nslices);
-#define KD_BN_SUMS(V, R) (void)kd::launch(bn_channel_sums<T, 1, V, R>, dim3(grid), kThreads, 0, x, go, mean, invstd, gamma, beta, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, pool_idx, by_w)
+#define KD_BN_SUMS(V, R) (void)kd::launch(bn_channel_sums<T, 1, V, R>, dim3(grid), kThreads, 0, x, go, mean, invstd, gamma, beta, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, gsrc)
     if (relu) { if (vec) KD_BN_SUMS(true, true); else KD_BN_SUMS(false, true); }
     else { if (vec) KD_BN_SUMS(true, false); else KD_BN_SUMS(false, false); }
 #undef KD_BN_SUMS
@@ -485,7 +579,7 @@ int bn_backward(const T* x, const T* gamma, const T* beta, const T* go, const T*
     const int64_t rows = static_cast<int64_t>(N) * C;
     const dim3 g2 = row_grid(rows, HW);
     const T m = static_cast<T>(static_cast<double>(N) * static_cast<double>(HW));
-#define KD_BN_APPLY(V, R) (void)kd::launch(bn_apply_bwd<T, V, R>, dim3(g2), kThreads, 0, x, go, gamma, beta, mean, invstd, pre_bias, p.sums, dx, rows, C, HW, m, pool_idx, by_w)
+#define KD_BN_APPLY(V, R) (void)kd::launch(bn_apply_bwd<T, V, R>, dim3(g2), kThreads, 0, x, go, gamma, beta, mean, invstd, pre_bias, p.sums, dx, rows, C, HW, m, gsrc)
     if (relu) { if (vec) KD_BN_APPLY(true, true); else KD_BN_APPLY(false, true); }
     else { if (vec) KD_BN_APPLY(true, false); else KD_BN_APPLY(false, false); }
 #undef KD_BN_APPLY
@@ -563,3 +657,24 @@ KD_BN_BIAS_EXPORTS(double, f64)
     }
 KD_BN_POOL_EXPORTS(float, f32)
 KD_BN_POOL_EXPORTS(double, f64)
+
+// BatchNorm2d (+ ReLU) followed by GlobalAvgPool2d: forward writes only the (N, C) means, backward takes their
+// gradient; every element of plane (n, c) receives grad[n, c] * (1 / HW) as the pooling backward would have stored it.
+// Same bits as the separate layers.  HW a multiple of 4 and above 64, else -6 (use the separate entries).
+#define KD_BN_GAP_EXPORTS(T, SUF)                                                                                        \
+    KD_API int keydnn_cuda_bn2d_global_avgpool_forward_##SUF(const T* x, const T* pre_bias, const T* gamma, const T* beta, \
+                                                             T* y_mean, T* mean, T* invstd, T* running_mean,              \
+                                                             T* running_var, int N, int C, int64_t HW, T eps, T momentum, \
+                                                             int training, int relu) {                                    \
+        return bn_gap_forward<T>(x, gamma, beta, y_mean, mean, invstd, running_mean, running_var, N, C, HW, eps, momentum, \
+                                 training, relu, pre_bias);                                                               \
+    }                                                                                                                     \
+    KD_API int keydnn_cuda_bn2d_global_avgpool_backward_##SUF(const T* x, const T* pre_bias, const T* gamma,              \
+                                                              const T* beta, const T* grad_mean, const T* mean,           \
+                                                              const T* invstd, T* grad_x, T* grad_gamma, T* grad_beta,    \
+                                                              int N, int C, int64_t HW, int relu) {                       \
+        return bn_backward<T>(x, gamma, beta, grad_mean, mean, invstd, grad_x, grad_gamma, grad_beta, N, C, HW, relu,     \
+                              pre_bias, nullptr, 0, true);                                                                \
+    }
+KD_BN_GAP_EXPORTS(float, f32)
+KD_BN_GAP_EXPORTS(double, f64)

@@ -130,6 +130,7 @@ class BatchNorm2d(Module):
         self.fused_relu = False     # set by Sequential when a ReLU follows: one kernel pair does both layers
         self.pre_bias = None        # set by Sequential when a Conv2d precedes: its bias, added while x is read
         self.fused_pool = None      # set by Sequential when a MaxPool2d(2) follows: pooled in the same pass
+        self.fused_gap = None       # set by Sequential when a GlobalAvgPool2d follows: averaged in the same pass
 
     def parameters(self) -> List[Parameter]:
         return [self.gamma, self.beta] if self.affine else []
@@ -146,6 +147,8 @@ class BatchNorm2d(Module):
         pb = self.pre_bias
         if self.fused_pool is not None and H % 2 == 0 and W % 8 == 0 and N * C * H * W < (1 << 34):
             return self._forward_pooled(x, mean, invstd, ga, be, pb)
+        if self.fused_gap is not None and (H * W) % 4 == 0 and 64 < H * W < (1 << 31):
+            return self._forward_averaged(x, mean, invstd, ga, be, pb)
         y = Tensor.empty(x.shape, x.dtype)
         lib.call(f"keydnn_cuda_bn2d_forward_bias_{s}", x.data, pb.data if pb is not None else None, ga.data if ga else None,
                  be.data if be else None, y.data, mean.data, invstd.data, self.running_mean.data, self.running_var.data,
@@ -164,7 +167,34 @@ class BatchNorm2d(Module):
                 return (dx, dga, dbe) if self.affine else (dx,)
 
             y._ctx = Context((x, ga, be) if self.affine else (x,), backward_fn)
-        return y if self.fused_pool is None else self.fused_pool(y)
+        follow = self.fused_pool or self.fused_gap      # shapes the fused kernels do not take: the layer itself
+        return y if follow is None else follow(y)
+
+    def _forward_averaged(self, x: Tensor, mean: Tensor, invstd: Tensor, ga, be, pb) -> Tensor:
+        """BatchNorm (+ ReLU) and the GlobalAvgPool2d behind it in one pass each way: only the (N, C, 1, 1) means
+        are written; backward spreads their gradient over the planes on the fly."""
+        N, C, H, W = x.shape
+        lib, s = x.native, _suffix(x.dtype)
+        y = Tensor.empty((N, C, 1, 1), x.dtype)
+        relu = 1 if self.fused_relu else 0
+        lib.call(f"keydnn_cuda_bn2d_global_avgpool_forward_{s}", x.data, pb.data if pb is not None else None,
+                 ga.data if ga else None, be.data if be else None, y.data, mean.data, invstd.data,
+                 self.running_mean.data, self.running_var.data, N, C, H * W, _cfloat(x.dtype, self.eps),
+                 _cfloat(x.dtype, self.momentum), 1 if self.training else 0, relu)
+        if x._needs_grad() or (self.affine and (ga.requires_grad or be.requires_grad)):
+            y.requires_grad = True
+
+            def backward_fn(g: Tensor):
+                dx = Tensor.empty(x.shape, x.dtype)
+                dga = Tensor.empty((C,), x.dtype) if self.affine else None
+                dbe = Tensor.empty((C,), x.dtype) if self.affine else None
+                lib.call(f"keydnn_cuda_bn2d_global_avgpool_backward_{s}", x.data, pb.data if pb is not None else None,
+                         ga.data if ga else None, be.data if be else None, g.data, mean.data, invstd.data, dx.data,
+                         dga.data if dga else None, dbe.data if dbe else None, N, C, H * W, relu)
+                return (dx, dga, dbe) if self.affine else (dx,)
+
+            y._ctx = Context((x, ga, be) if self.affine else (x,), backward_fn)
+        return y
 
     def _forward_pooled(self, x: Tensor, mean: Tensor, invstd: Tensor, ga, be, pb) -> Tensor:
         """BatchNorm (+ ReLU) and the MaxPool2d(2) behind it in one pass each way: only the pooled tensor and its
@@ -251,8 +281,8 @@ class Sequential(Module):
     """Runs its layers in order (``models/_sequential.py:130-152``).  With ``fuse=True`` (default) a ReLU that
     directly follows a BatchNorm2d is folded into that layer's kernels, and the bias of a Conv2d that directly
     precedes a BatchNorm2d is added by the BatchNorm kernels as they read the activation (the convolution then
-    skips its bias pass), and a MaxPool2d(2) that follows a BatchNorm2d (+ ReLU) is computed by the BatchNorm
-    kernels as well (the normalised activation and its gradient are never stored).  Results are bit-identical to
+    skips its bias pass), and a MaxPool2d(2) or GlobalAvgPool2d that follows a BatchNorm2d (+ ReLU) is computed by
+    the BatchNorm kernels as well (the normalised activation and its gradient are never stored).  Results are bit-identical to
     the separate layers."""
 
     def __init__(self, *layers, fuse: bool = True) -> None:
@@ -275,6 +305,9 @@ class Sequential(Module):
                 if (isinstance(a, BatchNorm2d) and isinstance(nxt, MaxPool2d) and nxt.kernel_size == (2, 2)
                         and nxt.stride == (2, 2) and nxt.padding == (0, 0)):
                     a.fused_pool = nxt         # pooled by the BatchNorm kernels; shapes they do not take go through nxt
+                    self._skip.add(j)
+                elif isinstance(a, BatchNorm2d) and isinstance(nxt, GlobalAvgPool2d):
+                    a.fused_gap = nxt
                     self._skip.add(j)
 
     def forward(self, x: Tensor) -> Tensor:

@@ -194,6 +194,37 @@ def test_batchnorm_relu_maxpool_in_one_pass_is_bit_identical_to_the_layers(shape
         np.testing.assert_array_equal(a.view(view), b.view(view), err_msg=str(i))
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("shape,relu", [((6, 5, 16, 16), True), ((3, 4, 10, 12), False), ((2, 3, 6, 6), True)])
+def test_batchnorm_relu_global_avgpool_in_one_pass_is_bit_identical_to_the_layers(shape, relu, dtype):
+    """BatchNorm2d (+ ReLU) -> GlobalAvgPool2d computed by the BatchNorm kernels against the separate layers; the
+    last shape (HW <= 64) takes the fallback."""
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import nn
+
+    N, C, H, W = shape
+    rng = np.random.default_rng(H + W)
+    x = rng.standard_normal(shape).astype(dtype)
+    g = rng.standard_normal((N, C, 1, 1)).astype(dtype)
+    outs = []
+    for fuse in (True, False):
+        bn = nn.BatchNorm2d(C, dtype=dtype)
+        bn.gamma.copy_from_numpy(np.linspace(-1.0, 1.5, C).astype(dtype))
+        bn.beta.copy_from_numpy(np.linspace(0.3, -0.3, C).astype(dtype))
+        layers = [bn] + ([nn.ReLU()] if relu else []) + [nn.GlobalAvgPool2d()]
+        seq = nn.Sequential(*layers, fuse=fuse)
+        assert (bn.fused_gap is not None) == fuse
+        tx = kd.Tensor.from_numpy(x, requires_grad=True)
+        y = seq(tx)
+        assert y.shape == (N, C, 1, 1)
+        y.backward(kd.Tensor.from_numpy(g))
+        outs.append((y.to_numpy(), tx.grad.to_numpy(), bn.gamma.grad.to_numpy(), bn.beta.grad.to_numpy(),
+                     bn.running_mean.to_numpy(), bn.running_var.to_numpy()))
+    view = np.uint32 if dtype == np.float32 else np.uint64
+    for i, (a, b) in enumerate(zip(*outs)):
+        np.testing.assert_array_equal(a.view(view), b.view(view), err_msg=str(i))
+
+
 def test_graphed_training_step_follows_the_eager_one():
     """A CUDA-graph replay of the step must train exactly like the eager step sequence."""
     import keydnn_v2_b200 as kd
