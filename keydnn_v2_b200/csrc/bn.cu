@@ -39,6 +39,15 @@ __device__ __forceinline__ bool bn_take_ticket(unsigned int* counter, unsigned i
 // upstream gradient is first multiplied by that mask, which is recomputed from x here.
 template <typename T> __device__ __forceinline__ T relu_mask(T z) { return z > T(0) ? T(1) : T(0); }
 
+__device__ __forceinline__ void load_pair(const float* p, float& a, float& b) {
+    const float2 v = __ldg(reinterpret_cast<const float2*>(p));
+    a = v.x; b = v.y;
+}
+__device__ __forceinline__ void load_pair(const double* p, double& a, double& b) {
+    const double2 v = __ldg(reinterpret_cast<const double2*>(p));
+    a = v.x; b = v.y;
+}
+
 // Gradient of four neighbouring elements (e .. e+3 of one input row, e % 4 == 0) of a plane that went through a
 // 2x2 / stride 2 max pooling: the pooled gradient where the recorded position says so, zero elsewhere - exactly
 // the values the separate pooling backward writes (`0 + go`: it accumulates onto a zeroed buffer).  `pool_go` /
@@ -48,8 +57,11 @@ __device__ __forceinline__ Pack4<T> pooled_grad4(const T* __restrict__ pool_go, 
                                                  int64_t pooled_plane_base, unsigned e, kd::FastDiv by_w) {
     const unsigned h = by_w.div(e), w0 = e - h * by_w.d;
     const int64_t at = pooled_plane_base + static_cast<int64_t>(h >> 1) * (by_w.d >> 1) + (w0 >> 1);
-    const T g0 = __ldg(pool_go + at), g1 = __ldg(pool_go + at + 1);
-    const long long i0 = __ldg(pool_idx + at), i1 = __ldg(pool_idx + at + 1);
+    // `at` is even (w0 % 4 == 0, W % 4 == 0): the two gradients and the two positions come as one access each
+    T g0, g1;
+    load_pair(pool_go + at, g0, g1);
+    const longlong2 ii = __ldg(reinterpret_cast<const longlong2*>(pool_idx + at));
+    const long long i0 = ii.x, i1 = ii.y;
     Pack4<T> r;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -108,6 +120,7 @@ bn_channel_sums(const T* __restrict__ x, const T* __restrict__ g, const T* __res
         T p0 = T(0), p1 = T(0), q0 = T(0), q1 = T(0);      // short per-image partials in T
         if (VEC) {
             const int64_t b4 = HW >> 2;
+#pragma unroll 2
             for (int64_t p = threadIdx.x; p < b4; p += kThreads) {
                 Pack4<T> vx = kd::load4_stream(x + base + 4 * p);
                 if (biased) {
@@ -560,7 +573,7 @@ int bn_backward(const T* x, const T* gamma, const T* beta, const T* go, const T*
     if (pool_idx) {
         // `go` and `pool_idx` are the (H/2, W/2) planes behind a 2x2 / stride 2 max pooling of this layer's output
         if (W <= 0 || W % 4 != 0 || HW % W != 0 || ((HW / W) & 1) || HW >= (int64_t(1) << 32) || !vec) return -6;
-        if ((reinterpret_cast<uintptr_t>(go) & 7u) || (reinterpret_cast<uintptr_t>(pool_idx) & 15u)) return -6;
+        if ((reinterpret_cast<uintptr_t>(go) & (2 * sizeof(T) - 1)) || (reinterpret_cast<uintptr_t>(pool_idx) & 15u)) return -6;
         by_w = kd::FastDiv(static_cast<unsigned>(W));
     } else if (gap) {
         if (!vec || HW >= (int64_t(1) << 32)) return -6;        // `go` is the (N, C) gradient behind a global average pooling
