@@ -48,8 +48,10 @@ inline unsigned grid_for(int64_t work_items, int per_sm) {
 
 // CTAs of `kernel` that one SM holds at once (cached per kernel).
 template <typename K> inline int occupancy(K kernel, int threads, size_t smem = 0) {
-    static std::unordered_map<const void*, int> cache;
-    const void* key = reinterpret_cast<const void*>(kernel);
+    // kernels of one signature share this map: the key is the kernel's address mixed with the launch shape
+    static std::unordered_map<uint64_t, int> cache;
+    const uint64_t key = static_cast<uint64_t>(reinterpret_cast<uintptr_t>(kernel)) * 0x9E3779B97F4A7C15ull ^
+                         (static_cast<uint64_t>(smem) << 12) ^ static_cast<uint64_t>(threads);
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
     int n = 0;
