@@ -46,6 +46,10 @@ int keydnn_cuda_memcpy_h2d_async(uint64_t dst_dev_ptr, const void* src_host_ptr,
 int keydnn_cuda_memcpy_d2h_async(void* dst_host_ptr, uint64_t src_dev_ptr, size_t nbytes);
 int keydnn_cuda_empty_cache(void);
 int keydnn_cuda_pool_stats(uint64_t* out4); /* reserved, in use, driver mallocs, requests */
+/* reduction scratch of the current device: partial bytes, ticket slots, driver allocations made for them,
+ * outgrown buffers parked for a recorded graph */
+int keydnn_cuda_scratch_stats(uint64_t* out4);
+int keydnn_cuda_mem_info(uint64_t* out2);   /* cudaMemGetInfo: free, total */
 int keydnn_cuda_host_alloc(void** out, size_t nbytes); /* pinned host memory */
 int keydnn_cuda_host_free(void* p);
 int keydnn_cuda_get_stream(uint64_t* out);
@@ -172,6 +176,10 @@ int keydnn_cuda_sum_to_shape_f64(const double* x, double* y, const int64_t* in_s
  * (do it outside stream capture).  Calls that overlap on the GPU race on the shared array. */
 #define KEYDNN_NOALLOC_MAX_COLS 65536
 int keydnn_cuda_sum_axis0_noalloc_f32(const float* x, float* y, int rows, int cols);
+/* additive, host-only (no device work): launch shape of the axis-0 reductions for a (rows, cols) matrix of
+ * elem_size-byte elements: out3 = rows per chunk, chunks, column stripes; -2 where the entry points return -2
+ * (row indices are 32-bit in the kernels: chunks * rows-per-chunk must stay below 2^31). */
+int keydnn_cuda_debug_col_chunks(int rows, int cols, int elem_size, int ctas_per_sm, int64_t* out3);
 /* additive: the reference has no axis-wise mean (tensor/mixins/reduction/_tensor_mean.py:91-192
  * is all-elements only), no all-elements max (_tensor_max.py:70-85 is 2-D, axis 0/1), and its max
  * backward needs a zero-fill pass before it (ops/reduce_cuda.py:409-414). */

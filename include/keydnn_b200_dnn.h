@@ -14,8 +14,13 @@
 extern "C" {
 #endif
 
-/* additive: stream the cuBLAS / cuDNN calls are enqueued on (default: legacy default stream) */
+/* additive: the stream of the cuBLAS / cuDNN calls.  bind_stream_source takes the address of
+ * libkeydnn_b200.so's keydnn_cuda_get_stream (int f(uint64_t* out)); from then on every call asks it, so both
+ * libraries always share one stream (the reference has one: the default stream, NC/keydnn_cuda_conv2d.cu:53-61).
+ * set_stream sets an explicit stream and drops a bound source (default: legacy default stream). */
 int keydnn_dnn_set_stream(uint64_t stream);
+int keydnn_dnn_bind_stream_source(uint64_t get_stream_fn);
+int keydnn_dnn_get_stream(uint64_t* out);
 
 /* ref: NC/keydnn_cuda_conv2d.hpp:17-99 (planes already padded by the caller) */
 int keydnn_cuda_conv2d_forward_f32(const float* x_pad, const float* w, const float* b, float* y, int N, int C_in,

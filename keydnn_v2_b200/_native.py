@@ -121,8 +121,16 @@ def _load(path: str) -> Native:
 
 @lru_cache(maxsize=1)
 def load_dnn() -> Native:
-    """The cuBLAS / cuDNN wrapper library (Conv2d, Linear); needs libcudnn / libcublas at load time."""
-    return Native(Path(os.environ.get("KEYDNN_B200_DNN_LIB") or DNN_LIB_PATH), header=DNN_HEADER_PATH)
+    """The cuBLAS / cuDNN wrapper library (Conv2d, Linear); needs libcudnn / libcublas at load time.
+
+    Its calls are enqueued on the operator library's stream: the address of that library's
+    ``keydnn_cuda_get_stream`` is bound here once and asked before every cuDNN / cuBLAS call, so there is
+    one stream state for both libraries (``keydnn_cuda_set_stream`` moves both)."""
+    dnn = Native(Path(os.environ.get("KEYDNN_B200_DNN_LIB") or DNN_LIB_PATH), header=DNN_HEADER_PATH)
+    main = load()
+    getter = ctypes.cast(main.raw("keydnn_cuda_get_stream"), ctypes.c_void_p).value
+    dnn.call("keydnn_dnn_bind_stream_source", getter)
+    return dnn
 
 
 def load(path: str | os.PathLike | None = None) -> Native:

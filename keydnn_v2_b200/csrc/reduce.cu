@@ -735,23 +735,40 @@ int max_rows(const T* x, T* y, long long* idx, int64_t rows, int cols) {
 // what the machine holds at once, so every CTA is resident from the start, all do
 // the same amount of work and there is no partial last wave; partial traffic is
 // nchunks * cols elements (under 1% of the input at the benchmark sizes).
-inline int pick_row_chunk(int rows, int stripes, int ctas_per_sm) {
+// All of this arithmetic is 64-bit: `rows` may be close to 2^31 for a narrow matrix.
+inline int64_t pick_row_chunk(int rows, int stripes, int ctas_per_sm) {
     const int64_t slots = static_cast<int64_t>(kd::sm_count()) * ctas_per_sm;
     int64_t nchunks = slots / stripes;
-    const int64_t max_chunks = (rows + 4 * kWarps - 1) / (4 * kWarps);   // at least 32 rows per chunk
+    const int64_t max_chunks = (static_cast<int64_t>(rows) + 4 * kWarps - 1) / (4 * kWarps);   // at least 32 rows per chunk
     if (nchunks > max_chunks) nchunks = max_chunks;
     if (nchunks < 1) nchunks = 1;
-    int rch = static_cast<int>((rows + nchunks - 1) / nchunks);
+    int64_t rch = (static_cast<int64_t>(rows) + nchunks - 1) / nchunks;
     rch = ((rch + kWarps - 1) / kWarps) * kWarps;
     return rch;
+}
+
+// The (stripe, chunk) launch shape of a column reduction, or false when it cannot be launched: the kernels
+// index rows with 32-bit integers, so chunk * rch, r_begin + rch and the unrolled look-ahead of the row loop
+// (r + 3 * kWarps) must all stay below 2^31, and gridDim.y is limited to 65,535.
+struct ColChunks {
+    int rch = 0, nchunks = 0;
+};
+inline bool col_chunks(int rows, int64_t rch, ColChunks* out) {
+    if (rch < 1) return false;
+    const int64_t nchunks = (static_cast<int64_t>(rows) + rch - 1) / rch;
+    const int64_t reach = nchunks * rch + 4 * kWarps;       // largest row index any thread computes
+    if (nchunks > 65535 || reach > std::numeric_limits<int>::max()) return false;
+    out->rch = static_cast<int>(rch);
+    out->nchunks = static_cast<int>(nchunks);
+    return true;
 }
 
 template <typename T, int V>
 int sum_cols_v(const T* x, T* y, int rows, int cols, T scale, bool apply_scale) {
     const int stripes = (cols + 32 * V - 1) / (32 * V);
-    const int rch = pick_row_chunk(rows, stripes, kd::occupancy(sum_cols_kernel<T, V>, kThreads));
-    const int nchunks = (rows + rch - 1) / rch;
-    if (nchunks > 65535) return -2;
+    ColChunks cc;
+    if (!col_chunks(rows, pick_row_chunk(rows, stripes, kd::occupancy(sum_cols_kernel<T, V>, kThreads)), &cc)) return -2;
+    const int rch = cc.rch, nchunks = cc.nchunks;
     T* partials = nullptr;
     unsigned int* counters = nullptr;
     if (nchunks > 1) {
@@ -775,9 +792,9 @@ int sum_cols(const T* x, T* y, int rows, int cols, T scale, bool apply_scale) {
 template <typename T, int V>
 int max_cols_v(const T* x, T* y, long long* idx, int rows, int cols) {
     const int stripes = (cols + 32 * V - 1) / (32 * V);
-    const int rch = pick_row_chunk(rows, stripes, kd::occupancy(max_cols_kernel<T, V>, kThreads));
-    const int nchunks = (rows + rch - 1) / rch;
-    if (nchunks > 65535) return -2;
+    ColChunks cc;
+    if (!col_chunks(rows, pick_row_chunk(rows, stripes, kd::occupancy(max_cols_kernel<T, V>, kThreads)), &cc)) return -2;
+    const int rch = cc.rch, nchunks = cc.nchunks;
     T* pval = nullptr;
     int* pidx = nullptr;
     unsigned int* counters = nullptr;
@@ -1036,6 +1053,22 @@ int sum_to_shape(const T* x, T* y, const int64_t* in_shape, const int64_t* out_s
 KD_REDUCE(float, f32)
 KD_REDUCE(double, f64)
 
+// Additive, host-only: the launch shape the column reductions would use for a (rows, cols) matrix of
+// `elem_size`-byte elements with `ctas_per_sm` resident CTAs per SM: out3 = {rows per chunk, chunks, stripes}.
+// Returns -2 where the entry points return -2 (the shape cannot be indexed with 32-bit rows).  No device work.
+KD_API int keydnn_cuda_debug_col_chunks(int rows, int cols, int elem_size, int ctas_per_sm, int64_t* out3) {
+    if (!out3) return -1;
+    if (rows <= 0 || cols <= 0 || ctas_per_sm <= 0 || !(elem_size == 4 || elem_size == 8)) return -2;
+    const int V = 32 / elem_size;
+    const int stripes = (cols + 32 * V - 1) / (32 * V);
+    ColChunks cc;
+    if (!col_chunks(rows, pick_row_chunk(rows, stripes, ctas_per_sm), &cc)) return -2;
+    out3[0] = cc.rch;
+    out3[1] = cc.nchunks;
+    out3[2] = stripes;
+    return 0;
+}
+
 // ---------------------------------------------------------------------------
 // Column sums without any device allocation
 // ---------------------------------------------------------------------------
@@ -1089,11 +1122,12 @@ int noalloc_sum_cols(const float* x, float* y, int rows, int cols, unsigned char
     int occ = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, sum_cols_kernel<float, V>, kThreads, 0) != cudaSuccess || occ < 1)
         occ = 1;
-    int rch = pick_row_chunk(rows, stripes, occ);
+    int64_t rch64 = pick_row_chunk(rows, stripes, occ);
     // fewer, taller chunks until the partials fit the static array
-    while (static_cast<size_t>((rows + rch - 1) / rch) * cols * sizeof(float) > kNoAllocPartialBytes) rch *= 2;
-    const int nchunks = (rows + rch - 1) / rch;
-    if (nchunks > 65535) return kNoAllocTooLarge;
+    while (static_cast<size_t>((rows + rch64 - 1) / rch64) * cols * sizeof(float) > kNoAllocPartialBytes) rch64 *= 2;
+    ColChunks cc;
+    if (!col_chunks(rows, rch64, &cc)) return kNoAllocTooLarge;
+    const int rch = cc.rch, nchunks = cc.nchunks;
     unsigned int* counters = reinterpret_cast<unsigned int*>(base);
     float* partials = reinterpret_cast<float*>(base + kNoAllocCounterBytes);
     cudaStream_t s = kd::stream();

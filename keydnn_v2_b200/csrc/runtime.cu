@@ -7,10 +7,13 @@
 //
 // Differences that callers can observe only as speed:
 //  * keydnn_cuda_malloc / keydnn_cuda_free go through a per-device caching pool.
-//    Every kernel and copy of this library is ordered on one stream, so a block
-//    handed back by `free` can be handed out again at once: work that still
-//    reads it was enqueued earlier on the same stream.  cudaFree's implicit
-//    device synchronisation disappears from the per-op path.
+//    Work of this library is ordered on the library stream, so a block handed
+//    back by `free` can be handed out again at once: work that still reads it was
+//    enqueued earlier on the same stream.  Every cached block remembers the
+//    stream that was current when it was freed; when it is handed out while
+//    another stream is current, that stream first waits (an event, on the device)
+//    for the work enqueued on the old one.  cudaFree's implicit device
+//    synchronisation disappears from the per-op path.
 //  * copies are enqueued on the library stream and the host waits on that
 //    stream only.
 #include "common.cuh"
@@ -42,6 +45,9 @@ struct DevicePool {
     bool capturing = false;
     std::multimap<size_t, void*> capture_free;         // freed during the recording, reusable inside it
     std::unordered_map<void*, size_t> graph_blocks;    // every block owned by a recorded graph
+    int live_graphs = 0;                               // recorded graphs not yet destroyed
+    std::unordered_map<void*, cudaStream_t> freed_on;  // cached block -> stream that was current at its free
+    cudaEvent_t handover = nullptr;                    // orders a block's old stream before its new one
 };
 
 struct DeviceState {
@@ -51,13 +57,16 @@ struct DeviceState {
     size_t scratch_bytes = 0;
     unsigned int* counters = nullptr;
     size_t counters_len = 0;
+    size_t scratch_allocs = 0;     // driver allocations made for scratch / counters
+    std::vector<void*> parked;     // outgrown scratch / counter buffers a recorded graph may still write to
+    cudaStream_t stream = nullptr; // the library stream of this device: legacy default stream unless the caller sets one
     DevicePool pool;
 };
 
 std::mutex g_mu;
 DeviceState g_dev[kMaxDevices];
-cudaStream_t g_stream = nullptr;   // legacy default stream unless the caller sets one
 bool g_pool_enabled = true;
+size_t g_scratch_min = size_t(8) << 20;   // first size of the reduction scratch (KEYDNN_B200_SCRATCH_MIN, bytes)
 
 int current_device() {
     int d = 0;
@@ -73,6 +82,10 @@ DeviceState& state() {
         if (s.sm_count <= 0) s.sm_count = 148;
         const char* e = std::getenv("KEYDNN_B200_NO_POOL");
         if (e && e[0] == '1') g_pool_enabled = false;
+        if (const char* m = std::getenv("KEYDNN_B200_SCRATCH_MIN")) {
+            const long long v = std::atoll(m);
+            if (v >= 256) g_scratch_min = static_cast<size_t>(v);
+        }
         s.inited = true;
     }
     return s;
@@ -96,13 +109,45 @@ void release_cached(DevicePool& p) {
         p.bytes_reserved -= kv.first;
     }
     p.free_blocks.clear();
+    p.freed_on.clear();
+}
+
+// The library stream of the current device (the fast path of every launch: no lock, one TLS read).
+inline cudaStream_t& dev_stream() { return g_dev[current_device()].stream; }
+
+// A cached block leaves the pool: if it was freed while another stream was current, work enqueued on that
+// stream may still touch it, so the current stream waits for it on the device.  Not while a graph is being
+// recorded (the recording's blocks are recycled inside it, in the recorded order).
+void hand_over(DevicePool& p, void* q, cudaStream_t now) {
+    auto it = p.freed_on.find(q);
+    if (it == p.freed_on.end()) return;
+    const cudaStream_t then = it->second;
+    p.freed_on.erase(it);
+    if (then == now || p.capturing) return;
+    if (!p.handover && cudaEventCreateWithFlags(&p.handover, cudaEventDisableTiming) != cudaSuccess) {
+        p.handover = nullptr;
+        (void)cudaGetLastError();
+        cudaStreamSynchronize(then);
+        return;
+    }
+    if (cudaEventRecord(p.handover, then) != cudaSuccess || cudaStreamWaitEvent(now, p.handover, 0) != cudaSuccess) {
+        (void)cudaGetLastError();
+        cudaStreamSynchronize(then);
+    }
+}
+
+// Outgrown scratch buffers: freed at once unless a recorded graph (or a recording in progress) holds their address.
+void retire(DeviceState& s, void* old) {
+    if (!old) return;
+    if (s.pool.live_graphs > 0 || s.pool.capturing) s.parked.push_back(old);
+    else cudaFree(old);     // synchronises with earlier kernels that still use it
 }
 
 }  // namespace
 
 namespace kd {
 
-cudaStream_t stream() { return g_stream; }
+cudaStream_t stream() { return dev_stream(); }
 
 bool pdl_enabled() {
     static const bool on = [] {
@@ -117,19 +162,27 @@ int sm_count() {
     return state().sm_count;
 }
 
+// Growth rules (both buffers):
+//  * while a graph is being recorded nothing may be allocated: a reduction whose shape needs more than the
+//    buffer holds fails (nullptr -> cudaErrorMemoryAllocation from the entry point); run the step eagerly
+//    once before recording it, as keydnn_cuda_graph_capture_begin asks.
+//  * while a recorded graph is alive its launches hold the old address: the outgrown buffer is parked until
+//    keydnn_cuda_graph_destroy instead of being freed, so a later, larger eager reduction cannot pull the
+//    memory from under a replay.
 void* scratch(size_t nbytes) {
     std::lock_guard<std::mutex> lk(g_mu);
     DeviceState& s = state();
     if (nbytes > s.scratch_bytes) {
-        // Earlier kernels that use the old buffer are ordered before the free
-        // by cudaFree's own synchronisation.
-        if (s.scratch) cudaFree(s.scratch);
-        size_t want = nbytes < (size_t(8) << 20) ? (size_t(8) << 20) : nbytes;
-        if (cudaMalloc(&s.scratch, want) != cudaSuccess) {
-            s.scratch = nullptr;
-            s.scratch_bytes = 0;
+        if (s.pool.capturing) return nullptr;
+        size_t want = nbytes < g_scratch_min ? g_scratch_min : nbytes;
+        void* fresh = nullptr;
+        if (cudaMalloc(&fresh, want) != cudaSuccess) {
+            (void)cudaGetLastError();
             return nullptr;
         }
+        retire(s, s.scratch);
+        s.scratch_allocs++;
+        s.scratch = fresh;
         s.scratch_bytes = want;
     }
     return s.scratch;
@@ -139,14 +192,17 @@ unsigned int* counters(size_t count) {
     std::lock_guard<std::mutex> lk(g_mu);
     DeviceState& s = state();
     if (count > s.counters_len) {
-        if (s.counters) cudaFree(s.counters);
+        if (s.pool.capturing) return nullptr;
         size_t want = count < 4096 ? 4096 : count;
-        if (cudaMalloc(reinterpret_cast<void**>(&s.counters), want * sizeof(unsigned int)) != cudaSuccess) {
-            s.counters = nullptr;
-            s.counters_len = 0;
+        void* fresh = nullptr;
+        if (cudaMalloc(&fresh, want * sizeof(unsigned int)) != cudaSuccess) {
+            (void)cudaGetLastError();
             return nullptr;
         }
-        cudaMemset(s.counters, 0, want * sizeof(unsigned int));
+        cudaMemset(fresh, 0, want * sizeof(unsigned int));
+        retire(s, s.counters);
+        s.scratch_allocs++;
+        s.counters = static_cast<unsigned int*>(fresh);
         s.counters_len = want;
     }
     return s.counters;
@@ -195,6 +251,7 @@ KD_API int keydnn_cuda_malloc(std::uint64_t* out_ptr, std::size_t nbytes) {
         void* q = it->second;
         size_t sz = it->first;
         p.free_blocks.erase(it);
+        hand_over(p, q, s.stream);
         p.live.emplace(q, sz);
         p.bytes_in_use += sz;
         if (p.capturing) p.graph_blocks.emplace(q, sz);
@@ -238,6 +295,7 @@ KD_API int keydnn_cuda_free(std::uint64_t ptr) {
                 g_dev[d].pool.live.erase(jt);
                 g_dev[d].pool.bytes_in_use -= sz;
                 g_dev[d].pool.free_blocks.emplace(sz, q);
+                g_dev[d].pool.freed_on[q] = g_dev[d].stream;
                 return 0;
             }
         }
@@ -252,12 +310,13 @@ KD_API int keydnn_cuda_free(std::uint64_t ptr) {
         return 0;
     }
     p.free_blocks.emplace(sz, q);
+    p.freed_on[q] = s.stream;
     return 0;
 }
 
 // Additive: hand every cached block back to the driver.
 KD_API int keydnn_cuda_empty_cache() {
-    cudaError_t st = cudaStreamSynchronize(g_stream);
+    cudaError_t st = cudaDeviceSynchronize();       // blocks may have been freed under any stream
     std::lock_guard<std::mutex> lk(g_mu);
     release_cached(state().pool);
     return kd::status(st);
@@ -276,22 +335,46 @@ KD_API int keydnn_cuda_pool_stats(std::uint64_t* out4) {
     return 0;
 }
 
+// Additive: the reduction scratch of the current device.  out[0] = bytes of the partials buffer, out[1] =
+// completion-ticket slots, out[2] = driver allocations made for either so far, out[3] = outgrown buffers
+// parked for a recorded graph.
+KD_API int keydnn_cuda_scratch_stats(std::uint64_t* out4) {
+    if (!out4) return -1;
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& s = state();
+    out4[0] = s.scratch_bytes;
+    out4[1] = s.counters_len;
+    out4[2] = s.scratch_allocs;
+    out4[3] = s.parked.size();
+    return 0;
+}
+
+// Additive: free and total bytes of the current device as the driver sees them (cudaMemGetInfo).
+KD_API int keydnn_cuda_mem_info(std::uint64_t* out2) {
+    if (!out2) return -1;
+    size_t f = 0, t = 0;
+    cudaError_t st = cudaMemGetInfo(&f, &t);
+    out2[0] = f;
+    out2[1] = t;
+    return kd::status(st);
+}
+
 KD_API int keydnn_cuda_memcpy_h2d(std::uint64_t dst_dev, const void* src_host, std::size_t nbytes) {
     if (nbytes == 0) return 0;
     cudaError_t st = cudaMemcpyAsync(reinterpret_cast<void*>(dst_dev), src_host, nbytes,
-                                     cudaMemcpyHostToDevice, g_stream);
+                                     cudaMemcpyHostToDevice, dev_stream());
     if (st != cudaSuccess) return static_cast<int>(st);
     // Pageable sources are staged before the call returns; pinned sources are
     // read by the DMA engine, so wait for it: the caller may reuse the buffer.
-    return kd::status(cudaStreamSynchronize(g_stream));
+    return kd::status(cudaStreamSynchronize(dev_stream()));
 }
 
 KD_API int keydnn_cuda_memcpy_d2h(void* dst_host, std::uint64_t src_dev, std::size_t nbytes) {
     if (nbytes == 0) return 0;
     cudaError_t st = cudaMemcpyAsync(dst_host, reinterpret_cast<const void*>(src_dev), nbytes,
-                                     cudaMemcpyDeviceToHost, g_stream);
+                                     cudaMemcpyDeviceToHost, dev_stream());
     if (st != cudaSuccess) return static_cast<int>(st);
-    return kd::status(cudaStreamSynchronize(g_stream));
+    return kd::status(cudaStreamSynchronize(dev_stream()));
 }
 
 // Additive: host->device copy that returns as soon as it is enqueued (the
@@ -299,7 +382,7 @@ KD_API int keydnn_cuda_memcpy_d2h(void* dst_host, std::uint64_t src_dev, std::si
 KD_API int keydnn_cuda_memcpy_h2d_async(std::uint64_t dst_dev, const void* src_host, std::size_t nbytes) {
     if (nbytes == 0) return 0;
     return kd::status(cudaMemcpyAsync(reinterpret_cast<void*>(dst_dev), src_host, nbytes,
-                                      cudaMemcpyHostToDevice, g_stream));
+                                      cudaMemcpyHostToDevice, dev_stream()));
 }
 
 // Additive: device->host copy that returns as soon as it is enqueued; the destination (pinned, to be
@@ -307,19 +390,19 @@ KD_API int keydnn_cuda_memcpy_h2d_async(std::uint64_t dst_dev, const void* src_h
 KD_API int keydnn_cuda_memcpy_d2h_async(void* dst_host, std::uint64_t src_dev, std::size_t nbytes) {
     if (nbytes == 0) return 0;
     return kd::status(cudaMemcpyAsync(dst_host, reinterpret_cast<const void*>(src_dev), nbytes,
-                                      cudaMemcpyDeviceToHost, g_stream));
+                                      cudaMemcpyDeviceToHost, dev_stream()));
 }
 
 KD_API int keydnn_cuda_memcpy_d2d(void* dst, const void* src, std::size_t nbytes) {
     if (nbytes == 0) return 0;
     if (!dst || !src) return 1;
-    cudaError_t st = cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToDevice, g_stream);
+    cudaError_t st = cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToDevice, dev_stream());
     return st == cudaSuccess ? 0 : 2;
 }
 
 KD_API int keydnn_cuda_memset(std::uint64_t dev_ptr, int value, std::size_t nbytes) {
     if (nbytes == 0) return 0;
-    return kd::status(cudaMemsetAsync(reinterpret_cast<void*>(dev_ptr), value, nbytes, g_stream));
+    return kd::status(cudaMemsetAsync(reinterpret_cast<void*>(dev_ptr), value, nbytes, dev_stream()));
 }
 
 KD_API int keydnn_cuda_synchronize() {
@@ -338,13 +421,14 @@ KD_API int keydnn_cuda_host_free(void* p) {
 }
 
 // Additive: the stream all work of this library is enqueued on.
+// The stream belongs to the current device (keydnn_cuda_set_device): each device keeps its own.
 KD_API int keydnn_cuda_get_stream(std::uint64_t* out) {
     if (!out) return -1;
-    *out = reinterpret_cast<std::uint64_t>(g_stream);
+    *out = reinterpret_cast<std::uint64_t>(dev_stream());
     return 0;
 }
 KD_API int keydnn_cuda_set_stream(std::uint64_t s) {
-    g_stream = reinterpret_cast<cudaStream_t>(s);
+    dev_stream() = reinterpret_cast<cudaStream_t>(s);
     return 0;
 }
 KD_API int keydnn_cuda_stream_create(std::uint64_t* out) {
@@ -356,11 +440,25 @@ KD_API int keydnn_cuda_stream_create(std::uint64_t* out) {
 }
 KD_API int keydnn_cuda_stream_destroy(std::uint64_t s) {
     if (!s) return 0;
-    if (reinterpret_cast<cudaStream_t>(s) == g_stream) g_stream = nullptr;
-    return kd::status(cudaStreamDestroy(reinterpret_cast<cudaStream_t>(s)));
+    const cudaStream_t dead = reinterpret_cast<cudaStream_t>(s);
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        bool synced = false;
+        for (int d = 0; d < kMaxDevices; ++d) {
+            if (g_dev[d].stream == dead) g_dev[d].stream = nullptr;
+            // cached blocks freed under this stream: let its work finish now, the handle is about to go
+            auto& tags = g_dev[d].pool.freed_on;
+            for (auto it = tags.begin(); it != tags.end();) {
+                if (it->second != dead) { ++it; continue; }
+                if (!synced) { cudaStreamSynchronize(dead); synced = true; }
+                it = tags.erase(it);
+            }
+        }
+    }
+    return kd::status(cudaStreamDestroy(dead));
 }
 KD_API int keydnn_cuda_stream_synchronize() {
-    return kd::status(cudaStreamSynchronize(g_stream));
+    return kd::status(cudaStreamSynchronize(dev_stream()));
 }
 
 // Additive: CUDA events on the library stream.  These are the names the
@@ -374,11 +472,11 @@ KD_API int keydnn_cuda_event_create(std::uint64_t* out) {
     return kd::status(st);
 }
 KD_API int keydnn_cuda_event_record(std::uint64_t ev) {
-    return kd::status(cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev), g_stream));
+    return kd::status(cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev), dev_stream()));
 }
 // Work enqueued on the library stream after this call starts only once `ev` has completed.
 KD_API int keydnn_cuda_stream_wait_event(std::uint64_t ev) {
-    return kd::status(cudaStreamWaitEvent(g_stream, reinterpret_cast<cudaEvent_t>(ev), 0));
+    return kd::status(cudaStreamWaitEvent(dev_stream(), reinterpret_cast<cudaEvent_t>(ev), 0));
 }
 KD_API int keydnn_cuda_event_synchronize(std::uint64_t ev) {
     return kd::status(cudaEventSynchronize(reinterpret_cast<cudaEvent_t>(ev)));
@@ -400,14 +498,14 @@ KD_API int keydnn_cuda_event_destroy(std::uint64_t ev) {
 // blocks allocated during the recording stay reserved for the graph until graph_destroy.
 // One recording at a time, one graph alive per device.
 KD_API int keydnn_cuda_graph_capture_begin() {
-    if (!g_stream) return -3;                       // the legacy default stream cannot be captured
+    if (!dev_stream()) return -3;                       // the legacy default stream cannot be captured
     {
         std::lock_guard<std::mutex> lk(g_mu);
         DevicePool& p = state().pool;
         if (p.capturing || !p.graph_blocks.empty()) return -4;
         p.capturing = true;
     }
-    cudaError_t st = cudaStreamBeginCapture(g_stream, cudaStreamCaptureModeRelaxed);
+    cudaError_t st = cudaStreamBeginCapture(dev_stream(), cudaStreamCaptureModeRelaxed);
     if (st != cudaSuccess) {
         std::lock_guard<std::mutex> lk(g_mu);
         state().pool.capturing = false;
@@ -419,7 +517,7 @@ KD_API int keydnn_cuda_graph_capture_end(std::uint64_t* out_exec) {
     if (!out_exec) return -1;
     *out_exec = 0;
     cudaGraph_t graph = nullptr;
-    cudaError_t st = cudaStreamEndCapture(g_stream, &graph);
+    cudaError_t st = cudaStreamEndCapture(dev_stream(), &graph);
     {
         std::lock_guard<std::mutex> lk(g_mu);
         DevicePool& p = state().pool;
@@ -436,26 +534,36 @@ KD_API int keydnn_cuda_graph_capture_end(std::uint64_t* out_exec) {
     st = cudaGraphInstantiate(&exec, graph, 0);
     cudaGraphDestroy(graph);
     if (st != cudaSuccess) return kd::status(st);
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        state().pool.live_graphs++;
+    }
     *out_exec = reinterpret_cast<std::uint64_t>(exec);
     return 0;
 }
 
 KD_API int keydnn_cuda_graph_launch(std::uint64_t exec) {
     if (!exec) return -1;
-    return kd::status(cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(exec), g_stream));
+    return kd::status(cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(exec), dev_stream()));
 }
 
 KD_API int keydnn_cuda_graph_destroy(std::uint64_t exec) {
     cudaError_t st = cudaSuccess;
     if (exec) {
-        cudaStreamSynchronize(g_stream);
+        cudaStreamSynchronize(dev_stream());
         st = cudaGraphExecDestroy(reinterpret_cast<cudaGraphExec_t>(exec));
     }
     std::lock_guard<std::mutex> lk(g_mu);
-    DevicePool& p = state().pool;
+    DeviceState& ds = state();
+    DevicePool& p = ds.pool;
     for (auto& kv : p.graph_blocks)
         if (!p.live.count(kv.first)) p.free_blocks.emplace(kv.second, kv.first);   // live ones return on their free
     p.graph_blocks.clear();
+    if (exec && p.live_graphs > 0) p.live_graphs--;
+    if (p.live_graphs == 0) {
+        for (void* q : ds.parked) cudaFree(q);      // outgrown scratch the graph could still have written to
+        ds.parked.clear();
+    }
     return kd::status(st);
 }
 

@@ -24,7 +24,17 @@
 
 namespace {
 
+// One source of truth for the stream.  The operator library (libkeydnn_b200.so) owns "the library stream";
+// its keydnn_cuda_get_stream is bound here once (keydnn_dnn_bind_stream_source) and asked before every
+// cuDNN / cuBLAS call, so a convolution is always enqueued on the stream the BatchNorm / pooling / loss /
+// optimizer kernels around it use and program order is stream order, as on the reference's single default
+// stream (KeyDNNV2CudaNative/keydnn_cuda_conv2d.cu:53-61).  Without a bound source the stream is whatever
+// keydnn_dnn_set_stream last set (default: the legacy default stream).
+using StreamSource = int (*)(std::uint64_t*);
+StreamSource g_stream_source = nullptr;
 cudaStream_t g_stream = nullptr;
+cudaStream_t g_last_stream = nullptr;      // stream of the previous call: the workspace is shared between calls
+bool g_have_last = false;
 cublasHandle_t g_blas = nullptr;
 cudnnHandle_t g_dnn = nullptr;
 void* g_ws = nullptr;
@@ -32,14 +42,34 @@ size_t g_ws_bytes = 0;
 
 inline int cudnn_status(cudnnStatus_t s) { return s == CUDNN_STATUS_SUCCESS ? 0 : 100000 + static_cast<int>(s); }
 
+cudaStream_t current_stream() {
+    cudaStream_t s = g_stream;
+    if (g_stream_source) {
+        std::uint64_t v = 0;
+        if (g_stream_source(&v) == 0) s = reinterpret_cast<cudaStream_t>(v);
+    }
+    if (g_have_last && s != g_last_stream) {
+        // Calls on the previous stream may still use the shared workspace (and cuDNN's handle state): let them
+        // finish before the first call on the new stream.  While the new stream is being recorded into a graph
+        // nothing may block; the caller has run the step eagerly on that stream before recording it.
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (s == nullptr || cudaStreamIsCapturing(s, &cs) != cudaSuccess) cs = cudaStreamCaptureStatusNone;
+        if (cs == cudaStreamCaptureStatusNone) cudaStreamSynchronize(g_last_stream);
+        (void)cudaGetLastError();
+    }
+    g_last_stream = s;
+    g_have_last = true;
+    return s;
+}
+
 cudnnHandle_t dnn() {
     if (!g_dnn && cudnnCreate(&g_dnn) != CUDNN_STATUS_SUCCESS) g_dnn = nullptr;
-    if (g_dnn) cudnnSetStream(g_dnn, g_stream);
+    if (g_dnn) cudnnSetStream(g_dnn, current_stream());
     return g_dnn;
 }
 cublasHandle_t blas() {
     if (!g_blas && cublasCreate(&g_blas) != CUBLAS_STATUS_SUCCESS) g_blas = nullptr;
-    if (g_blas) cublasSetStream(g_blas, g_stream);
+    if (g_blas) cublasSetStream(g_blas, current_stream());
     return g_blas;
 }
 void* workspace(size_t bytes) {
@@ -248,8 +278,29 @@ int matmul(const T* A, const T* B, T* C, int M, int N, int K, int transA, int tr
 
 }  // namespace
 
+// An explicit stream for callers that use this library on its own; it also drops a bound source.
 KD_API int keydnn_dnn_set_stream(std::uint64_t stream) {
+    g_stream_source = nullptr;
     g_stream = reinterpret_cast<cudaStream_t>(stream);
+    return 0;
+}
+
+// `get_stream_fn` is the address of a function `int f(uint64_t* out)` that stores the stream every call of
+// this library must be enqueued on (libkeydnn_b200.so's keydnn_cuda_get_stream); 0 unbinds.
+KD_API int keydnn_dnn_bind_stream_source(std::uint64_t get_stream_fn) {
+    g_stream_source = reinterpret_cast<StreamSource>(get_stream_fn);
+    return 0;
+}
+
+// The stream the next call would be enqueued on (tests; diagnostics).
+KD_API int keydnn_dnn_get_stream(std::uint64_t* out) {
+    if (!out) return -1;
+    cudaStream_t s = g_stream;
+    if (g_stream_source) {
+        std::uint64_t v = 0;
+        if (g_stream_source(&v) == 0) s = reinterpret_cast<cudaStream_t>(v);
+    }
+    *out = reinterpret_cast<std::uint64_t>(s);
     return 0;
 }
 

@@ -555,8 +555,8 @@ class GraphedTrainStep:
             raise
 
     def _use(self, stream: int) -> None:
+        # the cuDNN / cuBLAS library follows the operator library's stream (bound at load, `_native.load_dnn`)
         self.lib.call("keydnn_cuda_set_stream", stream)
-        self.dnn.call("keydnn_dnn_set_stream", stream)
 
     def run(self) -> Tensor:
         self.lib.call("keydnn_cuda_graph_launch", self.exec.value)

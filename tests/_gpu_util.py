@@ -29,8 +29,18 @@ def ref_cuda():
     return Native(REF_CUDA, strict=False)
 
 
+GUARD = 256                 # bytes of sentinel on each side of every test buffer
+SENTINEL = 0xA5
+OVERRUNS: list[str] = []    # guard bands found damaged (tests/conftest.py fails the test that left an entry)
+
+
 class Buf:
-    """A device buffer owned by `lib` (either library: both export malloc/free/memcpy)."""
+    """A device buffer owned by `lib` (either library: both export malloc/free/memcpy).
+
+    The allocation carries a guard band of `GUARD` sentinel bytes directly in front of the buffer and directly
+    behind its last byte.  The caching pool rounds sizes up (512-byte classes), so a kernel that writes a few
+    elements past the end of a ragged buffer would otherwise land in slack that nobody reads; the bands are
+    compared on every `get()` and when the buffer is released, which stands in for a memory checker."""
 
     def __init__(self, lib, arr=None, *, shape=None, dtype=None, fill=None):
         self.lib = lib
@@ -40,23 +50,43 @@ class Buf:
         self.shape, self.dtype = tuple(shape), np.dtype(dtype)
         self.nbytes = int(np.prod(self.shape, dtype=np.int64)) * self.dtype.itemsize
         out = ctypes.c_uint64(0)
-        lib.call("keydnn_cuda_malloc", ctypes.byref(out), max(self.nbytes, 16))
-        self.ptr = out.value
+        lib.call("keydnn_cuda_malloc", ctypes.byref(out), GUARD + max(self.nbytes, 16) + GUARD)
+        self.base = out.value
+        self.ptr = self.base + GUARD          # still 256-byte aligned
+        lib.call("keydnn_cuda_memset", self.base, SENTINEL, GUARD)
+        lib.call("keydnn_cuda_memset", self.ptr + self.nbytes, SENTINEL, GUARD)
         if arr is not None and self.nbytes:
             lib.call("keydnn_cuda_memcpy_h2d", self.ptr, arr.ctypes.data, self.nbytes)
         elif fill is not None and self.nbytes:
             lib.call("keydnn_cuda_memset", self.ptr, int(fill), self.nbytes)
 
+    def check_guards(self) -> None:
+        """Records (and raises on) any byte of either guard band that no longer holds the sentinel."""
+        band = np.empty(GUARD, np.uint8)
+        self.lib.call("keydnn_cuda_synchronize")
+        for name, addr in (("in front of", self.base), ("behind", self.ptr + self.nbytes)):
+            self.lib.call("keydnn_cuda_memcpy_d2h", band.ctypes.data, addr, GUARD)
+            bad = np.flatnonzero(band != SENTINEL)
+            if bad.size:
+                msg = (f"out-of-bounds write {name} a {self.shape} {self.dtype} buffer: {bad.size} guard bytes changed, "
+                       f"first at offset {int(bad[0])}")
+                OVERRUNS.append(msg)
+                raise AssertionError(msg)
+
     def get(self) -> np.ndarray:
         out = np.empty(self.shape, self.dtype)
+        self.check_guards()
         if self.nbytes:
-            self.lib.call("keydnn_cuda_synchronize")
             self.lib.call("keydnn_cuda_memcpy_d2h", out.ctypes.data, self.ptr, self.nbytes)
         return out
 
     def __del__(self):
         try:
-            self.lib.raw("keydnn_cuda_free")(ctypes.c_uint64(self.ptr))
+            self.check_guards()
+        except Exception:
+            pass                               # recorded in OVERRUNS; the fixture fails the test
+        try:
+            self.lib.raw("keydnn_cuda_free")(ctypes.c_uint64(self.base))
         except Exception:
             pass
 

@@ -31,3 +31,18 @@ def oracle():
 
     ob.build_oracle()
     return keydnn_oracle
+
+
+@pytest.fixture(autouse=True)
+def _guard_bands_intact(request):
+    """GPU tests: every `tests/_gpu_util.Buf` released during the test must have both guard bands intact."""
+    yield
+    if request.node.get_closest_marker("gpu") is None:
+        return
+    import gc
+
+    import _gpu_util
+
+    gc.collect()
+    found, _gpu_util.OVERRUNS[:] = list(_gpu_util.OVERRUNS), []
+    assert not found, found

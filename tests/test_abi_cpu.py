@@ -62,3 +62,51 @@ def test_product_package_never_imports_the_oracle():
     for py in (REPO / "keydnn_v2_b200").glob("*.py"):
         text = py.read_text()
         assert "oracle" not in text.replace("# oracle", ""), f"{py.name} mentions the oracle"
+
+
+def test_dnn_library_exports_every_declared_symbol():
+    from keydnn_v2_b200._native import DNN_HEADER_PATH, parse_header
+    from keydnn_v2_b200.build import build_dnn
+
+    declared = set(parse_header(DNN_HEADER_PATH))
+    exported = {s for s in _exports(build_dnn()) if s.startswith("keydnn_")}
+    assert declared - exported == set()
+    assert exported - declared == set(), "every export must be declared in include/keydnn_b200_dnn.h"
+
+
+def test_both_libraries_share_one_stream_state(lib_path):
+    """The cuDNN / cuBLAS library has no stream of its own once loaded through the package: it asks the operator
+    library before every call, so `keydnn_cuda_set_stream` moves both (no device call is made here: the stream
+    values are only stored and read back)."""
+    from keydnn_v2_b200 import load
+    from keydnn_v2_b200._native import load_dnn
+
+    lib, dnn = load(), load_dnn()
+    seen = ctypes.c_uint64(1)
+    try:
+        for value in (0xABC0, 0x1230, 0):
+            lib.call("keydnn_cuda_set_stream", value)
+            dnn.call("keydnn_dnn_get_stream", ctypes.byref(seen))
+            assert seen.value == value
+    finally:
+        lib.call("keydnn_cuda_set_stream", 0)
+
+
+def test_column_reduction_chunk_arithmetic_is_64_bit(lib_path):
+    """Narrow matrices with close to 2^31 rows: rows per chunk and the chunk count come out of 64-bit
+    arithmetic, and a shape whose last chunk would reach past 2^31 - 1 is refused (-2) instead of
+    wrapping around.  Host arithmetic only, nothing is allocated or launched."""
+    from keydnn_v2_b200 import load
+
+    f = load().raw("keydnn_cuda_debug_col_chunks")
+    out = (ctypes.c_int64 * 3)()
+    for rows in (1, 31, 32, 33, 4096, 8192, 1 << 20, (1 << 30) + 7, (1 << 31) - 4096):
+        for cols, esz in ((8, 4), (1024, 4), (4096, 8)):
+            st = f(rows, cols, esz, 8, out)
+            assert st == 0, (rows, cols, esz)
+            rch, nchunks, stripes = out
+            assert rch > 0 and rch % 8 == 0 and 1 <= nchunks <= 65535 and stripes >= 1
+            assert (nchunks - 1) * rch < rows <= nchunks * rch
+            assert nchunks * rch + 32 <= 2**31 - 1
+    assert f(2**31 - 1, 8, 4, 8, out) == -2         # the last chunk would end beyond INT_MAX
+    assert f(0, 8, 4, 8, out) == -2

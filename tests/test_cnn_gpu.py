@@ -255,6 +255,48 @@ def test_graphed_training_step_follows_the_eager_one():
     assert losses["eager"][-1] < losses["eager"][0]
 
 
+def test_training_off_the_default_stream_equals_training_on_it():
+    """Five eager training steps with the library moved to a created non-blocking stream: Conv2d / Linear (cuDNN /
+    cuBLAS, second library) must follow the BatchNorm / pooling / loss / optimizer kernels onto that stream.  A
+    library left on the legacy stream races with them (a non-blocking stream does not synchronise with it) and the
+    losses come out different or NaN.  Tolerance 1e-5: cuDNN's weight-gradient algorithm may add in any order."""
+    import ctypes
+
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200 import nn
+    from keydnn_v2_b200._native import load_dnn
+
+    lib, dnn = kd.load(), load_dnn()
+    rng = np.random.default_rng(21)
+    hx = rng.standard_normal((64, 3, 64, 64)).astype(np.float32)
+    ht = np.eye(10, dtype=np.float32)[rng.integers(0, 10, 64)]
+    prev, stream, seen = ctypes.c_uint64(0), ctypes.c_uint64(0), ctypes.c_uint64(0)
+    lib.call("keydnn_cuda_get_stream", ctypes.byref(prev))
+    lib.call("keydnn_cuda_stream_create", ctypes.byref(stream))
+    runs = {}
+    try:
+        for where in ("default", "created"):
+            lib.call("keydnn_cuda_synchronize")
+            lib.call("keydnn_cuda_set_stream", prev.value if where == "default" else stream.value)
+            dnn.call("keydnn_dnn_get_stream", ctypes.byref(seen))
+            assert seen.value == (prev.value if where == "default" else stream.value)
+            np.random.seed(5)
+            model = nn.small_cnn()
+            opt = nn.SGD(model.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
+            x, t = kd.Tensor.from_numpy(hx), kd.Tensor.from_numpy(ht)
+            losses = [nn.train_step(model, opt, x, t) for _ in range(5)]      # no host read between the steps
+            runs[where] = ([v.item() for v in losses], [p.to_numpy() for p in model.parameters()])
+    finally:
+        lib.call("keydnn_cuda_synchronize")
+        lib.call("keydnn_cuda_set_stream", prev.value)
+        lib.call("keydnn_cuda_stream_destroy", stream.value)
+    assert np.all(np.isfinite(runs["created"][0]))
+    np.testing.assert_allclose(runs["created"][0], runs["default"][0], rtol=1e-5)
+    for a, b in zip(runs["created"][1], runs["default"][1]):
+        np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6)
+    assert runs["default"][0][-1] < runs["default"][0][0]
+
+
 def test_pipelined_feeding_trains_on_the_batches_it_is_given():
     """step_async / loss_of: two alternating batches fed from pinned host memory through the staging
     buffers must give the losses of the same sequence run with plain copies and graph launches."""
