@@ -21,6 +21,8 @@ LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libkeydnn_b200.so"
 DNN_SRC = PKG_DIR / "csrc_dnn" / "dnn.cu"
 DNN_LIB_PATH = LIB_DIR / "libkeydnn_b200_dnn.so"
+DROPIN_SRC = PKG_DIR / "csrc_dropin" / "dropin.c"
+DROPIN_LIB_PATH = LIB_DIR / "libkeydnn_b200_dropin.so"
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = [
@@ -111,7 +113,23 @@ def build_dnn(force: bool = False, verbose: bool = False) -> Path:
     return DNN_LIB_PATH
 
 
+def build_dropin(force: bool = False, verbose: bool = False) -> Path:
+    """The single file that stands in for the reference's one CUDA DLL: depends on both libraries above (found
+    next to it through $ORIGIN) and binds their stream state when it is loaded."""
+    if not force and _newer(DROPIN_LIB_PATH, [DROPIN_SRC, LIB_PATH, DNN_LIB_PATH, Path(__file__)]):
+        return DROPIN_LIB_PATH
+    cmd = ["gcc", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", str(DROPIN_SRC), "-o", str(DROPIN_LIB_PATH),
+           "-L", str(LIB_DIR), "-Wl,--no-as-needed", "-lkeydnn_b200", "-lkeydnn_b200_dnn", "-Wl,-rpath,$ORIGIN"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"gcc failed for {DROPIN_SRC.name}:\n{r.stdout}\n{r.stderr}")
+    return DROPIN_LIB_PATH
+
+
 if __name__ == "__main__":
     print(build_dnn(force="--force" in sys.argv, verbose=True))
     p = build_native(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv)
     print(p)
+    print(build_dropin(force="--force" in sys.argv, verbose=True))
