@@ -1,6 +1,7 @@
 """Benchmark of the reduction hot path (configuration [1] of the benchmark definition) on N GPUs of one node.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--kernels all|none]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--windows R] [--impl ours|reference]
+                    [--kernels auto|none|step|suite|full]
 
 A step is one pass of sum / mean / max over axis 0, axis 1 and all axes, each followed by its
 backward with an upstream gradient of ones, on an fp32 (8192, 8192) and an fp64 (4096, 4096)
@@ -8,6 +9,18 @@ matrix per GPU (rows sharded across ranks; partials of axis-0 and all-axes reduc
 NVLink through NCCL).  `value` is algorithmic bytes moved per second by all ranks, inputs
 resident in HBM; `e2e` is the same through the Tensor API with pinned host inputs copied in and
 results copied out every step.  Rank 0 prints one JSON line.
+
+Timing: after W warm-up steps the K-step loop is timed R times (`--windows`, default 10), every window
+bracketed by a device synchronisation and a barrier on both sides and timed with events on the library stream,
+the maximum over ranks taken per window; `value` / `ms_per_step` are the MEDIAN window, and `windows` carries
+the minimum and maximum so that a single stall is visible instead of moving the figure.
+
+The line also carries: `kernels` (every kernel of the step), `suite` (the kernels of configurations [0], [2],
+[3]: pooling, element-wise, optimizer step; N = 1), `roofline` (the kernel of all those with the lowest
+fraction of the measured HBM peak), `ref_cuda` columns (the reference's own CUDA kernels, compiled unmodified,
+timed on the same buffers: the kernel to beat), `cpu_baseline` (the reference's CPU path on the host cores),
+`cnn_step` (configuration [4]) with its own CPU baseline, and at N > 1 `check` (a small sharded problem
+verified against NumPy on the whole matrix).  A wrong or non-finite result makes the process exit non-zero.
 """
 from __future__ import annotations
 
@@ -32,6 +45,8 @@ ROWS32, COLS32 = 8192, 8192
 ROWS64, COLS64 = 4096, 4096
 OPS = [(op, ax) for op in ("sum", "mean", "max") for ax in (0, 1, None)]
 METRIC = "fwd+bwd HBM GB/s (sum/mean/max reductions over axis 0, axis 1, all axes; fp32 8192^2 + fp64 4096^2)"
+WORKLOAD = ("configs[1]: sum/mean/max over axis 0, axis 1, all axes, fwd + bwd (grad of ones), "
+            "fp32 (8192,8192) N(0,1) + fp64 (4096,4096) N(0,1) per GPU, rows sharded across GPUs")
 
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of each kernel of the step, from one
@@ -203,9 +218,10 @@ def kernel_table(lib, reducers, timer, reps: int, peak: float) -> list[dict]:
     return rows
 
 
-def suite_table(lib, timer, peak: float, reps: int = 10, warm: int = 3) -> list[dict]:
+def suite_table(lib, timer, peak: float, reps: int = 10, warm: int = 3, extras: bool = False) -> list[dict]:
     """Per-kernel device time for the other benchmark configurations (pool, elementwise,
-    optimizer step), each launched `reps` times back to back on inputs larger than L2."""
+    optimizer step), each launched `reps` times back to back on inputs larger than L2; with `extras` also
+    the kernels either side of the path (activations, softmax, losses, layer glue)."""
     import keydnn_v2_b200 as kd
     from keydnn_v2_b200 import pooling
 
@@ -285,6 +301,8 @@ def suite_table(lib, timer, peak: float, reps: int = 10, warm: int = 3) -> list[
         "keydnn_cuda_adam_step_f32", p.data, g.data, m.data, v.data, n, cf(1e-3), cf(0.9), cf(0.999), cf(1e-8), cf(1e-4),
         cf(0.1), cf(0.001), cf(0.1), cf(0.001), cf(1.0)))
     del p, g, v, m
+    if not extras:
+        return rows
     # activations, softmax and losses on 2^27 fp32 elements (537 MB per tensor)
     n = 1 << 27
     x = T.from_numpy(rng.standard_normal(n, dtype=np.float32))
@@ -339,10 +357,79 @@ def suite_table(lib, timer, peak: float, reps: int = 10, warm: int = 3) -> list[
     return rows
 
 
+def split_suite(rows: list[dict]) -> tuple[list[dict], list[dict]]:
+    """Rows of the benchmark configurations ([0], [2], [3]: names carry _c1_ / _c3_ / _c4_) and the rest
+    (activations, softmax, losses, layer glue: kernels either side of the path)."""
+    named = [r for r in rows if any(t in r["kernel"] for t in ("_c1_", "_c3_", "_c4_"))]
+    return named, [r for r in rows if r not in named]
+
+
+def median_window(times_ms: list[float]) -> dict:
+    a = np.sort(np.asarray(times_ms, np.float64))
+    return {"n": int(a.size), "median_ms": float(np.median(a)), "min_ms": float(a[0]), "max_ms": float(a[-1])}
+
+
+def max_over_ranks(dist, values: list[float]) -> list[float]:
+    if dist is None:
+        return list(values)
+    import torch
+
+    t = torch.tensor(values, dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.tolist()]
+
+
+def sharded_result_check(lib, group, rows: int = 256, cols: int = 512) -> dict:
+    """A small row-sharded matrix reduced by all ranks, verified on every rank against NumPy on the whole matrix
+    (every rank can rebuild all shards from their seeds): sums / means over axis 0 and all axes to rounding,
+    maxima and their global first positions exactly.  Raises on a mismatch."""
+    import keydnn_v2_b200 as kd
+    from keydnn_v2_b200.sharded import ExchangeBucket, ShardedReductions
+
+    world, rank = group.world, group.rank
+    out = {}
+    for dt, tol in ((np.float32, dict(rtol=2e-5, atol=1e-4)), (np.float64, dict(rtol=1e-12, atol=1e-10))):
+        shards = [np.random.default_rng(1000 + r).standard_normal((rows, cols)).astype(dt) for r in range(world)]
+        shards[world // 2][3, 5] = shards[0][7, 5] = 9.5          # a tie across ranks: the lower global row must win
+        whole = np.concatenate(shards, axis=0)
+        bucket = ExchangeBucket.for_matrices(group, [(cols, dt)]) if world > 1 else None
+        red = ShardedReductions(kd.Tensor.from_numpy(shards[rank]), group, bucket=bucket)
+        for op, ax in (("sum", 0), ("mean", 0), ("sum", None), ("mean", None), ("max", 0), ("max", None)):
+            red.forward(op, ax, defer=True)
+        red.finish()
+        lib.call("keydnn_cuda_synchronize")
+
+        def read(ptr, n, dtype):
+            a = np.empty(n, dtype)
+            lib.call("keydnn_cuda_memcpy_d2h", a.ctypes.data, ptr, a.nbytes)
+            return a
+
+        w64 = whole.astype(np.float64)
+        np.testing.assert_allclose(read(*red.result("sum", 0), dt), w64.sum(0), **tol)
+        np.testing.assert_allclose(read(*red.result("mean", 0), dt), w64.mean(0), **tol)
+        np.testing.assert_allclose(read(*red.result("sum", None), dt)[0], w64.sum(), **tol)
+        np.testing.assert_allclose(read(*red.result("mean", None), dt)[0], w64.mean(), **tol)
+        np.testing.assert_array_equal(read(*red.result("max", 0), dt), whole.max(0))
+        np.testing.assert_array_equal(read(*red.result("max", None), dt)[0], whole.max())
+        if world > 1:
+            np.testing.assert_array_equal(read(red._iglobal[0].dev_ptr, cols, np.int64), whole.argmax(0))
+            np.testing.assert_array_equal(read(red._iglobal[None].dev_ptr, 1, np.int64)[0], whole.argmax())
+        # backward of max over axis 0: only the owner of each maximum writes the routed value
+        gx = red.backward("max", 0)
+        lib.call("keydnn_cuda_synchronize")
+        mine = read(gx, rows * cols, dt).reshape(rows, cols)
+        want = np.zeros_like(whole)
+        want[whole.argmax(0), np.arange(cols)] = 1
+        np.testing.assert_array_equal(mine, want[rank * rows:(rank + 1) * rows])
+        out[np.dtype(dt).name] = "ok"
+        del red, bucket
+    return {"sharded_vs_numpy": "ok", "shape_per_rank": [rows, cols], "world": world, **out}
+
+
 def run_ours(args) -> None:
     import keydnn_v2_b200 as kd
     from keydnn_v2_b200 import distributed
-    from keydnn_v2_b200.sharded import ShardedReductions
+    from keydnn_v2_b200.sharded import ExchangeBucket, ShardedReductions
 
     rank, world, local = _env_int("RANK", 0), _env_int("WORLD_SIZE", 1), _env_int("LOCAL_RANK", 0)
     lib = kd.load()
@@ -357,30 +444,42 @@ def run_ours(args) -> None:
         group = distributed.init_from_torch(device=local)
     else:
         group = distributed.single(lib)
+    steps, warmup, windows = max(1, args.steps), max(args.warmup, 3), max(1, args.windows)
+    kernels_mode = args.kernels
+    if kernels_mode == "auto":
+        kernels_mode = "suite" if world == 1 else "step"
+
+    def finish(code: int = 0) -> None:
+        if dist is not None:
+            group.destroy()
+            dist.destroy_process_group()
+        if code:
+            sys.exit(code)
 
     if args.workload == "cnn":
         timer = Timer(lib)
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        cnn = cnn_step_bench(lib, group, dist, args.steps, args.warmup, timer)
+        cnn = cnn_step_bench(lib, group, dist, steps, warmup, windows, timer)
         clocks = sampler.stop() if rank == 0 else None
         if rank == 0:
+            cnn["cpu_baseline"] = cnn_cpu_baseline() if world == 1 else None
             print(json.dumps({
                 "metric": "CNN training step samples/s (configs[4])", "value": cnn["samples_per_s"], "unit": "samples/s",
-                "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": cnn["ms_per_step"],
+                "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": cnn["ms_per_step"],
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": "configs[4]: " + cnn["model"], "global_batch": cnn["batch_per_gpu"] * world,
-                           "parallelism": cnn["parallelism"]},
+                           "parallelism": cnn["parallelism"], "timing": cnn["timing"]},
                 "e2e": {"value": cnn["e2e_samples_per_s"], "unit": "samples/s",
                         "h2d_bytes_per_step": cnn["h2d_bytes_per_step"], "d2h_bytes_per_step": cnn["d2h_bytes_per_step"]},
+                "gpu_launches": cnn["gpu_launches"], "windows": cnn["windows"], "cpu_baseline": cnn["cpu_baseline"],
                 "clocks": clocks, "cnn_step": cnn}), flush=True)
-        if dist is not None:
-            group.destroy()
-            dist.destroy_process_group()
+        finish(0 if cnn["check"]["ok"] else 3)
         return
 
-    # everything below runs on a created stream (the legacy default stream cannot be recorded into a graph)
+    # everything below runs on a created stream (the legacy default stream cannot be recorded into a graph);
+    # the cuDNN / cuBLAS library follows it (one stream state for both libraries)
     work_stream = ctypes.c_uint64(0)
     lib.call("keydnn_cuda_stream_create", ctypes.byref(work_stream))
     lib.call("keydnn_cuda_set_stream", work_stream.value)
@@ -388,20 +487,22 @@ def run_ours(args) -> None:
     T = kd.Tensor
     h32 = rng.standard_normal((ROWS32, COLS32), dtype=np.float32)
     h64 = rng.standard_normal((ROWS64, COLS64))
-    r32 = ShardedReductions(T.from_numpy(h32), group)
-    r64 = ShardedReductions(T.from_numpy(h64), group)
+    # at N > 1 both matrices put their partials into one send buffer: one all-gather per step for everything
+    bucket = ExchangeBucket.for_matrices(group, [(COLS32, np.float32), (COLS64, np.float64)]) if world > 1 else None
+    r32 = ShardedReductions(T.from_numpy(h32), group, bucket=bucket)
+    r64 = ShardedReductions(T.from_numpy(h64), group, bucket=bucket)
     reducers = [(r32, "f32"), (r64, "f64")]
     timer = Timer(lib)
     launches = [0]
 
     def step() -> None:
         # all forward reductions, then all backward passes (the order of a graph with eighteen reduction heads);
-        # the forward partials cross ranks in one bucket per matrix once the forward kernels are enqueued
+        # the forward partials of both matrices cross ranks in one bucket once the forward kernels are enqueued
         for op, ax in OPS:
             for red, _ in reducers:
                 red.forward(op, ax, defer=True)
         for red, _ in reducers:
-            red.flush()                  # one all-reduce + one all-gather per matrix, under the backward kernels
+            red.flush()                  # one all-gather for everything (the first call moves it), under the backward kernels
         for op, ax in OPS:
             for red, _ in reducers:
                 red.backward(op, ax)
@@ -420,21 +521,22 @@ def run_ours(args) -> None:
         lib.call("keydnn_cuda_synchronize")
         del r32, r64, reducers
         lib.call("keydnn_cuda_empty_cache")
-        suite_table(lib, timer, 1.0, reps=1, warm=0)
+        if kernels_mode in ("suite", "full"):
+            suite_table(lib, timer, 1.0, reps=1, warm=0, extras=kernels_mode == "full")
         lib.call("keydnn_cuda_synchronize")
         print("once: every kernel launched one time", flush=True)
         return
 
     # the clock sampler (one nvidia-smi process) is started before the warm-up: its start-up talks to the driver
-    # for tens of ms and must not fall into the K timed steps; its samples are kept from the end of the warm-up on
+    # for tens of ms and must not fall into the timed steps; its samples are kept from the end of the warm-up on
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(warmup):
         step()
     barrier()
     # At N > 1 the step (kernels, the second stream's collectives, the events between them) is recorded once and
-    # replayed with one launch per step: the ranks meet in four collectives per step, so a rank whose host thread
+    # replayed with one launch per step: the ranks meet in the collectives of every step, so a rank whose host thread
     # is late with its ~120 enqueue calls holds all of them up; a replay takes the host out of the loop.
     # (At N = 1 nothing waits on another process and the eager enqueue is far ahead of the GPU.)
     run_step, stepping, step_graph = step, "eager", ctypes.c_uint64(0)
@@ -456,26 +558,30 @@ def run_ours(args) -> None:
                 run_step()
         except Exception as exc:  # noqa: BLE001
             run_step, stepping = step, f"eager (graph capture failed: {type(exc).__name__})"
-        flags = [stepping]
-        if dist is not None:
-            gathered = [None] * world
-            dist.all_gather_object(gathered, stepping)
-            flags = gathered
-        if any(f != "cuda graph replay" for f in flags):        # all ranks replay, or none does
+        gathered = [None] * world
+        dist.all_gather_object(gathered, stepping)
+        if any(f != "cuda graph replay" for f in gathered):        # all ranks replay, or none does
             run_step, stepping = step, "eager"
-        barrier()
-    sampler.mark()
-    launches[0] = 0
     # the host only enqueues; a cyclic-collector pass of the interpreter (tens of ms once torch is imported at N > 1)
-    # inside K steps of ~1 ms would starve the GPU, so the collector is paused for the timed regions
+    # inside K steps of ~1 ms would starve the GPU, so the collector runs now and is paused for the timed regions
     gc.collect()
     gc.disable()
-    timer.start()
-    for _ in range(args.steps):
-        run_step()
-    ms = timer.stop_ms()
     barrier()
-    n_launch = launches[0]
+    sampler.mark()
+    launches[0] = 0
+    window_ms = []
+    for _ in range(windows):
+        barrier()
+        if world > 1:
+            run_step()                   # untimed: its collectives line the ranks up on the device after the host barrier
+            launches[0] -= 2 * len(OPS) * len(reducers)
+        timer.start()
+        for _ in range(steps):
+            run_step()
+        window_ms.append(timer.stop_ms())
+    barrier()
+    n_launch = launches[0] // windows
+    window_ms = max_over_ranks(dist, window_ms)
     if step_graph.value:
         lib.call("keydnn_cuda_graph_destroy", step_graph.value)
 
@@ -528,84 +634,259 @@ def run_ours(args) -> None:
             d2h[0] += red.cols * red.dt.itemsize
 
     e2e_step()
-    barrier()
-    gc.collect()
-    e2e_steps = max(2, min(args.steps, 5))
-    t0 = time.perf_counter()
-    timer.start()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e2e_ms = timer.stop_ms()
-    e2e_wall = (time.perf_counter() - t0) * 1e3
+    e2e_steps = max(2, min(steps, 5))
+    e2e_windows = max(1, min(windows, 5))
+    e2e_window_ms = []
+    for _ in range(e2e_windows):
+        barrier()
+        t0 = time.perf_counter()
+        timer.start()
+        for _ in range(e2e_steps):
+            e2e_step()
+        dev_ms = timer.stop_ms()
+        e2e_window_ms.append(max(dev_ms, (time.perf_counter() - t0) * 1e3))     # the last read-back ends on the host
     barrier()
     clocks = sampler.stop() if rank == 0 else None
+    e2e_window_ms = max_over_ranks(dist, e2e_window_ms)
 
-    if dist is not None:
-        import torch
-
-        t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+    # a wrong answer must not pass as a number: at N > 1 a small sharded problem is verified against NumPy
+    check = {"ok": True}
+    if world > 1:
+        try:
+            check.update(sharded_result_check(lib, group))
+        except AssertionError as exc:
+            check = {"ok": False, "sharded_vs_numpy": "FAILED: " + str(exc)[:400]}
+        flags = [None] * world
+        dist.all_gather_object(flags, check["ok"])
+        check["ok"] = all(flags)
 
     # per-kernel timings run on every rank; rank 0 reports its own
     peak, peak_src = measured_peak_gbs()
     # (at N > 1 the table times the local kernels alone: same shards, no exchange behind them)
-    local = reducers if world == 1 else [(ShardedReductions(red.x, distributed.single(lib)), tag) for red, tag in reducers]
-    table = kernel_table(lib, local, timer, 20, peak) if args.kernels != "none" else None
-    del local
-    suite = suite_table(lib, timer, peak) if args.kernels == "suite" else None
+    local_red = reducers if world == 1 else [(ShardedReductions(red.x, distributed.single(lib)), tag) for red, tag in reducers]
+    table = kernel_table(lib, local_red, timer, 20, peak) if kernels_mode != "none" else None
+    ref_rows = {}
+    if table is not None and world == 1 and args.ref_cuda == "on":
+        ref_rows.update(ref_cuda_reductions(lib, timer, local_red))
+    del local_red
+    suite = extras = None
     line = None
     if rank == 0:
+        w = median_window(window_ms)
+        ew = median_window(e2e_window_ms)
+        ms, e2e_ms = w["median_ms"], ew["median_ms"]
         bytes_step = algorithmic_bytes_per_step()
-        value = bytes_step * world * args.steps / ms / 1e6
-        e2e_val = bytes_step * world * e2e_steps / max(e2e_ms, e2e_wall) / 1e6
+        value = bytes_step * world * steps / ms / 1e6
+        e2e_val = bytes_step * world * e2e_steps / e2e_ms / 1e6
         line = {
-            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": round(ms / steps, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32+f64", "data": "synthetic",
-            "config": {"workload": "configs[1]: sum/mean/max over axis 0, axis 1, all axes, fwd + bwd (grad of ones), "
-                                   "fp32 (8192,8192) N(0,1) + fp64 (4096,4096) N(0,1) per GPU, rows sharded across GPUs",
+            "config": {"workload": WORKLOAD,
                        "l2": "inputs larger than L2 (268 MB and 134 MB vs 126 MB); no flush",
-                       "collectives": "none" if world == 1 else "NCCL all-reduce / all-gather of axis-0 and all-axes partials, "
-                                                                 "one bucket of each per matrix and step",
-                       "stepping": stepping},
+                       "collectives": "none" if world == 1 else "one NCCL all-gather per step carrying the axis-0 and all-axes partials of "
+                                                                 "both matrices; sums formed locally in rank order",
+                       "stepping": stepping,
+                       "timing": f"median of {windows} windows of {steps} steps, each between barriers, max over ranks per window"},
+            "windows": {"n": w["n"], "steps_per_window": steps,
+                        "ms_per_step": {"median": round(w["median_ms"] / steps, 4), "min": round(w["min_ms"] / steps, 4),
+                                        "max": round(w["max_ms"] / steps, 4)},
+                        "value_gbs": {"best": round(bytes_step * world * steps / w["min_ms"] / 1e6, 1),
+                                      "worst": round(bytes_step * world * steps / w["max_ms"] / 1e6, 1)}},
             "e2e": {"value": round(e2e_val, 1), "unit": "GB/s", "h2d_bytes_per_step": int(p32.nbytes + p64.nbytes),
-                    "d2h_bytes_per_step": int(d2h[0]), "steps": e2e_steps},
-            "gpu_launches": n_launch, "clocks": clocks,
+                    "d2h_bytes_per_step": int(d2h[0]), "steps": e2e_steps, "windows": ew["n"],
+                    "ms_per_step": {"median": round(ew["median_ms"] / e2e_steps, 3), "min": round(ew["min_ms"] / e2e_steps, 3),
+                                    "max": round(ew["max_ms"] / e2e_steps, 3)}},
+            "gpu_launches": n_launch, "clocks": clocks, "check": check,
         }
+    # the other benchmark configurations' kernels need the memory of the reducers
+    del r32, r64, reducers
+    lib.call("keydnn_cuda_empty_cache")
+    if kernels_mode in ("suite", "full"):
+        rows = suite_table(lib, timer, peak, extras=kernels_mode == "full")
+        suite, extras = split_suite(rows)
+        if world == 1 and args.ref_cuda == "on":
+            lib.call("keydnn_cuda_empty_cache")
+            ref_rows.update(ref_cuda_suite(lib, timer))
+    if rank == 0:
         if table is not None:
-            top = max(table, key=lambda r: r["us"])
-            line["roofline"] = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["gbs"], "peak": peak,
-                                "unit": "GB/s", "frac": top["frac"], "traffic": NCU_TRAFFIC_BYTES.get(top["kernel"]),
+            named = table + (suite or [])
+            for r in named:
+                if r["kernel"] in ref_rows:
+                    r["ref_cuda_us"] = ref_rows[r["kernel"]]["us"]
+                    r["ref_cuda_gbs"] = ref_rows[r["kernel"]]["gbs"]
+                    r["speedup_vs_ref_cuda"] = round(r["gbs"] / ref_rows[r["kernel"]]["gbs"], 2)
+            worst = min(named, key=lambda r: r["frac"])
+            slowest = max(table, key=lambda r: r["us"])
+            line["roofline"] = {"bound": "hbm", "kernel": worst["kernel"], "achieved": worst["gbs"], "peak": peak,
+                                "unit": "GB/s", "frac": worst["frac"], "traffic": NCU_TRAFFIC_BYTES.get(worst["kernel"]),
                                 "traffic_unit": "bytes per launch (ncu dram read+write, captured once; summary under profiles/)",
-                                "algorithmic_bytes": top["bytes"], "peak_source": peak_src,
-                                "frac_of_nominal_8000": round(top["gbs"] / 8000.0, 4)}
+                                "algorithmic_bytes": worst["bytes"], "peak_source": peak_src,
+                                "frac_of_nominal_8000": round(worst["gbs"] / 8000.0, 4),
+                                "choice": "lowest fraction among the kernels of configs[0]-[3] timed in this run",
+                                "kernels_below_0.857": sorted(r["kernel"] for r in named if r["frac"] < 0.857),
+                                "slowest_kernel_of_the_step": {"kernel": slowest["kernel"], "us": slowest["us"],
+                                                               "frac": slowest["frac"]}}
             line["kernels"] = table
             if suite is not None:
                 line["suite"] = suite
+            if extras:
+                line["extras"] = extras
+            line["ref_cuda"] = ({"library": "the reference's hot-path .cu files compiled unmodified for sm_100a (oracle/_ref)",
+                                 "kernels": len(ref_rows)} if ref_rows else
+                                {"unavailable": "oracle/_ref/libkeydnn_ref_cuda.so not built, N > 1, or --ref-cuda off"})
             line["whole_step_frac"] = round(value / world / peak, 4)
         # timed at N = 1 only: at N > 1 the other ranks would sit in the next collective while rank 0 computes
         line["cpu_baseline"] = cpu_baseline_sample() if world == 1 else None
     cnn = None
     if args.cnn != "off":
-        del r32, r64, reducers
-        lib.call("keydnn_cuda_empty_cache")
-        cnn = cnn_step_bench(lib, group, dist, max(args.steps, 10), args.warmup, timer)
+        cnn = cnn_step_bench(lib, group, dist, max(steps, 10), warmup, windows, timer)
+        if rank == 0 and world == 1:
+            cnn["cpu_baseline"] = cnn_cpu_baseline()
+        check["ok"] = check["ok"] and cnn["check"]["ok"]
     if rank == 0:
         line["cnn_step"] = cnn
         print(json.dumps(line), flush=True)
-    if dist is not None:
-        group.destroy()
-        dist.destroy_process_group()
+    finish(0 if check["ok"] else 3)
+
+
+# ---------------------------------------------------------------------------
+# the reference's own CUDA kernels (compiled unmodified into oracle/_ref), timed on the same buffers
+# ---------------------------------------------------------------------------
+def _ref_cuda_lib():
+    path = REPO / "oracle" / "_ref" / "libkeydnn_ref_cuda.so"
+    if not path.exists():
+        return None
+    from keydnn_v2_b200._native import Native
+
+    try:
+        return Native(path, strict=False)
+    except Exception:  # noqa: BLE001
+        return None
+
+
+class _LegacyStream:
+    """The reference library launches on the legacy default stream: while it is timed this library's stream (and
+    so the timer's events) is that stream as well."""
+
+    def __init__(self, lib) -> None:
+        self.lib, self.prev = lib, ctypes.c_uint64(0)
+
+    def __enter__(self):
+        self.lib.call("keydnn_cuda_synchronize")
+        self.lib.call("keydnn_cuda_get_stream", ctypes.byref(self.prev))
+        self.lib.call("keydnn_cuda_set_stream", 0)
+        return self
+
+    def __exit__(self, *exc):
+        self.lib.call("keydnn_cuda_synchronize")
+        self.lib.call("keydnn_cuda_set_stream", self.prev.value)
+
+
+def _time_ref(timer, nbytes: float, fn, reps: int = 3) -> dict:
+    fn()
+    timer.start()
+    for _ in range(reps):
+        fn()
+    ms = timer.stop_ms() / reps
+    return {"us": round(ms * 1e3, 2), "gbs": round(nbytes / ms / 1e6, 1)}
+
+
+def ref_cuda_reductions(lib, timer, reducers) -> dict:
+    """configs[1] through the reference's kernels: the same nine reductions forward, and backward as its Python
+    callers run it (the max backward includes the zero-fill its scatter kernel needs, ops/reduce_cuda.py:409-414).
+    Axis-wise mean and all-element max do not exist there."""
+    ref = _ref_cuda_lib()
+    if ref is None:
+        return {}
+    out = {}
+    with _LegacyStream(lib):
+        for red, tag in reducers:
+            x, rows, cols, nb = red.x.data, red.rows, red.cols, red.x.nbytes
+            y, idx, gx, go = red._sel[0].data, red._iglobal[0].dev_ptr, red.gx.data, red.ones.data
+            row_y, row_idx = red._out[("sum", 1)].data, red._idx[("max", 1)].dev_ptr
+            s = tag
+            cases = {
+                f"sum_axis0_fwd_{s}": lambda: ref.call(f"keydnn_cuda_sum_axis2d_forward_{s}", x, y, rows, cols, 0),
+                f"sum_axis1_fwd_{s}": lambda: ref.call(f"keydnn_cuda_sum_axis2d_forward_{s}", x, row_y, rows, cols, 1),
+                f"sum_all_fwd_{s}": lambda: ref.call(f"keydnn_cuda_sum_all_{s}", x, y, rows * cols),
+                f"mean_all_fwd_{s}": lambda: ref.call(f"keydnn_cuda_mean_all_{s}", x, y, rows * cols),
+                f"max_axis0_fwd_{s}": lambda: ref.call(f"keydnn_cuda_max_axis2d_forward_{s}", x, y, idx, rows, cols, 0),
+                f"max_axis1_fwd_{s}": lambda: ref.call(f"keydnn_cuda_max_axis2d_forward_{s}", x, row_y, row_idx, rows, cols, 1),
+                f"sum_axis0_bwd_{s}": lambda: ref.call(f"keydnn_cuda_sum_axis2d_backward_{s}", go, gx, rows, cols, 0),
+                f"sum_axis1_bwd_{s}": lambda: ref.call(f"keydnn_cuda_sum_axis2d_backward_{s}", go, gx, rows, cols, 1),
+                f"sum_all_bwd_{s}": lambda: ref.call(f"keydnn_cuda_sum_backward_fill_{s}", go, gx, rows * cols),
+                f"mean_all_bwd_{s}": lambda: ref.call(f"keydnn_cuda_mean_backward_fill_{s}", go, gx, rows * cols),
+            }
+            # indices for the max backward come from the forward just above
+            ref.call(f"keydnn_cuda_max_axis2d_forward_{s}", x, y, idx, rows, cols, 0)
+            ref.call(f"keydnn_cuda_max_axis2d_forward_{s}", x, row_y, row_idx, rows, cols, 1)
+
+            def max_bwd(axis, ip):
+                ref.call("keydnn_cuda_memset", gx, 0, nb)
+                ref.call(f"keydnn_cuda_max_axis2d_backward_{s}", go, ip, gx, rows, cols, axis)
+
+            cases[f"max_axis0_bwd_{s}"] = lambda: max_bwd(0, idx)
+            cases[f"max_axis1_bwd_{s}"] = lambda: max_bwd(1, row_idx)
+            for name, fn in cases.items():
+                out[name] = _time_ref(timer, nb, fn)
+    return out
+
+
+def ref_cuda_suite(lib, timer) -> dict:
+    """configs[0], [2], [3] through the reference's kernels (kernel only: its padding / cropping passes around the
+    pooling kernels are left out, the zero-fill its scatter / gather backward kernels need is included).  AvgPool
+    at the full configs[3] size cannot be launched by the reference (N*C = 65,536 exceeds gridDim.z): skipped."""
+    ref = _ref_cuda_lib()
+    if ref is None:
+        return {}
+    import keydnn_v2_b200 as kd
+
+    T = kd.Tensor
+    rng = np.random.default_rng(7)
+    out = {}
+    with _LegacyStream(lib):
+        x = T.from_numpy(rng.uniform(-1, 1, (32, 64, 112, 112)).astype(np.float32))
+        go = T.from_numpy(rng.standard_normal((32, 64, 56, 56), dtype=np.float32))
+        y, gx = T.empty((32, 64, 56, 56)), T.empty(x.shape)
+        idx = kd.Tensor.empty((32 * 64 * 56 * 56 * 2,))          # int64 positions
+        nb = x.nbytes + y.nbytes + y.numel * 8
+        out["maxpool2d_fwd_c1_f32"] = _time_ref(timer, nb, lambda: ref.call(
+            "keydnn_cuda_maxpool2d_forward_f32", x.data, y.data, idx.data, 32, 64, 112, 112, 56, 56, 2, 2, 2, 2))
+
+        def pool_bwd():
+            ref.call("keydnn_cuda_memset", gx.data, 0, gx.nbytes)
+            ref.call("keydnn_cuda_maxpool2d_backward_f32", go.data, idx.data, gx.data, 32, 64, 56, 56, 112, 112)
+
+        out["maxpool2d_bwd_c1_f32"] = _time_ref(timer, nb, pool_bwd)
+        del x, go, y, gx, idx
+        x = T.from_numpy(rng.standard_normal((256, 2048, 7, 7), dtype=np.float32))
+        y, gx = T.empty((256, 2048, 1, 1)), T.empty(x.shape)
+        nb = x.nbytes + y.nbytes
+        out["global_avgpool_fwd_c4_f32"] = _time_ref(timer, nb, lambda: ref.call(
+            "keydnn_cuda_global_avgpool2d_forward_f32", x.data, y.data, 256, 2048, 7, 7))
+        out["global_avgpool_bwd_c4_f32"] = _time_ref(timer, nb, lambda: ref.call(
+            "keydnn_cuda_global_avgpool2d_backward_f32", y.data, gx.data, 256, 2048, 7, 7))
+        del x, y, gx
+        n = 1 << 28
+        a = T.from_numpy(rng.standard_normal(n, dtype=np.float32))
+        b = T.from_numpy(rng.uniform(0.5, 2.0, n).astype(np.float32))
+        y = T.empty((n,))
+        for op in ("add", "sub", "mul", "div", "gt"):
+            out[f"{op}_c3_f32"] = _time_ref(timer, 3.0 * a.nbytes, lambda op=op: ref.call(f"keydnn_cuda_{op}_f32", a.data, b.data, y.data, n))
+        out["neg_c3_f32"] = _time_ref(timer, 2.0 * a.nbytes, lambda: ref.call("keydnn_cuda_neg_f32", a.data, y.data, n))
+        del a, b, y
+    return out
 
 
 # ---------------------------------------------------------------------------
 # configs[4]: small-CNN training step, data parallel
 # ---------------------------------------------------------------------------
-def cnn_step_bench(lib, group, dist, steps: int, warmup: int, timer, batch: int = 256) -> dict:
+def cnn_step_bench(lib, group, dist, steps: int, warmup: int, windows: int, timer, batch: int = 256) -> dict:
     """Conv-BN-ReLU-MaxPool-Conv-BN-ReLU-GlobalAvgPool-Flatten-Linear, MSE, SGD-momentum; batch 256 per GPU,
     per-shard BatchNorm, one gradient all-reduce per step.  Returns samples/s with inputs resident and
-    end to end (pinned host batch copied in, loss copied out, every step)."""
+    end to end (pinned host batch copied in, loss copied out, every step), the median of `windows` windows of
+    `steps` steps each, and a result check (finite loss; identical parameters on every rank)."""
     import keydnn_v2_b200 as kd
     from keydnn_v2_b200 import nn
 
@@ -614,6 +895,7 @@ def cnn_step_bench(lib, group, dist, steps: int, warmup: int, timer, batch: int 
     model = nn.small_cnn()
     opt = nn.SGD(model.parameters(), lr=0.01, momentum=0.9, weight_decay=1e-4, group=group)
     rng = np.random.default_rng(100 + rank)
+
     def pinned(a: np.ndarray) -> np.ndarray:
         p = ctypes.c_void_p(0)
         lib.call("keydnn_cuda_host_alloc", ctypes.byref(p), a.nbytes)
@@ -645,107 +927,186 @@ def cnn_step_bench(lib, group, dist, steps: int, warmup: int, timer, batch: int 
         def run_step():
             return nn.train_step(model, opt, x, t)
 
+    if dist is not None:                          # all ranks replay, or none does
+        notes = [None] * world
+        dist.all_gather_object(notes, graph_note)
+        if any(n != "cuda graph replay" for n in notes) and graph is not None:
+            graph.close()
+            graph, graph_note = None, "eager"
+
+            def run_step():
+                return nn.train_step(model, opt, x, t)
+
     for _ in range(3):
         loss = run_step()
-    sync()
     gc.collect()
-    gc.disable()            # see run_ours: no collector pass inside the timed steps
-    timer.start()
-    for _ in range(steps):
-        loss = run_step()
-    ms = timer.stop_ms()
+    gc.disable()            # no collector pass inside the timed steps
+    sync()
+    window_ms = []
+    for _ in range(windows):
+        sync()
+        if world > 1:
+            run_step()      # untimed: its all-reduce lines the ranks up on the device after the host barrier
+        timer.start()
+        for _ in range(steps):
+            loss = run_step()
+        window_ms.append(timer.stop_ms())
     sync()
     last = loss.item()
+    e2e_window_ms = []
     if graph is not None:
         graph.loss_of(graph.step_async(hx, ht))     # builds the copy stream, events and staging buffers: not timed
+    for _ in range(max(1, min(windows, 5))):
         sync()
-    t0 = time.perf_counter()
-    timer.start()
-    if graph is not None:
-        # the public pipelined call: batch i+1 crosses PCIe on a copy stream while step i replays; every step's
-        # loss is copied to the host and read there one step later
-        pending = None
-        for _ in range(steps):
-            ticket = graph.step_async(hx, ht)
-            if pending is not None:
-                graph.loss_of(pending)
-            pending = ticket
-        graph.loss_of(pending)
-    else:
-        for _ in range(steps):
-            lib.call("keydnn_cuda_memcpy_h2d_async", x.data, hx.ctypes.data, hx.nbytes)
-            lib.call("keydnn_cuda_memcpy_h2d_async", t.data, ht.ctypes.data, ht.nbytes)
-            loss = run_step()
-            loss.item()
-    e2e_ms = max(timer.stop_ms(), (time.perf_counter() - t0) * 1e3)
+        t0 = time.perf_counter()
+        timer.start()
+        if graph is not None:
+            # the public pipelined call: batch i+1 crosses PCIe on a copy stream while step i replays; every step's
+            # loss is copied to the host and read there one step later
+            pending = None
+            for _ in range(steps):
+                ticket = graph.step_async(hx, ht)
+                if pending is not None:
+                    graph.loss_of(pending)
+                pending = ticket
+            e2e_last = graph.loss_of(pending)
+        else:
+            for _ in range(steps):
+                lib.call("keydnn_cuda_memcpy_h2d_async", x.data, hx.ctypes.data, hx.nbytes)
+                lib.call("keydnn_cuda_memcpy_h2d_async", t.data, ht.ctypes.data, ht.nbytes)
+                loss = run_step()
+                e2e_last = loss.item()
+        e2e_window_ms.append(max(timer.stop_ms(), (time.perf_counter() - t0) * 1e3))
     sync()
+    # result check: the loss is finite and fell, and every rank holds the same parameters (one all-reduced gradient)
+    flat = np.empty(opt.n, np.float32)
+    lib.call("keydnn_cuda_memcpy_d2h", flat.ctypes.data, opt.flat_p.dev_ptr, flat.nbytes)
+    digest = [float(np.sum(flat.astype(np.float64))), float(np.abs(flat).max())]
+    digests = [digest]
+    if dist is not None:
+        digests = [None] * world
+        dist.all_gather_object(digests, digest)
+    finite = bool(np.isfinite(first) and np.isfinite(last) and np.isfinite(e2e_last) and np.all(np.isfinite(flat)))
+    same = all(d == digests[0] for d in digests)
+    check = {"ok": bool(finite and same and e2e_last < first), "loss_finite": finite, "parameters_equal_on_all_ranks": same,
+             "loss_fell": bool(e2e_last < first)}
     if graph is not None:
         graph.close()
-    if dist is not None:
-        import torch
-
-        tt = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(tt[0]), float(tt[1])
-    return {"samples_per_s": round(batch * world * steps / ms * 1e3, 1), "ms_per_step": round(ms / steps, 4),
-            "e2e_samples_per_s": round(batch * world * steps / e2e_ms * 1e3, 1), "batch_per_gpu": batch, "steps": steps,
+    window_ms = max_over_ranks(dist, window_ms)
+    e2e_window_ms = max_over_ranks(dist, e2e_window_ms)
+    w, ew = median_window(window_ms), median_window(e2e_window_ms)
+    ms, e2e_ms = w["median_ms"], ew["median_ms"]
+    rate = lambda window: round(batch * world * steps / window * 1e3, 1)   # noqa: E731
+    return {"samples_per_s": rate(ms), "ms_per_step": round(ms / steps, 4),
+            "e2e_samples_per_s": rate(e2e_ms), "batch_per_gpu": batch, "steps": steps,
+            "windows": {"n": w["n"], "steps_per_window": steps,
+                        "ms_per_step": {"median": round(ms / steps, 4), "min": round(w["min_ms"] / steps, 4),
+                                        "max": round(w["max_ms"] / steps, 4)},
+                        "samples_per_s": {"best": rate(w["min_ms"]), "worst": rate(w["max_ms"])},
+                        "e2e_ms_per_step": {"median": round(e2e_ms / steps, 4), "min": round(ew["min_ms"] / steps, 4),
+                                            "max": round(ew["max_ms"] / steps, 4)}},
+            "timing": f"median of {windows} windows of {steps} steps, each between barriers, max over ranks per window",
             "h2d_bytes_per_step": int(hx.nbytes + ht.nbytes), "d2h_bytes_per_step": 4,
-            "loss_first": round(first, 6), "loss_last": round(last, 6), "stepping": graph_note,
+            "loss_first": round(first, 6), "loss_last": round(last, 6), "loss_after_e2e": round(e2e_last, 6),
+            "check": check, "stepping": graph_note,
+            "gpu_launches": "one graph launch per step (about a hundred recorded kernels)" if graph_note == "cuda graph replay" else "eager",
             "model": "Conv(3-32)-BN-ReLU-MaxPool2-Conv(32-64)-BN-ReLU-GAP-Flatten-Linear(64-10), MSE, SGD momentum 0.9 wd 1e-4",
             "parallelism": f"dp{world}, per-shard BatchNorm, one NCCL all-reduce of the flat gradient buffer per step"}
 
 
 # ---------------------------------------------------------------------------
-# CPU baseline and the reference arm
+# CPU baselines and the reference arm
 # ---------------------------------------------------------------------------
-def cpu_baseline_sample(rows32: int = ROWS32 // 4, rows64: int = ROWS64 // 4, budget_s: float = 12.0) -> dict:
-    """The reference's CPU path (single-threaded NumPy expressions) on a quarter of the rows of the configs[1]
-    matrices, repeated until about `budget_s` seconds of CPU work have been timed."""
+def _reference_cpu():
+    """The reference's own CPU code (staged under oracle/_ref/tree) if it is there, else None."""
+    try:
+        from oracle import reference_cpu
+
+        return reference_cpu if reference_cpu.available() else None
+    except Exception:  # noqa: BLE001
+        return None
+
+
+def _reduce_sample(frac: int):
+    rng = np.random.default_rng(1)
+    return (rng.standard_normal((ROWS32 // frac, COLS32), dtype=np.float32), rng.standard_normal((ROWS64 // frac, COLS64)))
+
+
+def cpu_baseline_sample(budget_s: float = 12.0) -> dict:
+    """The reference's CPU path on a slice of the rows of the configs[1] matrices, repeated until about `budget_s`
+    seconds of CPU work have been timed: its own Tensor methods and autograd when the staged copy of the
+    reference is present (kind "reference"), else the NumPy expressions those methods run (kind "port")."""
     from oracle import cpu_baseline
 
-    rng = np.random.default_rng(1)
-    x32 = rng.standard_normal((rows32, COLS32), dtype=np.float32)
-    x64 = rng.standard_normal((rows64, COLS64))
-    cpu_baseline.time_reduce_workload(x32[:64], x64[:64])
+    ref = _reference_cpu()
+    frac = 16 if ref is not None else 4
+    x32, x64 = _reduce_sample(frac)
+    run = ref.time_reduce_workload if ref is not None else cpu_baseline.time_reduce_workload
+    run(x32[:64], x64[:64])
     nbytes = seconds = 0.0
     passes = 0
     while seconds < budget_s and passes < 48:
-        r = cpu_baseline.time_reduce_workload(x32, x64)
+        r = run(x32, x64)
         nbytes += r["bytes"]
         seconds += r["seconds"]
         passes += 1
-    return {"value": round(nbytes / seconds / 1e9, 3), "unit": "GB/s", "cores": 1, "kind": "port",
-            "sample": f"{passes} passes over a quarter of the rows ({rows32}x{COLS32} fp32 + {rows64}x{COLS64} fp64, all 9 reductions "
-                      f"fwd+bwd), {seconds:.1f} s; NumPy expressions of the reference's CPU Tensor methods",
+    what = ("the reference's CPU Tensor.sum / mean / max + backward (NumPy inside, single-threaded); axis-wise mean and "
+            "all-element max, which it lacks, as NumPy expressions" if ref is not None else
+            "NumPy expressions of the reference's CPU Tensor methods")
+    return {"value": round(nbytes / seconds / 1e9, 3), "unit": "GB/s", "cores": 1, "kind": "reference" if ref is not None else "port",
+            "sample": f"{passes} passes over 1/{frac} of the rows ({x32.shape[0]}x{COLS32} fp32 + {x64.shape[0]}x{COLS64} fp64, all 9 "
+                      f"reductions fwd+bwd), {seconds:.1f} s; {what}",
             "host_cores": os.cpu_count()}
 
 
+def cnn_cpu_baseline(batch: int = 8, budget_s: float = 12.0) -> dict:
+    """configs[4] on the reference's CPU path (its Sequential.train_on_batch: OpenMP C++ convolutions, NumPy
+    BatchNorm, MSE, SGD with weight decay; it has no momentum) on a reduced batch, as samples/s."""
+    ref = _reference_cpu()
+    if ref is None:
+        return {"unavailable": "no staged copy of the reference under oracle/_ref/tree"}
+    try:
+        probe = ref.cnn_training_steps(batch, 1, warmup=1)
+        steps = int(max(2, min(16, budget_s / max(probe["seconds_per_step"], 1e-3))))
+        r = ref.cnn_training_steps(batch, steps, warmup=1)
+    except Exception as exc:  # noqa: BLE001
+        return {"unavailable": f"the reference's CPU training step failed here: {type(exc).__name__}: {exc}"[:300]}
+    return {"value": round(batch / r["seconds_per_step"], 2), "unit": "samples/s", "cores": ref.omp_threads(), "kind": "reference",
+            "sample": f"{steps} steps of batch {batch} (the benchmark uses 256 per GPU) through the reference's "
+                      f"Sequential.train_on_batch on its CPU path, {r['seconds_per_step']:.2f} s per step; plain SGD (no momentum there)",
+            "loss_first": round(r["loss_first"], 6), "loss_last": round(r["loss_last"], 6), "host_cores": os.cpu_count()}
+
+
 def run_reference(args) -> None:
+    """The reference's own CPU implementation of the workload on the host cores, same metric and unit; rank 0 only."""
     rank, world = _env_int("RANK", 0), _env_int("WORLD_SIZE", 1)
     if rank != 0:
         return
     from oracle import cpu_baseline
 
-    rng = np.random.default_rng(1)
-    rows32, rows64 = ROWS32 // 4, ROWS64 // 4          # one step = a quarter of the rows, about a second of CPU work
-    x32 = rng.standard_normal((rows32, COLS32), dtype=np.float32)
-    x64 = rng.standard_normal((rows64, COLS64))
+    ref = _reference_cpu()
+    frac = 16 if ref is not None else 4      # one step = this slice of the rows: about a second of CPU work
+    x32, x64 = _reduce_sample(frac)
+    run = ref.time_reduce_workload if ref is not None else cpu_baseline.time_reduce_workload
+    kind = "reference" if ref is not None else "port"
     for _ in range(max(1, min(args.warmup, 2))):
-        cpu_baseline.time_reduce_workload(x32, x64)
+        run(x32, x64)
     t0 = time.perf_counter()
     nbytes = 0.0
     for _ in range(args.steps):
-        nbytes += cpu_baseline.time_reduce_workload(x32, x64)["bytes"]
+        nbytes += run(x32, x64)["bytes"]
     dt = time.perf_counter() - t0
     value = nbytes / dt / 1e9
-    sample = (f"each step = a quarter of the rows ({rows32}x{COLS32} fp32 + {rows64}x{COLS64} fp64, all 9 reductions fwd+bwd) "
-              "on the host cores (NumPy is single-threaded for these expressions)")
+    sample = (f"each step = 1/{frac} of the rows ({x32.shape[0]}x{COLS32} fp32 + {x64.shape[0]}x{COLS64} fp64, all 9 reductions "
+              f"fwd+bwd) on the host cores, normalised to GB/s of the same algorithmic bytes; "
+              + ("the reference's own CPU Tensor methods and autograd (NumPy inside: single-threaded)" if ref is not None
+                 else "NumPy expressions of the reference's CPU Tensor methods (no staged copy of the reference here)"))
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32+f64", "data": "synthetic",
-        "config": {"workload": "configs[1] reductions fwd+bwd, CPU path of the reference (NumPy)"},
-        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample,
+        "config": {"workload": WORKLOAD, "rows": f"1/{frac} of the rows per step (bounded CPU sample)", "device": "host CPU"},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": 1, "kind": kind, "sample": sample,
                          "host_cores": os.cpu_count()},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
@@ -756,13 +1117,20 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--windows", type=int, default=10, help="how many times the K-step loop is timed (the median is reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--kernels", default="all", choices=["all", "none", "suite"])
+    ap.add_argument("--kernels", default="auto", choices=["auto", "none", "step", "suite", "full", "all"],
+                    help="per-kernel tables: step = the reductions of the step; suite = + configs[0], [2], [3] (pool, element-wise, "
+                         "optimizer); full = + activations / softmax / losses / layer glue; auto = suite at N = 1, step at N > 1")
     ap.add_argument("--workload", default="reduce", choices=["reduce", "cnn"],
                     help="reduce: configs[1] (the default line); cnn: only the configs[4] training step, reported as samples/s")
     ap.add_argument("--cnn", default="on", choices=["on", "off"], help="also time the small-CNN training step (configs[4])")
+    ap.add_argument("--ref-cuda", dest="ref_cuda", default="on", choices=["on", "off"],
+                    help="time the reference's own CUDA kernels (oracle/_ref) beside each kernel (N = 1)")
     ap.add_argument("--once", action="store_true", help="launch every kernel once and exit (profiler captures)")
     args = ap.parse_args()
+    if args.kernels == "all":
+        args.kernels = "step"
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -477,6 +477,14 @@ int keydnn_nccl_allreduce_sum_f32(float* buf, int64_t count);  /* in place */
 int keydnn_nccl_allreduce_sum_f64(double* buf, int64_t count);
 int keydnn_nccl_allgather(const void* send, void* recv, int64_t nbytes);
 int keydnn_nccl_broadcast(void* buf, int64_t nbytes, int root);
+/* out[i] = sum over the `world` gathered blocks, in rank order (double accumulation, one rounding), of element i,
+ * times seg_scale[k] where seg_begin[k] <= i < seg_end[k] (HOST arrays, nseg <= 8; the 1/count of a mean).
+ * stride = elements between two ranks' blocks.  Behind keydnn_nccl_allgather this is an all-reduce whose result
+ * does not depend on the collective's internal order. */
+int keydnn_cuda_rank_sum_f32(const float* blocks, int world, int64_t stride, int64_t n, float* out,
+                             const int64_t* seg_begin, const int64_t* seg_end, const float* seg_scale, int nseg);
+int keydnn_cuda_rank_sum_f64(const double* blocks, int world, int64_t stride, int64_t n, double* out,
+                             const int64_t* seg_begin, const int64_t* seg_end, const double* seg_scale, int nseg);
 /* Winner per column among `world` per-rank (value, local position) maxima; rank r's n values start at
  * vals + r*val_stride and its n positions at idx + r*idx_stride (strides in elements, so both can live
  * in one gathered block per rank): greater value, else lower rank; global position = rank*span + local;

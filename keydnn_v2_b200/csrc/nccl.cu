@@ -92,6 +92,51 @@ int argmax_select(const T* vals, const long long* idx, int world, int rank, long
     return kd::launch_status();
 }
 
+// out[i] = (sum over ranks r = 0 .. world-1, in that order, of blocks[r * stride + i]) [* scale of the segment i
+// lies in].  The sum of one element is formed in double and rounded once; up to kMaxSegments index ranges carry
+// a scale (a mean's 1/count), applied as one multiplication in the element type.  With an all-gather in front
+// this is an all-reduce whose result does not depend on the collective's internal order.
+constexpr int kMaxSegments = 8;
+template <typename T> struct Segments {
+    int n;
+    long long begin[kMaxSegments], end[kMaxSegments];
+    T scale[kMaxSegments];
+};
+
+template <typename T>
+__global__ void rank_sum_kernel(const T* __restrict__ blocks, int world, int64_t stride, int64_t n, T* __restrict__ out,
+                                Segments<T> seg) {
+    kd::pdl_prologue();
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        double s = 0.0;
+        for (int r = 0; r < world; ++r) s += static_cast<double>(blocks[r * stride + i]);
+        T v = static_cast<T>(s);
+        for (int k = 0; k < seg.n; ++k)
+            if (i >= seg.begin[k] && i < seg.end[k]) v = v * seg.scale[k];
+        out[i] = v;
+    }
+}
+
+template <typename T>
+int rank_sum(const T* blocks, int world, int64_t stride, int64_t n, T* out, const int64_t* seg_begin, const int64_t* seg_end,
+             const T* seg_scale, int nseg) {
+    if (!blocks || !out) return -1;
+    if (world <= 0 || n <= 0 || stride < n || nseg < 0 || nseg > kMaxSegments) return -2;
+    if (nseg > 0 && (!seg_begin || !seg_end || !seg_scale)) return -1;
+    Segments<T> seg;
+    seg.n = nseg;
+    for (int k = 0; k < nseg; ++k) {
+        seg.begin[k] = seg_begin[k];
+        seg.end[k] = seg_end[k];
+        seg.scale[k] = seg_scale[k];
+    }
+    (void)cudaGetLastError();
+    const unsigned grid = kd::grid_for((n + 255) / 256, 8);
+    (void)kd::launch(rank_sum_kernel<T>, dim3(grid), 256, 0, blocks, world, stride, n, out, seg);
+    return kd::launch_status();
+}
+
 }  // namespace
 
 KD_API int keydnn_nccl_unique_id(void* out128) {
@@ -168,4 +213,16 @@ KD_API int keydnn_cuda_argmax_select_f64(const double* vals, const int64_t* idx,
     return argmax_select<double>(vals, reinterpret_cast<const long long*>(idx), world, rank, span, n, val_stride,
                               idx_stride, out_val,
                                  reinterpret_cast<long long*>(out_global), reinterpret_cast<long long*>(out_local));
+}
+
+// out[i] = sum over the `world` gathered blocks (rank order, double accumulation, one rounding) of element i,
+// times seg_scale[k] where seg_begin[k] <= i < seg_end[k] (host arrays, nseg <= 8).  stride: elements between
+// two ranks' blocks.  Behind keydnn_nccl_allgather it replaces an all-reduce.
+KD_API int keydnn_cuda_rank_sum_f32(const float* blocks, int world, int64_t stride, int64_t n, float* out,
+                                    const int64_t* seg_begin, const int64_t* seg_end, const float* seg_scale, int nseg) {
+    return rank_sum<float>(blocks, world, stride, n, out, seg_begin, seg_end, seg_scale, nseg);
+}
+KD_API int keydnn_cuda_rank_sum_f64(const double* blocks, int world, int64_t stride, int64_t n, double* out,
+                                    const int64_t* seg_begin, const int64_t* seg_end, const double* seg_scale, int nseg) {
+    return rank_sum<double>(blocks, world, stride, n, out, seg_begin, seg_end, seg_scale, nseg);
 }

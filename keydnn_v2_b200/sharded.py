@@ -22,6 +22,13 @@ all-gather (both max candidate blocks lie side by side): two latency-bound colle
 instead of six, issued where the caller chooses - e.g. after the last forward kernel, so that they run
 under the streaming backward kernels and not next to the one-wave reduction kernels whose grids fill
 every SM exactly.
+
+``ExchangeBucket`` goes one step further: several ``ShardedReductions`` (say an fp32 and an fp64 matrix) place
+their partial blocks in ONE send buffer, and a flush is ONE byte all-gather for all of them followed by local
+kernels: the sums are formed from the gathered blocks in rank order (``keydnn_cuda_rank_sum``: double
+accumulation, one rounding, the mean's 1/count folded in), the maxima by the same selection as before.  One
+latency-bound collective per step instead of four, and the sum no longer depends on the order a collective
+library happens to add in.
 """
 from __future__ import annotations
 
@@ -44,13 +51,87 @@ class _View:
         self.data = self.dev_ptr = int(ptr)
 
 
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class ExchangeBucket:
+    """One send buffer shared by several ``ShardedReductions`` and one all-gather per ``flush()``.
+
+    ``nbytes`` must cover the members' needs (``ExchangeBucket.bytes_for(cols, dtype)`` each).  Create the bucket,
+    pass it to every ``ShardedReductions(x, group, bucket=bucket)``, run the forward reductions with
+    ``defer=True`` and call ``flush()`` on the bucket (or on any member) once: everything postponed by all
+    members crosses the ranks together."""
+
+    def __init__(self, group: Group, nbytes: int) -> None:
+        self.g, self.lib = group, group.native
+        self.total = _align(int(nbytes))
+        self.used = 0
+        self.members: list = []
+        self.send = CudaStorage.allocate(self.total, np.uint8)
+        self.recv = CudaStorage.allocate(self.total * group.world, np.uint8)
+        self.lib.call("keydnn_cuda_memset", self.send.dev_ptr, 0, self.total)
+        self._main = ctypes.c_uint64(0)
+        self.lib.call("keydnn_cuda_get_stream", ctypes.byref(self._main))
+        self._comm, self._ready, self._done = ctypes.c_uint64(0), ctypes.c_uint64(0), ctypes.c_uint64(0)
+        if group.world > 1:
+            self.lib.call("keydnn_cuda_stream_create", ctypes.byref(self._comm))
+            self.lib.call("keydnn_cuda_event_create", ctypes.byref(self._ready))
+            self.lib.call("keydnn_cuda_event_create", ctypes.byref(self._done))
+
+    @staticmethod
+    def bytes_for(cols: int, dtype) -> int:
+        """Bytes one (rows, cols) matrix of `dtype` needs in the bucket: its sum block and its max block."""
+        isz = np.dtype(dtype).itemsize
+        cpad = (cols + 3) // 4 * 4
+        max_bytes = 0
+        for n in (cols, 1):
+            max_bytes += (n * isz + 7) // 8 * 8 + n * 8
+        return _align((2 * cpad + 2) * isz) + _align(max_bytes)
+
+    @classmethod
+    def for_matrices(cls, group: Group, shapes) -> "ExchangeBucket":
+        """`shapes`: (cols, dtype) of every matrix that will join."""
+        return cls(group, sum(cls.bytes_for(c, d) for c, d in shapes))
+
+    def take(self, nbytes: int) -> int:
+        """Offset of a fresh 256-byte aligned piece of the send buffer."""
+        off = self.used
+        if off + _align(nbytes) > self.total:
+            raise ValueError("ExchangeBucket is too small for its members")
+        self.used += _align(nbytes)
+        return off
+
+    def flush(self) -> None:
+        todo = [(m, m._take_deferred()) for m in self.members]
+        todo = [(m, items) for m, items in todo if items]
+        if not todo:
+            return
+        lib = self.lib
+        lib.call("keydnn_cuda_event_record", self._ready.value)
+        lib.call("keydnn_cuda_set_stream", self._comm.value)
+        try:
+            lib.call("keydnn_cuda_stream_wait_event", self._ready.value)
+            self.g.allgather(self.send.dev_ptr, self.recv.dev_ptr, self.total)
+            for m, items in todo:
+                m._after_gather(items, self.recv.dev_ptr, self.total)
+            lib.call("keydnn_cuda_event_record", self._done.value)
+        finally:
+            lib.call("keydnn_cuda_set_stream", self._main.value)
+        for m, items in todo:
+            for key, _ in items:
+                m._pending.add(key)
+                m._wait_for[key] = self._done.value
+
+
 class ShardedReductions:
-    def __init__(self, x: Tensor, group: Optional[Group] = None) -> None:
+    def __init__(self, x: Tensor, group: Optional[Group] = None, bucket: Optional[ExchangeBucket] = None) -> None:
         if x.ndim != 2:
             raise ValueError("ShardedReductions needs a 2-D local shard")
         self.x = x
         self.g = group or single(x.native)
         self.lib = x.native
+        self.bucket = bucket if (bucket is not None and self.g.world > 1) else None
         self.rows, self.cols = x.shape
         self.dt = x.dtype
         self.suf = _suffix(self.dt)
@@ -62,13 +143,24 @@ class ShardedReductions:
         self._blk: Dict[Key, Tuple[object, int, int]] = {}
         # the four partials that cross ranks share one buffer: [sum ax0 | mean ax0 | sum all | mean all]
         cpad = (self.cols + 3) // 4 * 4
-        self._sumblk = Tensor.empty((2 * cpad + 2,), self.dt)
+        self._cpad = cpad
         self._sum_count = 2 * cpad + 2
-        for i, key in enumerate((("sum", 0), ("mean", 0))):
-            self._out[key] = _View(self._sumblk.data + i * cpad * isz)
-        for i, key in enumerate((("sum", None), ("mean", None))):
-            self._out[key] = _View(self._sumblk.data + (2 * cpad + i) * isz)
-        self.lib.call("keydnn_cuda_memset", self._sumblk.data, 0, self._sum_count * isz)
+        if self.bucket is not None:
+            # partials go straight into the shared send buffer; the reduced values land in a buffer of their own
+            self._sum_off = self.bucket.take(self._sum_count * isz)
+            self._sumblk = _View(self.bucket.send.dev_ptr + self._sum_off)
+            self._sumres = Tensor.empty((self._sum_count,), self.dt)
+            self.lib.call("keydnn_cuda_memset", self._sumres.data, 0, self._sum_count * isz)
+            self.bucket.members.append(self)
+        else:
+            self._sumblk = Tensor.empty((self._sum_count,), self.dt)
+            self._sumres = self._sumblk
+            self.lib.call("keydnn_cuda_memset", self._sumblk.data, 0, self._sum_count * isz)
+        self._sum_pos = {("sum", 0): 0, ("mean", 0): cpad, ("sum", None): 2 * cpad, ("mean", None): 2 * cpad + 1}
+        self._res: Dict[Key, "_View"] = {}
+        for key, pos in self._sum_pos.items():
+            self._out[key] = _View(self._sumblk.data + pos * isz)
+            self._res[key] = _View(self._sumres.data + pos * isz)
         for op in ("sum", "mean"):
             self._out[(op, 1)] = Tensor.empty((self.rows,), self.dt)
         # max: value block and position block side by side, and the two blocks that cross ranks (axis 0, all
@@ -78,9 +170,13 @@ class ShardedReductions:
             n = self.cols if ax == 0 else self.rows if ax == 1 else 1
             voff = (n * isz + 7) // 8 * 8
             sizes[ax] = (voff, voff + n * 8)
-        self._maxblk = CudaStorage.allocate(sizes[0][1] + sizes[None][1], np.uint8)
-        self.lib.call("keydnn_cuda_memset", self._maxblk.dev_ptr, 0, sizes[0][1] + sizes[None][1])
         self._maxblk_bytes = sizes[0][1] + sizes[None][1]
+        if self.bucket is not None:
+            self._max_off = self.bucket.take(self._maxblk_bytes)
+            self._maxblk = _View(self.bucket.send.dev_ptr + self._max_off)
+        else:
+            self._maxblk = CudaStorage.allocate(self._maxblk_bytes, np.uint8)
+            self.lib.call("keydnn_cuda_memset", self._maxblk.dev_ptr, 0, self._maxblk_bytes)
         own1 = CudaStorage.allocate(sizes[1][1], np.uint8)
         for ax, base, owner in ((0, self._maxblk.dev_ptr, self._maxblk), (None, self._maxblk.dev_ptr + sizes[0][1], self._maxblk),
                                 (1, own1.dev_ptr, own1)):
@@ -90,7 +186,7 @@ class ShardedReductions:
             self._idx[("max", ax)] = _View(base + voff)
         # cross-rank max: gathered candidates (per axis, and of both blocks at once) and the selection
         self._gathered = {ax: CudaStorage.allocate(w * self._blk[("max", ax)][2], np.uint8) for ax in (0, None)}
-        self._gathered_all = CudaStorage.allocate(w * self._maxblk_bytes, np.uint8)
+        self._gathered_all = CudaStorage.allocate(w * self._maxblk_bytes, np.uint8) if self.bucket is None else None
         self._deferred: list = []
         self._sel = {ax: Tensor.empty((n,), self.dt) for ax, n in ((0, self.cols), (None, 1))}
         self._iglobal = {ax: CudaStorage.allocate(n * 8, np.int64) for ax, n in ((0, self.cols), (None, 1))}
@@ -157,6 +253,9 @@ class ShardedReductions:
     def flush(self) -> None:
         """Exchange everything ``forward(..., defer=True)`` postponed: one all-reduce over the shared sum buffer,
         one all-gather over the shared max block, the mean scales and the selections behind them."""
+        if self.bucket is not None:
+            self.bucket.flush()
+            return
         if not self._deferred:
             return
         todo, self._deferred = self._deferred, []
@@ -187,6 +286,45 @@ class ShardedReductions:
 
         self._on_comm_stream([k for k, _ in todo], exchange, ("bucket", None))
 
+    # ------------------------------------------------------- shared-bucket exchange
+    def _take_deferred(self) -> list:
+        todo, self._deferred = self._deferred, []
+        return todo
+
+    def _after_gather(self, items, recv: int, total: int) -> None:
+        """Local kernels behind the bucket's all-gather (`recv` holds world blocks of `total` bytes): sums of the
+        gathered partials in rank order with the mean scales folded in, selections of the gathered maxima."""
+        lib, s, w, isz = self.lib, self.suf, self.g.world, self.dt.itemsize
+        i64, ct = ctypes.c_int64, (ctypes.c_float if self.dt == np.float32 else ctypes.c_double)
+        sums = [(k, meta) for k, meta in items if k[0] != "max"]
+        maxes = [(k, meta) for k, meta in items if k[0] == "max"]
+        base = recv + self._sum_off
+        if len(sums) == 4:
+            scales = {k: 1.0 / count for k, (n, count) in sums if k[0] == "mean"}
+            segs = [(self._sum_pos[k], self._sum_pos[k] + n, scales[k]) for k, (n, _) in sums if k[0] == "mean"]
+            lib.call(f"keydnn_cuda_rank_sum_{s}", base, w, total // isz, self._sum_count, self._sumres.data,
+                     (i64 * len(segs))(*[a for a, _, _ in segs]), (i64 * len(segs))(*[b for _, b, _ in segs]),
+                     (ct * len(segs))(*[c for _, _, c in segs]), len(segs))
+        else:
+            for k, (n, count) in sums:                                 # never touch a finished neighbour
+                off = self._sum_pos[k] * isz
+                seg = ((i64 * 1)(0), (i64 * 1)(n), (ct * 1)(1.0 / count), 1) if k[0] == "mean" else (None, None, None, 0)
+                lib.call(f"keydnn_cuda_rank_sum_{s}", base + off, w, total // isz, n, self._sumres.data + off, *seg)
+        for (op, ax), (n, span) in maxes:
+            vbase = recv + self._max_off + (self._out[(op, ax)].data - self._maxblk.dev_ptr)
+            voff = self._blk[(op, ax)][1]
+            lib.call(f"keydnn_cuda_argmax_select_{s}", vbase, vbase + voff, w, self.g.rank, span, n, total // isz, total // 8,
+                     self._sel[ax].data, self._iglobal[ax].dev_ptr, self._ilocal[ax].dev_ptr)
+
+    def result(self, op: str, axis: Optional[int]) -> Tuple[int, int]:
+        """(device pointer, element count) of the complete value of (op, axis) (after ``wait`` / ``finish``)."""
+        n = self.rows if axis == 1 else self.cols if axis == 0 else 1
+        if op == "max":
+            return (self._sel[axis].data if (self.g.world > 1 and axis != 1) else self._out[(op, axis)].data), n
+        if axis == 1:
+            return self._out[(op, axis)].data, n
+        return (self._res[(op, axis)].data if self.bucket is not None else self._out[(op, axis)].data), n
+
     # ------------------------------------------------------------------ forward
     def forward(self, op: str, axis: Optional[int], defer: bool = False) -> Tuple[int, int]:
         """Runs one reduction; returns (device pointer, element count) of the result.  At
@@ -214,6 +352,11 @@ class ShardedReductions:
                     return out, 1
                 lib.call(f"keydnn_cuda_sum_all_{s}", x.data, out, rows * cols)
                 n, count = 1, rows * cols * w
+            if self.bucket is not None:
+                self._deferred.append((key, (n, count)))
+                if not defer:
+                    self.bucket.flush()
+                return self._res[key].data, n
             if w > 1 and defer:
                 self._deferred.append((key, (n, count)))
             elif w > 1:
@@ -239,8 +382,10 @@ class ShardedReductions:
         if w == 1:
             return out, n
 
-        if defer:
+        if defer or self.bucket is not None:
             self._deferred.append((key, (n, span)))
+            if not defer:
+                self.bucket.flush()
             return self._sel[axis].data, n
         _, voff, blk_bytes = self._blk[key]
         gathered = self._gathered[axis].dev_ptr

@@ -21,9 +21,21 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     for key in ("metric", "value", "n_gpus", "steps", "warmup", "ms_per_step", "scaling", "vs_baseline", "dtype", "data",
                 "config", "cpu_baseline", "e2e"):
         assert key in d, key
-    assert d["value"] > 0 and d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] == 1
+    staged = (REPO / "oracle" / "_ref" / "tree" / ".staged").exists()        # the reference's own code, else the NumPy port
+    assert d["value"] > 0 and d["cpu_baseline"]["kind"] == ("reference" if staged else "port") and d["cpu_baseline"]["cores"] == 1
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
-    assert "workload" in d["config"] and "model" not in d["config"]
+    assert "workload" in d["config"] and "model" not in d["config"] and "rows" in d["config"]
+
+
+def test_both_arms_name_the_same_workload():
+    sys.path.insert(0, str(REPO))
+    import bench
+
+    assert bench.WORKLOAD.startswith("configs[1]") and "8192" in bench.METRIC
+    w = bench.median_window([3.0, 1.0, 2.0, 10.0, 2.5])
+    assert w == {"n": 5, "median_ms": 2.5, "min_ms": 1.0, "max_ms": 10.0}
+    named, rest = bench.split_suite([{"kernel": "add_c3_f32"}, {"kernel": "exp_f32"}, {"kernel": "maxpool2d_fwd_c1_f32"}])
+    assert [r["kernel"] for r in named] == ["add_c3_f32", "maxpool2d_fwd_c1_f32"] and [r["kernel"] for r in rest] == ["exp_f32"]
 
 
 def test_reference_arm_is_silent_on_other_ranks():

@@ -55,6 +55,10 @@ def test_sharded_reductions_match_numpy_on_the_whole_matrix(tmp_path):
                     for what in ("y", "gx"):
                         np.testing.assert_array_equal(res[r][f"{tag}/bucket/{op}/{ax}/{what}"], res[r][f"{tag}/{op}/{ax}/{what}"],
                                                       err_msg=f"bucket {tag} {op} {ax} {what}")
+                        # one shared bucket for both matrices (a single all-gather, sums formed locally in rank
+                        # order): the inputs are multiples of 1/4, so every order of addition gives the same bits
+                        np.testing.assert_array_equal(res[r][f"{tag}/shared/{op}/{ax}/{what}"], res[r][f"{tag}/{op}/{ax}/{what}"],
+                                                      err_msg=f"shared bucket {tag} {op} {ax} {what}")
                 if ax == 0:
                     np.testing.assert_array_equal(res[r][f"{tag}/partial/mean/0/y"], ym)
                     np.testing.assert_array_equal(res[r][f"{tag}/partial/sum/0/y"], ys)     # untouched by the partial bucket
