@@ -33,7 +33,7 @@ namespace {
 using StreamSource = int (*)(std::uint64_t*);
 StreamSource g_stream_source = nullptr;
 cudaStream_t g_stream = nullptr;
-cudaStream_t g_last_stream = nullptr;      // stream of the previous call: the workspace is shared between calls
+cudaStream_t g_last_stream = nullptr;      // stream of the previous call (compared, never dereferenced)
 bool g_have_last = false;
 cublasHandle_t g_blas = nullptr;
 cudnnHandle_t g_dnn = nullptr;
@@ -49,12 +49,14 @@ cudaStream_t current_stream() {
         if (g_stream_source(&v) == 0) s = reinterpret_cast<cudaStream_t>(v);
     }
     if (g_have_last && s != g_last_stream) {
-        // Calls on the previous stream may still use the shared workspace (and cuDNN's handle state): let them
-        // finish before the first call on the new stream.  While the new stream is being recorded into a graph
-        // nothing may block; the caller has run the step eagerly on that stream before recording it.
+        // Calls enqueued under the previous stream may still use the shared workspace (and cuDNN's handle state):
+        // let them finish before the first call on the new stream.  The old handle itself is not touched (its
+        // owner may have destroyed it since), so the whole device is waited for; stream changes are rare.
+        // While the new stream is being recorded into a graph nothing may block: the caller has run the step
+        // eagerly on that stream before recording it.
         cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
         if (s == nullptr || cudaStreamIsCapturing(s, &cs) != cudaSuccess) cs = cudaStreamCaptureStatusNone;
-        if (cs == cudaStreamCaptureStatusNone) cudaStreamSynchronize(g_last_stream);
+        if (cs == cudaStreamCaptureStatusNone) cudaDeviceSynchronize();
         (void)cudaGetLastError();
     }
     g_last_stream = s;
