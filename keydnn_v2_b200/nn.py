@@ -106,7 +106,7 @@ class Conv2d(Module):
 
             def backward_fn(g: Tensor):
                 gx = Tensor.empty(x.shape, x.dtype) if x.requires_grad else None
-                gw = Tensor.empty(w.shape, w.dtype)
+                gw = w.grad_buffer()
                 dnn.call(f"keydnn_cuda_conv2d_backward_ex_{s}", x.data, w.data, g.data, gx.data if gx else None, gw.data,
                          *dims)
                 if b is None:
@@ -159,8 +159,8 @@ class BatchNorm2d(Module):
 
             def backward_fn(g: Tensor):
                 dx = Tensor.empty(x.shape, x.dtype)
-                dga = Tensor.empty((C,), x.dtype) if self.affine else None
-                dbe = Tensor.empty((C,), x.dtype) if self.affine else None
+                dga = ga.grad_buffer() if self.affine else None
+                dbe = be.grad_buffer() if self.affine else None
                 lib.call(f"keydnn_cuda_bn2d_backward_bias_{s}", x.data, pb.data if pb is not None else None,
                          ga.data if ga else None, be.data if be else None, g.data, mean.data, invstd.data, dx.data,
                          dga.data if dga else None, dbe.data if dbe else None, N, C, H * W, 1 if self.fused_relu else 0)
@@ -186,8 +186,8 @@ class BatchNorm2d(Module):
 
             def backward_fn(g: Tensor):
                 dx = Tensor.empty(x.shape, x.dtype)
-                dga = Tensor.empty((C,), x.dtype) if self.affine else None
-                dbe = Tensor.empty((C,), x.dtype) if self.affine else None
+                dga = ga.grad_buffer() if self.affine else None
+                dbe = be.grad_buffer() if self.affine else None
                 lib.call(f"keydnn_cuda_bn2d_global_avgpool_backward_{s}", x.data, pb.data if pb is not None else None,
                          ga.data if ga else None, be.data if be else None, g.data, mean.data, invstd.data, dx.data,
                          dga.data if dga else None, dbe.data if dbe else None, N, C, H * W, relu)
@@ -213,8 +213,8 @@ class BatchNorm2d(Module):
 
             def backward_fn(g: Tensor):
                 dx = Tensor.empty(x.shape, x.dtype)
-                dga = Tensor.empty((C,), x.dtype) if self.affine else None
-                dbe = Tensor.empty((C,), x.dtype) if self.affine else None
+                dga = ga.grad_buffer() if self.affine else None
+                dbe = be.grad_buffer() if self.affine else None
                 lib.call(f"keydnn_cuda_bn2d_maxpool2x2_backward_{s}", x.data, pb.data if pb is not None else None,
                          ga.data if ga else None, be.data if be else None, g.data, idx.dev_ptr, mean.data, invstd.data,
                          dx.data, dga.data if dga else None, dbe.data if dbe else None, N, C, H, W, relu)
@@ -265,7 +265,7 @@ class Linear(Module):
                 if x.requires_grad:
                     gx = Tensor.empty(x.shape, x.dtype)
                     dnn.call(f"keydnn_cuda_matmul_ex_{s}", g.data, w.data, gx.data, B, I, O, 0, 0)      # g @ W
-                gw = Tensor.empty(w.shape, w.dtype)
+                gw = w.grad_buffer()
                 dnn.call(f"keydnn_cuda_matmul_ex_{s}", g.data, x.data, gw.data, O, I, B, 1, 0)          # g.T @ x
                 if b is None:
                     return (gx, gw)
@@ -376,6 +376,9 @@ class _FlatOptimizer:
         for p, o in zip(self.params, self.offsets):
             self.native.call("keydnn_cuda_memcpy_d2d", self.flat_p.dev_ptr + o, p.data, p.nbytes)
             p.storage = _ViewStorage(self.flat_p, o, p.nbytes, self.dtype)
+            # gradients are written straight into the flat buffer by the layers that compute them
+            p._grad_slot = Tensor(_ViewStorage(self.flat_g, o, p.nbytes, self.dtype), p.shape, self.dtype)
+            p._slot_taken = False
 
     def zero_grad(self) -> None:
         for p in self.params:
@@ -387,7 +390,7 @@ class _FlatOptimizer:
         for p, o in zip(self.params, self.offsets):
             if p.grad is None:
                 lib.call("keydnn_cuda_memset", self.flat_g.dev_ptr + o, 0, p.nbytes)
-            else:
+            elif p.grad.data != self.flat_g.dev_ptr + o:           # not already written in place (`Parameter.grad_buffer`)
                 lib.call("keydnn_cuda_memcpy_d2d", self.flat_g.dev_ptr + o, p.grad.data, p.nbytes)
         world = 1 if self.group is None else self.group.world
         if world > 1:

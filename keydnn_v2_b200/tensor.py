@@ -706,13 +706,33 @@ class Tensor:
 
 
 class Parameter(Tensor):
-    """Trainable leaf (``src/keydnn/infrastructure/_parameter.py``)."""
+    """Trainable leaf (``src/keydnn/infrastructure/_parameter.py``).
 
-    __slots__ = ()
+    An optimizer that keeps all gradients in one flat buffer may give a parameter a *gradient slot*: a tensor
+    of the parameter's shape inside that buffer.  The layer that computes the parameter's gradient asks for
+    ``grad_buffer()`` instead of allocating one and so writes the gradient where the optimizer (and the
+    gradient all-reduce in front of it) reads it: no copy per parameter and step.  The slot is handed out once
+    per step (``zero_grad`` re-arms it); a parameter used twice in a graph gets an ordinary buffer the second
+    time and the autograd walk adds the two as it always does."""
+
+    __slots__ = ("_grad_slot", "_slot_taken")
 
     def __init__(self, storage, shape, dtype, **kw) -> None:
         kw["requires_grad"] = True
         super().__init__(storage, shape, dtype, **kw)
+        self._grad_slot: Optional[Tensor] = None
+        self._slot_taken = False
+
+    def grad_buffer(self) -> Tensor:
+        """Where the gradient of this parameter should be written by the kernel that computes it."""
+        if self._grad_slot is not None and not self._slot_taken:
+            self._slot_taken = True
+            return self._grad_slot
+        return Tensor.empty(self.shape, self.dtype)
+
+    def zero_grad(self) -> None:
+        self.grad = None
+        self._slot_taken = False
 
     @classmethod
     def from_numpy(cls, arr: np.ndarray, **_) -> "Parameter":

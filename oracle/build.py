@@ -30,6 +30,7 @@ REF_DIR = HERE / "_ref"
 REF_NATIVE = REF_DIR / "libkeydnn_ref_native.so"
 REF_CUDA = REF_DIR / "libkeydnn_ref_cuda.so"
 REF_NATIVE_OMP = REF_DIR / "libkeydnn_ref_native_omp.so"     # all four CPU kernels files, OpenMP build
+REF_CUDA_FULL = REF_DIR / "libkeydnn_ref_cuda_full.so"       # every .cu of the reference DLL (links cuBLAS / cuDNN)
 
 # hot-path translation units of the reference CUDA library (no cuBLAS / cuDNN needed)
 REF_CUDA_SOURCES = [
@@ -99,6 +100,17 @@ def build_reference(ref_root: str | Path | None = None, force: bool = False) -> 
         _run([nvcc, "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
               "-shared", "-w", *map(str, cus), "-o", str(REF_CUDA)])
     out["cuda"] = REF_CUDA
+    # the whole reference DLL (matmul / conv2d / conv2d_transpose / stack included): the control when one of the
+    # reference's own tests fails against this repository's library - does it pass against the reference's?
+    all_cus = sorted((ref_root / REF_CUDA_SUBDIR).glob("*.cu"))
+    if force or not REF_CUDA_FULL.exists():
+        try:
+            _run([nvcc, "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
+                  "-shared", "-w", *map(str, all_cus), "-o", str(REF_CUDA_FULL), "-lcublas", "-lcudnn"])
+        except RuntimeError as exc:     # optional: needs the cuBLAS / cuDNN development files
+            print(f"reference DLL with cuBLAS / cuDNN not built: {str(exc)[:300]}", file=sys.stderr)
+    if REF_CUDA_FULL.exists():
+        out["cuda_full"] = REF_CUDA_FULL
     return out
 
 
