@@ -89,6 +89,22 @@ NCU_TRAFFIC_BYTES = {
     "max_all_fwd_f64": 138227000,
     "max_all_bwd_f32": 209150000,
     "max_all_bwd_f64": 74351000,
+    # configs[0], [2], [3] (same capture)
+    "maxpool2d_fwd_c1_f32": 130080000,
+    "maxpool2d_bwd_c1_f32": 125152000,
+    "avgpool2d_fwd_c4_f32": 1010825000,
+    "avgpool2d_bwd_c4_f32": 971990000,
+    "global_avgpool_fwd_c4_f32": 106414000,
+    "global_avgpool_bwd_c4_f32": 45580000,
+    "add_c3_f32": 3185189000,
+    "sub_c3_f32": 3181366000,
+    "mul_c3_f32": 3182574000,
+    "div_c3_f32": 3182143000,
+    "gt_c3_f32": 3184754000,
+    "neg_c3_f32": 2093558000,
+    "mul_backward_c3_f32": 5324011000,
+    "div_backward_c3_f32": 5325598000,
+    "sgd_momentum_step_c3_f32": 449905000,
 }
 
 

@@ -107,6 +107,27 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, unsigned threads,
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Launch with the CTAs of one grid column (gridDim.y) grouped into thread-block clusters of `cluster_y`: they are
+// co-scheduled on one GPC, synchronise with the hardware cluster barrier and read each other's shared memory.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_cluster_y(void (*kernel)(KArgs...), dim3 grid, unsigned threads, unsigned cluster_y, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = cluster_y;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define KD_LAUNCH(KERNEL, WORK, THREADS, SMEM, ...)                                                           \
     do {                                                                                                      \
         auto kd_fn_ = (KERNEL);                                                                               \

@@ -35,6 +35,7 @@ constexpr size_t kSmallLimit = 1u << 20;     // below this, round up to a power 
 struct DevicePool {
     std::multimap<size_t, void*> free_blocks;          // size -> block
     std::unordered_map<void*, size_t> live;            // block -> rounded size
+    std::map<uintptr_t, size_t> requested;             // live block -> bytes the caller asked for (bounds of copies)
     size_t bytes_reserved = 0;                         // total held from the driver
     size_t bytes_in_use = 0;
     size_t n_driver_mallocs = 0;
@@ -110,6 +111,24 @@ void release_cached(DevicePool& p) {
     }
     p.free_blocks.clear();
     p.freed_on.clear();
+}
+
+// Copies and memsets are checked against the size the caller asked for, not the rounded block: cudaMemcpy
+// rejects a device range that leaves its allocation (cudaErrorInvalidValue), and the reference's wrappers rely on
+// that to catch buffers that are too small (ops/matmul_cuda.py probes the last byte of every operand).  With
+// size classes the driver would let such a copy through; this keeps the answer the caller would have got from
+// a plain cudaMalloc.  Pointers that are not inside a live pool block are left to the driver.
+bool range_ok(const void* p, size_t n) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    std::lock_guard<std::mutex> lk(g_mu);
+    const auto& req = g_dev[current_device()].pool.requested;
+    auto it = req.upper_bound(a);
+    if (it == req.begin()) return true;
+    --it;
+    const auto& live = g_dev[current_device()].pool.live;
+    auto lt = live.find(reinterpret_cast<void*>(it->first));
+    if (lt == live.end() || a >= it->first + lt->second) return true;      // beyond the block: not ours to judge
+    return a + n <= it->first + it->second;
 }
 
 // The library stream of the current device (the fast path of every launch: no lock, one TLS read).
@@ -240,6 +259,7 @@ KD_API int keydnn_cuda_malloc(std::uint64_t* out_ptr, std::size_t nbytes) {
             size_t sz = ct->first;
             p.capture_free.erase(ct);
             p.live.emplace(q, sz);
+            p.requested[reinterpret_cast<uintptr_t>(q)] = nbytes;
             p.bytes_in_use += sz;
             *out_ptr = reinterpret_cast<std::uint64_t>(q);
             return 0;
@@ -253,6 +273,7 @@ KD_API int keydnn_cuda_malloc(std::uint64_t* out_ptr, std::size_t nbytes) {
         p.free_blocks.erase(it);
         hand_over(p, q, s.stream);
         p.live.emplace(q, sz);
+        p.requested[reinterpret_cast<uintptr_t>(q)] = nbytes;
         p.bytes_in_use += sz;
         if (p.capturing) p.graph_blocks.emplace(q, sz);
         *out_ptr = reinterpret_cast<std::uint64_t>(q);
@@ -274,6 +295,7 @@ KD_API int keydnn_cuda_malloc(std::uint64_t* out_ptr, std::size_t nbytes) {
     p.bytes_reserved += want;
     p.bytes_in_use += want;
     p.live.emplace(q, want);
+    p.requested[reinterpret_cast<uintptr_t>(q)] = nbytes;
     if (p.capturing) p.graph_blocks.emplace(q, want);
     *out_ptr = reinterpret_cast<std::uint64_t>(q);
     return 0;
@@ -293,6 +315,7 @@ KD_API int keydnn_cuda_free(std::uint64_t ptr) {
             if (jt != g_dev[d].pool.live.end()) {
                 size_t sz = jt->second;
                 g_dev[d].pool.live.erase(jt);
+                g_dev[d].pool.requested.erase(reinterpret_cast<uintptr_t>(q));
                 g_dev[d].pool.bytes_in_use -= sz;
                 g_dev[d].pool.free_blocks.emplace(sz, q);
                 g_dev[d].pool.freed_on[q] = g_dev[d].stream;
@@ -303,6 +326,7 @@ KD_API int keydnn_cuda_free(std::uint64_t ptr) {
     }
     size_t sz = it->second;
     p.live.erase(it);
+    p.requested.erase(reinterpret_cast<uintptr_t>(q));
     p.bytes_in_use -= sz;
     if (p.graph_blocks.count(q)) {
         // owned by a recorded graph: reusable only inside the recording, never by anybody else
@@ -361,6 +385,7 @@ KD_API int keydnn_cuda_mem_info(std::uint64_t* out2) {
 
 KD_API int keydnn_cuda_memcpy_h2d(std::uint64_t dst_dev, const void* src_host, std::size_t nbytes) {
     if (nbytes == 0) return 0;
+    if (!range_ok(reinterpret_cast<const void*>(dst_dev), nbytes)) return static_cast<int>(cudaErrorInvalidValue);
     cudaError_t st = cudaMemcpyAsync(reinterpret_cast<void*>(dst_dev), src_host, nbytes,
                                      cudaMemcpyHostToDevice, dev_stream());
     if (st != cudaSuccess) return static_cast<int>(st);
@@ -371,6 +396,7 @@ KD_API int keydnn_cuda_memcpy_h2d(std::uint64_t dst_dev, const void* src_host, s
 
 KD_API int keydnn_cuda_memcpy_d2h(void* dst_host, std::uint64_t src_dev, std::size_t nbytes) {
     if (nbytes == 0) return 0;
+    if (!range_ok(reinterpret_cast<const void*>(src_dev), nbytes)) return static_cast<int>(cudaErrorInvalidValue);
     cudaError_t st = cudaMemcpyAsync(dst_host, reinterpret_cast<const void*>(src_dev), nbytes,
                                      cudaMemcpyDeviceToHost, dev_stream());
     if (st != cudaSuccess) return static_cast<int>(st);
@@ -381,6 +407,7 @@ KD_API int keydnn_cuda_memcpy_d2h(void* dst_host, std::uint64_t src_dev, std::si
 // source must stay valid and, to overlap, be pinned).
 KD_API int keydnn_cuda_memcpy_h2d_async(std::uint64_t dst_dev, const void* src_host, std::size_t nbytes) {
     if (nbytes == 0) return 0;
+    if (!range_ok(reinterpret_cast<const void*>(dst_dev), nbytes)) return static_cast<int>(cudaErrorInvalidValue);
     return kd::status(cudaMemcpyAsync(reinterpret_cast<void*>(dst_dev), src_host, nbytes,
                                       cudaMemcpyHostToDevice, dev_stream()));
 }
@@ -389,6 +416,7 @@ KD_API int keydnn_cuda_memcpy_h2d_async(std::uint64_t dst_dev, const void* src_h
 // asynchronous) may be read after an event recorded behind the copy has completed.
 KD_API int keydnn_cuda_memcpy_d2h_async(void* dst_host, std::uint64_t src_dev, std::size_t nbytes) {
     if (nbytes == 0) return 0;
+    if (!range_ok(reinterpret_cast<const void*>(src_dev), nbytes)) return static_cast<int>(cudaErrorInvalidValue);
     return kd::status(cudaMemcpyAsync(dst_host, reinterpret_cast<const void*>(src_dev), nbytes,
                                       cudaMemcpyDeviceToHost, dev_stream()));
 }
@@ -396,12 +424,14 @@ KD_API int keydnn_cuda_memcpy_d2h_async(void* dst_host, std::uint64_t src_dev, s
 KD_API int keydnn_cuda_memcpy_d2d(void* dst, const void* src, std::size_t nbytes) {
     if (nbytes == 0) return 0;
     if (!dst || !src) return 1;
+    if (!range_ok(dst, nbytes) || !range_ok(src, nbytes)) return 2;
     cudaError_t st = cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToDevice, dev_stream());
     return st == cudaSuccess ? 0 : 2;
 }
 
 KD_API int keydnn_cuda_memset(std::uint64_t dev_ptr, int value, std::size_t nbytes) {
     if (nbytes == 0) return 0;
+    if (!range_ok(reinterpret_cast<const void*>(dev_ptr), nbytes)) return static_cast<int>(cudaErrorInvalidValue);
     return kd::status(cudaMemsetAsync(reinterpret_cast<void*>(dev_ptr), value, nbytes, dev_stream()));
 }
 

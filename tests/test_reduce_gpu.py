@@ -101,6 +101,70 @@ def test_max_axis2d_forward_backward_bit_exact(oracle, shape, dtype):
             assert_same_bits(dgz.get(), want)
 
 
+@pytest.mark.parametrize("shape", [(1000, 2500), (4096, 4096), (513, 3072), (2047, 4104)])
+def test_fp64_column_reductions_through_the_cluster_kernels(oracle, shape):
+    """Shapes for which the row chunks of a column stripe form one thread-block cluster (8-byte elements, about
+    sixteen chunks per stripe fill the machine) and the fold goes through distributed shared memory: ragged last
+    stripe, ragged last chunk, ties, NaN and -inf columns; sums to rounding, maxima and first rows exactly, twice
+    in a row with the same bits."""
+    lib = native()
+    rows, cols = shape
+    rng = np.random.default_rng(rows + cols)
+    x = rng.standard_normal(shape)
+    x[:, 3] = -np.inf
+    x[:, 5] = np.nan
+    x[::7, 11] = 4.25                                 # ties: the first of them must win
+    x[rows // 2, 17] = np.nan
+    x[rows - 1, cols - 1] = 99.0                      # last row of the last (ragged) chunk and stripe
+    dx = Buf(lib, x)
+    dy, di = Buf(lib, shape=(cols,), dtype=np.float64, fill=0xFF), Buf(lib, shape=(cols,), dtype=np.int64, fill=0xFF)
+    clean = np.where(np.isnan(x), 0.0, x)
+    clean[:, 3] = 0.0
+    dc = Buf(lib, clean)
+    for _ in range(2):
+        lib.call("keydnn_cuda_max_axis2d_forward_f64", dx.ptr, dy.ptr, di.ptr, rows, cols, 0)
+        val, idx = oracle.max_axis2d(x, 0)
+        np.testing.assert_array_equal(dy.get(), val)
+        np.testing.assert_array_equal(di.get(), idx)
+    assert di.get()[11] == 0 and di.get()[cols - 1] == rows - 1 and di.get()[3] == 0 and dy.get()[5] == -np.inf
+    first = None
+    for _ in range(2):
+        lib.call("keydnn_cuda_sum_axis2d_forward_f64", dc.ptr, dy.ptr, rows, cols, 0)
+        got = dy.get()
+        np.testing.assert_allclose(got, oracle.sum_axis2d(clean, 0), rtol=1e-12, atol=1e-10)
+        if first is not None:
+            assert_same_bits(got, first)
+        first = got
+    lib.call("keydnn_cuda_mean_axis2d_forward_f64", dc.ptr, dy.ptr, rows, cols, 0)
+    np.testing.assert_allclose(dy.get(), oracle.mean_axis2d(clean, 0), rtol=1e-12, atol=1e-12)
+    lib.call("keydnn_cuda_sum_axis2d_forward_f64", dx.ptr, dy.ptr, rows, cols, 0)      # NaN / -inf propagate as in NumPy
+    got = dy.get()
+    assert np.isnan(got[5]) and got[3] == -np.inf and np.isnan(got[17])
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_full_reductions_over_many_tiles(oracle, dtype):
+    """Sizes around the tile kernels' limits: one tile, a ragged last tile, more tiles than one fold round takes
+    (4096), more than two rounds' worth (the tiles then grow), with 1-3 trailing elements; the maximum sits in the
+    last tile / the tail and is tied with an earlier element."""
+    lib = native()
+    s = suf(dtype)
+    rng = np.random.default_rng(77)
+    for n in (8192, 8192 * 3 + 1029, 8192 * 4096 + 3, 8192 * 4100 + 2, 8192 * 9000 + 1):
+        x = rng.standard_normal(n).astype(dtype)
+        x[n - 1] = x[n // 3] = 7.5
+        dx, dy, di = Buf(lib, x), Buf(lib, shape=(1,), dtype=dtype), Buf(lib, shape=(1,), dtype=np.int64)
+        lib.call(f"keydnn_cuda_sum_all_{s}", dx.ptr, dy.ptr, n)
+        np.testing.assert_allclose(dy.get()[0], np.sum(x.astype(np.float64)), **_sum_tol(dtype, n))
+        lib.call(f"keydnn_cuda_max_all_forward_{s}", dx.ptr, dy.ptr, di.ptr, n)
+        assert dy.get()[0] == 7.5 and di.get()[0] == n // 3
+        x[n // 3] = 0.0
+        dx2 = Buf(lib, x)
+        lib.call(f"keydnn_cuda_max_all_forward_{s}", dx2.ptr, dy.ptr, di.ptr, n)
+        assert dy.get()[0] == 7.5 and di.get()[0] == n - 1
+        del dx, dx2
+
+
 def test_max_nan_inf_rules(oracle):
     lib = native()
     x = np.array([[np.nan, 1.0, 1.0, -2.0], [-np.inf] * 4, [np.nan] * 4, [np.inf, 5.0, np.inf, 0.0]], np.float32)

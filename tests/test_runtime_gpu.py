@@ -128,3 +128,27 @@ def test_cached_block_handed_to_another_stream_waits_for_the_old_one():
         lib.call("keydnn_cuda_set_stream", prev.value)
         lib.call("keydnn_cuda_stream_destroy", a.value)
         lib.call("keydnn_cuda_stream_destroy", b.value)
+
+
+def test_copies_are_bounded_by_the_requested_size_not_the_pool_block():
+    """A 40-byte allocation sits in a 512-byte pool block.  cudaMemcpy on a plain cudaMalloc'ed buffer rejects a
+    range that leaves the allocation, and the reference's wrappers use that as a size probe
+    (ops/matmul_cuda.py reads the last byte each operand should have); the pool must give the same answer."""
+    import ctypes
+
+    lib = native()
+    p = ctypes.c_uint64(0)
+    lib.call("keydnn_cuda_malloc", ctypes.byref(p), 40)
+    host = np.zeros(64, np.uint8)
+    try:
+        d2h, h2d = lib.raw("keydnn_cuda_memcpy_d2h"), lib.raw("keydnn_cuda_memcpy_h2d")
+        assert d2h(host.ctypes.data, p.value, 40) == 0
+        assert d2h(host.ctypes.data, p.value + 39, 1) == 0
+        assert d2h(host.ctypes.data, p.value + 59, 1) == 1            # cudaErrorInvalidValue, as from the driver
+        assert d2h(host.ctypes.data, p.value, 41) == 1
+        assert h2d(p.value + 8, host.ctypes.data, 33) == 1
+        assert lib.raw("keydnn_cuda_memset")(p.value, 0, 64) == 1
+        assert lib.raw("keydnn_cuda_memcpy_d2d")(p.value, p.value + 20, 21) == 2
+        assert lib.raw("keydnn_cuda_memcpy_d2d")(p.value, p.value + 20, 20) == 0
+    finally:
+        lib.call("keydnn_cuda_free", p.value)
