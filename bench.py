@@ -1061,7 +1061,7 @@ def cpu_baseline_sample(budget_s: float = 12.0) -> dict:
     run(x32[:64], x64[:64])
     nbytes = seconds = 0.0
     passes = 0
-    while seconds < budget_s and passes < 48:
+    while seconds < budget_s and passes < 160:
         r = run(x32, x64)
         nbytes += r["bytes"]
         seconds += r["seconds"]

@@ -946,7 +946,7 @@ sum_akb_kernel(const T* __restrict__ x, T* __restrict__ y, int A, int K, int64_t
         return;
     }
     if (threadIdx.x == 0) partials[static_cast<int64_t>(slice) * K + k] = s;
-    if (take_ticket(counters + k, nslices)) {
+    if (take_ticket_t0(counters + k, nslices)) {
         double v = 0.0;
         for (int q = threadIdx.x; q < nslices; q += kThreads) v += ld_cg(partials + static_cast<int64_t>(q) * K + k);
         v = kd::block_sum(v, sm);
