@@ -49,32 +49,33 @@ WORKLOAD = ("configs[1]: sum/mean/max over axis 0, axis 1, all axes, fwd + bwd (
             "fp32 (8192,8192) N(0,1) + fp64 (4096,4096) N(0,1) per GPU, rows sharded across GPUs")
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of each kernel of the step, from one
-# `ncu --set full` capture at these sizes (summary committed under profiles/).  Writes are under-counted there:
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of each kernel of the step, from
+# `ncu --set full` captures at these sizes (summaries committed under profiles/: the tile and cluster reduction
+# kernels from ncu_full_reduction_tiles_cluster_b200.md, the others from ncu_full_every_kernel_b200.md).  Writes are under-counted there:
 # lines still dirty in L2 when a kernel ends are not in its DRAM count.
 NCU_TRAFFIC_BYTES = {
     "sum_axis0_fwd_f32": 272715000,
-    "sum_axis0_fwd_f64": 137865000,
+    "sum_axis0_fwd_f64": 138806000,
     "sum_axis0_bwd_f32": 209817000,
     "sum_axis0_bwd_f64": 75364000,
     "sum_axis1_fwd_f32": 272213000,
     "sum_axis1_fwd_f64": 137958000,
     "sum_axis1_bwd_f32": 211139000,
     "sum_axis1_bwd_f64": 77029000,
-    "sum_all_fwd_f32": 273015000,
-    "sum_all_fwd_f64": 140446000,
+    "sum_all_fwd_f32": 272028000,
+    "sum_all_fwd_f64": 137698000,
     "sum_all_bwd_f32": 210100000,
     "sum_all_bwd_f64": 74301000,
     "mean_axis0_fwd_f32": 271950000,
-    "mean_axis0_fwd_f64": 138020000,
+    "mean_axis0_fwd_f64": 137657000,
     "mean_axis0_bwd_f32": 209788000,
     "mean_axis0_bwd_f64": 75297000,
     "mean_axis1_fwd_f32": 272030000,
     "mean_axis1_fwd_f64": 137968000,
     "mean_axis1_bwd_f32": 212215000,
     "mean_axis1_bwd_f64": 76049000,
-    "mean_all_fwd_f32": 271924000,
-    "mean_all_fwd_f64": 137805000,
+    "mean_all_fwd_f32": 276022000,
+    "mean_all_fwd_f64": 138462000,
     "mean_all_bwd_f32": 209136000,
     "mean_all_bwd_f64": 75153000,
     "max_axis0_fwd_f32": 275074000,

@@ -637,10 +637,10 @@ max_cols_kernel(const T* __restrict__ x, T* __restrict__ y, long long* __restric
 }
 
 // Column reductions whose row chunks form one thread-block cluster.  grid = (stripes, CS), cluster = (1, CS, 1):
-// the CS chunks of a column stripe are co-scheduled, every CTA leaves its per-column partial in its own shared
-// memory, and after one hardware cluster barrier each CTA finishes 32*V/CS columns by reading the CS partials
-// over distributed shared memory (a fixed shuffle tree, so the result is reproducible).  No global partials, no
-// atomics, no scratch: what is left of the tail is two cluster barriers.  Measured on B200, fp64 4096 x 4096:
+// the CS chunks of a column stripe are co-scheduled, every CTA pushes its per-column partials into the shared
+// memory of the CTA that finishes that column (distributed shared memory stores), and after ONE hardware cluster
+// barrier each CTA adds the CS values it received for its 32*V/CS columns (a fixed shuffle tree, so the result is
+// reproducible).  No global partials, no atomics, no scratch: what is left of the tail is one cluster barrier.  Measured on B200, fp64 4096 x 4096:
 // sum 23.1 us against 24.1 us for the ticketed kernel above, max 23.9 us against 26.4 us; for fp32 8192 x 8192
 // the ticketed kernels are as fast (sum) or faster (max: its registers let only three CTAs share an SM, and 16-CTA
 // clusters then no longer all fit at once), so the launcher takes this path for 8-byte elements only.
@@ -651,9 +651,10 @@ __global__ void __launch_bounds__(kThreads)
 sum_cols_cluster_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int cols, int rch, T scale, bool apply_scale) {
     kd::pdl_prologue();
     cg::cluster_group cluster = cg::this_cluster();
+    cluster.barrier_arrive();                          // "this CTA runs": awaited before anybody stores into its shared memory
     constexpr int TC = 32 * V;
     __shared__ T sm[kWarps][TC + 1];
-    __shared__ double part[TC];
+    __shared__ double recv[TC];                        // [chunk q][column slot]: what the chunks of the stripe push to this CTA
     const int lane = threadIdx.x & 31, phase = threadIdx.x >> 5;
     const int stripe = blockIdx.x, chunk = blockIdx.y;
     const int c0 = (stripe * 32 + lane) * V;
@@ -684,26 +685,31 @@ sum_cols_cluster_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, in
 #pragma unroll
     for (int k = 0; k < V; ++k) sm[phase][lane * V + k] = acc[k];
     __syncthreads();
+    // Column j of the stripe is finished by the CTA of rank j / W: every chunk pushes its partial there (a remote
+    // shared-memory store, nothing waits for it), one cluster barrier makes the pushes visible, and each CTA adds
+    // the CS values it received from its own shared memory.  Nobody touches remote memory after the barrier, so
+    // CTAs leave as they finish.
+    const unsigned cs = cluster.num_blocks(), rank = cluster.block_rank();
+    const unsigned W = TC / cs;
+    cluster.barrier_wait();                            // every CTA of the cluster has started (long ago)
     for (int j = threadIdx.x; j < TC; j += kThreads) {
         double s = 0.0;
 #pragma unroll
         for (int p = 0; p < kWarps; ++p) s += static_cast<double>(sm[p][j]);
-        part[j] = s;
+        cluster.map_shared_rank(recv, j / W)[rank * W + j % W] = s;
     }
-    cluster.sync();                                    // every chunk's partials are in its shared memory
-    const unsigned cs = cluster.num_blocks(), rank = cluster.block_rank();
+    cluster.sync();
     if (threadIdx.x < TC) {                            // whole warps: TC is a multiple of 32
-        const unsigned q = threadIdx.x % cs, j = rank * (TC / cs) + threadIdx.x / cs;   // (chunk to read, column)
-        double v = cluster.map_shared_rank(part, q)[j];
+        const unsigned q = threadIdx.x % cs, slot = threadIdx.x / cs;      // (chunk, column slot)
+        double v = recv[q * W + slot];
         for (unsigned o = cs >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        const int c = stripe * TC + static_cast<int>(j);
+        const int c = stripe * TC + static_cast<int>(rank * W + slot);
         if (q == 0 && c < cols) {
             T out = static_cast<T>(v);
             if (apply_scale) out = out * scale;
             y[c] = out;
         }
     }
-    cluster.sync();                                    // nobody leaves while its shared memory is being read
 }
 
 template <typename T, int V>
@@ -711,12 +717,13 @@ __global__ void __launch_bounds__(kThreads)
 max_cols_cluster_kernel(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, int rows, int cols, int rch) {
     kd::pdl_prologue();
     cg::cluster_group cluster = cg::this_cluster();
+    cluster.barrier_arrive();                          // "this CTA runs": awaited before anybody stores into its shared memory
     constexpr int TC = 32 * V;
     constexpr int kNone = std::numeric_limits<int>::max();
     __shared__ T smv[kWarps][TC + 1];
     __shared__ int smi[kWarps][TC + 1];
-    __shared__ T pv[TC];
-    __shared__ int pi[TC];
+    __shared__ T rv[TC];                               // [chunk q][column slot] pushed here by the chunks of the stripe
+    __shared__ int ri[TC];
     const int lane = threadIdx.x & 31, phase = threadIdx.x >> 5;
     const int stripe = blockIdx.x, chunk = blockIdx.y;
     const int c0 = (stripe * 32 + lane) * V;
@@ -750,6 +757,9 @@ max_cols_cluster_kernel(const T* __restrict__ x, T* __restrict__ y, long long* _
 #pragma unroll
     for (int k = 0; k < V; ++k) { smv[phase][lane * V + k] = best[k]; smi[phase][lane * V + k] = brow[k]; }
     __syncthreads();
+    const unsigned cs = cluster.num_blocks(), rank = cluster.block_rank();
+    const unsigned W = TC / cs;
+    cluster.barrier_wait();
     for (int j = threadIdx.x; j < TC; j += kThreads) {
         T bv = kd::neg_inf<T>();
         int bi = kNone;
@@ -759,27 +769,25 @@ max_cols_cluster_kernel(const T* __restrict__ x, T* __restrict__ y, long long* _
             const int i = smi[p][j];
             if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
         }
-        pv[j] = bv;
-        pi[j] = bi;
+        cluster.map_shared_rank(rv, j / W)[rank * W + j % W] = bv;     // pushed to the CTA that finishes column j
+        cluster.map_shared_rank(ri, j / W)[rank * W + j % W] = bi;
     }
     cluster.sync();
-    const unsigned cs = cluster.num_blocks(), rank = cluster.block_rank();
     if (threadIdx.x < TC) {
-        const unsigned q = threadIdx.x % cs, j = rank * (TC / cs) + threadIdx.x / cs;
-        T bv = cluster.map_shared_rank(pv, q)[j];
-        int bi = cluster.map_shared_rank(pi, q)[j];
+        const unsigned q = threadIdx.x % cs, slot = threadIdx.x / cs;
+        T bv = rv[q * W + slot];
+        int bi = ri[q * W + slot];
         for (unsigned o = cs >> 1; o > 0; o >>= 1) {
             const T v = __shfl_xor_sync(0xffffffffu, bv, o);
             const int i = __shfl_xor_sync(0xffffffffu, bi, o);
             if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
         }
-        const int c = stripe * TC + static_cast<int>(j);
+        const int c = stripe * TC + static_cast<int>(rank * W + slot);
         if (q == 0 && c < cols) {
             y[c] = bv;
             idx[c] = (bi == kNone) ? 0 : bi;
         }
     }
-    cluster.sync();
 }
 
 // ---------------------------------------------------------------------------
