@@ -110,3 +110,30 @@ def test_column_reduction_chunk_arithmetic_is_64_bit(lib_path):
             assert nchunks * rch + 32 <= 2**31 - 1
     assert f(2**31 - 1, 8, 4, 8, out) == -2         # the last chunk would end beyond INT_MAX
     assert f(0, 8, 4, 8, out) == -2
+
+
+def test_every_reference_signature_is_declared_with_the_same_argument_classes():
+    """All argument lists, not a sample: tests/golden/reference_cuda_signatures.json holds the argument list of every
+    `keydnn_*` function of the reference's CUDA library reduced to register classes (pointer, 32 / 64-bit integer,
+    float, double; made by tests/golden/make_signatures.py from its .hpp / .cu text).  Every one this repository
+    declares - in either header - must have exactly that list."""
+    import json
+
+    from keydnn_v2_b200._native import DNN_HEADER_PATH, parse_header
+
+    ref = json.loads((REPO / "tests" / "golden" / "reference_cuda_signatures.json").read_text())
+    ours = {**parse_header(), **parse_header(DNN_HEADER_PATH)}
+    classes = {ctypes.c_void_p: "ptr", ctypes.c_int: "i32", ctypes.c_int64: "i64", ctypes.c_uint64: "u64",
+               ctypes.c_size_t: "u64", ctypes.c_float: "f32", ctypes.c_double: "f64"}
+    hot_path = set((REPO / "tests" / "golden" / "reference_cuda_exports.txt").read_text().split())
+    checked, wrong = 0, {}
+    for name, want in ref.items():
+        if name not in ours:
+            assert name not in hot_path, f"{name} is a hot-path export of the reference and is not declared here"
+            continue                      # out of scope (conv2d_transpose, stack, debug helpers)
+        got = [classes[t] for t in ours[name][1]]
+        checked += 1
+        if got != want:
+            wrong[name] = (got, want)
+    assert not wrong, wrong
+    assert checked >= len(hot_path) and hot_path <= set(ours)
