@@ -11,6 +11,7 @@
 #include <cstdint>
 #include <cstdlib>
 #include <limits>
+#include <mutex>
 #include <unordered_map>
 
 #define KD_API extern "C" __attribute__((visibility("default")))
@@ -50,8 +51,10 @@ inline unsigned grid_for(int64_t work_items, int per_sm) {
 template <typename K> inline int occupancy(K kernel, int threads, size_t smem = 0) {
     // kernels of one signature share this map: the key is the kernel's address mixed with the launch shape
     static std::unordered_map<uint64_t, int> cache;
+    static std::mutex mu;
     const uint64_t key = static_cast<uint64_t>(reinterpret_cast<uintptr_t>(kernel)) * 0x9E3779B97F4A7C15ull ^
                          (static_cast<uint64_t>(smem) << 12) ^ static_cast<uint64_t>(threads);
+    std::lock_guard<std::mutex> lk(mu);
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
     int n = 0;

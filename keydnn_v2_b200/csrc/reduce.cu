@@ -22,6 +22,8 @@
 
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 namespace {
 
 namespace cg = cooperative_groups;
@@ -1496,12 +1498,14 @@ struct NoAllocDevice {
     unsigned char* base = nullptr;
 };
 NoAllocDevice g_noalloc_device[16];
+std::mutex g_noalloc_mu;           // the first call per device may come from any host thread
 
 int noalloc_base(unsigned char** out) {
     int dev = -1;
     cudaError_t st = cudaGetDevice(&dev);
     if (st != cudaSuccess) return static_cast<int>(st);
     if (dev < 0 || dev >= 16) return static_cast<int>(cudaErrorInvalidDevice);
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
     NoAllocDevice& d = g_noalloc_device[dev];
     if (!d.ready) {
         void* p = nullptr;
