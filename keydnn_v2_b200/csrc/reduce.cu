@@ -1359,12 +1359,17 @@ int sum_to_shape(const T* x, T* y, const int64_t* in_shape, const int64_t* out_s
     if (ng == 3 && red[0] && ext[0] <= imax && ext[1] <= imax) {
         const int A = static_cast<int>(ext[0]), K = static_cast<int>(ext[1]);
         const int64_t B = ext[2];
-        // enough (k, slice) CTAs to cover the machine a few times
-        int nslices = static_cast<int>((static_cast<int64_t>(kd::sm_count()) * 8 + K - 1) / K);
-        if (nslices > A) nslices = A;
-        if (nslices < 1) nslices = 1;
-        const int ach = (A + nslices - 1) / nslices;
-        nslices = (A + ach - 1) / ach;
+        // Short CTAs (about 32 KiB of input each, as for the full reductions) handed out as SMs free up; at most
+        // kThreads slices per kept index so that the CTA that draws the last ticket folds them in one round, and
+        // never fewer CTAs than cover the machine a few times.
+        int64_t ach64 = (int64_t(32) << 10) / static_cast<int64_t>(sizeof(T)) / (B > 0 ? B : 1);
+        if (ach64 < 1) ach64 = 1;
+        const int64_t fill = (static_cast<int64_t>(kd::sm_count()) * 8 + K - 1) / K;      // slices that fill the machine
+        if ((A + ach64 - 1) / ach64 < fill) ach64 = (A + fill - 1) / fill;
+        if (ach64 < 1) ach64 = 1;
+        if ((A + ach64 - 1) / ach64 > kThreads) ach64 = (A + kThreads - 1) / kThreads;
+        const int ach = static_cast<int>(ach64);
+        int nslices = (A + ach - 1) / ach;
         double* partials = nullptr;
         unsigned int* counters = nullptr;
         if (nslices > 1) {
