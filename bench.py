@@ -78,16 +78,16 @@ NCU_TRAFFIC_BYTES = {
     "mean_all_fwd_f64": 138462000,
     "mean_all_bwd_f32": 209136000,
     "mean_all_bwd_f64": 75153000,
-    "max_axis0_fwd_f32": 275074000,
-    "max_axis0_fwd_f64": 139061000,
+    "max_axis0_fwd_f32": 273302000,
+    "max_axis0_fwd_f64": 138626000,
     "max_axis0_bwd_f32": 209138000,
     "max_axis0_bwd_f64": 76473000,
     "max_axis1_fwd_f32": 271911000,
     "max_axis1_fwd_f64": 138318000,
     "max_axis1_bwd_f32": 209431000,
     "max_axis1_bwd_f64": 75042000,
-    "max_all_fwd_f32": 271762000,
-    "max_all_fwd_f64": 138227000,
+    "max_all_fwd_f32": 273282000,
+    "max_all_fwd_f64": 138122000,
     "max_all_bwd_f32": 209150000,
     "max_all_bwd_f64": 74351000,
     # configs[0], [2], [3] (same capture)
