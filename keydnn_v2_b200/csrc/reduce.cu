@@ -642,14 +642,16 @@ max_cols_kernel(const T* __restrict__ x, T* __restrict__ y, long long* __restric
 // the CS chunks of a column stripe are co-scheduled, every CTA pushes its per-column partials into the shared
 // memory of the CTA that finishes that column (distributed shared memory stores), and after ONE hardware cluster
 // barrier each CTA adds the CS values it received for its 32*V/CS columns (a fixed shuffle tree, so the result is
-// reproducible).  No global partials, no atomics, no scratch: what is left of the tail is one cluster barrier.  Measured on B200, fp64 4096 x 4096:
-// sum 23.1 us against 24.1 us for the ticketed kernel above, max 23.9 us against 26.4 us; for fp32 8192 x 8192
-// the ticketed kernels are as fast (sum) or faster (max: its registers let only three CTAs share an SM, and 16-CTA
-// clusters then no longer all fit at once), so the launcher takes this path for 8-byte elements only.
+// reproducible).  No global partials, no atomics, no scratch: what is left of the tail is one cluster barrier.
+// Measured on B200, fp64 4096 x 4096: sum 22.4 us against 24.1 us for the ticketed kernel above, max 22.9 us against
+// 26.4 us.  For fp32 8192 x 8192 the ticketed sum is as fast (42.0 against 41.8 us), so fp32 sums stay there; the
+// fp32 arg-max gains (43.0 against 44.1 us) once its registers are held to 48, i.e. five CTAs per SM: at four per SM
+// the thirty-two 16-CTA clusters of the grid fit at once only if every GPC has sixteen SMs to give, and a second
+// wave costs 40 % (60 us measured).
 constexpr int kClusterChunks = 16;      // CTAs per cluster (above 8: needs the non-portable size attribute)
 
 template <typename T, int V>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads)         // 44-48 registers: five CTAs per SM without asking
 sum_cols_cluster_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int cols, int rch, T scale, bool apply_scale) {
     kd::pdl_prologue();
     cg::cluster_group cluster = cg::this_cluster();
@@ -715,7 +717,7 @@ sum_cols_cluster_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, in
 }
 
 template <typename T, int V>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 5)      // five CTAs per SM: 32 clusters of 16 then fit whatever the GPC sizes
 max_cols_cluster_kernel(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, int rows, int cols, int rch) {
     kd::pdl_prologue();
     cg::cluster_group cluster = cg::this_cluster();
@@ -1113,8 +1115,9 @@ inline bool col_chunks(int rows, int64_t rch, ColChunks* out) {
 // ticketed kernels would use), and a device that can hold at least one such cluster.  `kernel` must be the
 // instantiation that will be launched; the non-portable cluster size is enabled on it once.
 template <typename K>
-inline bool cluster_cols_plan(K kernel, size_t elem_size, int V, int rows, int stripes, int ctas_per_sm, int* rch_out) {
-    if (elem_size != 8 || V != 4) return false;
+inline bool cluster_cols_plan(K kernel, size_t elem_size, int V, int rows, int stripes, int ctas_per_sm, bool f32_too,
+                              int* rch_out) {
+    if (!((elem_size == 8 && V == 4) || (f32_too && elem_size == 4 && V == 8))) return false;     // 32 bytes per lane
     const int64_t slots = static_cast<int64_t>(kd::sm_count()) * ctas_per_sm;
     const int64_t wanted = slots / stripes;
     if (wanted < 12 || wanted > 32) return false;
@@ -1155,7 +1158,10 @@ template <typename T, int V>
 int sum_cols_v(const T* x, T* y, int rows, int cols, T scale, bool apply_scale) {
     const int stripes = (cols + 32 * V - 1) / (32 * V);
     int crch = 0;
-    if (cluster_cols_plan(sum_cols_cluster_kernel<T, V>, sizeof(T), V, rows, stripes, kd::occupancy(sum_cols_kernel<T, V>, kThreads), &crch)) {
+    // fp32 sums stay on the ticketed kernel: measured equal there (41.8 against 42.0 us), and the allocation-free
+    // entry then keeps giving the regular entry's bits
+    if (cluster_cols_plan(sum_cols_cluster_kernel<T, V>, sizeof(T), V, rows, stripes, kd::occupancy(sum_cols_kernel<T, V>, kThreads), false,
+                          &crch)) {
         if (kd::launch_cluster_y(sum_cols_cluster_kernel<T, V>, dim3(stripes, kClusterChunks), kThreads, kClusterChunks, x, y, rows, cols,
                                  crch, scale, apply_scale) == cudaSuccess)
             return kd::launch_status();
@@ -1188,7 +1194,8 @@ template <typename T, int V>
 int max_cols_v(const T* x, T* y, long long* idx, int rows, int cols) {
     const int stripes = (cols + 32 * V - 1) / (32 * V);
     int crch = 0;
-    if (cluster_cols_plan(max_cols_cluster_kernel<T, V>, sizeof(T), V, rows, stripes, kd::occupancy(max_cols_kernel<T, V>, kThreads), &crch)) {
+    if (cluster_cols_plan(max_cols_cluster_kernel<T, V>, sizeof(T), V, rows, stripes, kd::occupancy(max_cols_kernel<T, V>, kThreads), true,
+                          &crch)) {
         if (kd::launch_cluster_y(max_cols_cluster_kernel<T, V>, dim3(stripes, kClusterChunks), kThreads, kClusterChunks, x, y, idx, rows,
                                  cols, crch) == cudaSuccess)
             return kd::launch_status();
