@@ -180,7 +180,8 @@ def test_pool_matches_reference_golden(golden):
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
-@pytest.mark.parametrize("shape", [(3, 5, 7, 7), (2, 37, 7, 7), (4, 8, 2, 2), (2, 3, 8, 8), (2, 4, 32, 32), (1, 3, 9, 11)])
+@pytest.mark.parametrize("shape", [(3, 5, 7, 7), (2, 37, 7, 7), (4, 8, 2, 2), (2, 3, 8, 8), (2, 4, 32, 32), (1, 3, 9, 11), (3, 5, 2, 4),
+                                   (2, 7, 3, 3), (5, 13, 1, 1), (64, 200, 7, 7)])
 def test_global_avgpool(oracle, shape, dtype):
     lib = native()
     N, C, H, W = shape
