@@ -54,7 +54,10 @@ REF_CUDA_SOURCES = [
 DEFAULT_REF_ROOT = Path(os.environ.get("KEYDNN_REFERENCE_ROOT") or HERE.parent.parent / "reference")
 REF_TREE = REF_DIR / "tree"
 # the reference's test directories that exercise its CUDA library (relative to tests/infrastructure)
-REF_TEST_DIRS = ["native_cuda", "tensors/cuda", "ops", "reduce", "pool2d"]
+REF_TEST_DIRS = ["native_cuda", "tensors", "ops", "reduce", "pool2d", "linear", "conv2d", "models", "dropout", "flatten"]
+# ... and single files of tests/infrastructure that train whole models on the CUDA path
+REF_TEST_FILES = ["test_xor_grad_parity_f32_cpu_vs_cuda.py", "test_parameter.py", "test_activations.py", "test_losses.py",
+                  "test_optimizers.py", "test_function.py", "test_exp.py"]
 REF_CUDA_SUBDIR = "src/keydnn/infrastructure/native_cuda/keydnn_v2_cuda_native/KeyDNNV2CudaNative"
 REF_NATIVE_SUBDIR = "src/keydnn/infrastructure/native/src"
 
@@ -140,6 +143,9 @@ def stage_reference_tree(ref_root: str | Path | None = None, force: bool = False
             src_init = tests_src / "infrastructure" / Path(d).parent / "__init__.py"
             if parent != tests_dst / "infrastructure" and src_init.exists():
                 shutil.copy(src_init, parent / "__init__.py")
+    for f in REF_TEST_FILES:
+        if (tests_src / "infrastructure" / f).exists():
+            shutil.copy(tests_src / "infrastructure" / f, tests_dst / "infrastructure" / f)
     # the reference's CPU pooling kernels where its loader looks for them (native/python/_native_loader.py:110-117)
     if REF_NATIVE_OMP.exists():
         shutil.copy(REF_NATIVE_OMP, REF_TREE / "src" / "keydnn" / "infrastructure" / "native" / "python" / "libkeydnn_native_omp.so")

@@ -46,6 +46,14 @@ GROUPS = {
     "ops": ["tests/infrastructure/ops", "tests/infrastructure/reduce"],
     "tensor": ["tests/infrastructure/tensors/cuda"],
     "pool2d": ["tests/infrastructure/pool2d"],
+    # whole-stack: Linear / Conv2d Functions and Modules, model training and saving on the CUDA path, the XOR
+    # CPU-vs-CUDA gradient parity, activations / losses / optimizers, the remaining Tensor tests
+    "stack": ["tests/infrastructure/linear", "tests/infrastructure/conv2d", "tests/infrastructure/models",
+              "tests/infrastructure/dropout", "tests/infrastructure/flatten", "tests/infrastructure/tensors/test_*.py",
+              "tests/infrastructure/test_xor_grad_parity_f32_cpu_vs_cuda.py", "tests/infrastructure/test_parameter.py",
+              "tests/infrastructure/test_activations.py", "tests/infrastructure/test_losses.py",
+              "tests/infrastructure/test_optimizers.py", "tests/infrastructure/test_function.py",
+              "tests/infrastructure/test_exp.py"],
 }
 # exports of the reference DLL that are out of scope here
 OUT_OF_SCOPE = ("conv2d_transpose", "stack")
@@ -59,6 +67,7 @@ def run_reference_tests(paths, lib=None):
     dropin.place(TREE / "src" / "keydnn", lib=lib)
     (TREE / "conftest.py").write_text(CONFTEST.format(repo=str(REPO)))
     deselect = " and ".join(f"not {w}" for w in OUT_OF_SCOPE)
+    paths = [q for p in paths for q in (sorted(str(f.relative_to(TREE)) for f in TREE.glob(p)) if "*" in p else [p])]
     cmd = [sys.executable, "-m", "pytest", "-q", "-p", "no:cacheprovider", "--maxfail=1000", "-k", deselect, "--no-header",
            "-rfE", *paths]
     env = dict(os.environ, PYTHONDONTWRITEBYTECODE="1")
