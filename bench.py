@@ -1129,6 +1129,32 @@ def run_reference(args) -> None:
     }), flush=True)
 
 
+def run_dropin(args) -> None:
+    """The reference's own Python stack (its loader, bindings, Tensor dispatch, autograd, pooling Functions, Linear,
+    SGD: the staged copy, unmodified) on its CUDA path, timed twice in child processes: over this repository's
+    drop-in library and over the reference's own library compiled unmodified.  Same Python, same inputs; only the
+    file at the DLL path differs.  Host time per iteration (device synchronised at both ends), one JSON line."""
+    tree = REPO / "oracle" / "_ref" / "tree" / ".staged"
+    ref_lib = REPO / "oracle" / "_ref" / "libkeydnn_ref_cuda_full.so"
+    if not tree.exists() or not ref_lib.exists():
+        print(json.dumps({"workload": "dropin", "unavailable": "no staged copy of the reference / its library under oracle/_ref"}))
+        return
+    res = {}
+    for tag, lib in (("reference_library", str(ref_lib)), ("this_library", "ours")):
+        r = subprocess.run([sys.executable, "-m", "oracle.reference_cuda_stack", lib, str(max(10, args.steps // 2))], cwd=REPO,
+                           capture_output=True, text=True, timeout=1500)
+        if r.returncode != 0:
+            print(json.dumps({"workload": "dropin", "unavailable": f"{tag}: {r.stderr[-400:]}"}))
+            return
+        res[tag] = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1])
+    rows = [{"workload": k, "reference_library_ms": round(res["reference_library"][k], 3), "this_library_ms": round(res["this_library"][k], 3),
+             "speedup": round(res["reference_library"][k] / res["this_library"][k], 2)} for k in res["this_library"]]
+    print(json.dumps({"metric": "the reference's own Python stack on CUDA: ms per iteration over its own library and over this one",
+                      "unit": "ms", "higher_is_better": False, "n_gpus": 1, "data": "synthetic", "rows": rows,
+                      "config": {"workload": "reference stack (staged copy, unmodified) over two native libraries; host time per "
+                                             "iteration, device synchronised at both ends; inputs resident on the device"}}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1139,8 +1165,9 @@ def main() -> None:
     ap.add_argument("--kernels", default="auto", choices=["auto", "none", "step", "suite", "full", "all"],
                     help="per-kernel tables: step = the reductions of the step; suite = + configs[0], [2], [3] (pool, element-wise, "
                          "optimizer); full = + activations / softmax / losses / layer glue; auto = suite at N = 1, step at N > 1")
-    ap.add_argument("--workload", default="reduce", choices=["reduce", "cnn"],
-                    help="reduce: configs[1] (the default line); cnn: only the configs[4] training step, reported as samples/s")
+    ap.add_argument("--workload", default="reduce", choices=["reduce", "cnn", "dropin"],
+                    help="reduce: configs[1] (the default line); cnn: only the configs[4] training step, reported as samples/s; "
+                         "dropin: the reference's own Python stack over its own CUDA library and over this one")
     ap.add_argument("--cnn", default="on", choices=["on", "off"], help="also time the small-CNN training step (configs[4])")
     ap.add_argument("--ref-cuda", dest="ref_cuda", default="on", choices=["on", "off"],
                     help="time the reference's own CUDA kernels (oracle/_ref) beside each kernel (N = 1)")
@@ -1150,6 +1177,8 @@ def main() -> None:
         args.kernels = "step"
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "dropin":
+        run_dropin(args)
     else:
         run_ours(args)
 
