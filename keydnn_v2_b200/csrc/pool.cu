@@ -24,6 +24,7 @@ namespace {
 using kd::Pack4;
 
 constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
 
 struct PoolGeom {
     int H, W;        // un-padded input plane
@@ -616,6 +617,45 @@ crop2d_kernel(const T* __restrict__ xp, T* __restrict__ y, int Hp, int Wp, int p
     }
 }
 
+// Row-wise forms: a warp owns a row of the output plane (one multiply-high per ROW instead of four 64-bit
+// divisions per ELEMENT), its lanes walk the row, so loads and stores are contiguous.  rows < 2^31.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+pad2d_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int H, int W, int ph, int pw, T value, unsigned rows,
+                  kd::FastDiv by_hp) {
+    kd::pdl_prologue();
+    const int Hp = H + 2 * ph, Wp = W + 2 * pw;
+    const int lane = threadIdx.x & 31;
+    for (unsigned r = blockIdx.x * kWarps + (threadIdx.x >> 5); r < rows; r += gridDim.x * kWarps) {
+        const unsigned nc = by_hp.div(r);
+        const int h = static_cast<int>(r - nc * static_cast<unsigned>(Hp)) - ph;
+        T* dst = y + static_cast<int64_t>(r) * Wp;
+        if (h < 0 || h >= H) {
+            for (int w = lane; w < Wp; w += 32) dst[w] = value;
+        } else {
+            const T* src = x + (static_cast<int64_t>(nc) * H + h) * W - pw;
+            for (int w = lane; w < Wp; w += 32) dst[w] = (w >= pw && w < pw + W) ? src[w] : value;
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+crop2d_rows_kernel(const T* __restrict__ xp, T* __restrict__ y, int Hp, int Wp, int ph, int pw, int H, int W, unsigned rows,
+                   kd::FastDiv by_h) {
+    kd::pdl_prologue();
+    const int lane = threadIdx.x & 31;
+    for (unsigned r = blockIdx.x * kWarps + (threadIdx.x >> 5); r < rows; r += gridDim.x * kWarps) {
+        const unsigned nc = by_h.div(r);
+        const int hp = static_cast<int>(r - nc * static_cast<unsigned>(H)) + ph;
+        if (hp >= Hp) continue;                       // rows the padded plane does not have stay untouched, as in the flat kernel
+        const T* src = xp + (static_cast<int64_t>(nc) * Hp + hp) * Wp + pw;
+        T* dst = y + static_cast<int64_t>(r) * W;
+        for (int w = lane; w < W; w += 32)
+            if (w + pw < Wp) dst[w] = src[w];
+    }
+}
+
 // ===========================================================================
 // Host-side dispatch
 // ===========================================================================
@@ -785,6 +825,14 @@ int pad2d(const T* x, T* y, int N, int C, int H, int W, int ph, int pw, T value)
     if (ph < 0 || pw < 0) return -3;
     (void)cudaGetLastError();
     const int64_t total = static_cast<int64_t>(N) * C * (H + 2 * ph) * (W + 2 * pw);
+    if (ph == 0 && pw == 0)         // nothing to add: the reference pads even then (ops/pool2d_cuda_ext.py:56-184)
+        return kd::status(cudaMemcpyAsync(y, x, static_cast<size_t>(total) * sizeof(T), cudaMemcpyDeviceToDevice, kd::stream()));
+    const int64_t rows = static_cast<int64_t>(N) * C * (H + 2 * ph);
+    if (rows < (int64_t(1) << 31)) {
+        KD_LAUNCH_W(pad2d_rows_kernel<T>, 8, (rows + kWarps - 1) / kWarps, kThreads, 0, x, y, H, W, ph, pw, value,
+                    static_cast<unsigned>(rows), kd::FastDiv(static_cast<unsigned>(H + 2 * ph)));
+        return kd::launch_status();
+    }
     (void)kd::launch(pad2d_kernel<T>, dim3(flat_grid(total)), kThreads, 0, x, y, H, W, ph, pw, value, total);
     return kd::launch_status();
 }
@@ -797,6 +845,14 @@ int crop2d(const T* xp, T* y, int N, int C, int Hp, int Wp, int ph, int pw, int 
     if (ph < 0 || pw < 0) return -4;
     (void)cudaGetLastError();
     const int64_t total = static_cast<int64_t>(N) * C * H * W;
+    if (ph == 0 && pw == 0 && Hp == H && Wp == W)
+        return kd::status(cudaMemcpyAsync(y, xp, static_cast<size_t>(total) * sizeof(T), cudaMemcpyDeviceToDevice, kd::stream()));
+    const int64_t rows = static_cast<int64_t>(N) * C * H;
+    if (rows < (int64_t(1) << 31)) {
+        KD_LAUNCH_W(crop2d_rows_kernel<T>, 8, (rows + kWarps - 1) / kWarps, kThreads, 0, xp, y, Hp, Wp, ph, pw, H, W,
+                    static_cast<unsigned>(rows), kd::FastDiv(static_cast<unsigned>(H)));
+        return kd::launch_status();
+    }
     (void)kd::launch(crop2d_kernel<T>, dim3(flat_grid(total)), kThreads, 0, xp, y, Hp, Wp, ph, pw, H, W, total);
     return kd::launch_status();
 }
