@@ -274,6 +274,7 @@ avgpool_fwd_generic(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int6
 // in that range (checked exhaustively on a CPU: 3,355,443,202 values, no mismatch).  Anything
 // else (zeros, subnormal-range, huge, inf, NaN, and double) takes the true division.
 template <typename T> __device__ __forceinline__ T div9(T x) { return x / T(9); }
+__device__ __noinline__ float div9_by_division(float x) { return x / 9.0f; }   // a call, so that the rare path is not if-converted
 template <> __device__ __forceinline__ float div9<float>(float x) {
     constexpr float r = 1.0f / 9.0f;
     const float q0 = __fmul_rn(x, r);
@@ -281,7 +282,7 @@ template <> __device__ __forceinline__ float div9<float>(float x) {
     const float q = __fmaf_rn(e, r, q0);
     const float ax = fabsf(x);
     if (__builtin_expect(ax >= 0x1p-100f && ax <= 0x1p100f, 1)) return q;
-    return x / 9.0f;
+    return div9_by_division(x);
 }
 
 // kernel 3x3, stride 2, padding 1, W % 8 == 0 (so Wo = W/2, Wo % 4 == 0).
@@ -361,6 +362,362 @@ avgpool_bwd_gather(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int
                 acc += __ldg(go + obase + static_cast<int64_t>(i) * g.Wo + j) / denom;
         if (ACCUM) gx[e] += acc;
         else gx[e] = acc;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Band kernels: any window, stride and padding, any alignment.
+// A CTA takes a band of whole rows of one plane.  Everything the band reads is one contiguous
+// span of memory (rows are complete), so it is staged in shared memory with coalesced loads and
+// the stencil reads shared memory; global traffic is fully coalesced whatever the stride of the
+// window.  A thread then owns one column of the band and walks down its rows, so that everything
+// that depends on the column only is computed once and a row costs a pointer increment: both
+// kernels are bound by instruction issue before they are bound by memory, and index arithmetic
+// per element is what has to go.  The arithmetic on the data is that of the one-thread-per-element
+// kernels above, tap for tap.  `lanes` (a power of two, 32..256) threads share a row.
+// ---------------------------------------------------------------------------
+constexpr int kBandBytes = 16 * 1024;          // staged span per band
+constexpr int kBandRowsMax = 512;              // backward: rows of a band (one table entry each)
+
+template <typename T> struct BandVec { static constexpr int value = 16 / static_cast<int>(sizeof(T)); };
+
+struct BandPlan {
+    bool ok;
+    int rows;        // rows of the band (output rows forward, input rows backward)
+    int bands;       // bands per plane
+    size_t smem;
+};
+
+constexpr int kBandThreads = 128;
+
+// log2 of the threads that share a row: the smallest power of two >= width, 32..kBandThreads
+inline int band_lane_bits(int width) {
+    int bits = 5;
+    while ((1 << bits) < width && (1 << bits) < kBandThreads) ++bits;
+    return bits;
+}
+
+// Forward: `rows` output rows need (rows-1)*sh + kh input rows.
+template <typename T> inline BandPlan band_plan_fwd(const PoolGeom& g) {
+    BandPlan p = {false, 0, 0, 0};
+    const int64_t cap = kBandBytes / static_cast<int64_t>(sizeof(T));
+    if (static_cast<int64_t>(g.kh) * g.W > cap) return p;
+    int64_t r = (cap / g.W - g.kh) / g.sh + 1;
+    if (r > g.Ho) r = g.Ho;
+    if (r < 1) return p;
+    p.bands = static_cast<int>((g.Ho + r - 1) / r);
+    p.rows = (g.Ho + p.bands - 1) / p.bands;
+    p.smem = (static_cast<size_t>((p.rows - 1) * g.sh + g.kh) * g.W + BandVec<T>::value) * sizeof(T);
+    p.ok = true;
+    return p;
+}
+
+// Backward: `rows` input rows are covered by at most (rows + kh - 2) / sh + 1 output rows; they are staged
+// with one more column and one more row, both zero.
+inline int64_t band_go_rows(const PoolGeom& g, int64_t r) { return (r + g.kh - 2) / g.sh + 1; }
+
+template <typename T> inline BandPlan band_plan_bwd(const PoolGeom& g) {
+    BandPlan p = {false, 0, 0, 0};
+    const int64_t cap = kBandBytes / static_cast<int64_t>(sizeof(T));
+    const int64_t pitch = g.Wo + 1;
+    if ((band_go_rows(g, 1) + 1) * pitch > cap) return p;
+    int64_t r = (cap / pitch - 2) * g.sh - g.kh + 2;
+    if (r < 1) r = 1;
+    while (r > 1 && (band_go_rows(g, r) + 1) * pitch > cap) --r;
+    const int64_t most = (8192 + g.W - 1) / g.W;             // and at most ~8192 elements a band
+    if (r > most) r = most;
+    if (r > kBandRowsMax) r = kBandRowsMax;
+    if (r > g.H) r = g.H;
+    p.bands = static_cast<int>((g.H + r - 1) / r);
+    p.rows = (g.H + p.bands - 1) / p.bands;
+    p.smem = ((static_cast<size_t>(p.rows) * sizeof(int2) + 15) & ~size_t(15)) +
+             static_cast<size_t>((band_go_rows(g, p.rows) + 1) * pitch) * sizeof(T);
+    p.ok = true;
+    return p;
+}
+
+// Copies src[0, n) to s[mis, mis + n), where mis is the element offset of src inside its 16-byte packet (which
+// keeps the packets aligned on both sides): 16-byte loads, single elements before the first and after the last
+// boundary.  All threads of the CTA call it.
+template <typename T>
+__device__ __forceinline__ void band_stage(const T* __restrict__ src, int n, T* s, int mis) {
+    constexpr int V = BandVec<T>::value;
+    int head = (V - mis) & (V - 1);
+    if (head > n) head = n;
+    const int nv = (n - head) / V;
+    if (static_cast<int>(threadIdx.x) < head) s[mis + threadIdx.x] = __ldg(src + threadIdx.x);
+    const T* body = src + head;
+    T* sbody = s + mis + head;                                    // a multiple of V elements into s
+#pragma unroll 4
+    for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+        if constexpr (sizeof(T) == 4)
+            reinterpret_cast<float4*>(sbody)[v] = __ldcs(reinterpret_cast<const float4*>(body) + v);
+        else
+            reinterpret_cast<double2*>(sbody)[v] = __ldcs(reinterpret_cast<const double2*>(body) + v);
+    }
+    const int done = head + nv * V;
+    if (static_cast<int>(threadIdx.x) < n - done) s[mis + done + threadIdx.x] = __ldg(src + done + threadIdx.x);
+}
+
+template <typename T> __device__ __forceinline__ int band_misalign(const T* p) {
+    return static_cast<int>((reinterpret_cast<uintptr_t>(p) / sizeof(T)) & (BandVec<T>::value - 1));
+}
+
+// x / taps: the exact short forms where they exist.  TAPS > 0: known when the kernel is compiled.
+template <typename T, int TAPS> struct WindowDiv {
+    T d, inv;
+    int kind;                                                     // 0: division, 1: nine, 2: power of two
+    __device__ explicit WindowDiv(int taps) : d(static_cast<T>(taps)), inv(T(1) / static_cast<T>(taps)),
+                                              kind(taps == 9 ? 1 : ((taps & (taps - 1)) == 0 ? 2 : 0)) {}
+    __device__ __forceinline__ T operator()(T x) const {
+        if (TAPS == 9) return div9<T>(x);
+        if (TAPS > 0 && (TAPS & (TAPS - 1)) == 0) return x * (T(1) / T(TAPS > 0 ? TAPS : 1));
+        if (kind == 1) return div9<T>(x);
+        if (kind == 2) return x * inv;                            // exact scaling, gradual underflow included
+        return x / d;
+    }
+};
+
+// KH, KW: the window when the kernel is compiled for it, 0 = taken from g.  EDGES: a window may reach outside the
+// plane (padding, or an output size that lets the last window hang over); such taps contribute +0, which leaves the
+// running sum as it is (it starts at +0 and is therefore never -0).
+// What depends on the band only is recomputed when a CTA moves to a different band; with one band per plane (planes
+// up to 16 KiB) that is once per CTA, and an item costs its staging and the stencil.
+template <typename T, int KH, int KW, bool EDGES>
+__global__ void __launch_bounds__(kBandThreads)
+avgpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int rows, unsigned items, kd::FastDiv by_bands,
+                 int lane_bits) {
+    extern __shared__ __align__(16) unsigned char band_smem[];
+    T* s = reinterpret_cast<T*>(band_smem);
+    kd::pdl_prologue();
+    const int kh = KH ? KH : g.kh, kw = KW ? KW : g.kw;
+    const WindowDiv<T, KH * KW> divide(kh * kw);
+    const int lanes = 1 << lane_bits;
+    const int group = threadIdx.x >> lane_bits, lig = threadIdx.x & (lanes - 1), ngroups = blockDim.x >> lane_bits;
+    const int step = ngroups * g.sh;
+    const int64_t plane_in = static_cast<int64_t>(g.H) * g.W, plane_out = static_cast<int64_t>(g.Ho) * g.Wo;
+    unsigned cur = ~0u;
+    int nout = 0, nrows = 0, first = 0, in_off = 0, out_off = 0;
+    for (unsigned item = blockIdx.x; item < items; item += gridDim.x) {
+        unsigned nc, band;
+        by_bands.divmod(item, nc, band);
+        if (band != cur) {
+            cur = band;
+            const int i0 = static_cast<int>(band) * rows;
+            nout = min(g.Ho, i0 + rows) - i0;
+            const int h_lo = max(0, i0 * g.sh - g.ph);
+            nrows = min(g.H, (i0 + nout - 1) * g.sh - g.ph + kh) - h_lo;
+            in_off = h_lo * g.W;
+            out_off = i0 * g.Wo;
+            first = i0 * g.sh - g.ph - h_lo + group * g.sh;              // staged row of this thread's first tap
+        }
+        const T* src = x + nc * plane_in + in_off;
+        const int mis = band_misalign(src);
+        if (nrows > 0) band_stage(src, nrows * g.W, s, mis);
+        __syncthreads();
+        T* dst = y + nc * plane_out + out_off + group * g.Wo;
+        for (int j = lig; j < g.Wo; j += lanes) {
+            const int w0 = j * g.sw - g.pw;
+            int hh = first;
+            const T* t = s + mis + hh * g.W + w0;                              // dereferenced only where the tap exists
+            T* out = dst + j;
+            for (int ii = group; ii < nout; ii += ngroups, hh += step, t += step * g.W, out += ngroups * g.Wo) {
+                T sum = T(0);
+                if (KH > 0 && !EDGES) {
+#pragma unroll
+                    for (int a = 0; a < KH; ++a)
+#pragma unroll
+                        for (int b = 0; b < KW; ++b) sum += t[a * g.W + b];
+                } else if (KH > 0) {
+#pragma unroll
+                    for (int a = 0; a < KH; ++a) {
+                        const bool row_ok = hh + a >= 0 && hh + a < nrows;
+#pragma unroll
+                        for (int b = 0; b < KW; ++b)
+                            sum += (row_ok && w0 + b >= 0 && w0 + b < g.W) ? t[a * g.W + b] : T(0);
+                    }
+                } else {
+                    for (int a = 0; a < kh; ++a) {
+                        if (EDGES && (hh + a < 0 || hh + a >= nrows)) continue;
+                        for (int b = 0; b < kw; ++b) {
+                            if (EDGES && (w0 + b < 0 || w0 + b >= g.W)) continue;
+                            sum += t[a * g.W + b];
+                        }
+                    }
+                }
+                *out = divide(sum);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// Backward.  The quotients go / (kh*kw) of the output rows that cover the band are staged once, in rows of Wo + 1
+// with a zero in the extra column, followed by a row of zeros.  What depends on the column only (the first covering
+// output column and how many there are) is computed once per thread; what depends on the row only comes from a table
+// that is refilled when the CTA moves to a different band (with one band per plane: once).  TWO: no element is covered
+// by more than two windows along either axis (kh <= 2 sh, kw <= 2 sw); the table holds the staged (byte) offsets of the two
+// covering rows and the thread those of the two covering columns, a window that does not exist being replaced by the
+// zero row / zero column, so the four taps are taken without a branch or a predicate.  A zero tap leaves the running
+// sum as it is (it starts at +0 and is therefore never -0).  Otherwise the table holds {offset of the first covering
+// row, number of covering rows} and the taps are counted loops.  A thread owns V adjacent columns, moved with one
+// access of 4 to 16 bytes, and has 8 / V rows in flight.
+template <typename T> struct BandColumn { int j_lo, nj, a, b; };
+
+template <typename T>
+__device__ __forceinline__ BandColumn<T> band_column(const PoolGeom& g, int w, const kd::FastDiv& by_sw) {
+    const int wp = w + g.pw;
+    const int c0 = wp - g.kw + 1;
+    BandColumn<T> c;
+    c.j_lo = c0 <= 0 ? 0 : static_cast<int>(by_sw.div(static_cast<unsigned>(c0 + g.sw - 1)));
+    c.nj = min(g.Wo - 1, static_cast<int>(by_sw.div(static_cast<unsigned>(wp)))) - c.j_lo + 1;
+    c.a = c.nj >= 1 ? c.j_lo : g.Wo;
+    c.b = c.nj >= 2 ? c.j_lo + 1 : g.Wo;
+    return c;
+}
+
+// V adjacent elements with one access (V * sizeof(T) = 4, 8 or 16 bytes, the address aligned to that); touched once.
+template <typename T, int V> __device__ __forceinline__ void band_load(const T* p, T (&v)[V]) {
+    if constexpr (V == 1) {
+        v[0] = __ldcs(p);
+    } else if constexpr (sizeof(T) * V == 8) {
+        const float2 t = __ldcs(reinterpret_cast<const float2*>(p));
+        v[0] = t.x; v[1] = t.y;
+    } else if constexpr (sizeof(T) == 4) {
+        const float4 t = __ldcs(reinterpret_cast<const float4*>(p));
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+        const double2 t = __ldcs(reinterpret_cast<const double2*>(p));
+        v[0] = t.x; v[1] = t.y;
+    }
+}
+template <typename T, int V> __device__ __forceinline__ void band_store(T* p, const T (&v)[V]) {
+    if constexpr (V == 1) __stcs(p, v[0]);
+    else if constexpr (sizeof(T) * V == 8) __stcs(reinterpret_cast<float2*>(p), make_float2(v[0], v[1]));
+    else if constexpr (sizeof(T) == 4) __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3]));
+    else __stcs(reinterpret_cast<double2*>(p), make_double2(v[0], v[1]));
+}
+
+// V: adjacent columns per thread, moved with one access (W % V == 0 and the tensor aligned to V elements).
+template <typename T, bool ACCUM, bool TWO, int V>
+__global__ void __launch_bounds__(kBandThreads)
+avgpool_bwd_band(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int rows, unsigned items, kd::FastDiv by_bands,
+                 int lane_bits, kd::FastDiv by_sh, kd::FastDiv by_sw, kd::FastDiv by_wo) {
+    extern __shared__ __align__(16) unsigned char band_smem[];
+    int2* rowinfo = reinterpret_cast<int2*>(band_smem);
+    T* q = reinterpret_cast<T*>(band_smem + ((static_cast<size_t>(rows) * sizeof(int2) + 15) & ~size_t(15)));
+    kd::pdl_prologue();
+    const WindowDiv<T, 0> divide(g.kh * g.kw);
+    const int lanes = 1 << lane_bits;
+    const int group = threadIdx.x >> lane_bits, lig = threadIdx.x & (lanes - 1), ngroups = blockDim.x >> lane_bits;
+    const int pitch = g.Wo + 1;
+    constexpr int U = 8 / V;                   // rows in flight per thread
+    const int wv = g.W / V;                    // column groups
+    const int64_t stride = static_cast<int64_t>(ngroups) * g.W;
+    const int64_t plane_in = static_cast<int64_t>(g.H) * g.W, plane_out = static_cast<int64_t>(g.Ho) * g.Wo;
+    BandColumn<T> mine[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) mine[k] = band_column<T>(g, lig * V + k, by_sw);
+    unsigned cur = ~0u;
+    int nrows = 0, ngo = 0, in_off = 0, go_off = 0;
+    for (unsigned item = blockIdx.x; item < items; item += gridDim.x) {
+        unsigned nc, band;
+        by_bands.divmod(item, nc, band);
+        const bool moved = band != cur;
+        int h0 = 0, i_first = 0;
+        if (moved) {
+            cur = band;
+            h0 = static_cast<int>(band) * rows;
+            nrows = min(g.H, h0 + rows) - h0;
+            const int a_first = h0 + g.ph - g.kh + 1;
+            i_first = a_first <= 0 ? 0 : static_cast<int>(by_sh.div(static_cast<unsigned>(a_first + g.sh - 1)));
+            const int i_last = min(g.Ho - 1, static_cast<int>(by_sh.div(static_cast<unsigned>(h0 + nrows - 1 + g.ph))));
+            ngo = max(0, i_last - i_first + 1);
+            in_off = h0 * g.W + group * g.W;
+            go_off = i_first * g.Wo;
+        }
+        T* plane = gx + nc * plane_in + in_off;                       // this thread's first row of the band
+        // what the buffer holds in this thread's first rows is requested before anything else, so that
+        // the reads are under way while the quotients are staged
+        T held[U][V];
+        if (ACCUM && lig < wv) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (group + u * ngroups < nrows) band_load<T, V>(plane + lig * V + u * stride, held[u]);
+            }
+        }
+        const T* src = go + nc * plane_out + go_off;
+        const int n = ngo * g.Wo;
+        auto stage = [&](auto quotient) {
+#pragma unroll 4
+            for (int e = threadIdx.x; e < n; e += blockDim.x) {
+                unsigned r, c;
+                by_wo.divmod(static_cast<unsigned>(e), r, c);
+                q[r * pitch + c] = quotient(__ldcs(src + e));
+            }
+        };
+        if (divide.kind == 1) stage([](T v) { return div9<T>(v); });
+        else if (divide.kind == 2) stage([&](T v) { return v * divide.inv; });
+        else stage([&](T v) { return v / divide.d; });
+        if (moved) {
+            for (int r = threadIdx.x; r < ngo; r += blockDim.x) q[r * pitch + g.Wo] = T(0);
+            for (int c = threadIdx.x; c < pitch; c += blockDim.x) q[ngo * pitch + c] = T(0);
+            for (int hh = threadIdx.x; hh < nrows; hh += blockDim.x) {
+                const int hp = h0 + hh + g.ph;
+                const int a0 = hp - g.kh + 1;
+                const int i_lo = a0 <= 0 ? 0 : static_cast<int>(by_sh.div(static_cast<unsigned>(a0 + g.sh - 1)));
+                const int ni = min(g.Ho - 1, static_cast<int>(by_sh.div(static_cast<unsigned>(hp)))) - i_lo + 1;
+                const int first = (i_lo - i_first) * pitch;
+                constexpr int B = static_cast<int>(sizeof(T));                 // TWO: byte offsets
+                if (TWO) rowinfo[hh] = make_int2((ni >= 1 ? first : ngo * pitch) * B, (ni >= 2 ? first + pitch : ngo * pitch) * B);
+                else rowinfo[hh] = make_int2(first, max(0, ni));
+            }
+        }
+        __syncthreads();
+        for (int c = lig; c < wv; c += lanes) {
+            BandColumn<T> col[V];
+#pragma unroll
+            for (int k = 0; k < V; ++k) col[k] = c == lig ? mine[k] : band_column<T>(g, c * V + k, by_sw);
+            const char* pa[V];
+            const char* pb[V];
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                pa[k] = reinterpret_cast<const char*>(q + col[k].a);
+                pb[k] = reinterpret_cast<const char*>(q + col[k].b);
+            }
+            T* out = plane + c * V;
+            for (int hb = group; hb < nrows; hb += U * ngroups, out += U * stride) {
+                if (ACCUM && (c != lig || hb != group)) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        if (hb + u * ngroups < nrows) band_load<T, V>(out + u * stride, held[u]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int hh = hb + u * ngroups;
+                    if (hh >= nrows) break;
+                    const int2 ro = rowinfo[hh];
+                    T res[V];
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        T acc = T(0);
+                        if (TWO) {
+                            acc += *reinterpret_cast<const T*>(pa[k] + ro.x);
+                            acc += *reinterpret_cast<const T*>(pb[k] + ro.x);
+                            acc += *reinterpret_cast<const T*>(pa[k] + ro.y);
+                            acc += *reinterpret_cast<const T*>(pb[k] + ro.y);
+                        } else {
+                            for (int a = 0; a < ro.y; ++a)
+                                for (int b = 0; b < col[k].nj; ++b) acc += q[ro.x + a * pitch + col[k].j_lo + b];
+                        }
+                        res[k] = ACCUM ? held[u][k] + acc : acc;
+                    }
+                    band_store<T, V>(out + u * stride, res);
+                }
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -747,6 +1104,23 @@ int avgpool_forward(const T* x, T* y, int N, int C, PoolGeom g) {
         const int64_t groups = total >> 2;
         KD_LAUNCH1(avgpool3x3s2p1_fwd<T>, (groups + kThreads - 1) / kThreads, kThreads, 0, x, y, g.H, g.W, g.Ho, g.Wo, groups,
                    kd::FastDiv(g.Wo / 4), kd::FastDiv(g.Ho));
+        return kd::launch_status();
+    }
+    const BandPlan plan = band_plan_fwd<T>(g);
+    if (plan.ok && nc * plan.bands < (int64_t(1) << 31)) {
+        const unsigned items = static_cast<unsigned>(nc * plan.bands);
+        const kd::FastDiv by_bands(plan.bands);
+        const int lanes = band_lane_bits(g.Wo);
+        // no window reaches outside the plane: no padding, and the last window ends inside
+        const bool inside = g.ph == 0 && g.pw == 0 && static_cast<int64_t>(g.Ho - 1) * g.sh + g.kh <= g.H &&
+                            static_cast<int64_t>(g.Wo - 1) * g.sw + g.kw <= g.W;
+#define KD_FWD_BAND(KH_, KW_, EDGES_)                                                                               \
+    KD_LAUNCH_W((avgpool_fwd_band<T, KH_, KW_, EDGES_>), 8, items, kBandThreads, plan.smem, x, y, g, plan.rows, items, by_bands, lanes)
+        if (g.kh == 3 && g.kw == 3) { if (inside) KD_FWD_BAND(3, 3, false); else KD_FWD_BAND(3, 3, true); }
+        else if (g.kh == 2 && g.kw == 2) { if (inside) KD_FWD_BAND(2, 2, false); else KD_FWD_BAND(2, 2, true); }
+        else if (inside) KD_FWD_BAND(0, 0, false);
+        else KD_FWD_BAND(0, 0, true);
+#undef KD_FWD_BAND
     } else {
         (void)kd::launch(avgpool_fwd_generic<T>, dim3(flat_grid(total)), kThreads, 0, x, y, g, total);
     }
@@ -770,6 +1144,33 @@ int avgpool_backward(const T* go, T* gx, int N, int C, PoolGeom g, bool accumula
         const int64_t blocks = nc * ((g.H + 1) / 2) * (g.W / 8);
         KD_LAUNCH(avgpool3x3s2p1_bwd<T>, (blocks + kThreads - 1) / kThreads, kThreads, 0, go, gx, g.H, g.W, g.Ho, g.Wo, blocks,
                   kd::FastDiv(g.W / 8), kd::FastDiv((g.H + 1) / 2));
+        return kd::launch_status();
+    }
+    const BandPlan plan = band_plan_bwd<T>(g);
+    if (plan.ok && nc * plan.bands < (int64_t(1) << 31)) {
+        const unsigned items = static_cast<unsigned>(nc * plan.bands);
+        const kd::FastDiv by_bands(plan.bands), by_sh(g.sh), by_sw(g.sw);
+        const kd::FastDiv by_wo(g.Wo);
+        const bool two = g.kh <= 2 * g.sh && g.kw <= 2 * g.sw;
+        // columns per thread: as many as one aligned access of up to 16 bytes holds, for every row of every plane
+        int v = 16 / static_cast<int>(sizeof(T));
+        while (v > 1 && (g.W % v != 0 || (reinterpret_cast<uintptr_t>(gx) % (v * sizeof(T))) != 0)) v /= 2;
+        const int lanes = band_lane_bits(g.W / v);
+#define KD_BWD_BAND_V(ACC, TWO_, V_)                                                                                 \
+    KD_LAUNCH_W((avgpool_bwd_band<T, ACC, TWO_, V_>), 8, items, kBandThreads, plan.smem, go, gx, g, plan.rows, items, by_bands, \
+                lanes, by_sh, by_sw, by_wo)
+#define KD_BWD_BAND(ACC, TWO_)                                                                                      \
+    do {                                                                                                            \
+        if (v == 4) { if constexpr (sizeof(T) == 4) KD_BWD_BAND_V(ACC, TWO_, 4); }                                  \
+        else if (v == 2) KD_BWD_BAND_V(ACC, TWO_, 2);                                                               \
+        else KD_BWD_BAND_V(ACC, TWO_, 1);                                                                           \
+    } while (0)
+        if (accumulate && two) KD_BWD_BAND(true, true);
+        else if (accumulate) KD_BWD_BAND(true, false);
+        else if (two) KD_BWD_BAND(false, true);
+        else KD_BWD_BAND(false, false);
+#undef KD_BWD_BAND_V
+#undef KD_BWD_BAND
     } else if (accumulate) {
         (void)kd::launch(avgpool_bwd_gather<T, true>, dim3(flat_grid(total)), kThreads, 0, go, gx, g, total);
     } else {

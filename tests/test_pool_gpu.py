@@ -92,6 +92,61 @@ def test_avgpool_ex_forward_backward_bit_exact(oracle, geom, dtype):
     assert_same_bits(dgx.get(), oracle.avgpool2d_backward(go, x.shape, k, s, p))
 
 
+# several bands of rows per plane, spans that start off a 16-byte boundary, windows over the edge, rows too long to stage
+BAND_GEOMS = [
+    (2, 3, 130, 70, (3, 3), (2, 2), (1, 1)),
+    (1, 2, 200, 33, (2, 2), (2, 2), (0, 0)),
+    (2, 2, 58, 58, (3, 3), (2, 2), (0, 0)),      # the padded plane of a 56x56 layer
+    (1, 2, 300, 9, (5, 3), (3, 2), (2, 1)),
+    (1, 3, 64, 64, (4, 4), (4, 4), (0, 0)),
+    (1, 1, 12, 1500, (3, 3), (1, 1), (1, 1)),    # three rows exceed a band: the one-thread-per-element kernels
+    (1, 2, 37, 41, (3, 3), (3, 3), (2, 2)),      # whole windows inside the padding
+]
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("offset", [0, 1, 2, 3])
+@pytest.mark.parametrize("geom", BAND_GEOMS)
+def test_avgpool_row_bands_any_alignment_bit_exact(oracle, geom, offset, dtype):
+    """Every tensor starts `offset` elements into its allocation; the elements in front must stay untouched."""
+    lib = native()
+    N, C, H, W, k, s, p = geom
+    Ho, Wo = _ohw(H, W, k, s, p)
+    rng = np.random.default_rng(H * 7 + W + offset)
+    item = np.dtype(dtype).itemsize
+    x = rng.uniform(-1, 1, (N, C, H, W)).astype(dtype)
+    go = rng.standard_normal((N, C, Ho, Wo)).astype(dtype)
+    front = rng.standard_normal(offset).astype(dtype)
+
+    def flat(a=None, n=None):
+        body = a.ravel() if a is not None else np.full(n, np.nan, dtype)
+        return Buf(lib, np.concatenate([front, body]))
+
+    dx, dgo, dy, dgx = flat(x), flat(go), flat(n=go.size), flat(n=x.size)
+    sfx = suf(dtype)
+    at = lambda b: b.ptr + offset * item
+    lib.call(f"keydnn_cuda_avgpool2d_forward_ex_{sfx}", at(dx), at(dy), N, C, H, W, Ho, Wo, k[0], k[1], s[0], s[1], p[0], p[1])
+    got = dy.get()
+    assert_same_bits(got[:offset], front)
+    assert_same_bits(got[offset:].reshape(go.shape), oracle.avgpool2d_forward(x, k, s, p))
+    lib.call(f"keydnn_cuda_avgpool2d_backward_ex_{sfx}", at(dgo), at(dgx), N, C, H, W, Ho, Wo, k[0], k[1], s[0], s[1], p[0], p[1])
+    got = dgx.get()
+    assert_same_bits(got[:offset], front)
+    want = oracle.avgpool2d_backward(go, x.shape, k, s, p)
+    assert_same_bits(got[offset:].reshape(x.shape), want)
+    if p == (0, 0):
+        # the reference-signature entry adds onto what the buffer holds (keydnn_avgpool2d_cuda.cu:197)
+        held = rng.standard_normal(x.shape).astype(dtype)
+        dacc = flat(held)
+        lib.call(f"keydnn_cuda_avgpool2d_backward_{sfx}", at(dgo), at(dacc), N, C, Ho, Wo, H, W, k[0], k[1], s[0], s[1])
+        got = dacc.get()
+        assert_same_bits(got[:offset], front)
+        assert_same_bits(got[offset:].reshape(x.shape), held + want)
+        dy2 = flat(n=go.size)
+        lib.call(f"keydnn_cuda_avgpool2d_forward_{sfx}", at(dx), at(dy2), N, C, H, W, Ho, Wo, k[0], k[1], s[0], s[1])
+        assert_same_bits(dy2.get()[offset:].reshape(go.shape), oracle.avgpool2d_forward(x, k, s, p))
+
+
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 def test_reference_signature_entries_on_padded_planes(oracle, dtype):
     """pad2d -> pool -> (memset) -> backward -> crop2d, the reference's own call sequence
