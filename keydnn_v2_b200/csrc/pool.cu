@@ -552,6 +552,81 @@ avgpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int row
     }
 }
 
+// MaxPool forward on the same bands: the selection rule of maxpool_fwd_generic tap for tap (row-major scan, strictly
+// greater replaces, taps outside the plane are never candidates), the position as h * (W + 2 pw) + w in the padded plane.
+template <typename T, int KH, int KW, bool EDGES>
+__global__ void __launch_bounds__(kBandThreads)
+maxpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, PoolGeom g, int rows, unsigned items,
+                 kd::FastDiv by_bands, int lane_bits) {
+    extern __shared__ __align__(16) unsigned char band_smem[];
+    T* s = reinterpret_cast<T*>(band_smem);
+    kd::pdl_prologue();
+    const int kh = KH ? KH : g.kh, kw = KW ? KW : g.kw;
+    const int lanes = 1 << lane_bits;
+    const int group = threadIdx.x >> lane_bits, lig = threadIdx.x & (lanes - 1), ngroups = blockDim.x >> lane_bits;
+    const int step = ngroups * g.sh;
+    const int Wp = g.W + 2 * g.pw;
+    const int64_t plane_in = static_cast<int64_t>(g.H) * g.W, plane_out = static_cast<int64_t>(g.Ho) * g.Wo;
+    unsigned cur = ~0u;
+    int nout = 0, nrows = 0, first = 0, in_off = 0, out_off = 0, hp_first = 0;
+    for (unsigned item = blockIdx.x; item < items; item += gridDim.x) {
+        unsigned nc, band;
+        by_bands.divmod(item, nc, band);
+        if (band != cur) {
+            cur = band;
+            const int i0 = static_cast<int>(band) * rows;
+            nout = min(g.Ho, i0 + rows) - i0;
+            const int h_lo = max(0, i0 * g.sh - g.ph);
+            nrows = min(g.H, (i0 + nout - 1) * g.sh - g.ph + kh) - h_lo;
+            in_off = h_lo * g.W;
+            out_off = i0 * g.Wo;
+            first = i0 * g.sh - g.ph - h_lo + group * g.sh;              // staged row of this thread's first tap
+            hp_first = (i0 + group) * g.sh;                              // the same row in the padded plane
+        }
+        const T* src = x + nc * plane_in + in_off;
+        const int mis = band_misalign(src);
+        if (nrows > 0) band_stage(src, nrows * g.W, s, mis);
+        __syncthreads();
+        const int64_t obase = nc * plane_out + out_off + group * g.Wo;
+        for (int j = lig; j < g.Wo; j += lanes) {
+            const int wp0 = j * g.sw;
+            const int w0 = wp0 - g.pw;
+            int hh = first, hp0 = hp_first;
+            const T* t = s + mis + hh * g.W + w0;                              // dereferenced only where the tap exists
+            int64_t o = obase + j;
+            for (int ii = group; ii < nout; ii += ngroups, hh += step, hp0 += step, t += step * g.W, o += ngroups * g.Wo) {
+                T best = kd::neg_inf<T>();
+                int ba = 0, bb = 0;
+                if (KH > 0) {
+#pragma unroll
+                    for (int a = 0; a < KH; ++a) {
+                        const bool row_ok = !EDGES || (hh + a >= 0 && hh + a < nrows);
+#pragma unroll
+                        for (int b = 0; b < KW; ++b) {
+                            if (!EDGES || (row_ok && w0 + b >= 0 && w0 + b < g.W)) {
+                                const T v = t[a * g.W + b];
+                                if (v > best) { best = v; ba = a; bb = b; }
+                            }
+                        }
+                    }
+                } else {
+                    for (int a = 0; a < kh; ++a) {
+                        if (EDGES && (hh + a < 0 || hh + a >= nrows)) continue;
+                        for (int b = 0; b < kw; ++b) {
+                            if (EDGES && (w0 + b < 0 || w0 + b >= g.W)) continue;
+                            const T v = t[a * g.W + b];
+                            if (v > best) { best = v; ba = a; bb = b; }
+                        }
+                    }
+                }
+                y[o] = best;
+                idx[o] = static_cast<long long>(hp0 + ba) * Wp + (wp0 + bb);
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // Backward.  The quotients go / (kh*kw) of the output rows that cover the band are staged once, in rows of Wo + 1
 // with a zero in the extra column, followed by a row of zeros.  What depends on the column only (the first covering
 // output column and how many there are) is computed once per thread; what depends on the row only comes from a table
@@ -712,6 +787,154 @@ avgpool_bwd_band(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int r
                                 for (int b = 0; b < col[k].nj; ++b) acc += q[ro.x + a * pitch + col[k].j_lo + b];
                         }
                         res[k] = ACCUM ? held[u][k] + acc : acc;
+                    }
+                    band_store<T, V>(out + u * stride, res);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// MaxPool backward on bands of input rows: every element of gx is written once with the sum, in ascending (i, j), of
+// the gradients of the windows that recorded it (the rule of maxpool_bwd_gather).  The covering output rows are staged
+// as {gradient, tap}: tap = a * kw + b of the recorded position inside its own window, -1 when the position is not
+// inside it; an element at window offset (a, b) takes the gradient when the staged tap equals a * kw + b.  Rows of
+// Wo + 1 with {0, -1} in the extra column and a last row of {0, -1} stand in for windows that do not exist, as in the
+// AvgPool kernel; the row table holds {offset of the first covering row, offset of the second (TWO) or the number of
+// covering rows, a * kw of the element in the first covering row}.
+struct BandPlanMax { bool ok; int rows, bands; size_t smem; };
+
+template <typename T> inline BandPlanMax band_plan_maxbwd(const PoolGeom& g) {
+    BandPlanMax p = {false, 0, 0, 0};
+    const int64_t cap = kBandBytes / static_cast<int64_t>(sizeof(T) + sizeof(int));
+    const int64_t pitch = g.Wo + 1;
+    if ((band_go_rows(g, 1) + 1) * pitch > cap) return p;
+    int64_t r = (cap / pitch - 2) * g.sh - g.kh + 2;
+    if (r < 1) r = 1;
+    while (r > 1 && (band_go_rows(g, r) + 1) * pitch > cap) --r;
+    const int64_t most = (8192 + g.W - 1) / g.W;
+    if (r > most) r = most;
+    if (r > kBandRowsMax) r = kBandRowsMax;
+    if (r > g.H) r = g.H;
+    p.bands = static_cast<int>((g.H + r - 1) / r);
+    p.rows = (g.H + p.bands - 1) / p.bands;
+    const size_t staged = static_cast<size_t>((band_go_rows(g, p.rows) + 1) * pitch);
+    p.smem = static_cast<size_t>(p.rows) * sizeof(int4) + ((staged * sizeof(T) + 15) & ~size_t(15)) + staged * sizeof(int);
+    p.ok = true;
+    return p;
+}
+
+template <typename T, bool TWO, int V>
+__global__ void __launch_bounds__(kBandThreads)
+maxpool_bwd_band(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, PoolGeom g, int rows,
+                 unsigned items, kd::FastDiv by_bands, int lane_bits, kd::FastDiv by_sh, kd::FastDiv by_sw, kd::FastDiv by_wo,
+                 kd::FastDiv by_wp, int staged) {
+    extern __shared__ __align__(16) unsigned char band_smem[];
+    int4* rowinfo = reinterpret_cast<int4*>(band_smem);
+    T* q = reinterpret_cast<T*>(band_smem + static_cast<size_t>(rows) * sizeof(int4));
+    int* tap = reinterpret_cast<int*>(band_smem + static_cast<size_t>(rows) * sizeof(int4) +
+                                      ((static_cast<size_t>(staged) * sizeof(T) + 15) & ~size_t(15)));
+    kd::pdl_prologue();
+    const int lanes = 1 << lane_bits;
+    const int group = threadIdx.x >> lane_bits, lig = threadIdx.x & (lanes - 1), ngroups = blockDim.x >> lane_bits;
+    const int pitch = g.Wo + 1;
+    constexpr int U = 8 / V;
+    const int wv = g.W / V;
+    const int Wp = g.W + 2 * g.pw;
+    const long long padded = static_cast<long long>(g.H + 2 * g.ph) * Wp;
+    const int64_t stride = static_cast<int64_t>(ngroups) * g.W;
+    const int64_t plane_in = static_cast<int64_t>(g.H) * g.W, plane_out = static_cast<int64_t>(g.Ho) * g.Wo;
+    BandColumn<T> mine[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) mine[k] = band_column<T>(g, lig * V + k, by_sw);
+    unsigned cur = ~0u;
+    int nrows = 0, ngo = 0, in_off = 0, go_off = 0, i_first = 0;
+    for (unsigned item = blockIdx.x; item < items; item += gridDim.x) {
+        unsigned nc, band;
+        by_bands.divmod(item, nc, band);
+        const bool moved = band != cur;
+        int h0 = 0;
+        if (moved) {
+            cur = band;
+            h0 = static_cast<int>(band) * rows;
+            nrows = min(g.H, h0 + rows) - h0;
+            const int a_first = h0 + g.ph - g.kh + 1;
+            i_first = a_first <= 0 ? 0 : static_cast<int>(by_sh.div(static_cast<unsigned>(a_first + g.sh - 1)));
+            const int i_last = min(g.Ho - 1, static_cast<int>(by_sh.div(static_cast<unsigned>(h0 + nrows - 1 + g.ph))));
+            ngo = max(0, i_last - i_first + 1);
+            in_off = h0 * g.W + group * g.W;
+            go_off = i_first * g.Wo;
+        }
+        const T* src = go + nc * plane_out + go_off;
+        const long long* isrc = idx + nc * plane_out + go_off;
+        const int n = ngo * g.Wo;
+#pragma unroll 4
+        for (int e = threadIdx.x; e < n; e += blockDim.x) {
+            unsigned r, c;
+            by_wo.divmod(static_cast<unsigned>(e), r, c);
+            const long long p = __ldcs(isrc + e);
+            int code = -1;
+            if (p >= 0 && p < padded) {
+                unsigned hb, wb;
+                by_wp.divmod(static_cast<unsigned>(p), hb, wb);
+                const int a = static_cast<int>(hb) - (i_first + static_cast<int>(r)) * g.sh;
+                const int b = static_cast<int>(wb) - static_cast<int>(c) * g.sw;
+                if (a >= 0 && a < g.kh && b >= 0 && b < g.kw) code = a * g.kw + b;
+            }
+            q[r * pitch + c] = __ldcs(src + e);
+            tap[r * pitch + c] = code;
+        }
+        if (moved) {
+            for (int r = threadIdx.x; r < ngo; r += blockDim.x) { q[r * pitch + g.Wo] = T(0); tap[r * pitch + g.Wo] = -1; }
+            for (int c = threadIdx.x; c < pitch; c += blockDim.x) { q[ngo * pitch + c] = T(0); tap[ngo * pitch + c] = -1; }
+            for (int hh = threadIdx.x; hh < nrows; hh += blockDim.x) {
+                const int hp = h0 + hh + g.ph;
+                const int a0 = hp - g.kh + 1;
+                const int i_lo = a0 <= 0 ? 0 : static_cast<int>(by_sh.div(static_cast<unsigned>(a0 + g.sh - 1)));
+                const int ni = min(g.Ho - 1, static_cast<int>(by_sh.div(static_cast<unsigned>(hp)))) - i_lo + 1;
+                const int first = (i_lo - i_first) * pitch;
+                const int rp = (hp - i_lo * g.sh) * g.kw;
+                if (TWO) rowinfo[hh] = make_int4(ni >= 1 ? first : ngo * pitch, ni >= 2 ? first + pitch : ngo * pitch, rp, 0);
+                else rowinfo[hh] = make_int4(first, max(0, ni), rp, 0);
+            }
+        }
+        __syncthreads();
+        T* plane = gx + nc * plane_in + in_off;                       // this thread's first row of the band
+        const int row_step = g.sh * g.kw;
+        for (int c = lig; c < wv; c += lanes) {
+            BandColumn<T> col[V];
+            int cp[V];                                                // b of the element in its first covering column
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                col[k] = c == lig ? mine[k] : band_column<T>(g, c * V + k, by_sw);
+                cp[k] = c * V + k + g.pw - col[k].j_lo * g.sw;
+            }
+            T* out = plane + c * V;
+            for (int hb = group; hb < nrows; hb += U * ngroups, out += U * stride) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int hh = hb + u * ngroups;
+                    if (hh >= nrows) break;
+                    const int4 ro = rowinfo[hh];
+                    T res[V];
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        T acc = T(0);
+                        if (TWO) {
+                            const int e00 = ro.z + cp[k], e01 = e00 - g.sw, e10 = e00 - row_step, e11 = e10 - g.sw;
+                            acc += tap[ro.x + col[k].a] == e00 ? q[ro.x + col[k].a] : T(0);
+                            acc += tap[ro.x + col[k].b] == e01 ? q[ro.x + col[k].b] : T(0);
+                            acc += tap[ro.y + col[k].a] == e10 ? q[ro.y + col[k].a] : T(0);
+                            acc += tap[ro.y + col[k].b] == e11 ? q[ro.y + col[k].b] : T(0);
+                        } else {
+                            for (int a = 0; a < ro.y; ++a)
+                                for (int b = 0; b < col[k].nj; ++b) {
+                                    const int at = ro.x + a * pitch + col[k].j_lo + b;
+                                    if (tap[at] == ro.z - a * row_step + cp[k] - b * g.sw) acc += q[at];
+                                }
+                        }
+                        res[k] = acc;
                     }
                     band_store<T, V>(out + u * stride, res);
                 }
@@ -1026,6 +1249,12 @@ inline bool out_dims_ok(const PoolGeom& g) {
            (static_cast<int64_t>(g.Wo - 1) * g.sw < g.W + 2 * g.pw);
 }
 
+// no window reaches outside the plane: no padding, and the last window ends inside
+inline bool windows_inside(const PoolGeom& g) {
+    return g.ph == 0 && g.pw == 0 && static_cast<int64_t>(g.Ho - 1) * g.sh + g.kh <= g.H &&
+           static_cast<int64_t>(g.Wo - 1) * g.sw + g.kw <= g.W;
+}
+
 template <typename T>
 int maxpool_forward(const T* x, T* y, long long* idx, int N, int C, PoolGeom g) {
     if (!x || !y || !idx) return -1;
@@ -1044,6 +1273,22 @@ int maxpool_forward(const T* x, T* y, long long* idx, int N, int C, PoolGeom g) 
         const int64_t groups = total >> 2;
         KD_LAUNCH((maxpool2x2_fwd<T, U>), (groups + kThreads * U - 1) / (kThreads * U), kThreads, 0, x, y, idx, g.H, g.W,
                   g.Ho, g.Wo, groups, kd::FastDiv(g.Wo / 4), kd::FastDiv(g.Ho));
+        return kd::launch_status();
+    }
+    const BandPlan plan = band_plan_fwd<T>(g);
+    if (plan.ok && nc * plan.bands < (int64_t(1) << 31)) {
+        const unsigned items = static_cast<unsigned>(nc * plan.bands);
+        const kd::FastDiv by_bands(plan.bands);
+        const int lanes = band_lane_bits(g.Wo);
+        const bool inside = windows_inside(g);
+#define KD_FWD_BAND(KH_, KW_, EDGES_)                                                                               \
+    KD_LAUNCH_W((maxpool_fwd_band<T, KH_, KW_, EDGES_>), 8, items, kBandThreads, plan.smem, x, y, idx, g, plan.rows, items, \
+                by_bands, lanes)
+        if (g.kh == 3 && g.kw == 3) { if (inside) KD_FWD_BAND(3, 3, false); else KD_FWD_BAND(3, 3, true); }
+        else if (g.kh == 2 && g.kw == 2) { if (inside) KD_FWD_BAND(2, 2, false); else KD_FWD_BAND(2, 2, true); }
+        else if (inside) KD_FWD_BAND(0, 0, false);
+        else KD_FWD_BAND(0, 0, true);
+#undef KD_FWD_BAND
     } else {
         (void)kd::launch(maxpool_fwd_generic<T>, dim3(flat_grid(total)), kThreads, 0, x, y, idx, g, total);
     }
@@ -1068,6 +1313,31 @@ int maxpool_backward_ex(const T* go, const long long* idx, T* gx, int N, int C, 
         const int64_t blocks = (nc * g.H * g.W) >> 3;
         KD_LAUNCH((maxpool2x2_bwd<T, U>), (blocks + kThreads * U - 1) / (kThreads * U), kThreads, 0, go, idx, gx, g.H,
                   g.W, g.Ho, g.Wo, blocks, kd::FastDiv(g.W / 8), kd::FastDiv(g.H));
+        return kd::launch_status();
+    }
+    const BandPlanMax plan = band_plan_maxbwd<T>(g);
+    const int64_t padded = static_cast<int64_t>(g.H + 2 * g.ph) * (g.W + 2 * g.pw);
+    if (plan.ok && nc * plan.bands < (int64_t(1) << 31) && padded < (int64_t(1) << 31)) {
+        const unsigned items = static_cast<unsigned>(nc * plan.bands);
+        const kd::FastDiv by_bands(plan.bands), by_sh(g.sh), by_sw(g.sw), by_wo(g.Wo), by_wp(g.W + 2 * g.pw);
+        const bool two = g.kh <= 2 * g.sh && g.kw <= 2 * g.sw;
+        int v = 16 / static_cast<int>(sizeof(T));
+        while (v > 1 && (g.W % v != 0 || (reinterpret_cast<uintptr_t>(gx) % (v * sizeof(T))) != 0)) v /= 2;
+        const int lanes = band_lane_bits(g.W / v);
+        const int staged = static_cast<int>((band_go_rows(g, plan.rows) + 1) * (g.Wo + 1));
+#define KD_BWD_BAND_V(TWO_, V_)                                                                                      \
+    KD_LAUNCH_W((maxpool_bwd_band<T, TWO_, V_>), 8, items, kBandThreads, plan.smem, go, idx, gx, g, plan.rows, items, by_bands, \
+                lanes, by_sh, by_sw, by_wo, by_wp, staged)
+#define KD_BWD_BAND(TWO_)                                                                                           \
+    do {                                                                                                            \
+        if (v == 4) { if constexpr (sizeof(T) == 4) KD_BWD_BAND_V(TWO_, 4); }                                       \
+        else if (v == 2) KD_BWD_BAND_V(TWO_, 2);                                                                    \
+        else KD_BWD_BAND_V(TWO_, 1);                                                                                \
+    } while (0)
+        if (two) KD_BWD_BAND(true);
+        else KD_BWD_BAND(false);
+#undef KD_BWD_BAND_V
+#undef KD_BWD_BAND
     } else {
         const int64_t total = nc * g.H * g.W;
         (void)kd::launch(maxpool_bwd_gather<T>, dim3(flat_grid(total)), kThreads, 0, go, idx, gx, g, total);
@@ -1111,9 +1381,7 @@ int avgpool_forward(const T* x, T* y, int N, int C, PoolGeom g) {
         const unsigned items = static_cast<unsigned>(nc * plan.bands);
         const kd::FastDiv by_bands(plan.bands);
         const int lanes = band_lane_bits(g.Wo);
-        // no window reaches outside the plane: no padding, and the last window ends inside
-        const bool inside = g.ph == 0 && g.pw == 0 && static_cast<int64_t>(g.Ho - 1) * g.sh + g.kh <= g.H &&
-                            static_cast<int64_t>(g.Wo - 1) * g.sw + g.kw <= g.W;
+        const bool inside = windows_inside(g);
 #define KD_FWD_BAND(KH_, KW_, EDGES_)                                                                               \
     KD_LAUNCH_W((avgpool_fwd_band<T, KH_, KW_, EDGES_>), 8, items, kBandThreads, plan.smem, x, y, g, plan.rows, items, by_bands, lanes)
         if (g.kh == 3 && g.kw == 3) { if (inside) KD_FWD_BAND(3, 3, false); else KD_FWD_BAND(3, 3, true); }

@@ -148,6 +148,54 @@ def test_avgpool_row_bands_any_alignment_bit_exact(oracle, geom, offset, dtype):
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("offset", [0, 1, 2])
+@pytest.mark.parametrize("geom", BAND_GEOMS)
+def test_maxpool_row_bands_any_alignment(oracle, geom, offset, dtype):
+    """Values and int64 positions of the banded forward kernel, ties included, on tensors that start `offset`
+    elements into their allocation."""
+    lib = native()
+    N, C, H, W, k, s, p = geom
+    Ho, Wo = _ohw(H, W, k, s, p)
+    rng = np.random.default_rng(H * 11 + W + offset)
+    item = np.dtype(dtype).itemsize
+    x = (np.round(rng.uniform(-1, 1, (N, C, H, W)) * 8) / 8).astype(dtype)        # many ties
+    x[0, 0, : min(H, 4), : min(W, 4)] = -np.inf                                     # windows without a finite tap
+    x[-1, -1, H // 2, W // 2] = np.nan
+    front = rng.standard_normal(offset).astype(dtype)
+    dx = Buf(lib, np.concatenate([front, x.ravel()]))
+    dy = Buf(lib, np.concatenate([front, np.full(N * C * Ho * Wo, np.nan, dtype)]))
+    didx = Buf(lib, np.full(offset + N * C * Ho * Wo, -7, np.int64))
+    sfx = suf(dtype)
+    lib.call(f"keydnn_cuda_maxpool2d_forward_ex_{sfx}", dx.ptr + offset * item, dy.ptr + offset * item, didx.ptr + offset * 8,
+             N, C, H, W, Ho, Wo, k[0], k[1], s[0], s[1], p[0], p[1])
+    y_w, idx_w = oracle.maxpool2d_forward(x, k, s, p)
+    got, got_idx = dy.get(), didx.get()
+    assert_same_bits(got[:offset], front)
+    np.testing.assert_array_equal(got_idx[:offset], -7)
+    np.testing.assert_array_equal(got[offset:].reshape(y_w.shape), y_w)
+    np.testing.assert_array_equal(got_idx[offset:].reshape(idx_w.shape), idx_w)
+    # backward: every element written once; positions that point outside their window route nothing
+    go = rng.standard_normal((N, C, Ho, Wo)).astype(dtype)
+    idx_b = idx_w.copy()
+    idx_b[0, 0, 0, 0] = -5
+    idx_b[-1, -1, -1, -1] = 1 << 40
+    if Ho > 2 and Wo > 2:
+        idx_b[0, 0, 1, 1] = idx_w[0, 0, -1, -1]                  # inside the plane, outside its own window
+    want = oracle.maxpool2d_backward(go, np.where((idx_b == idx_w), idx_w, -1), x.shape, p)
+    dgo = Buf(lib, np.concatenate([front, go.ravel()]))
+    didx_b = Buf(lib, np.concatenate([np.zeros(offset, np.int64), idx_b.ravel()]))
+    dgx = Buf(lib, np.concatenate([front, np.full(x.size, np.nan, dtype)]))
+    lib.call(f"keydnn_cuda_maxpool2d_backward_ex_{sfx}", dgo.ptr + offset * item, didx_b.ptr + offset * 8, dgx.ptr + offset * item,
+             N, C, H, W, Ho, Wo, k[0], k[1], s[0], s[1], p[0], p[1])
+    got = dgx.get()
+    assert_same_bits(got[:offset], front)
+    if _overlaps(k, s):
+        np.testing.assert_allclose(got[offset:].reshape(x.shape), want, **TOL[np.dtype(dtype)])
+    else:
+        assert_same_bits(got[offset:].reshape(x.shape), want)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
 def test_reference_signature_entries_on_padded_planes(oracle, dtype):
     """pad2d -> pool -> (memset) -> backward -> crop2d, the reference's own call sequence
     (ops/pool2d_cuda_ext.py:56-522), gives the same results as the fused entries."""
