@@ -350,6 +350,29 @@ def suite_table(lib, timer, peak: float, reps: int = 10, warm: int = 3, extras: 
     timed("cce_backward_f32", 3.0 * x.nbytes, lambda: lib.call("keydnn_cuda_cce_backward_f32", pr.data, y.data, None, gx.data, n,
                                                              1 << 17))
     del x, y, gx, pr
+    # pooling outside the benchmark configurations: MaxPool 3x3 / stride 2 / padding 1, and the reference-signature
+    # entries on a plane the caller padded itself (row-band kernels; AvgPool's adds onto the buffer: read + write)
+    N_, C_, H_, Ho_ = 128, 64, 112, 56
+    x = T.from_numpy(rng.standard_normal((N_, C_, H_, H_), dtype=np.float32))
+    y, idx = T.empty((N_, C_, Ho_, Ho_)), T.empty((N_, C_, Ho_, Ho_), dtype=np.int64)
+    gx = T.empty(x.shape)
+    nb = x.nbytes + y.nbytes + idx.nbytes
+    timed("maxpool2d_3x3s2p1_fwd_f32", nb, lambda: lib.call("keydnn_cuda_maxpool2d_forward_ex_f32", x.data, y.data, idx.data,
+                                                          N_, C_, H_, H_, Ho_, Ho_, 3, 3, 2, 2, 1, 1))
+    timed("maxpool2d_3x3s2p1_bwd_f32", nb, lambda: lib.call("keydnn_cuda_maxpool2d_backward_ex_f32", y.data, idx.data, gx.data,
+                                                          N_, C_, H_, H_, Ho_, Ho_, 3, 3, 2, 2, 1, 1))
+    del x, y, idx, gx
+    N_, C_, Hp_, Ho_ = 128, 256, 58, 28
+    xp = T.from_numpy(rng.standard_normal((N_, C_, Hp_, Hp_), dtype=np.float32))
+    y, idx = T.empty((N_, C_, Ho_, Ho_)), T.empty((N_, C_, Ho_, Ho_), dtype=np.int64)
+    gxp = T.zeros(xp.shape)
+    timed("maxpool2d_fwd_padded_plane_58x58_f32", xp.nbytes + y.nbytes + idx.nbytes, lambda: lib.call(
+        "keydnn_cuda_maxpool2d_forward_f32", xp.data, y.data, idx.data, N_, C_, Hp_, Hp_, Ho_, Ho_, 3, 3, 2, 2))
+    timed("avgpool2d_fwd_padded_plane_58x58_f32", xp.nbytes + y.nbytes, lambda: lib.call(
+        "keydnn_cuda_avgpool2d_forward_f32", xp.data, y.data, N_, C_, Hp_, Hp_, Ho_, Ho_, 3, 3, 2, 2))
+    timed("avgpool2d_bwd_padded_plane_58x58_f32", 2.0 * xp.nbytes + y.nbytes, lambda: lib.call(
+        "keydnn_cuda_avgpool2d_backward_f32", y.data, gxp.data, N_, C_, Ho_, Ho_, Hp_, Hp_, 3, 3, 2, 2))
+    del xp, y, idx, gxp
     # layer glue: bias add, broadcast, un-broadcast, transpose on the CNN's activation shape
     N_, C_, HW_ = 256, 32, 64 * 64
     act = T.from_numpy(rng.standard_normal((N_, C_, HW_), dtype=np.float32))

@@ -180,6 +180,147 @@ maxpool2x2_bwd(const T* __restrict__ go, const long long* __restrict__ idx, T* _
     }
 }
 
+// kernel 3x3, stride 2, padding 1, W % 8 == 0: the register layout of avgpool3x3s2p1_fwd (four adjacent outputs per
+// thread, three rows of eight aligned inputs plus the one left of them) with the selection rule above.  A tap in the
+// padding is held as -inf, which can never replace the best.
+// (fp32: six CTAs per SM, which costs two spilled registers and gains 8 % - the kernel waits on its loads.)
+template <typename T>
+__global__ void __launch_bounds__(kThreads, sizeof(T) == 4 ? 6 : 1)
+maxpool3x3s2p1_fwd(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, int H, int W, int Ho, int Wo,
+                   int64_t groups, kd::FastDiv by_gpr, kd::FastDiv by_ho) {
+    kd::pdl_prologue();
+    const int Wp = W + 2;
+    for (int64_t gi = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; gi < groups;
+         gi += static_cast<int64_t>(gridDim.x) * kThreads) {
+        unsigned row, ujg, nc, ui;
+        by_gpr.divmod(static_cast<unsigned>(gi), row, ujg);
+        by_ho.divmod(row, nc, ui);
+        const int jg = static_cast<int>(ujg), i = static_cast<int>(ui);
+        const T* plane = x + static_cast<int64_t>(nc) * H * W;
+        T c[3][9];
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            const int h = 2 * i - 1 + r;
+            if (h >= 0 && h < H) {
+                const T* p = plane + static_cast<int64_t>(h) * W + 8 * jg;
+                const kd::Row8<T> a = kd::load8(p);
+                c[r][0] = jg > 0 ? __ldg(p - 1) : kd::neg_inf<T>();
+#pragma unroll
+                for (int k = 0; k < 8; ++k) c[r][1 + k] = a.v[k];
+            } else {
+#pragma unroll
+                for (int k = 0; k < 9; ++k) c[r][k] = kd::neg_inf<T>();
+            }
+        }
+        Pack4<T> out;
+        Pack4<long long> pos;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            T best = kd::neg_inf<T>();
+            int bt = 0;                                            // a * 4 + b of the best tap
+#pragma unroll
+            for (int r = 0; r < 3; ++r)
+#pragma unroll
+                for (int b = 0; b < 3; ++b) {
+                    const T v = c[r][2 * q + b];
+                    if (v > best) { best = v; bt = r * 4 + b; }
+                }
+            out.v[q] = best;
+            pos.v[q] = static_cast<long long>(2 * i + (bt >> 2)) * Wp + (2 * (4 * jg + q) + (bt & 3));
+        }
+        kd::store4(y + static_cast<int64_t>(row) * Wo + 4 * jg, out);
+        kd::store4(idx + static_cast<int64_t>(row) * Wo + 4 * jg, pos);
+    }
+}
+
+// Backward of the same geometry: the 2x8 block of gradient rows (2m, 2m+1) x [8jg, 8jg+8) per thread, as in
+// avgpool3x3s2p1_bwd.  Each of the ten windows that touch the block (five per output row) is reduced to
+// tap = recorded position - position of the window origin (a * Wp + b for a position inside the window, -1 otherwise);
+// an element takes the gradient of a covering window when the tap is the element's own offset in that window.
+// Windows are visited in ascending (i, j) as in maxpool_bwd_gather.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+maxpool3x3s2p1_bwd(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, int H, int W, int Ho, int Wo,
+                   int64_t blocks, kd::FastDiv by_bpr, kd::FastDiv by_hh) {
+    kd::pdl_prologue();
+    const int Wp = W + 2;
+    for (int64_t bi = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; bi < blocks;
+         bi += static_cast<int64_t>(gridDim.x) * kThreads) {
+        unsigned rowp, ujg, nc, um;                    // rowp = nc * ceil(H/2) + m
+        by_bpr.divmod(static_cast<unsigned>(bi), rowp, ujg);
+        by_hh.divmod(rowp, nc, um);
+        const int jg = static_cast<int>(ujg), m = static_cast<int>(um);
+        const int64_t p0 = (static_cast<int64_t>(nc) * Ho + m) * Wo + 4 * jg;
+        const bool has_fifth = 4 * jg + 4 < Wo;        // the fifth window exists
+        const bool second = m + 1 < Ho;                // output row m+1 exists
+        T g[2][5];
+        int tap[2][5];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const bool live = r == 0 || second;
+            Pack4<T> a;
+            Pack4<long long> p;
+            a.v[0] = a.v[1] = a.v[2] = a.v[3] = T(0);
+            p.v[0] = p.v[1] = p.v[2] = p.v[3] = -1;
+            T e = T(0);
+            long long pe = -1;
+            if (live) {
+                a = kd::load4(go + p0 + r * Wo);
+                p = kd::load4(idx + p0 + r * Wo);
+                if (has_fifth) { e = __ldg(go + p0 + r * Wo + 4); pe = __ldg(idx + p0 + r * Wo + 4); }
+            }
+            const long long origin = static_cast<long long>(2 * (m + r)) * Wp + 8 * jg;      // of the first window
+#pragma unroll
+            for (int k = 0; k < 5; ++k) {
+                const long long d = (k < 4 ? p.v[k] : pe) - (origin + 2 * k);
+                g[r][k] = k < 4 ? a.v[k] : e;
+                tap[r][k] = (d >= 0 && d < 3 * static_cast<long long>(Wp)) ? static_cast<int>(d) : -1;
+            }
+            if (!live || !has_fifth) tap[r][4] = -1;
+            if (!live) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) tap[r][k] = -1;
+            }
+        }
+        T* r0 = gx + (static_cast<int64_t>(nc) * H + 2 * m) * W + 8 * jg;
+        {   // row 2m (padded row 2m+1): a = 1 in output row m
+            kd::Row8<T> out;
+#pragma unroll
+            for (int cidx = 0; cidx < 8; ++cidx) {
+                const int k = cidx >> 1;
+                T acc = T(0);
+                if (cidx & 1) {
+                    acc += tap[0][k] == Wp + 2 ? g[0][k] : T(0);
+                    acc += tap[0][k + 1] == Wp ? g[0][k + 1] : T(0);
+                } else {
+                    acc += tap[0][k] == Wp + 1 ? g[0][k] : T(0);
+                }
+                out.v[cidx] = acc;
+            }
+            kd::store8(r0, out);
+        }
+        if (2 * m + 1 < H) {   // row 2m+1 (padded row 2m+2): a = 2 in output row m, a = 0 in output row m+1
+            kd::Row8<T> out;
+#pragma unroll
+            for (int cidx = 0; cidx < 8; ++cidx) {
+                const int k = cidx >> 1;
+                T acc = T(0);
+                if (cidx & 1) {
+                    acc += tap[0][k] == 2 * Wp + 2 ? g[0][k] : T(0);
+                    acc += tap[0][k + 1] == 2 * Wp ? g[0][k + 1] : T(0);
+                    acc += tap[1][k] == 2 ? g[1][k] : T(0);
+                    acc += tap[1][k + 1] == 0 ? g[1][k + 1] : T(0);
+                } else {
+                    acc += tap[0][k] == 2 * Wp + 1 ? g[0][k] : T(0);
+                    acc += tap[1][k] == 1 ? g[1][k] : T(0);
+                }
+                out.v[cidx] = acc;
+            }
+            kd::store8(r0 + W, out);
+        }
+    }
+}
+
 // Any geometry: one thread per un-padded input element gathers, in ascending
 // (i, j) order, the gradients of the windows that recorded it.  Writes every
 // element once.  (The reference sums overlapping windows with float atomics in
@@ -1249,6 +1390,12 @@ inline bool out_dims_ok(const PoolGeom& g) {
            (static_cast<int64_t>(g.Wo - 1) * g.sw < g.W + 2 * g.pw);
 }
 
+// the geometry of the 3x3 / stride 2 / padding 1 kernels: rows of a multiple of eight elements, every output present
+inline bool is_3x3s2p1(const PoolGeom& g) {
+    return g.kh == 3 && g.kw == 3 && g.sh == 2 && g.sw == 2 && g.ph == 1 && g.pw == 1 && (g.W % 8 == 0) && g.Wo == g.W / 2 &&
+           g.Ho == (g.H - 1) / 2 + 1;
+}
+
 // no window reaches outside the plane: no padding, and the last window ends inside
 inline bool windows_inside(const PoolGeom& g) {
     return g.ph == 0 && g.pw == 0 && static_cast<int64_t>(g.Ho - 1) * g.sh + g.kh <= g.H &&
@@ -1273,6 +1420,13 @@ int maxpool_forward(const T* x, T* y, long long* idx, int N, int C, PoolGeom g) 
         const int64_t groups = total >> 2;
         KD_LAUNCH((maxpool2x2_fwd<T, U>), (groups + kThreads * U - 1) / (kThreads * U), kThreads, 0, x, y, idx, g.H, g.W,
                   g.Ho, g.Wo, groups, kd::FastDiv(g.Wo / 4), kd::FastDiv(g.Ho));
+        return kd::launch_status();
+    }
+    if (is_3x3s2p1(g) && kd::aligned_row8<T>(x) && kd::aligned_pack<T>(y) && kd::aligned_pack<long long>(idx) &&
+        total < (int64_t(1) << 32)) {
+        const int64_t groups = total >> 2;
+        KD_LAUNCH1(maxpool3x3s2p1_fwd<T>, (groups + kThreads - 1) / kThreads, kThreads, 0, x, y, idx, g.H, g.W, g.Ho, g.Wo, groups,
+                   kd::FastDiv(g.Wo / 4), kd::FastDiv(g.Ho));
         return kd::launch_status();
     }
     const BandPlan plan = band_plan_fwd<T>(g);
@@ -1313,6 +1467,13 @@ int maxpool_backward_ex(const T* go, const long long* idx, T* gx, int N, int C, 
         const int64_t blocks = (nc * g.H * g.W) >> 3;
         KD_LAUNCH((maxpool2x2_bwd<T, U>), (blocks + kThreads * U - 1) / (kThreads * U), kThreads, 0, go, idx, gx, g.H,
                   g.W, g.Ho, g.Wo, blocks, kd::FastDiv(g.W / 8), kd::FastDiv(g.H));
+        return kd::launch_status();
+    }
+    if (is_3x3s2p1(g) && kd::aligned_pack<T>(go) && kd::aligned_pack<long long>(idx) && kd::aligned_row8<T>(gx) &&
+        nc * g.H * g.W < (int64_t(1) << 33)) {
+        const int64_t blocks = nc * ((g.H + 1) / 2) * (g.W / 8);
+        KD_LAUNCH(maxpool3x3s2p1_bwd<T>, (blocks + kThreads - 1) / kThreads, kThreads, 0, go, idx, gx, g.H, g.W, g.Ho, g.Wo, blocks,
+                  kd::FastDiv(g.W / 8), kd::FastDiv((g.H + 1) / 2));
         return kd::launch_status();
     }
     const BandPlanMax plan = band_plan_maxbwd<T>(g);
