@@ -409,6 +409,98 @@ avgpool_fwd_generic(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int6
     }
 }
 
+// kernel 2x2, stride 2, no padding, W % 8 == 0: the layout of maxpool2x2_fwd (four adjacent windows per thread, two
+// rows of eight inputs as 32-byte loads, one 16-byte store).  sum = 0; sum += the four taps row-major; the division
+// by four is an exact scaling.
+template <typename T, int U>
+__global__ void __launch_bounds__(kThreads)
+avgpool2x2_fwd(const T* __restrict__ x, T* __restrict__ y, int H, int W, int Ho, int Wo, int64_t groups, kd::FastDiv by_gpr,
+               kd::FastDiv by_ho) {
+    kd::pdl_prologue();
+    const int64_t tile = static_cast<int64_t>(kThreads) * U;
+    for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < groups;
+         base += static_cast<int64_t>(gridDim.x) * tile) {
+        kd::Row8<T> top8[U], bot8[U];
+        int64_t o[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t gi = base + u * kThreads + threadIdx.x;
+            if (gi < groups) {
+                unsigned rw, j4, nc, i;
+                by_gpr.divmod(static_cast<unsigned>(gi), rw, j4);     // groups < 2^31 (checked by the launcher)
+                by_ho.divmod(rw, nc, i);
+                o[u] = static_cast<int64_t>(rw) * Wo + 4 * j4;
+                const T* r0 = x + (static_cast<int64_t>(nc) * H + 2 * i) * W + 8 * j4;
+                top8[u] = kd::load8_stream(r0);
+                bot8[u] = kd::load8_stream(r0 + W);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t gi = base + u * kThreads + threadIdx.x;
+            if (gi < groups) {
+                Pack4<T> out;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    T sum = T(0);
+                    sum += top8[u].v[2 * q];
+                    sum += top8[u].v[2 * q + 1];
+                    sum += bot8[u].v[2 * q];
+                    sum += bot8[u].v[2 * q + 1];
+                    out.v[q] = sum * T(0.25);
+                }
+                kd::store4(y + o[u], out);
+            }
+        }
+    }
+}
+
+// Backward of the same geometry: eight adjacent gradient elements of one input row per thread (one 32-byte store, and
+// with ACCUM one 32-byte load), from one packet of grad_out; acc = 0; acc += go / 4.  Rows below the last window
+// (odd H) receive +0.
+template <typename T, bool ACCUM, int U>
+__global__ void __launch_bounds__(kThreads)
+avgpool2x2_bwd(const T* __restrict__ go, T* __restrict__ gx, int H, int W, int Ho, int Wo, int64_t blocks, kd::FastDiv by_bpr,
+               kd::FastDiv by_h) {
+    kd::pdl_prologue();
+    const int64_t tile = static_cast<int64_t>(kThreads) * U;
+    for (int64_t base = static_cast<int64_t>(blockIdx.x) * tile; base < blocks;
+         base += static_cast<int64_t>(gridDim.x) * tile) {
+        Pack4<T> gv[U];
+        kd::Row8<T> held[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t bi = base + u * kThreads + threadIdx.x;
+            if (bi < blocks) {
+                unsigned rowflat, jg, nc, h;                      // rowflat = nc * H + h
+                by_bpr.divmod(static_cast<unsigned>(bi), rowflat, jg);
+                by_h.divmod(rowflat, nc, h);
+                if (static_cast<int>(h >> 1) < Ho) {
+                    gv[u] = kd::load4(go + (static_cast<int64_t>(nc) * Ho + (h >> 1)) * Wo + 4 * jg);
+                } else {
+                    gv[u].v[0] = gv[u].v[1] = gv[u].v[2] = gv[u].v[3] = T(0);
+                }
+                if (ACCUM) held[u] = kd::load8_stream(gx + 8 * bi);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t bi = base + u * kThreads + threadIdx.x;
+            if (bi < blocks) {
+                kd::Row8<T> out;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    T acc = T(0);
+                    acc += gv[u].v[q] * T(0.25);
+                    out.v[2 * q] = ACCUM ? held[u].v[2 * q] + acc : acc;
+                    out.v[2 * q + 1] = ACCUM ? held[u].v[2 * q + 1] + acc : acc;
+                }
+                kd::store8(gx + 8 * bi, out);
+            }
+        }
+    }
+}
+
 // x / 9, correctly rounded.  For float inside [2^-100, 2^100] the quotient comes from the
 // rounded reciprocal and one exact FMA residual (q0 = x*r; e = fma(-q0, 9, x); q = fma(e, r, q0)),
 // three instructions instead of the division sequence; this equals RN(x / 9) for every float
@@ -526,21 +618,22 @@ struct BandPlan {
     bool ok;
     int rows;        // rows of the band (output rows forward, input rows backward)
     int bands;       // bands per plane
+    int buffer;      // forward: elements of one staging buffer
     size_t smem;
 };
 
 constexpr int kBandThreads = 128;
 
-// log2 of the threads that share a row: the smallest power of two >= width, 32..kBandThreads
+// log2 of the threads that share a row: the smallest power of two >= width, 8..kBandThreads
 inline int band_lane_bits(int width) {
-    int bits = 5;
+    int bits = 3;
     while ((1 << bits) < width && (1 << bits) < kBandThreads) ++bits;
     return bits;
 }
 
 // Forward: `rows` output rows need (rows-1)*sh + kh input rows.
 template <typename T> inline BandPlan band_plan_fwd(const PoolGeom& g) {
-    BandPlan p = {false, 0, 0, 0};
+    BandPlan p = {false, 0, 0, 0, 0};
     const int64_t cap = kBandBytes / static_cast<int64_t>(sizeof(T));
     if (static_cast<int64_t>(g.kh) * g.W > cap) return p;
     int64_t r = (cap / g.W - g.kh) / g.sh + 1;
@@ -548,18 +641,24 @@ template <typename T> inline BandPlan band_plan_fwd(const PoolGeom& g) {
     if (r < 1) return p;
     p.bands = static_cast<int>((g.Ho + r - 1) / r);
     p.rows = (g.Ho + p.bands - 1) / p.bands;
-    p.smem = (static_cast<size_t>((p.rows - 1) * g.sh + g.kh) * g.W + BandVec<T>::value) * sizeof(T);
+    // two staging buffers, each a whole number of 16-byte packets
+    p.buffer = (((p.rows - 1) * g.sh + g.kh) * g.W + 2 * BandVec<T>::value - 1) / BandVec<T>::value * BandVec<T>::value;
+    p.smem = 2 * static_cast<size_t>(p.buffer) * sizeof(T);
     p.ok = true;
     return p;
 }
 
 // Backward: `rows` input rows are covered by at most (rows + kh - 2) / sh + 1 output rows; they are staged
 // with one more column and one more row, both zero.
-inline int64_t band_go_rows(const PoolGeom& g, int64_t r) { return (r + g.kh - 2) / g.sh + 1; }
+inline __host__ __device__ int64_t band_go_rows(const PoolGeom& g, int64_t r) { return (r + g.kh - 2) / g.sh + 1; }
+inline __host__ __device__ size_t band_bwd_table_bytes(int rows) { return (static_cast<size_t>(rows) * sizeof(int2) + 15) & ~size_t(15); }
+template <typename T> inline __host__ __device__ size_t band_bwd_quotient_bytes(const PoolGeom& g, int rows) {
+    return (static_cast<size_t>((band_go_rows(g, rows) + 1) * (g.Wo + 1)) * sizeof(T) + 15) & ~size_t(15);
+}
 
 template <typename T> inline BandPlan band_plan_bwd(const PoolGeom& g) {
-    BandPlan p = {false, 0, 0, 0};
-    const int64_t cap = kBandBytes / static_cast<int64_t>(sizeof(T));
+    BandPlan p = {false, 0, 0, 0, 0};
+    const int64_t cap = kBandBytes / 2 / static_cast<int64_t>(sizeof(T));
     const int64_t pitch = g.Wo + 1;
     if ((band_go_rows(g, 1) + 1) * pitch > cap) return p;
     int64_t r = (cap / pitch - 2) * g.sh - g.kh + 2;
@@ -571,35 +670,16 @@ template <typename T> inline BandPlan band_plan_bwd(const PoolGeom& g) {
     if (r > g.H) r = g.H;
     p.bands = static_cast<int>((g.H + r - 1) / r);
     p.rows = (g.H + p.bands - 1) / p.bands;
-    p.smem = ((static_cast<size_t>(p.rows) * sizeof(int2) + 15) & ~size_t(15)) +
-             static_cast<size_t>((band_go_rows(g, p.rows) + 1) * pitch) * sizeof(T);
+    // the row table, the quotients (rows of Wo + 1, one more row), two buffers for the gradients as they arrive
+    constexpr int V = BandVec<T>::value;
+    p.buffer = static_cast<int>((band_go_rows(g, p.rows) * g.Wo + 2 * V - 1) / V * V);
+    p.smem = band_bwd_table_bytes(p.rows) + band_bwd_quotient_bytes<T>(g, p.rows) + 2 * static_cast<size_t>(p.buffer) * sizeof(T);
     p.ok = true;
     return p;
 }
 
-// Copies src[0, n) to s[mis, mis + n), where mis is the element offset of src inside its 16-byte packet (which
-// keeps the packets aligned on both sides): 16-byte loads, single elements before the first and after the last
-// boundary.  All threads of the CTA call it.
-template <typename T>
-__device__ __forceinline__ void band_stage(const T* __restrict__ src, int n, T* s, int mis) {
-    constexpr int V = BandVec<T>::value;
-    int head = (V - mis) & (V - 1);
-    if (head > n) head = n;
-    const int nv = (n - head) / V;
-    if (static_cast<int>(threadIdx.x) < head) s[mis + threadIdx.x] = __ldg(src + threadIdx.x);
-    const T* body = src + head;
-    T* sbody = s + mis + head;                                    // a multiple of V elements into s
-#pragma unroll 4
-    for (int v = threadIdx.x; v < nv; v += blockDim.x) {
-        if constexpr (sizeof(T) == 4)
-            reinterpret_cast<float4*>(sbody)[v] = __ldcs(reinterpret_cast<const float4*>(body) + v);
-        else
-            reinterpret_cast<double2*>(sbody)[v] = __ldcs(reinterpret_cast<const double2*>(body) + v);
-    }
-    const int done = head + nv * V;
-    if (static_cast<int>(threadIdx.x) < n - done) s[mis + done + threadIdx.x] = __ldg(src + done + threadIdx.x);
-}
-
+// mis: the element offset of a span inside its first 16-byte packet; element e is staged at s[mis + e], which keeps
+// the packets aligned on both sides.
 template <typename T> __device__ __forceinline__ int band_misalign(const T* p) {
     return static_cast<int>((reinterpret_cast<uintptr_t>(p) / sizeof(T)) & (BandVec<T>::value - 1));
 }
@@ -619,17 +699,58 @@ template <typename T, int TAPS> struct WindowDiv {
     }
 };
 
-// KH, KW: the window when the kernel is compiled for it, 0 = taken from g.  EDGES: a window may reach outside the
-// plane (padding, or an output size that lets the last window hang over); such taps contribute +0, which leaves the
-// running sum as it is (it starts at +0 and is therefore never -0).
-// What depends on the band only is recomputed when a CTA moves to a different band; with one band per plane (planes
-// up to 16 KiB) that is once per CTA, and an item costs its staging and the stencil.
+// Forward kernels.  KH, KW: the window when the kernel is compiled for it, 0 = taken from g.  EDGES: a window may
+// reach outside the plane (padding, or an output size that lets the last window hang over); such taps contribute +0
+// to an average, which leaves the running sum as it is (it starts at +0 and is therefore never -0), and are no
+// candidates for a maximum.
+// The staging is asynchronous (cp.async, 16 bytes each, no registers) into one of two buffers: the span of the CTA's
+// next item is requested before the stencil of the current one runs, so its loads are in flight under the arithmetic
+// and a CTA never waits for a full memory round trip between items.
+struct BandItem {
+    unsigned nc;
+    int nout, nrows, in_off, out_off, top;      // top: staged row of the first tap of the band's first output row
+    int i0;
+};
+
+__device__ __forceinline__ BandItem band_item(const PoolGeom& g, int kh, int rows, const kd::FastDiv& by_bands, unsigned item) {
+    BandItem it;
+    unsigned band;
+    by_bands.divmod(item, it.nc, band);
+    it.i0 = static_cast<int>(band) * rows;
+    it.nout = min(g.Ho, it.i0 + rows) - it.i0;
+    const int h_lo = max(0, it.i0 * g.sh - g.ph);
+    it.nrows = min(g.H, (it.i0 + it.nout - 1) * g.sh - g.ph + kh) - h_lo;
+    it.in_off = h_lo * g.W;
+    it.out_off = it.i0 * g.Wo;
+    it.top = it.i0 * g.sh - g.ph - h_lo;
+    return it;
+}
+
+// Requests src[0, n) into s[mis, mis + n): cp.async for the 16-byte packets, plain loads for the elements before the
+// first and after the last boundary.  The caller commits the group and waits for it.
+template <typename T>
+__device__ __forceinline__ void band_stage_async(const T* __restrict__ src, int n, T* s, int mis) {
+    constexpr int V = BandVec<T>::value;
+    int head = (V - mis) & (V - 1);
+    if (head > n) head = n;
+    const int nv = (n - head) / V;
+    if (static_cast<int>(threadIdx.x) < head) s[mis + threadIdx.x] = __ldg(src + threadIdx.x);
+    const T* body = src + head;
+    const unsigned sbody = static_cast<unsigned>(__cvta_generic_to_shared(s + mis + head));   // a multiple of 16 bytes
+    for (int v = threadIdx.x; v < nv; v += blockDim.x)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sbody + 16u * v), "l"(body + static_cast<size_t>(v) * V) : "memory");
+    const int done = head + nv * V;
+    if (static_cast<int>(threadIdx.x) < n - done) s[mis + done + threadIdx.x] = __ldg(src + done + threadIdx.x);
+}
+__device__ __forceinline__ void band_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void band_wait_all_but_newest() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
 template <typename T, int KH, int KW, bool EDGES>
 __global__ void __launch_bounds__(kBandThreads)
 avgpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int rows, unsigned items, kd::FastDiv by_bands,
-                 int lane_bits) {
+                 int lane_bits, int buffer_elems) {
     extern __shared__ __align__(16) unsigned char band_smem[];
-    T* s = reinterpret_cast<T*>(band_smem);
+    T* const buf = reinterpret_cast<T*>(band_smem);
     kd::pdl_prologue();
     const int kh = KH ? KH : g.kh, kw = KW ? KW : g.kw;
     const WindowDiv<T, KH * KW> divide(kh * kw);
@@ -637,32 +758,36 @@ avgpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int row
     const int group = threadIdx.x >> lane_bits, lig = threadIdx.x & (lanes - 1), ngroups = blockDim.x >> lane_bits;
     const int step = ngroups * g.sh;
     const int64_t plane_in = static_cast<int64_t>(g.H) * g.W, plane_out = static_cast<int64_t>(g.Ho) * g.Wo;
-    unsigned cur = ~0u;
-    int nout = 0, nrows = 0, first = 0, in_off = 0, out_off = 0;
-    for (unsigned item = blockIdx.x; item < items; item += gridDim.x) {
-        unsigned nc, band;
-        by_bands.divmod(item, nc, band);
-        if (band != cur) {
-            cur = band;
-            const int i0 = static_cast<int>(band) * rows;
-            nout = min(g.Ho, i0 + rows) - i0;
-            const int h_lo = max(0, i0 * g.sh - g.ph);
-            nrows = min(g.H, (i0 + nout - 1) * g.sh - g.ph + kh) - h_lo;
-            in_off = h_lo * g.W;
-            out_off = i0 * g.Wo;
-            first = i0 * g.sh - g.ph - h_lo + group * g.sh;              // staged row of this thread's first tap
+    unsigned item = blockIdx.x;
+    if (item >= items) return;
+    BandItem it = band_item(g, kh, rows, by_bands, item);
+    const T* src = x + it.nc * plane_in + it.in_off;
+    int mis = band_misalign(src);
+    int cur = 0;
+    if (it.nrows > 0) band_stage_async(src, it.nrows * g.W, buf, mis);
+    band_commit();
+    for (; item < items; item += gridDim.x) {
+        const unsigned next = item + gridDim.x;
+        BandItem nx = it;
+        int nmis = 0;
+        if (next < items) {
+            nx = band_item(g, kh, rows, by_bands, next);
+            const T* nsrc = x + nx.nc * plane_in + nx.in_off;
+            nmis = band_misalign(nsrc);
+            if (nx.nrows > 0) band_stage_async(nsrc, nx.nrows * g.W, buf + (cur ^ 1) * buffer_elems, nmis);
         }
-        const T* src = x + nc * plane_in + in_off;
-        const int mis = band_misalign(src);
-        if (nrows > 0) band_stage(src, nrows * g.W, s, mis);
+        band_commit();
+        band_wait_all_but_newest();
         __syncthreads();
-        T* dst = y + nc * plane_out + out_off + group * g.Wo;
+        const T* s = buf + cur * buffer_elems;
+        const int nrows = it.nrows;
+        T* dst = y + it.nc * plane_out + it.out_off + group * g.Wo;
         for (int j = lig; j < g.Wo; j += lanes) {
             const int w0 = j * g.sw - g.pw;
-            int hh = first;
+            int hh = it.top + group * g.sh;                                    // staged row of this thread's first tap
             const T* t = s + mis + hh * g.W + w0;                              // dereferenced only where the tap exists
             T* out = dst + j;
-            for (int ii = group; ii < nout; ii += ngroups, hh += step, t += step * g.W, out += ngroups * g.Wo) {
+            for (int ii = group; ii < it.nout; ii += ngroups, hh += step, t += step * g.W, out += ngroups * g.Wo) {
                 T sum = T(0);
                 if (KH > 0 && !EDGES) {
 #pragma unroll
@@ -690,6 +815,9 @@ avgpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int row
             }
         }
         __syncthreads();
+        it = nx;
+        mis = nmis;
+        cur ^= 1;
     }
 }
 
@@ -698,9 +826,9 @@ avgpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int row
 template <typename T, int KH, int KW, bool EDGES>
 __global__ void __launch_bounds__(kBandThreads)
 maxpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, PoolGeom g, int rows, unsigned items,
-                 kd::FastDiv by_bands, int lane_bits) {
+                 kd::FastDiv by_bands, int lane_bits, int buffer_elems) {
     extern __shared__ __align__(16) unsigned char band_smem[];
-    T* s = reinterpret_cast<T*>(band_smem);
+    T* const buf = reinterpret_cast<T*>(band_smem);
     kd::pdl_prologue();
     const int kh = KH ? KH : g.kh, kw = KW ? KW : g.kw;
     const int lanes = 1 << lane_bits;
@@ -708,34 +836,37 @@ maxpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, long long* __restri
     const int step = ngroups * g.sh;
     const int Wp = g.W + 2 * g.pw;
     const int64_t plane_in = static_cast<int64_t>(g.H) * g.W, plane_out = static_cast<int64_t>(g.Ho) * g.Wo;
-    unsigned cur = ~0u;
-    int nout = 0, nrows = 0, first = 0, in_off = 0, out_off = 0, hp_first = 0;
-    for (unsigned item = blockIdx.x; item < items; item += gridDim.x) {
-        unsigned nc, band;
-        by_bands.divmod(item, nc, band);
-        if (band != cur) {
-            cur = band;
-            const int i0 = static_cast<int>(band) * rows;
-            nout = min(g.Ho, i0 + rows) - i0;
-            const int h_lo = max(0, i0 * g.sh - g.ph);
-            nrows = min(g.H, (i0 + nout - 1) * g.sh - g.ph + kh) - h_lo;
-            in_off = h_lo * g.W;
-            out_off = i0 * g.Wo;
-            first = i0 * g.sh - g.ph - h_lo + group * g.sh;              // staged row of this thread's first tap
-            hp_first = (i0 + group) * g.sh;                              // the same row in the padded plane
+    unsigned item = blockIdx.x;
+    if (item >= items) return;
+    BandItem it = band_item(g, kh, rows, by_bands, item);
+    const T* src = x + it.nc * plane_in + it.in_off;
+    int mis = band_misalign(src);
+    int cur = 0;
+    if (it.nrows > 0) band_stage_async(src, it.nrows * g.W, buf, mis);
+    band_commit();
+    for (; item < items; item += gridDim.x) {
+        const unsigned next = item + gridDim.x;
+        BandItem nx = it;
+        int nmis = 0;
+        if (next < items) {
+            nx = band_item(g, kh, rows, by_bands, next);
+            const T* nsrc = x + nx.nc * plane_in + nx.in_off;
+            nmis = band_misalign(nsrc);
+            if (nx.nrows > 0) band_stage_async(nsrc, nx.nrows * g.W, buf + (cur ^ 1) * buffer_elems, nmis);
         }
-        const T* src = x + nc * plane_in + in_off;
-        const int mis = band_misalign(src);
-        if (nrows > 0) band_stage(src, nrows * g.W, s, mis);
+        band_commit();
+        band_wait_all_but_newest();
         __syncthreads();
-        const int64_t obase = nc * plane_out + out_off + group * g.Wo;
+        const T* s = buf + cur * buffer_elems;
+        const int nrows = it.nrows;
+        const int64_t obase = it.nc * plane_out + it.out_off + group * g.Wo;
         for (int j = lig; j < g.Wo; j += lanes) {
             const int wp0 = j * g.sw;
             const int w0 = wp0 - g.pw;
-            int hh = first, hp0 = hp_first;
+            int hh = it.top + group * g.sh, hp0 = (it.i0 + group) * g.sh;      // staged row / padded-plane row of the first tap
             const T* t = s + mis + hh * g.W + w0;                              // dereferenced only where the tap exists
             int64_t o = obase + j;
-            for (int ii = group; ii < nout; ii += ngroups, hh += step, hp0 += step, t += step * g.W, o += ngroups * g.Wo) {
+            for (int ii = group; ii < it.nout; ii += ngroups, hh += step, hp0 += step, t += step * g.W, o += ngroups * g.Wo) {
                 T best = kd::neg_inf<T>();
                 int ba = 0, bb = 0;
                 if (KH > 0) {
@@ -765,6 +896,9 @@ maxpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, long long* __restri
             }
         }
         __syncthreads();
+        it = nx;
+        mis = nmis;
+        cur ^= 1;
     }
 }
 
@@ -815,13 +949,32 @@ template <typename T, int V> __device__ __forceinline__ void band_store(T* p, co
 }
 
 // V: adjacent columns per thread, moved with one access (W % V == 0 and the tensor aligned to V elements).
+// The gradients of the covering output rows arrive asynchronously (cp.async into one of two buffers; those of the
+// CTA's next item are requested before the current one is worked on) and are turned into the staged quotients by a
+// short shared-to-shared pass.
+struct BandBwdItem { unsigned nc, band; int h0, nrows, i_first, ngo; };
+
+__device__ __forceinline__ BandBwdItem band_bwd_item(const PoolGeom& g, int rows, const kd::FastDiv& by_bands,
+                                                     const kd::FastDiv& by_sh, unsigned item) {
+    BandBwdItem it;
+    by_bands.divmod(item, it.nc, it.band);
+    it.h0 = static_cast<int>(it.band) * rows;
+    it.nrows = min(g.H, it.h0 + rows) - it.h0;
+    const int a_first = it.h0 + g.ph - g.kh + 1;
+    it.i_first = a_first <= 0 ? 0 : static_cast<int>(by_sh.div(static_cast<unsigned>(a_first + g.sh - 1)));
+    const int i_last = min(g.Ho - 1, static_cast<int>(by_sh.div(static_cast<unsigned>(it.h0 + it.nrows - 1 + g.ph))));
+    it.ngo = max(0, i_last - it.i_first + 1);
+    return it;
+}
+
 template <typename T, bool ACCUM, bool TWO, int V>
 __global__ void __launch_bounds__(kBandThreads)
 avgpool_bwd_band(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int rows, unsigned items, kd::FastDiv by_bands,
-                 int lane_bits, kd::FastDiv by_sh, kd::FastDiv by_sw, kd::FastDiv by_wo) {
+                 int lane_bits, kd::FastDiv by_sh, kd::FastDiv by_sw, kd::FastDiv by_wo, int buffer_elems) {
     extern __shared__ __align__(16) unsigned char band_smem[];
     int2* rowinfo = reinterpret_cast<int2*>(band_smem);
-    T* q = reinterpret_cast<T*>(band_smem + ((static_cast<size_t>(rows) * sizeof(int2) + 15) & ~size_t(15)));
+    T* q = reinterpret_cast<T*>(band_smem + band_bwd_table_bytes(rows));
+    T* const raw = reinterpret_cast<T*>(band_smem + band_bwd_table_bytes(rows) + band_bwd_quotient_bytes<T>(g, rows));
     kd::pdl_prologue();
     const WindowDiv<T, 0> divide(g.kh * g.kw);
     const int lanes = 1 << lane_bits;
@@ -834,27 +987,30 @@ avgpool_bwd_band(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int r
     BandColumn<T> mine[V];
 #pragma unroll
     for (int k = 0; k < V; ++k) mine[k] = band_column<T>(g, lig * V + k, by_sw);
-    unsigned cur = ~0u;
-    int nrows = 0, ngo = 0, in_off = 0, go_off = 0;
-    for (unsigned item = blockIdx.x; item < items; item += gridDim.x) {
-        unsigned nc, band;
-        by_bands.divmod(item, nc, band);
-        const bool moved = band != cur;
-        int h0 = 0, i_first = 0;
-        if (moved) {
-            cur = band;
-            h0 = static_cast<int>(band) * rows;
-            nrows = min(g.H, h0 + rows) - h0;
-            const int a_first = h0 + g.ph - g.kh + 1;
-            i_first = a_first <= 0 ? 0 : static_cast<int>(by_sh.div(static_cast<unsigned>(a_first + g.sh - 1)));
-            const int i_last = min(g.Ho - 1, static_cast<int>(by_sh.div(static_cast<unsigned>(h0 + nrows - 1 + g.ph))));
-            ngo = max(0, i_last - i_first + 1);
-            in_off = h0 * g.W + group * g.W;
-            go_off = i_first * g.Wo;
+    unsigned item = blockIdx.x;
+    if (item >= items) return;
+    BandBwdItem it = band_bwd_item(g, rows, by_bands, by_sh, item);
+    const T* src = go + it.nc * plane_out + static_cast<int64_t>(it.i_first) * g.Wo;
+    int mis = band_misalign(src);
+    int cur = 0;
+    unsigned tabled = ~0u;                     // the band the row table and the zero row are filled for
+    if (it.ngo > 0) band_stage_async(src, it.ngo * g.Wo, raw, mis);
+    band_commit();
+    for (; item < items; item += gridDim.x) {
+        const unsigned next = item + gridDim.x;
+        BandBwdItem nx = it;
+        int nmis = 0;
+        if (next < items) {
+            nx = band_bwd_item(g, rows, by_bands, by_sh, next);
+            const T* nsrc = go + nx.nc * plane_out + static_cast<int64_t>(nx.i_first) * g.Wo;
+            nmis = band_misalign(nsrc);
+            if (nx.ngo > 0) band_stage_async(nsrc, nx.ngo * g.Wo, raw + (cur ^ 1) * buffer_elems, nmis);
         }
-        T* plane = gx + nc * plane_in + in_off;                       // this thread's first row of the band
-        // what the buffer holds in this thread's first rows is requested before anything else, so that
-        // the reads are under way while the quotients are staged
+        band_commit();
+        const int nrows = it.nrows, ngo = it.ngo;
+        T* plane = gx + it.nc * plane_in + static_cast<int64_t>(it.h0 + group) * g.W;     // this thread's first row of the band
+        // what the buffer holds in this thread's first rows is requested now, so that the reads are under way
+        // while the quotients are prepared
         T held[U][V];
         if (ACCUM && lig < wv) {
 #pragma unroll
@@ -862,28 +1018,31 @@ avgpool_bwd_band(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int r
                 if (group + u * ngroups < nrows) band_load<T, V>(plane + lig * V + u * stride, held[u]);
             }
         }
-        const T* src = go + nc * plane_out + go_off;
+        band_wait_all_but_newest();
+        __syncthreads();
+        const T* arrived = raw + cur * buffer_elems + mis;
         const int n = ngo * g.Wo;
-        auto stage = [&](auto quotient) {
+        auto prepare = [&](auto quotient) {
 #pragma unroll 4
             for (int e = threadIdx.x; e < n; e += blockDim.x) {
                 unsigned r, c;
                 by_wo.divmod(static_cast<unsigned>(e), r, c);
-                q[r * pitch + c] = quotient(__ldcs(src + e));
+                q[r * pitch + c] = quotient(arrived[e]);
             }
         };
-        if (divide.kind == 1) stage([](T v) { return div9<T>(v); });
-        else if (divide.kind == 2) stage([&](T v) { return v * divide.inv; });
-        else stage([&](T v) { return v / divide.d; });
-        if (moved) {
+        if (divide.kind == 1) prepare([](T v) { return div9<T>(v); });
+        else if (divide.kind == 2) prepare([&](T v) { return v * divide.inv; });
+        else prepare([&](T v) { return v / divide.d; });
+        if (it.band != tabled) {
+            tabled = it.band;
             for (int r = threadIdx.x; r < ngo; r += blockDim.x) q[r * pitch + g.Wo] = T(0);
             for (int c = threadIdx.x; c < pitch; c += blockDim.x) q[ngo * pitch + c] = T(0);
             for (int hh = threadIdx.x; hh < nrows; hh += blockDim.x) {
-                const int hp = h0 + hh + g.ph;
+                const int hp = it.h0 + hh + g.ph;
                 const int a0 = hp - g.kh + 1;
                 const int i_lo = a0 <= 0 ? 0 : static_cast<int>(by_sh.div(static_cast<unsigned>(a0 + g.sh - 1)));
                 const int ni = min(g.Ho - 1, static_cast<int>(by_sh.div(static_cast<unsigned>(hp)))) - i_lo + 1;
-                const int first = (i_lo - i_first) * pitch;
+                const int first = (i_lo - it.i_first) * pitch;
                 constexpr int B = static_cast<int>(sizeof(T));                 // TWO: byte offsets
                 if (TWO) rowinfo[hh] = make_int2((ni >= 1 ? first : ngo * pitch) * B, (ni >= 2 ? first + pitch : ngo * pitch) * B);
                 else rowinfo[hh] = make_int2(first, max(0, ni));
@@ -933,7 +1092,9 @@ avgpool_bwd_band(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int r
                 }
             }
         }
-        __syncthreads();
+        it = nx;
+        mis = nmis;
+        cur ^= 1;
     }
 }
 
@@ -1396,6 +1557,12 @@ inline bool is_3x3s2p1(const PoolGeom& g) {
            g.Ho == (g.H - 1) / 2 + 1;
 }
 
+// the geometry of the 2x2 / stride 2 AvgPool kernels: no padding, rows of a multiple of eight elements, every window present
+inline bool is_2x2s2p0(const PoolGeom& g) {
+    return g.kh == 2 && g.kw == 2 && g.sh == 2 && g.sw == 2 && g.ph == 0 && g.pw == 0 && (g.W % 8 == 0) && g.Wo == g.W / 2 &&
+           g.Ho == g.H / 2;
+}
+
 // no window reaches outside the plane: no padding, and the last window ends inside
 inline bool windows_inside(const PoolGeom& g) {
     return g.ph == 0 && g.pw == 0 && static_cast<int64_t>(g.Ho - 1) * g.sh + g.kh <= g.H &&
@@ -1436,8 +1603,8 @@ int maxpool_forward(const T* x, T* y, long long* idx, int N, int C, PoolGeom g) 
         const int lanes = band_lane_bits(g.Wo);
         const bool inside = windows_inside(g);
 #define KD_FWD_BAND(KH_, KW_, EDGES_)                                                                               \
-    KD_LAUNCH_W((maxpool_fwd_band<T, KH_, KW_, EDGES_>), 8, items, kBandThreads, plan.smem, x, y, idx, g, plan.rows, items, \
-                by_bands, lanes)
+    KD_LAUNCH_W((maxpool_fwd_band<T, KH_, KW_, EDGES_>), 2, items, kBandThreads, plan.smem, x, y, idx, g, plan.rows, items, \
+                by_bands, lanes, plan.buffer)
         if (g.kh == 3 && g.kw == 3) { if (inside) KD_FWD_BAND(3, 3, false); else KD_FWD_BAND(3, 3, true); }
         else if (g.kh == 2 && g.kw == 2) { if (inside) KD_FWD_BAND(2, 2, false); else KD_FWD_BAND(2, 2, true); }
         else if (inside) KD_FWD_BAND(0, 0, false);
@@ -1537,6 +1704,13 @@ int avgpool_forward(const T* x, T* y, int N, int C, PoolGeom g) {
                    kd::FastDiv(g.Wo / 4), kd::FastDiv(g.Ho));
         return kd::launch_status();
     }
+    if (is_2x2s2p0(g) && kd::aligned_row8<T>(x) && kd::aligned_pack<T>(y) && total < (int64_t(1) << 32)) {
+        constexpr int U = 2;
+        const int64_t groups = total >> 2;
+        KD_LAUNCH((avgpool2x2_fwd<T, U>), (groups + kThreads * U - 1) / (kThreads * U), kThreads, 0, x, y, g.H, g.W, g.Ho, g.Wo,
+                  groups, kd::FastDiv(g.Wo / 4), kd::FastDiv(g.Ho));
+        return kd::launch_status();
+    }
     const BandPlan plan = band_plan_fwd<T>(g);
     if (plan.ok && nc * plan.bands < (int64_t(1) << 31)) {
         const unsigned items = static_cast<unsigned>(nc * plan.bands);
@@ -1544,7 +1718,8 @@ int avgpool_forward(const T* x, T* y, int N, int C, PoolGeom g) {
         const int lanes = band_lane_bits(g.Wo);
         const bool inside = windows_inside(g);
 #define KD_FWD_BAND(KH_, KW_, EDGES_)                                                                               \
-    KD_LAUNCH_W((avgpool_fwd_band<T, KH_, KW_, EDGES_>), 8, items, kBandThreads, plan.smem, x, y, g, plan.rows, items, by_bands, lanes)
+    KD_LAUNCH_W((avgpool_fwd_band<T, KH_, KW_, EDGES_>), 2, items, kBandThreads, plan.smem, x, y, g, plan.rows, items, by_bands, lanes, \
+                plan.buffer)
         if (g.kh == 3 && g.kw == 3) { if (inside) KD_FWD_BAND(3, 3, false); else KD_FWD_BAND(3, 3, true); }
         else if (g.kh == 2 && g.kw == 2) { if (inside) KD_FWD_BAND(2, 2, false); else KD_FWD_BAND(2, 2, true); }
         else if (inside) KD_FWD_BAND(0, 0, false);
@@ -1575,6 +1750,18 @@ int avgpool_backward(const T* go, T* gx, int N, int C, PoolGeom g, bool accumula
                   kd::FastDiv(g.W / 8), kd::FastDiv((g.H + 1) / 2));
         return kd::launch_status();
     }
+    if (is_2x2s2p0(g) && kd::aligned_pack<T>(go) && kd::aligned_row8<T>(gx) && total < (int64_t(1) << 33)) {
+        constexpr int U = 2;
+        const int64_t blocks = total >> 3;
+        const kd::FastDiv by_bpr(g.W / 8), by_h(g.H);
+        if (accumulate)
+            KD_LAUNCH((avgpool2x2_bwd<T, true, U>), (blocks + kThreads * U - 1) / (kThreads * U), kThreads, 0, go, gx, g.H, g.W,
+                      g.Ho, g.Wo, blocks, by_bpr, by_h);
+        else
+            KD_LAUNCH((avgpool2x2_bwd<T, false, U>), (blocks + kThreads * U - 1) / (kThreads * U), kThreads, 0, go, gx, g.H, g.W,
+                      g.Ho, g.Wo, blocks, by_bpr, by_h);
+        return kd::launch_status();
+    }
     const BandPlan plan = band_plan_bwd<T>(g);
     if (plan.ok && nc * plan.bands < (int64_t(1) << 31)) {
         const unsigned items = static_cast<unsigned>(nc * plan.bands);
@@ -1586,8 +1773,8 @@ int avgpool_backward(const T* go, T* gx, int N, int C, PoolGeom g, bool accumula
         while (v > 1 && (g.W % v != 0 || (reinterpret_cast<uintptr_t>(gx) % (v * sizeof(T))) != 0)) v /= 2;
         const int lanes = band_lane_bits(g.W / v);
 #define KD_BWD_BAND_V(ACC, TWO_, V_)                                                                                 \
-    KD_LAUNCH_W((avgpool_bwd_band<T, ACC, TWO_, V_>), 8, items, kBandThreads, plan.smem, go, gx, g, plan.rows, items, by_bands, \
-                lanes, by_sh, by_sw, by_wo)
+    KD_LAUNCH_W((avgpool_bwd_band<T, ACC, TWO_, V_>), 2, items, kBandThreads, plan.smem, go, gx, g, plan.rows, items, by_bands, \
+                lanes, by_sh, by_sw, by_wo, plan.buffer)
 #define KD_BWD_BAND(ACC, TWO_)                                                                                      \
     do {                                                                                                            \
         if (v == 4) { if constexpr (sizeof(T) == 4) KD_BWD_BAND_V(ACC, TWO_, 4); }                                  \
