@@ -1104,12 +1104,16 @@ avgpool_bwd_band(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int r
 // inside it; an element at window offset (a, b) takes the gradient when the staged tap equals a * kw + b.  Rows of
 // Wo + 1 with {0, -1} in the extra column and a last row of {0, -1} stand in for windows that do not exist, as in the
 // AvgPool kernel; the row table holds {offset of the first covering row, offset of the second (TWO) or the number of
-// covering rows, a * kw of the element in the first covering row}.
-struct BandPlanMax { bool ok; int rows, bands; size_t smem; };
+// covering rows, a * kw of the element in the first covering row}.  Gradients and positions arrive asynchronously
+// (cp.async, two buffers each; the next item's are requested before the current one is worked on) and a short
+// shared-to-shared pass turns them into the staged pairs.
+struct BandPlanMax { bool ok; int rows, bands, staged, buffer; size_t smem; };
+
+inline __host__ __device__ size_t band_round16(size_t bytes) { return (bytes + 15) & ~size_t(15); }
 
 template <typename T> inline BandPlanMax band_plan_maxbwd(const PoolGeom& g) {
-    BandPlanMax p = {false, 0, 0, 0};
-    const int64_t cap = kBandBytes / static_cast<int64_t>(sizeof(T) + sizeof(int));
+    BandPlanMax p = {false, 0, 0, 0, 0, 0};
+    const int64_t cap = 1024;                                // staged outputs per band (32 bytes of shared memory each)
     const int64_t pitch = g.Wo + 1;
     if ((band_go_rows(g, 1) + 1) * pitch > cap) return p;
     int64_t r = (cap / pitch - 2) * g.sh - g.kh + 2;
@@ -1121,8 +1125,10 @@ template <typename T> inline BandPlanMax band_plan_maxbwd(const PoolGeom& g) {
     if (r > g.H) r = g.H;
     p.bands = static_cast<int>((g.H + r - 1) / r);
     p.rows = (g.H + p.bands - 1) / p.bands;
-    const size_t staged = static_cast<size_t>((band_go_rows(g, p.rows) + 1) * pitch);
-    p.smem = static_cast<size_t>(p.rows) * sizeof(int4) + ((staged * sizeof(T) + 15) & ~size_t(15)) + staged * sizeof(int);
+    p.staged = static_cast<int>((band_go_rows(g, p.rows) + 1) * pitch);
+    p.buffer = static_cast<int>((band_go_rows(g, p.rows) * g.Wo + 7) / 4 * 4);        // whole packets for both element sizes
+    p.smem = static_cast<size_t>(p.rows) * sizeof(int4) + band_round16(p.staged * sizeof(T)) + band_round16(p.staged * sizeof(int)) +
+             2 * band_round16(p.buffer * sizeof(long long)) + 2 * band_round16(p.buffer * sizeof(T));
     p.ok = true;
     return p;
 }
@@ -1131,12 +1137,20 @@ template <typename T, bool TWO, int V>
 __global__ void __launch_bounds__(kBandThreads)
 maxpool_bwd_band(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, PoolGeom g, int rows,
                  unsigned items, kd::FastDiv by_bands, int lane_bits, kd::FastDiv by_sh, kd::FastDiv by_sw, kd::FastDiv by_wo,
-                 kd::FastDiv by_wp, int staged) {
+                 kd::FastDiv by_wp, int staged, int buffer_elems) {
     extern __shared__ __align__(16) unsigned char band_smem[];
-    int4* rowinfo = reinterpret_cast<int4*>(band_smem);
-    T* q = reinterpret_cast<T*>(band_smem + static_cast<size_t>(rows) * sizeof(int4));
-    int* tap = reinterpret_cast<int*>(band_smem + static_cast<size_t>(rows) * sizeof(int4) +
-                                      ((static_cast<size_t>(staged) * sizeof(T) + 15) & ~size_t(15)));
+    unsigned char* at = band_smem;
+    int4* rowinfo = reinterpret_cast<int4*>(at);
+    at += static_cast<size_t>(rows) * sizeof(int4);
+    T* q = reinterpret_cast<T*>(at);
+    at += band_round16(static_cast<size_t>(staged) * sizeof(T));
+    int* tap = reinterpret_cast<int*>(at);
+    at += band_round16(static_cast<size_t>(staged) * sizeof(int));
+    long long* const raw_idx = reinterpret_cast<long long*>(at);
+    at += 2 * band_round16(static_cast<size_t>(buffer_elems) * sizeof(long long));
+    T* const raw_go = reinterpret_cast<T*>(at);
+    const int idx_stride = static_cast<int>(band_round16(static_cast<size_t>(buffer_elems) * sizeof(long long)) / sizeof(long long));
+    const int go_stride = static_cast<int>(band_round16(static_cast<size_t>(buffer_elems) * sizeof(T)) / sizeof(T));
     kd::pdl_prologue();
     const int lanes = 1 << lane_bits;
     const int group = threadIdx.x >> lane_bits, lig = threadIdx.x & (lanes - 1), ngroups = blockDim.x >> lane_bits;
@@ -1147,63 +1161,76 @@ maxpool_bwd_band(const T* __restrict__ go, const long long* __restrict__ idx, T*
     const long long padded = static_cast<long long>(g.H + 2 * g.ph) * Wp;
     const int64_t stride = static_cast<int64_t>(ngroups) * g.W;
     const int64_t plane_in = static_cast<int64_t>(g.H) * g.W, plane_out = static_cast<int64_t>(g.Ho) * g.Wo;
+    const int row_step = g.sh * g.kw;
     BandColumn<T> mine[V];
 #pragma unroll
     for (int k = 0; k < V; ++k) mine[k] = band_column<T>(g, lig * V + k, by_sw);
-    unsigned cur = ~0u;
-    int nrows = 0, ngo = 0, in_off = 0, go_off = 0, i_first = 0;
-    for (unsigned item = blockIdx.x; item < items; item += gridDim.x) {
-        unsigned nc, band;
-        by_bands.divmod(item, nc, band);
-        const bool moved = band != cur;
-        int h0 = 0;
-        if (moved) {
-            cur = band;
-            h0 = static_cast<int>(band) * rows;
-            nrows = min(g.H, h0 + rows) - h0;
-            const int a_first = h0 + g.ph - g.kh + 1;
-            i_first = a_first <= 0 ? 0 : static_cast<int>(by_sh.div(static_cast<unsigned>(a_first + g.sh - 1)));
-            const int i_last = min(g.Ho - 1, static_cast<int>(by_sh.div(static_cast<unsigned>(h0 + nrows - 1 + g.ph))));
-            ngo = max(0, i_last - i_first + 1);
-            in_off = h0 * g.W + group * g.W;
-            go_off = i_first * g.Wo;
+    unsigned item = blockIdx.x;
+    if (item >= items) return;
+    BandBwdItem it = band_bwd_item(g, rows, by_bands, by_sh, item);
+    int64_t first_out = it.nc * plane_out + static_cast<int64_t>(it.i_first) * g.Wo;
+    int mis_go = band_misalign(go + first_out), mis_idx = band_misalign(idx + first_out);
+    int cur = 0;
+    unsigned tabled = ~0u;
+    if (it.ngo > 0) {
+        band_stage_async(go + first_out, it.ngo * g.Wo, raw_go, mis_go);
+        band_stage_async(idx + first_out, it.ngo * g.Wo, raw_idx, mis_idx);
+    }
+    band_commit();
+    for (; item < items; item += gridDim.x) {
+        const unsigned next = item + gridDim.x;
+        BandBwdItem nx = it;
+        int nmis_go = 0, nmis_idx = 0;
+        if (next < items) {
+            nx = band_bwd_item(g, rows, by_bands, by_sh, next);
+            const int64_t nfirst = nx.nc * plane_out + static_cast<int64_t>(nx.i_first) * g.Wo;
+            nmis_go = band_misalign(go + nfirst);
+            nmis_idx = band_misalign(idx + nfirst);
+            if (nx.ngo > 0) {
+                band_stage_async(go + nfirst, nx.ngo * g.Wo, raw_go + (cur ^ 1) * go_stride, nmis_go);
+                band_stage_async(idx + nfirst, nx.ngo * g.Wo, raw_idx + (cur ^ 1) * idx_stride, nmis_idx);
+            }
         }
-        const T* src = go + nc * plane_out + go_off;
-        const long long* isrc = idx + nc * plane_out + go_off;
+        band_commit();
+        band_wait_all_but_newest();
+        __syncthreads();
+        const int nrows = it.nrows, ngo = it.ngo;
+        const T* go_in = raw_go + cur * go_stride + mis_go;
+        const long long* idx_in = raw_idx + cur * idx_stride + mis_idx;
         const int n = ngo * g.Wo;
 #pragma unroll 4
         for (int e = threadIdx.x; e < n; e += blockDim.x) {
             unsigned r, c;
             by_wo.divmod(static_cast<unsigned>(e), r, c);
-            const long long p = __ldcs(isrc + e);
+            const long long p = idx_in[e];
             int code = -1;
             if (p >= 0 && p < padded) {
                 unsigned hb, wb;
                 by_wp.divmod(static_cast<unsigned>(p), hb, wb);
-                const int a = static_cast<int>(hb) - (i_first + static_cast<int>(r)) * g.sh;
+                const int a = static_cast<int>(hb) - (it.i_first + static_cast<int>(r)) * g.sh;
                 const int b = static_cast<int>(wb) - static_cast<int>(c) * g.sw;
                 if (a >= 0 && a < g.kh && b >= 0 && b < g.kw) code = a * g.kw + b;
             }
-            q[r * pitch + c] = __ldcs(src + e);
+            q[r * pitch + c] = go_in[e];
             tap[r * pitch + c] = code;
         }
-        if (moved) {
+        if (it.band != tabled) {
+            tabled = it.band;
             for (int r = threadIdx.x; r < ngo; r += blockDim.x) { q[r * pitch + g.Wo] = T(0); tap[r * pitch + g.Wo] = -1; }
             for (int c = threadIdx.x; c < pitch; c += blockDim.x) { q[ngo * pitch + c] = T(0); tap[ngo * pitch + c] = -1; }
             for (int hh = threadIdx.x; hh < nrows; hh += blockDim.x) {
-                const int hp = h0 + hh + g.ph;
+                const int hp = it.h0 + hh + g.ph;
                 const int a0 = hp - g.kh + 1;
                 const int i_lo = a0 <= 0 ? 0 : static_cast<int>(by_sh.div(static_cast<unsigned>(a0 + g.sh - 1)));
                 const int ni = min(g.Ho - 1, static_cast<int>(by_sh.div(static_cast<unsigned>(hp)))) - i_lo + 1;
-                const int first = (i_lo - i_first) * pitch;
+                const int first = (i_lo - it.i_first) * pitch;
                 const int rp = (hp - i_lo * g.sh) * g.kw;
                 if (TWO) rowinfo[hh] = make_int4(ni >= 1 ? first : ngo * pitch, ni >= 2 ? first + pitch : ngo * pitch, rp, 0);
                 else rowinfo[hh] = make_int4(first, max(0, ni), rp, 0);
             }
         }
         __syncthreads();
-        T* plane = gx + nc * plane_in + in_off;                       // this thread's first row of the band
-        const int row_step = g.sh * g.kw;
+        T* plane = gx + it.nc * plane_in + static_cast<int64_t>(it.h0 + group) * g.W;     // this thread's first row of the band
         for (int c = lig; c < wv; c += lanes) {
             BandColumn<T> col[V];
             int cp[V];                                                // b of the element in its first covering column
@@ -1232,8 +1259,8 @@ maxpool_bwd_band(const T* __restrict__ go, const long long* __restrict__ idx, T*
                         } else {
                             for (int a = 0; a < ro.y; ++a)
                                 for (int b = 0; b < col[k].nj; ++b) {
-                                    const int at = ro.x + a * pitch + col[k].j_lo + b;
-                                    if (tap[at] == ro.z - a * row_step + cp[k] - b * g.sw) acc += q[at];
+                                    const int at_ = ro.x + a * pitch + col[k].j_lo + b;
+                                    if (tap[at_] == ro.z - a * row_step + cp[k] - b * g.sw) acc += q[at_];
                                 }
                         }
                         res[k] = acc;
@@ -1242,7 +1269,10 @@ maxpool_bwd_band(const T* __restrict__ go, const long long* __restrict__ idx, T*
                 }
             }
         }
-        __syncthreads();
+        it = nx;
+        mis_go = nmis_go;
+        mis_idx = nmis_idx;
+        cur ^= 1;
     }
 }
 
@@ -1652,10 +1682,9 @@ int maxpool_backward_ex(const T* go, const long long* idx, T* gx, int N, int C, 
         int v = 16 / static_cast<int>(sizeof(T));
         while (v > 1 && (g.W % v != 0 || (reinterpret_cast<uintptr_t>(gx) % (v * sizeof(T))) != 0)) v /= 2;
         const int lanes = band_lane_bits(g.W / v);
-        const int staged = static_cast<int>((band_go_rows(g, plan.rows) + 1) * (g.Wo + 1));
 #define KD_BWD_BAND_V(TWO_, V_)                                                                                      \
-    KD_LAUNCH_W((maxpool_bwd_band<T, TWO_, V_>), 8, items, kBandThreads, plan.smem, go, idx, gx, g, plan.rows, items, by_bands, \
-                lanes, by_sh, by_sw, by_wo, by_wp, staged)
+    KD_LAUNCH_W((maxpool_bwd_band<T, TWO_, V_>), 2, items, kBandThreads, plan.smem, go, idx, gx, g, plan.rows, items, by_bands, \
+                lanes, by_sh, by_sw, by_wo, by_wp, plan.staged, plan.buffer)
 #define KD_BWD_BAND(TWO_)                                                                                           \
     do {                                                                                                            \
         if (v == 4) { if constexpr (sizeof(T) == 4) KD_BWD_BAND_V(TWO_, 4); }                                       \
