@@ -362,6 +362,26 @@ def suite_table(lib, timer, peak: float, reps: int = 10, warm: int = 3, extras: 
     timed("maxpool2d_3x3s2p1_bwd_f32", nb, lambda: lib.call("keydnn_cuda_maxpool2d_backward_ex_f32", y.data, idx.data, gx.data,
                                                           N_, C_, H_, H_, Ho_, Ho_, 3, 3, 2, 2, 1, 1))
     del x, y, idx, gx
+    # AvgPool 2x2 / stride 2, and 3x3 / 2 / 1 on an odd plane (rows off the 32-byte grid: the row-band kernels)
+    N_, C_, H_, Ho_ = 128, 256, 56, 28
+    x = T.from_numpy(rng.standard_normal((N_, C_, H_, H_), dtype=np.float32))
+    y, gx = T.empty((N_, C_, Ho_, Ho_)), T.empty(x.shape)
+    timed("avgpool2d_2x2s2_fwd_f32", x.nbytes + y.nbytes, lambda: lib.call("keydnn_cuda_avgpool2d_forward_ex_f32", x.data, y.data,
+                                                                          N_, C_, H_, H_, Ho_, Ho_, 2, 2, 2, 2, 0, 0))
+    timed("avgpool2d_2x2s2_bwd_f32", x.nbytes + y.nbytes, lambda: lib.call("keydnn_cuda_avgpool2d_backward_ex_f32", y.data, gx.data,
+                                                                          N_, C_, H_, H_, Ho_, Ho_, 2, 2, 2, 2, 0, 0))
+    del x, y, gx
+    N_, C_, H_, Ho_ = 64, 64, 113, 57
+    x = T.from_numpy(rng.standard_normal((N_, C_, H_, H_), dtype=np.float32))
+    y, idx = T.empty((N_, C_, Ho_, Ho_)), T.empty((N_, C_, Ho_, Ho_), dtype=np.int64)
+    gx = T.empty(x.shape)
+    for kind, extra in (("maxpool", idx.nbytes), ("avgpool", 0)):
+        mid = (idx.data,) if kind == "maxpool" else ()
+        timed(f"{kind}2d_3x3s2p1_fwd_113x113_f32", x.nbytes + y.nbytes + extra, lambda kind=kind, mid=mid: lib.call(
+            f"keydnn_cuda_{kind}2d_forward_ex_f32", x.data, y.data, *mid, N_, C_, H_, H_, Ho_, Ho_, 3, 3, 2, 2, 1, 1))
+        timed(f"{kind}2d_3x3s2p1_bwd_113x113_f32", x.nbytes + y.nbytes + extra, lambda kind=kind, mid=mid: lib.call(
+            f"keydnn_cuda_{kind}2d_backward_ex_f32", y.data, *mid, gx.data, N_, C_, H_, H_, Ho_, Ho_, 3, 3, 2, 2, 1, 1))
+    del x, y, idx, gx
     N_, C_, Hp_, Ho_ = 128, 256, 58, 28
     xp = T.from_numpy(rng.standard_normal((N_, C_, Hp_, Hp_), dtype=np.float32))
     y, idx = T.empty((N_, C_, Ho_, Ho_)), T.empty((N_, C_, Ho_, Ho_), dtype=np.int64)
