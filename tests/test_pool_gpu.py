@@ -197,6 +197,47 @@ def test_maxpool_row_bands_any_alignment(oracle, geom, offset, dtype):
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_random_geometries_against_oracle(oracle, dtype):
+    """Sixty seeded random windows / strides / paddings / plane sizes (rectangular, stride larger than the window,
+    windows reaching into the padding, one-pixel planes), all four pooling passes through the C ABI."""
+    lib = native()
+    rng = np.random.default_rng(20240521)
+    sfx = suf(dtype)
+    done = 0
+    while done < 60:
+        N, C = int(rng.integers(1, 3)), int(rng.integers(1, 4))
+        H, W = int(rng.integers(1, 41)), int(rng.integers(1, 41))
+        k = (int(rng.integers(1, 6)), int(rng.integers(1, 6)))
+        s = (int(rng.integers(1, 5)), int(rng.integers(1, 5)))
+        p = (int(rng.integers(0, k[0] // 2 + 1)), int(rng.integers(0, k[1] // 2 + 1)))
+        if H + 2 * p[0] < k[0] or W + 2 * p[1] < k[1]:
+            continue
+        done += 1
+        Ho, Wo = _ohw(H, W, k, s, p)
+        x = (np.round(rng.uniform(-1, 1, (N, C, H, W)) * 16) / 16).astype(dtype)
+        go = rng.standard_normal((N, C, Ho, Wo)).astype(dtype)
+        tag = f"N{N} C{C} {H}x{W} k{k} s{s} p{p}"
+        dx, dgo = Buf(lib, x), Buf(lib, go)
+        dy, didx = Buf(lib, shape=go.shape, dtype=dtype), Buf(lib, shape=go.shape, dtype=np.int64)
+        dgx = Buf(lib, shape=x.shape, dtype=dtype, fill=0xFF)
+        geom = (N, C, H, W, Ho, Wo, k[0], k[1], s[0], s[1], p[0], p[1])
+        lib.call(f"keydnn_cuda_avgpool2d_forward_ex_{sfx}", dx.ptr, dy.ptr, *geom)
+        assert_same_bits(dy.get(), oracle.avgpool2d_forward(x, k, s, p), tag)
+        lib.call(f"keydnn_cuda_avgpool2d_backward_ex_{sfx}", dgo.ptr, dgx.ptr, *geom)
+        assert_same_bits(dgx.get(), oracle.avgpool2d_backward(go, x.shape, k, s, p), tag)
+        lib.call(f"keydnn_cuda_maxpool2d_forward_ex_{sfx}", dx.ptr, dy.ptr, didx.ptr, *geom)
+        y_w, idx_w = oracle.maxpool2d_forward(x, k, s, p)
+        np.testing.assert_array_equal(dy.get(), y_w, tag)
+        np.testing.assert_array_equal(didx.get(), idx_w, tag)
+        lib.call(f"keydnn_cuda_maxpool2d_backward_ex_{sfx}", dgo.ptr, didx.ptr, dgx.ptr, *geom)
+        want = oracle.maxpool2d_backward(go, idx_w, x.shape, p)
+        if _overlaps(k, s):
+            np.testing.assert_allclose(dgx.get(), want, err_msg=tag, **TOL[np.dtype(dtype)])
+        else:
+            assert_same_bits(dgx.get(), want, tag)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
 def test_reference_signature_entries_on_padded_planes(oracle, dtype):
     """pad2d -> pool -> (memset) -> backward -> crop2d, the reference's own call sequence
     (ops/pool2d_cuda_ext.py:56-522), gives the same results as the fused entries."""
