@@ -1,4 +1,4 @@
-"""The row-sharded reductions with world_size 2 on CPU (gloo): the host-side logic of `keydnn_v2_b200.sharded` -
+"""The row-sharded reductions with world_size 2 and 8 on CPU (gloo): the host-side logic of `keydnn_v2_b200.sharded` -
 buffer layout inside the shared exchange bucket, offsets and strides handed to the selection / rank-order-sum
 kernels, which collective moves what, which results are complete when - driven against a stand-in for the native
 library that keeps "device" memory in host arrays, computes every called entry with NumPy and moves the
@@ -172,14 +172,17 @@ def _rank(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_sharded_reductions_world_size_2_over_gloo():
+import pytest
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_sharded_reductions_over_gloo(world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + os.getpid() % 1500
-    world = 2
+    port = 29700 + (os.getpid() + 7 * world) % 1500
     ps = [ctx.Process(target=_rank, args=(r, world, port, q)) for r in range(world)]
     [p.start() for p in ps]
-    got = sorted((q.get(timeout=180) for _ in ps), key=lambda t: t[0])
+    got = sorted((q.get(timeout=400) for _ in ps), key=lambda t: t[0])
     [p.join(timeout=60) for p in ps]
     for rank, out, wholes in got:
         # one byte all-gather per flush for BOTH matrices with the shared bucket; an all-reduce and an all-gather per matrix without
