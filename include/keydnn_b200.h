@@ -115,6 +115,13 @@ int keydnn_cuda_crop2d_f32(const float* x_pad, float* y, int N, int C, int H_pad
 int keydnn_cuda_crop2d_f64(const double* x_pad, double* y, int N, int C, int H_pad, int W_pad, int p_h, int p_w, int H,
                            int W);
 
+/* additive, host-only (no device work): how the row-band pooling kernels (any window / stride / padding / alignment)
+ * would split one (H, W) plane.  kind 0 = forward (rows = output rows per band), 1 = AvgPool backward, 2 = MaxPool
+ * backward (rows = input rows per band); out5 = usable (0 = the one-thread-per-element kernels run instead), rows per
+ * band, bands per plane, dynamic shared memory in bytes, elements of one arrival buffer. */
+int keydnn_cuda_debug_pool_band_plan(int kind, int elem_size, int H, int W, int H_out, int W_out, int k_h, int k_w, int s_h,
+                                     int s_w, int p_h, int p_w, int64_t* out5);
+
 /* ------------------------------------------------------------------------- */
 /* Pooling, fused entries (additive): un-padded tensors, explicit padding.      */
 /* Replace the pad->pool and memset->pool-backward->crop call sequences of      */

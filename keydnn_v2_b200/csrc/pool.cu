@@ -1593,6 +1593,11 @@ inline bool is_2x2s2p0(const PoolGeom& g) {
            g.Ho == g.H / 2;
 }
 
+// the band kernels index inside a plane with 32-bit integers
+inline bool band_indexable(const PoolGeom& g) {
+    return static_cast<int64_t>(g.H) * g.W < (int64_t(1) << 31) && static_cast<int64_t>(g.Ho) * g.Wo < (int64_t(1) << 31);
+}
+
 // no window reaches outside the plane: no padding, and the last window ends inside
 inline bool windows_inside(const PoolGeom& g) {
     return g.ph == 0 && g.pw == 0 && static_cast<int64_t>(g.Ho - 1) * g.sh + g.kh <= g.H &&
@@ -1627,7 +1632,7 @@ int maxpool_forward(const T* x, T* y, long long* idx, int N, int C, PoolGeom g) 
         return kd::launch_status();
     }
     const BandPlan plan = band_plan_fwd<T>(g);
-    if (plan.ok && nc * plan.bands < (int64_t(1) << 31)) {
+    if (plan.ok && nc * plan.bands < (int64_t(1) << 31) && band_indexable(g)) {
         const unsigned items = static_cast<unsigned>(nc * plan.bands);
         const kd::FastDiv by_bands(plan.bands);
         const int lanes = band_lane_bits(g.Wo);
@@ -1675,7 +1680,7 @@ int maxpool_backward_ex(const T* go, const long long* idx, T* gx, int N, int C, 
     }
     const BandPlanMax plan = band_plan_maxbwd<T>(g);
     const int64_t padded = static_cast<int64_t>(g.H + 2 * g.ph) * (g.W + 2 * g.pw);
-    if (plan.ok && nc * plan.bands < (int64_t(1) << 31) && padded < (int64_t(1) << 31)) {
+    if (plan.ok && nc * plan.bands < (int64_t(1) << 31) && padded < (int64_t(1) << 31) && band_indexable(g)) {
         const unsigned items = static_cast<unsigned>(nc * plan.bands);
         const kd::FastDiv by_bands(plan.bands), by_sh(g.sh), by_sw(g.sw), by_wo(g.Wo), by_wp(g.W + 2 * g.pw);
         const bool two = g.kh <= 2 * g.sh && g.kw <= 2 * g.sw;
@@ -1741,7 +1746,7 @@ int avgpool_forward(const T* x, T* y, int N, int C, PoolGeom g) {
         return kd::launch_status();
     }
     const BandPlan plan = band_plan_fwd<T>(g);
-    if (plan.ok && nc * plan.bands < (int64_t(1) << 31)) {
+    if (plan.ok && nc * plan.bands < (int64_t(1) << 31) && band_indexable(g)) {
         const unsigned items = static_cast<unsigned>(nc * plan.bands);
         const kd::FastDiv by_bands(plan.bands);
         const int lanes = band_lane_bits(g.Wo);
@@ -1792,7 +1797,7 @@ int avgpool_backward(const T* go, T* gx, int N, int C, PoolGeom g, bool accumula
         return kd::launch_status();
     }
     const BandPlan plan = band_plan_bwd<T>(g);
-    if (plan.ok && nc * plan.bands < (int64_t(1) << 31)) {
+    if (plan.ok && nc * plan.bands < (int64_t(1) << 31) && band_indexable(g)) {
         const unsigned items = static_cast<unsigned>(nc * plan.bands);
         const kd::FastDiv by_bands(plan.bands), by_sh(g.sh), by_sw(g.sw);
         const kd::FastDiv by_wo(g.Wo);
@@ -1958,6 +1963,28 @@ inline PoolGeom geom(int H, int W, int Ho, int Wo, int kh, int kw, int sh, int s
 
 KD_POOL_LEGACY(float, f32)
 KD_POOL_LEGACY(double, f64)
+
+// Host-only: how the row-band kernels would split a plane (nothing is launched).  kind 0: forward (rows = output rows
+// of a band), 1: AvgPool backward, 2: MaxPool backward (rows = input rows of a band).  out5 = {usable, rows per band,
+// bands per plane, dynamic shared memory in bytes, elements of one arrival buffer}.
+KD_API int keydnn_cuda_debug_pool_band_plan(int kind, int elem_size, int H, int W, int H_out, int W_out, int k_h, int k_w, int s_h,
+                                            int s_w, int p_h, int p_w, std::int64_t* out5) {
+    if (!out5) return -1;
+    if ((elem_size != 4 && elem_size != 8) || kind < 0 || kind > 2) return -2;
+    if (H <= 0 || W <= 0 || H_out <= 0 || W_out <= 0 || k_h <= 0 || k_w <= 0 || s_h <= 0 || s_w <= 0 || p_h < 0 || p_w < 0) return -3;
+    const PoolGeom g = geom(H, W, H_out, W_out, k_h, k_w, s_h, s_w, p_h, p_w);
+    if (kind == 2) {
+        const BandPlanMax p = elem_size == 4 ? band_plan_maxbwd<float>(g) : band_plan_maxbwd<double>(g);
+        out5[0] = p.ok && band_indexable(g); out5[1] = p.rows; out5[2] = p.bands; out5[3] = static_cast<std::int64_t>(p.smem);
+        out5[4] = p.buffer;
+        return 0;
+    }
+    const BandPlan p = kind == 0 ? (elem_size == 4 ? band_plan_fwd<float>(g) : band_plan_fwd<double>(g))
+                                 : (elem_size == 4 ? band_plan_bwd<float>(g) : band_plan_bwd<double>(g));
+    out5[0] = p.ok && band_indexable(g); out5[1] = p.rows; out5[2] = p.bands; out5[3] = static_cast<std::int64_t>(p.smem);
+    out5[4] = p.buffer;
+    return 0;
+}
 
 // ---------------------------------------------------------------------------
 // C ABI: fused entries (additive).  x / grad_x are the un-padded (N,C,H,W)

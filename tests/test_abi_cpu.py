@@ -8,6 +8,7 @@ import ctypes
 import subprocess
 from pathlib import Path
 
+import numpy as np
 import pytest
 
 REPO = Path(__file__).resolve().parents[1]
@@ -110,6 +111,57 @@ def test_column_reduction_chunk_arithmetic_is_64_bit(lib_path):
             assert nchunks * rch + 32 <= 2**31 - 1
     assert f(2**31 - 1, 8, 4, 8, out) == -2         # the last chunk would end beyond INT_MAX
     assert f(0, 8, 4, 8, out) == -2
+
+
+def test_pool_band_plans_fit_their_shared_memory(lib_path):
+    """The split of a plane into row bands, for two thousand seeded geometries and both element sizes: the bands cover
+    the plane, the dynamic shared memory stays under the 48 KiB a launch gets without opting in, and every region the
+    kernels index (staging buffers with up to one packet of alignment slack, the quotient rows with their extra column
+    and row, the row table) fits - with the number of output rows that cover a band counted by brute force, not by
+    the bound the planner uses.  Host arithmetic only, nothing is allocated or launched."""
+    from keydnn_v2_b200 import load
+
+    f = load().raw("keydnn_cuda_debug_pool_band_plan")
+    out = (ctypes.c_int64 * 5)()
+    rng = np.random.default_rng(11)
+    usable = 0
+    for _ in range(2000):
+        H, W = int(rng.integers(1, 600)), int(rng.integers(1, 2500))
+        k = (int(rng.integers(1, 8)), int(rng.integers(1, 8)))
+        s = (int(rng.integers(1, 6)), int(rng.integers(1, 6)))
+        p = (int(rng.integers(0, k[0] // 2 + 1)), int(rng.integers(0, k[1] // 2 + 1)))
+        if H + 2 * p[0] < k[0] or W + 2 * p[1] < k[1]:
+            continue
+        Ho, Wo = (H + 2 * p[0] - k[0]) // s[0] + 1, (W + 2 * p[1] - k[1]) // s[1] + 1
+        for esz in (4, 8):
+            vec = 16 // esz
+            for kind in (0, 1, 2):
+                assert f(kind, esz, H, W, Ho, Wo, k[0], k[1], s[0], s[1], p[0], p[1], out) == 0
+                ok, rows, bands, smem, buf = out
+                if not ok:
+                    continue
+                usable += 1
+                extent = Ho if kind == 0 else H
+                assert rows >= 1 and bands >= 1 and rows * (bands - 1) < extent <= rows * bands
+                assert smem <= 48 * 1024, (kind, esz, H, W, k, s, p, smem)
+                if kind == 0:
+                    span = ((rows - 1) * s[0] + k[0]) * W                 # input elements a band can stage
+                    assert buf % vec == 0 and buf >= span + vec - 1 and smem >= 2 * buf * esz
+                    continue
+                covering = 0                                            # most output rows that cover one band
+                for b in range(bands):
+                    h0, h1 = b * rows, min(H, (b + 1) * rows)
+                    lo = max(0, -(-(h0 + p[0] - k[0] + 1) // s[0]))
+                    hi = min(Ho - 1, (h1 - 1 + p[0]) // s[0])
+                    covering = max(covering, hi - lo + 1)
+                staged = (covering + 1) * (Wo + 1)
+                arrive = covering * Wo + (vec if kind == 1 else 4) - 1
+                assert buf >= arrive, (kind, esz, H, W, k, s, p)
+                if kind == 1:
+                    assert smem >= rows * 8 + staged * esz + 2 * buf * esz
+                else:
+                    assert smem >= rows * 16 + staged * (esz + 4) + 2 * buf * (esz + 8)
+    assert usable > 3000
 
 
 def test_every_reference_signature_is_declared_with_the_same_argument_classes():
