@@ -624,10 +624,14 @@ struct BandPlan {
 
 constexpr int kBandThreads = 128;
 
-// log2 of the threads that share a row: the smallest power of two >= width, 8..kBandThreads
-inline int band_lane_bits(int width) {
+// Threads of a CTA for items of `work` thread-iterations (outputs forward, column groups x rows backward): a warp for
+// the smallest planes, so that an SM holds more of them and a barrier stops fewer threads.
+inline int band_threads(int64_t work) { return work <= 64 ? 32 : (work <= 384 ? 64 : kBandThreads); }
+
+// log2 of the threads that share a row: the smallest power of two >= width, 8..threads
+inline int band_lane_bits(int width, int threads) {
     int bits = 3;
-    while ((1 << bits) < width && (1 << bits) < kBandThreads) ++bits;
+    while ((1 << bits) < width && (1 << bits) < threads) ++bits;
     return bits;
 }
 
@@ -1635,10 +1639,11 @@ int maxpool_forward(const T* x, T* y, long long* idx, int N, int C, PoolGeom g) 
     if (plan.ok && nc * plan.bands < (int64_t(1) << 31) && band_indexable(g)) {
         const unsigned items = static_cast<unsigned>(nc * plan.bands);
         const kd::FastDiv by_bands(plan.bands);
-        const int lanes = band_lane_bits(g.Wo);
+        const int threads = band_threads(static_cast<int64_t>(plan.rows) * g.Wo);
+        const int lanes = band_lane_bits(g.Wo, threads);
         const bool inside = windows_inside(g);
 #define KD_FWD_BAND(KH_, KW_, EDGES_)                                                                               \
-    KD_LAUNCH_W((maxpool_fwd_band<T, KH_, KW_, EDGES_>), 2, items, kBandThreads, plan.smem, x, y, idx, g, plan.rows, items, \
+    KD_LAUNCH_W((maxpool_fwd_band<T, KH_, KW_, EDGES_>), 2, items, threads, plan.smem, x, y, idx, g, plan.rows, items, \
                 by_bands, lanes, plan.buffer)
         if (g.kh == 3 && g.kw == 3) { if (inside) KD_FWD_BAND(3, 3, false); else KD_FWD_BAND(3, 3, true); }
         else if (g.kh == 2 && g.kw == 2) { if (inside) KD_FWD_BAND(2, 2, false); else KD_FWD_BAND(2, 2, true); }
@@ -1686,9 +1691,10 @@ int maxpool_backward_ex(const T* go, const long long* idx, T* gx, int N, int C, 
         const bool two = g.kh <= 2 * g.sh && g.kw <= 2 * g.sw;
         int v = 16 / static_cast<int>(sizeof(T));
         while (v > 1 && (g.W % v != 0 || (reinterpret_cast<uintptr_t>(gx) % (v * sizeof(T))) != 0)) v /= 2;
-        const int lanes = band_lane_bits(g.W / v);
+        const int threads = band_threads(static_cast<int64_t>(plan.rows) * (g.W / v) / (8 / v));
+        const int lanes = band_lane_bits(g.W / v, threads);
 #define KD_BWD_BAND_V(TWO_, V_)                                                                                      \
-    KD_LAUNCH_W((maxpool_bwd_band<T, TWO_, V_>), 2, items, kBandThreads, plan.smem, go, idx, gx, g, plan.rows, items, by_bands, \
+    KD_LAUNCH_W((maxpool_bwd_band<T, TWO_, V_>), 2, items, threads, plan.smem, go, idx, gx, g, plan.rows, items, by_bands, \
                 lanes, by_sh, by_sw, by_wo, by_wp, plan.staged, plan.buffer)
 #define KD_BWD_BAND(TWO_)                                                                                           \
     do {                                                                                                            \
@@ -1749,10 +1755,11 @@ int avgpool_forward(const T* x, T* y, int N, int C, PoolGeom g) {
     if (plan.ok && nc * plan.bands < (int64_t(1) << 31) && band_indexable(g)) {
         const unsigned items = static_cast<unsigned>(nc * plan.bands);
         const kd::FastDiv by_bands(plan.bands);
-        const int lanes = band_lane_bits(g.Wo);
+        const int threads = band_threads(static_cast<int64_t>(plan.rows) * g.Wo);
+        const int lanes = band_lane_bits(g.Wo, threads);
         const bool inside = windows_inside(g);
 #define KD_FWD_BAND(KH_, KW_, EDGES_)                                                                               \
-    KD_LAUNCH_W((avgpool_fwd_band<T, KH_, KW_, EDGES_>), 2, items, kBandThreads, plan.smem, x, y, g, plan.rows, items, by_bands, lanes, \
+    KD_LAUNCH_W((avgpool_fwd_band<T, KH_, KW_, EDGES_>), 2, items, threads, plan.smem, x, y, g, plan.rows, items, by_bands, lanes, \
                 plan.buffer)
         if (g.kh == 3 && g.kw == 3) { if (inside) KD_FWD_BAND(3, 3, false); else KD_FWD_BAND(3, 3, true); }
         else if (g.kh == 2 && g.kw == 2) { if (inside) KD_FWD_BAND(2, 2, false); else KD_FWD_BAND(2, 2, true); }
@@ -1805,9 +1812,10 @@ int avgpool_backward(const T* go, T* gx, int N, int C, PoolGeom g, bool accumula
         // columns per thread: as many as one aligned access of up to 16 bytes holds, for every row of every plane
         int v = 16 / static_cast<int>(sizeof(T));
         while (v > 1 && (g.W % v != 0 || (reinterpret_cast<uintptr_t>(gx) % (v * sizeof(T))) != 0)) v /= 2;
-        const int lanes = band_lane_bits(g.W / v);
+        const int threads = band_threads(static_cast<int64_t>(plan.rows) * (g.W / v) / (8 / v));
+        const int lanes = band_lane_bits(g.W / v, threads);
 #define KD_BWD_BAND_V(ACC, TWO_, V_)                                                                                 \
-    KD_LAUNCH_W((avgpool_bwd_band<T, ACC, TWO_, V_>), 2, items, kBandThreads, plan.smem, go, gx, g, plan.rows, items, by_bands, \
+    KD_LAUNCH_W((avgpool_bwd_band<T, ACC, TWO_, V_>), 2, items, threads, plan.smem, go, gx, g, plan.rows, items, by_bands, \
                 lanes, by_sh, by_sw, by_wo, plan.buffer)
 #define KD_BWD_BAND(ACC, TWO_)                                                                                      \
     do {                                                                                                            \
