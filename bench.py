@@ -1198,6 +1198,140 @@ def run_dropin(args) -> None:
                                              "iteration, device synchronised at both ends; inputs resident on the device"}}), flush=True)
 
 
+def run_abi(args) -> None:
+    """Every kind of reference-signature entry of the hot path - the calls the reference's ctypes bindings make - timed on
+    this library and on the reference's own CUDA kernels (its .cu files compiled unmodified, oracle/_ref) with the same
+    arguments on the same device buffers: CUDA events on the legacy default stream (where the reference launches),
+    three warm-up calls, five timed.  One JSON line; `speedup` = reference time / this library's time."""
+    import keydnn_v2_b200 as kd
+
+    lib = kd.load()
+    lib.call("keydnn_cuda_set_device", 0)
+    ref = _ref_cuda_lib()
+    if ref is None:
+        print(json.dumps({"workload": "abi", "unavailable": "oracle/_ref/libkeydnn_ref_cuda.so is not built"}))
+        return
+    timer = Timer(lib)
+    T = kd.Tensor
+    rng = np.random.default_rng(5)
+    i64, cf = ctypes.c_int64, ctypes.c_float
+    rows: list[dict] = []
+
+    def shape(*d):
+        return (i64 * len(d))(*d)
+
+    def timed(entry: str, what: str, call, before=None) -> None:
+        """call(L) makes the same call on library L; `before` (e.g. the zero-fill an accumulating entry needs) runs
+        inside the timed region on both."""
+        us = {}
+        for tag, L in (("this_library_us", lib), ("reference_us", ref)):
+            def once():
+                if before is not None:
+                    before(L)
+                call(L)
+            for _ in range(3):
+                once()
+            timer.start()
+            for _ in range(5):
+                once()
+            us[tag] = round(timer.stop_ms() / 5 * 1e3, 2)
+        rows.append({"entry": entry, "workload": what, **us, "speedup": round(us["reference_us"] / us["this_library_us"], 2)})
+
+    with _LegacyStream(lib):
+        # pooling as the reference's ops call it (ops/pool2d_cuda_ext.py:56-522): pad, pool the padded plane, zero-fill,
+        # backward onto the padded plane, crop
+        N, C, H, Hp, Ho = 128, 256, 56, 58, 28
+        x = T.from_numpy(rng.standard_normal((N, C, H, H), dtype=np.float32))
+        xp, gxp = T.empty((N, C, Hp, Hp)), T.empty((N, C, Hp, Hp))
+        y, idx, gx = T.empty((N, C, Ho, Ho)), T.empty((N, C, Ho, Ho), dtype=np.int64), T.empty(x.shape)
+        where = f"({N},{C},{H},{H}) fp32, k3 s2 p1"
+        zero = lambda L: L.call("keydnn_cuda_memset", gxp.data, 0, gxp.nbytes)
+        timed("pad2d", where, lambda L: L.call("keydnn_cuda_pad2d_f32", x.data, xp.data, N, C, H, H, 1, 1, cf(0.0)))
+        timed("maxpool2d_forward", where + " (padded plane)", lambda L: L.call(
+            "keydnn_cuda_maxpool2d_forward_f32", xp.data, y.data, idx.data, N, C, Hp, Hp, Ho, Ho, 3, 3, 2, 2))
+        timed("memset + maxpool2d_backward", where, lambda L: L.call(
+            "keydnn_cuda_maxpool2d_backward_f32", y.data, idx.data, gxp.data, N, C, Ho, Ho, Hp, Hp), before=zero)
+        timed("avgpool2d_forward", where + " (padded plane)", lambda L: L.call(
+            "keydnn_cuda_avgpool2d_forward_f32", xp.data, y.data, N, C, Hp, Hp, Ho, Ho, 3, 3, 2, 2))
+        timed("memset + avgpool2d_backward", where, lambda L: L.call(
+            "keydnn_cuda_avgpool2d_backward_f32", y.data, gxp.data, N, C, Ho, Ho, Hp, Hp, 3, 3, 2, 2), before=zero)
+        timed("crop2d", where, lambda L: L.call("keydnn_cuda_crop2d_f32", gxp.data, gx.data, N, C, Hp, Hp, 1, 1, H, H))
+        del x, xp, gxp, y, idx, gx
+        N, C, H, Ho = 32, 64, 112, 56
+        x = T.from_numpy(rng.standard_normal((N, C, H, H), dtype=np.float32))
+        y, idx, gx = T.empty((N, C, Ho, Ho)), T.empty((N, C, Ho, Ho), dtype=np.int64), T.empty(x.shape)
+        where = f"({N},{C},{H},{H}) fp32, k2 s2"
+        zero2 = lambda L: L.call("keydnn_cuda_memset", gx.data, 0, gx.nbytes)
+        timed("maxpool2d_forward", where, lambda L: L.call(
+            "keydnn_cuda_maxpool2d_forward_f32", x.data, y.data, idx.data, N, C, H, H, Ho, Ho, 2, 2, 2, 2))
+        timed("memset + maxpool2d_backward", where, lambda L: L.call(
+            "keydnn_cuda_maxpool2d_backward_f32", y.data, idx.data, gx.data, N, C, Ho, Ho, H, H), before=zero2)
+        timed("avgpool2d_forward", where, lambda L: L.call(
+            "keydnn_cuda_avgpool2d_forward_f32", x.data, y.data, N, C, H, H, Ho, Ho, 2, 2, 2, 2))
+        timed("memset + avgpool2d_backward", where, lambda L: L.call(
+            "keydnn_cuda_avgpool2d_backward_f32", y.data, gx.data, N, C, Ho, Ho, H, H, 2, 2, 2, 2), before=zero2)
+        del x, y, idx, gx
+        x = T.from_numpy(rng.standard_normal((256, 2048, 7, 7), dtype=np.float32))
+        y, gx = T.empty((256, 2048, 1, 1)), T.empty(x.shape)
+        timed("global_avgpool2d_forward", "(256,2048,7,7) fp32", lambda L: L.call(
+            "keydnn_cuda_global_avgpool2d_forward_f32", x.data, y.data, 256, 2048, 7, 7))
+        timed("global_avgpool2d_backward", "(256,2048,7,7) fp32", lambda L: L.call(
+            "keydnn_cuda_global_avgpool2d_backward_f32", y.data, gx.data, 256, 2048, 7, 7))
+        del x, y, gx
+        # reductions with their backward passes, element-wise, in-place, broadcasting and layer glue on (65536, 1024) fp32
+        R, M = 65536, 1024
+        n = R * M
+        a = T.from_numpy(rng.standard_normal((R, M), dtype=np.float32))
+        b = T.from_numpy(rng.uniform(0.5, 2.0, (R, M)).astype(np.float32))
+        out = T.empty((R, M))
+        vec = T.from_numpy(rng.standard_normal(R, dtype=np.float32))
+        pos = T.empty((R,), dtype=np.int64)
+        where = f"({R},{M}) fp32"
+        zero3 = lambda L: L.call("keydnn_cuda_memset", out.data, 0, out.nbytes)
+        for axis in (0, 1):
+            timed("sum_axis2d_forward", f"{where} axis {axis}", lambda L, axis=axis: L.call(
+                "keydnn_cuda_sum_axis2d_forward_f32", a.data, vec.data, R, M, axis))
+            timed("sum_axis2d_backward", f"{where} axis {axis}", lambda L, axis=axis: L.call(
+                "keydnn_cuda_sum_axis2d_backward_f32", vec.data, out.data, R, M, axis))
+            timed("max_axis2d_forward", f"{where} axis {axis}", lambda L, axis=axis: L.call(
+                "keydnn_cuda_max_axis2d_forward_f32", a.data, vec.data, pos.data, R, M, axis))
+            timed("memset + max_axis2d_backward", f"{where} axis {axis}", lambda L, axis=axis: L.call(
+                "keydnn_cuda_max_axis2d_backward_f32", vec.data, pos.data, out.data, R, M, axis), before=zero3)
+        timed("sum_all", where, lambda L: L.call("keydnn_cuda_sum_all_f32", a.data, vec.data, i64(n)))
+        timed("mean_all", where, lambda L: L.call("keydnn_cuda_mean_all_f32", a.data, vec.data, i64(n)))
+        timed("sum_backward_fill", where, lambda L: L.call("keydnn_cuda_sum_backward_fill_f32", vec.data, out.data, i64(n)))
+        timed("mean_backward_fill", where, lambda L: L.call("keydnn_cuda_mean_backward_fill_f32", vec.data, out.data, i64(n)))
+        for op in ("add", "div", "gt", "eq"):
+            timed(op, where, lambda L, op=op: L.call(f"keydnn_cuda_{op}_f32", a.data, b.data, out.data, n))
+        timed("neg", where, lambda L: L.call("keydnn_cuda_neg_f32", a.data, out.data, n))
+        timed("exp", where, lambda L: L.call("keydnn_cuda_exp_f32", a.data, out.data, ctypes.c_int(n)))
+        timed("mul_scalar", where, lambda L: L.call("keydnn_cuda_mul_scalar_f32", a.data, cf(0.5), out.data, n))
+        timed("gt_scalar", where, lambda L: L.call("keydnn_cuda_gt_scalar_f32", a.data, cf(0.0), out.data, n))
+        timed("add_inplace", where, lambda L: L.call("keydnn_cuda_add_inplace_f32", out.data, b.data, n))
+        timed("div_scalar_inplace", where, lambda L: L.call("keydnn_cuda_div_scalar_inplace_f32", out.data, cf(1.0001), n))
+        timed("fill", where, lambda L: L.call("keydnn_cuda_fill_f32", out.data, n, cf(1.5)))
+        timed("bias_add", where, lambda L: L.call("keydnn_cuda_bias_add_f32", a.data, vec.data, out.data, R, M))
+        timed("bias_add_inplace", where, lambda L: L.call("keydnn_cuda_bias_add_inplace_f32", out.data, vec.data, R, M))
+        timed("transpose2d", where, lambda L: L.call("keydnn_cuda_transpose2d_f32", a.data, out.data, R, M))
+        for src, tag in ((shape(1, M), "(1,M)"), (shape(R, 1), "(R,1)")):
+            timed("broadcast_to", f"{tag} -> {where}", lambda L, src=src: L.call(
+                "keydnn_cuda_broadcast_to_f32", vec.data, out.data, src, 2, shape(R, M), 2))
+            timed("sum_to_shape", f"{where} -> {tag}", lambda L, src=src: L.call(
+                "keydnn_cuda_sum_to_shape_f32", a.data, vec.data, shape(R, M), src, 2))
+        timed("sum_to_shape", "(256,32,64,64) -> (1,32,1,1) fp32", lambda L: L.call(
+            "keydnn_cuda_sum_to_shape_f32", a.data, vec.data, shape(256, 32, 64, 64), shape(1, 32, 1, 1), 4))
+        timed("broadcast_to", "(1,32,1,1) -> (256,32,64,64) fp32", lambda L: L.call(
+            "keydnn_cuda_broadcast_to_f32", vec.data, out.data, shape(1, 32, 1, 1), 4, shape(256, 32, 64, 64), 4))
+    slower = [r["entry"] + " " + r["workload"] for r in rows if r["speedup"] < 0.97]       # beyond run-to-run noise
+    print(json.dumps({"metric": "reference-signature entries: device time per call on this library and on the reference's own CUDA kernels",
+                      "unit": "us", "higher_is_better": False, "n_gpus": 1, "data": "synthetic", "rows": rows,
+                      "slower_than_the_reference_by_more_than_3_percent": slower,
+                      "geomean_speedup": round(float(np.exp(np.mean([np.log(r["speedup"]) for r in rows]))), 2),
+                      "config": {"workload": "same C-ABI call, same device buffers, CUDA events on the legacy default stream; "
+                                             "3 warm-up + 5 timed calls; zero-fills that the accumulating backward entries need are "
+                                             "inside the timed region for both"}}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1208,9 +1342,10 @@ def main() -> None:
     ap.add_argument("--kernels", default="auto", choices=["auto", "none", "step", "suite", "full", "all"],
                     help="per-kernel tables: step = the reductions of the step; suite = + configs[0], [2], [3] (pool, element-wise, "
                          "optimizer); full = + activations / softmax / losses / layer glue; auto = suite at N = 1, step at N > 1")
-    ap.add_argument("--workload", default="reduce", choices=["reduce", "cnn", "dropin"],
+    ap.add_argument("--workload", default="reduce", choices=["reduce", "cnn", "dropin", "abi"],
                     help="reduce: configs[1] (the default line); cnn: only the configs[4] training step, reported as samples/s; "
-                         "dropin: the reference's own Python stack over its own CUDA library and over this one")
+                         "dropin: the reference's own Python stack over its own CUDA library and over this one; "
+                         "abi: every kind of reference-signature entry on this library and on the reference's own kernels")
     ap.add_argument("--cnn", default="on", choices=["on", "off"], help="also time the small-CNN training step (configs[4])")
     ap.add_argument("--ref-cuda", dest="ref_cuda", default="on", choices=["on", "off"],
                     help="time the reference's own CUDA kernels (oracle/_ref) beside each kernel (N = 1)")
@@ -1222,6 +1357,8 @@ def main() -> None:
         run_reference(args)
     elif args.workload == "dropin":
         run_dropin(args)
+    elif args.workload == "abi":
+        run_abi(args)
     else:
         run_ours(args)
 
