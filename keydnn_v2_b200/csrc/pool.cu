@@ -655,7 +655,7 @@ template <typename T> inline BandPlan band_plan_fwd(const PoolGeom& g) {
 // Backward: `rows` input rows are covered by at most (rows + kh - 2) / sh + 1 output rows; they are staged
 // with one more column and one more row, both zero.
 inline __host__ __device__ int64_t band_go_rows(const PoolGeom& g, int64_t r) { return (r + g.kh - 2) / g.sh + 1; }
-inline __host__ __device__ size_t band_bwd_table_bytes(int rows) { return (static_cast<size_t>(rows) * sizeof(int2) + 15) & ~size_t(15); }
+inline __host__ __device__ size_t band_bwd_table_bytes(int rows) { return static_cast<size_t>(rows) * sizeof(int4); }
 template <typename T> inline __host__ __device__ size_t band_bwd_quotient_bytes(const PoolGeom& g, int rows) {
     return (static_cast<size_t>((band_go_rows(g, rows) + 1) * (g.Wo + 1)) * sizeof(T) + 15) & ~size_t(15);
 }
@@ -909,14 +909,15 @@ maxpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, long long* __restri
 // Backward.  The quotients go / (kh*kw) of the output rows that cover the band are staged once, in rows of Wo + 1
 // with a zero in the extra column, followed by a row of zeros.  What depends on the column only (the first covering
 // output column and how many there are) is computed once per thread; what depends on the row only comes from a table
-// that is refilled when the CTA moves to a different band (with one band per plane: once).  TWO: no element is covered
-// by more than two windows along either axis (kh <= 2 sh, kw <= 2 sw); the table holds the staged (byte) offsets of the two
-// covering rows and the thread those of the two covering columns, a window that does not exist being replaced by the
-// zero row / zero column, so the four taps are taken without a branch or a predicate.  A zero tap leaves the running
-// sum as it is (it starts at +0 and is therefore never -0).  Otherwise the table holds {offset of the first covering
+// that is refilled when the CTA moves to a different band (with one band per plane: once).  MAXW = 2 or 3: no element is
+// covered by more than MAXW windows along either axis (kh <= MAXW sh, kw <= MAXW sw: 3x3 / 2, 2x2 / 2 ... and 3x3 / 1,
+// 5x5 / 2 ...); the table holds the staged (byte) offsets of the covering rows and the thread those of the covering
+// columns, a window that does not exist being replaced by the zero row / zero column, so the MAXW x MAXW taps are taken
+// without a branch or a predicate.  A zero tap leaves the running
+// sum as it is (it starts at +0 and is therefore never -0).  MAXW = 0: the table holds {offset of the first covering
 // row, number of covering rows} and the taps are counted loops.  A thread owns V adjacent columns, moved with one
 // access of 4 to 16 bytes, and has 8 / V rows in flight.
-template <typename T> struct BandColumn { int j_lo, nj, a, b; };
+template <typename T> struct BandColumn { int j_lo, nj, a, b, c; };   // a, b, c: the first three covering columns, Wo where there is none
 
 template <typename T>
 __device__ __forceinline__ BandColumn<T> band_column(const PoolGeom& g, int w, const kd::FastDiv& by_sw) {
@@ -927,6 +928,7 @@ __device__ __forceinline__ BandColumn<T> band_column(const PoolGeom& g, int w, c
     c.nj = min(g.Wo - 1, static_cast<int>(by_sw.div(static_cast<unsigned>(wp)))) - c.j_lo + 1;
     c.a = c.nj >= 1 ? c.j_lo : g.Wo;
     c.b = c.nj >= 2 ? c.j_lo + 1 : g.Wo;
+    c.c = c.nj >= 3 ? c.j_lo + 2 : g.Wo;
     return c;
 }
 
@@ -971,12 +973,12 @@ __device__ __forceinline__ BandBwdItem band_bwd_item(const PoolGeom& g, int rows
     return it;
 }
 
-template <typename T, bool ACCUM, bool TWO, int V>
+template <typename T, bool ACCUM, int MAXW, int V>
 __global__ void __launch_bounds__(kBandThreads)
 avgpool_bwd_band(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int rows, unsigned items, kd::FastDiv by_bands,
                  int lane_bits, kd::FastDiv by_sh, kd::FastDiv by_sw, kd::FastDiv by_wo, int buffer_elems) {
     extern __shared__ __align__(16) unsigned char band_smem[];
-    int2* rowinfo = reinterpret_cast<int2*>(band_smem);
+    int4* rowinfo = reinterpret_cast<int4*>(band_smem);
     T* q = reinterpret_cast<T*>(band_smem + band_bwd_table_bytes(rows));
     T* const raw = reinterpret_cast<T*>(band_smem + band_bwd_table_bytes(rows) + band_bwd_quotient_bytes<T>(g, rows));
     kd::pdl_prologue();
@@ -1047,9 +1049,12 @@ avgpool_bwd_band(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int r
                 const int i_lo = a0 <= 0 ? 0 : static_cast<int>(by_sh.div(static_cast<unsigned>(a0 + g.sh - 1)));
                 const int ni = min(g.Ho - 1, static_cast<int>(by_sh.div(static_cast<unsigned>(hp)))) - i_lo + 1;
                 const int first = (i_lo - it.i_first) * pitch;
-                constexpr int B = static_cast<int>(sizeof(T));                 // TWO: byte offsets
-                if (TWO) rowinfo[hh] = make_int2((ni >= 1 ? first : ngo * pitch) * B, (ni >= 2 ? first + pitch : ngo * pitch) * B);
-                else rowinfo[hh] = make_int2(first, max(0, ni));
+                constexpr int B = static_cast<int>(sizeof(T));                 // MAXW > 0: byte offsets
+                const int none = ngo * pitch;
+                if (MAXW > 0)
+                    rowinfo[hh] = make_int4((ni >= 1 ? first : none) * B, (ni >= 2 ? first + pitch : none) * B,
+                                            (ni >= 3 ? first + 2 * pitch : none) * B, 0);
+                else rowinfo[hh] = make_int4(first, max(0, ni), 0, 0);
             }
         }
         __syncthreads();
@@ -1059,10 +1064,12 @@ avgpool_bwd_band(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int r
             for (int k = 0; k < V; ++k) col[k] = c == lig ? mine[k] : band_column<T>(g, c * V + k, by_sw);
             const char* pa[V];
             const char* pb[V];
+            const char* pc[V];
 #pragma unroll
             for (int k = 0; k < V; ++k) {
                 pa[k] = reinterpret_cast<const char*>(q + col[k].a);
                 pb[k] = reinterpret_cast<const char*>(q + col[k].b);
+                pc[k] = reinterpret_cast<const char*>(q + col[k].c);
             }
             T* out = plane + c * V;
             for (int hb = group; hb < nrows; hb += U * ngroups, out += U * stride) {
@@ -1076,16 +1083,19 @@ avgpool_bwd_band(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int r
                 for (int u = 0; u < U; ++u) {
                     const int hh = hb + u * ngroups;
                     if (hh >= nrows) break;
-                    const int2 ro = rowinfo[hh];
+                    const int4 ro = rowinfo[hh];
                     T res[V];
 #pragma unroll
                     for (int k = 0; k < V; ++k) {
                         T acc = T(0);
-                        if (TWO) {
-                            acc += *reinterpret_cast<const T*>(pa[k] + ro.x);
-                            acc += *reinterpret_cast<const T*>(pb[k] + ro.x);
-                            acc += *reinterpret_cast<const T*>(pa[k] + ro.y);
-                            acc += *reinterpret_cast<const T*>(pb[k] + ro.y);
+                        if (MAXW > 0) {
+                            const int row_at[3] = {ro.x, ro.y, ro.z};
+#pragma unroll
+                            for (int r = 0; r < MAXW; ++r) {
+                                acc += *reinterpret_cast<const T*>(pa[k] + row_at[r]);
+                                acc += *reinterpret_cast<const T*>(pb[k] + row_at[r]);
+                                if (MAXW == 3) acc += *reinterpret_cast<const T*>(pc[k] + row_at[r]);
+                            }
                         } else {
                             for (int a = 0; a < ro.y; ++a)
                                 for (int b = 0; b < col[k].nj; ++b) acc += q[ro.x + a * pitch + col[k].j_lo + b];
@@ -1107,8 +1117,8 @@ avgpool_bwd_band(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int r
 // as {gradient, tap}: tap = a * kw + b of the recorded position inside its own window, -1 when the position is not
 // inside it; an element at window offset (a, b) takes the gradient when the staged tap equals a * kw + b.  Rows of
 // Wo + 1 with {0, -1} in the extra column and a last row of {0, -1} stand in for windows that do not exist, as in the
-// AvgPool kernel; the row table holds {offset of the first covering row, offset of the second (TWO) or the number of
-// covering rows, a * kw of the element in the first covering row}.  Gradients and positions arrive asynchronously
+// AvgPool kernel; the row table holds {offsets of the covering rows (MAXW = 2, 3) or first offset and number of rows
+// (MAXW = 0), a * kw of the element in the first covering row}.  Gradients and positions arrive asynchronously
 // (cp.async, two buffers each; the next item's are requested before the current one is worked on) and a short
 // shared-to-shared pass turns them into the staged pairs.
 struct BandPlanMax { bool ok; int rows, bands, staged, buffer; size_t smem; };
@@ -1137,7 +1147,7 @@ template <typename T> inline BandPlanMax band_plan_maxbwd(const PoolGeom& g) {
     return p;
 }
 
-template <typename T, bool TWO, int V>
+template <typename T, int MAXW, int V>
 __global__ void __launch_bounds__(kBandThreads)
 maxpool_bwd_band(const T* __restrict__ go, const long long* __restrict__ idx, T* __restrict__ gx, PoolGeom g, int rows,
                  unsigned items, kd::FastDiv by_bands, int lane_bits, kd::FastDiv by_sh, kd::FastDiv by_sw, kd::FastDiv by_wo,
@@ -1229,8 +1239,10 @@ maxpool_bwd_band(const T* __restrict__ go, const long long* __restrict__ idx, T*
                 const int ni = min(g.Ho - 1, static_cast<int>(by_sh.div(static_cast<unsigned>(hp)))) - i_lo + 1;
                 const int first = (i_lo - it.i_first) * pitch;
                 const int rp = (hp - i_lo * g.sh) * g.kw;
-                if (TWO) rowinfo[hh] = make_int4(ni >= 1 ? first : ngo * pitch, ni >= 2 ? first + pitch : ngo * pitch, rp, 0);
-                else rowinfo[hh] = make_int4(first, max(0, ni), rp, 0);
+                const int none = ngo * pitch;
+                if (MAXW > 0)
+                    rowinfo[hh] = make_int4(ni >= 1 ? first : none, ni >= 2 ? first + pitch : none, ni >= 3 ? first + 2 * pitch : none, rp);
+                else rowinfo[hh] = make_int4(first, max(0, ni), 0, rp);
             }
         }
         __syncthreads();
@@ -1254,17 +1266,21 @@ maxpool_bwd_band(const T* __restrict__ go, const long long* __restrict__ idx, T*
 #pragma unroll
                     for (int k = 0; k < V; ++k) {
                         T acc = T(0);
-                        if (TWO) {
-                            const int e00 = ro.z + cp[k], e01 = e00 - g.sw, e10 = e00 - row_step, e11 = e10 - g.sw;
-                            acc += tap[ro.x + col[k].a] == e00 ? q[ro.x + col[k].a] : T(0);
-                            acc += tap[ro.x + col[k].b] == e01 ? q[ro.x + col[k].b] : T(0);
-                            acc += tap[ro.y + col[k].a] == e10 ? q[ro.y + col[k].a] : T(0);
-                            acc += tap[ro.y + col[k].b] == e11 ? q[ro.y + col[k].b] : T(0);
+                        if (MAXW > 0) {
+                            const int row_at[3] = {ro.x, ro.y, ro.z};
+                            const int col_at[3] = {col[k].a, col[k].b, col[k].c};
+#pragma unroll
+                            for (int r = 0; r < MAXW; ++r)
+#pragma unroll
+                                for (int b = 0; b < MAXW; ++b) {
+                                    const int at_ = row_at[r] + col_at[b];
+                                    acc += tap[at_] == ro.w - r * row_step + cp[k] - b * g.sw ? q[at_] : T(0);
+                                }
                         } else {
                             for (int a = 0; a < ro.y; ++a)
                                 for (int b = 0; b < col[k].nj; ++b) {
                                     const int at_ = ro.x + a * pitch + col[k].j_lo + b;
-                                    if (tap[at_] == ro.z - a * row_step + cp[k] - b * g.sw) acc += q[at_];
+                                    if (tap[at_] == ro.w - a * row_step + cp[k] - b * g.sw) acc += q[at_];
                                 }
                         }
                         res[k] = acc;
@@ -1597,6 +1613,13 @@ inline bool is_2x2s2p0(const PoolGeom& g) {
            g.Ho == g.H / 2;
 }
 
+// most windows that cover one element along an axis, as far as the branch-free backward kernels go: 2, 3, or 0 (more)
+inline int band_max_windows(const PoolGeom& g) {
+    if (g.kh <= 2 * g.sh && g.kw <= 2 * g.sw) return 2;
+    if (g.kh <= 3 * g.sh && g.kw <= 3 * g.sw) return 3;
+    return 0;
+}
+
 // the band kernels index inside a plane with 32-bit integers
 inline bool band_indexable(const PoolGeom& g) {
     return static_cast<int64_t>(g.H) * g.W < (int64_t(1) << 31) && static_cast<int64_t>(g.Ho) * g.Wo < (int64_t(1) << 31);
@@ -1688,22 +1711,23 @@ int maxpool_backward_ex(const T* go, const long long* idx, T* gx, int N, int C, 
     if (plan.ok && nc * plan.bands < (int64_t(1) << 31) && padded < (int64_t(1) << 31) && band_indexable(g)) {
         const unsigned items = static_cast<unsigned>(nc * plan.bands);
         const kd::FastDiv by_bands(plan.bands), by_sh(g.sh), by_sw(g.sw), by_wo(g.Wo), by_wp(g.W + 2 * g.pw);
-        const bool two = g.kh <= 2 * g.sh && g.kw <= 2 * g.sw;
+        const int maxw = band_max_windows(g);
         int v = 16 / static_cast<int>(sizeof(T));
         while (v > 1 && (g.W % v != 0 || (reinterpret_cast<uintptr_t>(gx) % (v * sizeof(T))) != 0)) v /= 2;
         const int threads = band_threads(static_cast<int64_t>(plan.rows) * (g.W / v) / (8 / v));
         const int lanes = band_lane_bits(g.W / v, threads);
-#define KD_BWD_BAND_V(TWO_, V_)                                                                                      \
-    KD_LAUNCH_W((maxpool_bwd_band<T, TWO_, V_>), 2, items, threads, plan.smem, go, idx, gx, g, plan.rows, items, by_bands, \
+#define KD_BWD_BAND_V(MAXW_, V_)                                                                                     \
+    KD_LAUNCH_W((maxpool_bwd_band<T, MAXW_, V_>), 2, items, threads, plan.smem, go, idx, gx, g, plan.rows, items, by_bands, \
                 lanes, by_sh, by_sw, by_wo, by_wp, plan.staged, plan.buffer)
-#define KD_BWD_BAND(TWO_)                                                                                           \
+#define KD_BWD_BAND(MAXW_)                                                                                          \
     do {                                                                                                            \
-        if (v == 4) { if constexpr (sizeof(T) == 4) KD_BWD_BAND_V(TWO_, 4); }                                       \
-        else if (v == 2) KD_BWD_BAND_V(TWO_, 2);                                                                    \
-        else KD_BWD_BAND_V(TWO_, 1);                                                                                \
+        if (v == 4) { if constexpr (sizeof(T) == 4) KD_BWD_BAND_V(MAXW_, 4); }                                      \
+        else if (v == 2) KD_BWD_BAND_V(MAXW_, 2);                                                                   \
+        else KD_BWD_BAND_V(MAXW_, 1);                                                                               \
     } while (0)
-        if (two) KD_BWD_BAND(true);
-        else KD_BWD_BAND(false);
+        if (maxw == 2) KD_BWD_BAND(2);
+        else if (maxw == 3) KD_BWD_BAND(3);
+        else KD_BWD_BAND(0);
 #undef KD_BWD_BAND_V
 #undef KD_BWD_BAND
     } else {
@@ -1808,25 +1832,30 @@ int avgpool_backward(const T* go, T* gx, int N, int C, PoolGeom g, bool accumula
         const unsigned items = static_cast<unsigned>(nc * plan.bands);
         const kd::FastDiv by_bands(plan.bands), by_sh(g.sh), by_sw(g.sw);
         const kd::FastDiv by_wo(g.Wo);
-        const bool two = g.kh <= 2 * g.sh && g.kw <= 2 * g.sw;
+        const int maxw = band_max_windows(g);
         // columns per thread: as many as one aligned access of up to 16 bytes holds, for every row of every plane
         int v = 16 / static_cast<int>(sizeof(T));
         while (v > 1 && (g.W % v != 0 || (reinterpret_cast<uintptr_t>(gx) % (v * sizeof(T))) != 0)) v /= 2;
         const int threads = band_threads(static_cast<int64_t>(plan.rows) * (g.W / v) / (8 / v));
         const int lanes = band_lane_bits(g.W / v, threads);
-#define KD_BWD_BAND_V(ACC, TWO_, V_)                                                                                 \
-    KD_LAUNCH_W((avgpool_bwd_band<T, ACC, TWO_, V_>), 2, items, threads, plan.smem, go, gx, g, plan.rows, items, by_bands, \
+#define KD_BWD_BAND_V(ACC, MAXW_, V_)                                                                                \
+    KD_LAUNCH_W((avgpool_bwd_band<T, ACC, MAXW_, V_>), 2, items, threads, plan.smem, go, gx, g, plan.rows, items, by_bands, \
                 lanes, by_sh, by_sw, by_wo, plan.buffer)
-#define KD_BWD_BAND(ACC, TWO_)                                                                                      \
+#define KD_BWD_BAND(ACC, MAXW_)                                                                                     \
     do {                                                                                                            \
-        if (v == 4) { if constexpr (sizeof(T) == 4) KD_BWD_BAND_V(ACC, TWO_, 4); }                                  \
-        else if (v == 2) KD_BWD_BAND_V(ACC, TWO_, 2);                                                               \
-        else KD_BWD_BAND_V(ACC, TWO_, 1);                                                                           \
+        if (v == 4) { if constexpr (sizeof(T) == 4) KD_BWD_BAND_V(ACC, MAXW_, 4); }                                 \
+        else if (v == 2) KD_BWD_BAND_V(ACC, MAXW_, 2);                                                              \
+        else KD_BWD_BAND_V(ACC, MAXW_, 1);                                                                          \
     } while (0)
-        if (accumulate && two) KD_BWD_BAND(true, true);
-        else if (accumulate) KD_BWD_BAND(true, false);
-        else if (two) KD_BWD_BAND(false, true);
-        else KD_BWD_BAND(false, false);
+        if (accumulate) {
+            if (maxw == 2) KD_BWD_BAND(true, 2);
+            else if (maxw == 3) KD_BWD_BAND(true, 3);
+            else KD_BWD_BAND(true, 0);
+        } else {
+            if (maxw == 2) KD_BWD_BAND(false, 2);
+            else if (maxw == 3) KD_BWD_BAND(false, 3);
+            else KD_BWD_BAND(false, 0);
+        }
 #undef KD_BWD_BAND_V
 #undef KD_BWD_BAND
     } else if (accumulate) {

@@ -101,6 +101,8 @@ BAND_GEOMS = [
     (1, 3, 64, 64, (4, 4), (4, 4), (0, 0)),
     (1, 1, 12, 1500, (3, 3), (1, 1), (1, 1)),    # three rows exceed a band: the one-thread-per-element kernels
     (1, 2, 37, 41, (3, 3), (3, 3), (2, 2)),      # whole windows inside the padding
+    (2, 3, 70, 60, (3, 3), (1, 1), (1, 1)),      # stride 1: three windows per axis cover an element, several bands
+    (1, 2, 40, 36, (5, 4), (2, 2), (2, 1)),      # 5x4 / 2: three by two
     (2, 2, 11, 16, (2, 2), (2, 2), (0, 0)),      # the 2x2/2 kernels when aligned (odd H: a last row without a window), bands otherwise
 ]
 
