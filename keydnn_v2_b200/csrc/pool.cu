@@ -601,13 +601,15 @@ avgpool_bwd_gather(const T* __restrict__ go, T* __restrict__ gx, PoolGeom g, int
 // ---------------------------------------------------------------------------
 // Band kernels: any window, stride and padding, any alignment.
 // A CTA takes a band of whole rows of one plane.  Everything the band reads is one contiguous
-// span of memory (rows are complete), so it is staged in shared memory with coalesced loads and
-// the stencil reads shared memory; global traffic is fully coalesced whatever the stride of the
-// window.  A thread then owns one column of the band and walks down its rows, so that everything
-// that depends on the column only is computed once and a row costs a pointer increment: both
-// kernels are bound by instruction issue before they are bound by memory, and index arithmetic
-// per element is what has to go.  The arithmetic on the data is that of the one-thread-per-element
-// kernels above, tap for tap.  `lanes` (a power of two, 32..256) threads share a row.
+// span of memory (rows are complete), so it is staged in shared memory with 16-byte cp.async
+// copies (two buffers: the next item's span arrives while the current one is worked on) and the
+// stencil reads shared memory; global traffic is fully coalesced whatever the stride of the
+// window.  A thread then owns one column of the band (backward: 1, 2 or 4 adjacent columns) and
+// walks down its rows, so that everything that depends on the column only is computed once and a
+// row costs a pointer increment: these kernels are bound by instruction issue before they are
+// bound by memory, and index arithmetic per element is what has to go.  The arithmetic on the
+// data is that of the one-thread-per-element kernels above, tap for tap.  `lanes` (a power of
+// two, 8 .. the CTA) threads share a row; a CTA has 32, 64 or 128 threads by the size of an item.
 // ---------------------------------------------------------------------------
 constexpr int kBandBytes = 16 * 1024;          // staged span per band
 constexpr int kBandRowsMax = 512;              // backward: rows of a band (one table entry each)
@@ -618,7 +620,7 @@ struct BandPlan {
     bool ok;
     int rows;        // rows of the band (output rows forward, input rows backward)
     int bands;       // bands per plane
-    int buffer;      // forward: elements of one staging buffer
+    int buffer;      // elements of one arrival buffer (forward: the input span; backward: the gradients)
     size_t smem;
 };
 
