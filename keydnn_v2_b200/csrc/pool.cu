@@ -1551,8 +1551,11 @@ crop2d_kernel(const T* __restrict__ xp, T* __restrict__ y, int Hp, int Wp, int p
     }
 }
 
-// Row-wise forms: a warp owns a row of the output plane (one multiply-high per ROW instead of four 64-bit
-// divisions per ELEMENT), its lanes walk the row, so loads and stores are contiguous.  rows < 2^31.
+// Row-wise forms: a warp owns four consecutive rows of the output (one multiply-high per ROW instead of four 64-bit
+// divisions per ELEMENT), its lanes walk the rows, so loads and stores are contiguous; the loads of the four rows are
+// issued before the first store, which keeps enough bytes in flight for rows as short as 56 elements.  rows < 2^31.
+constexpr int kRowsPerWarp = 4;
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 pad2d_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int H, int W, int ph, int pw, T value, unsigned rows,
@@ -1560,15 +1563,28 @@ pad2d_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int H, int W, int 
     kd::pdl_prologue();
     const int Hp = H + 2 * ph, Wp = W + 2 * pw;
     const int lane = threadIdx.x & 31;
-    for (unsigned r = blockIdx.x * kWarps + (threadIdx.x >> 5); r < rows; r += gridDim.x * kWarps) {
-        const unsigned nc = by_hp.div(r);
-        const int h = static_cast<int>(r - nc * static_cast<unsigned>(Hp)) - ph;
-        T* dst = y + static_cast<int64_t>(r) * Wp;
-        if (h < 0 || h >= H) {
-            for (int w = lane; w < Wp; w += 32) dst[w] = value;
-        } else {
-            const T* src = x + (static_cast<int64_t>(nc) * H + h) * W - pw;
-            for (int w = lane; w < Wp; w += 32) dst[w] = (w >= pw && w < pw + W) ? src[w] : value;
+    for (unsigned r0 = (blockIdx.x * kWarps + (threadIdx.x >> 5)) * kRowsPerWarp; r0 < rows; r0 += gridDim.x * kWarps * kRowsPerWarp) {
+        const T* src[kRowsPerWarp];
+        bool live[kRowsPerWarp], data[kRowsPerWarp];
+#pragma unroll
+        for (int u = 0; u < kRowsPerWarp; ++u) {
+            const unsigned r = r0 + u;
+            live[u] = r < rows;
+            const unsigned nc = by_hp.div(live[u] ? r : 0u);
+            const int h = static_cast<int>((live[u] ? r : 0u) - nc * static_cast<unsigned>(Hp)) - ph;
+            data[u] = live[u] && h >= 0 && h < H;
+            src[u] = x + (static_cast<int64_t>(nc) * H + (data[u] ? h : 0)) * W - pw;
+        }
+        T* dst = y + static_cast<int64_t>(r0) * Wp;
+#pragma unroll 1
+        for (int w = lane; w < Wp; w += 32) {
+            const bool inside = w >= pw && w < pw + W;
+            T v[kRowsPerWarp];
+#pragma unroll
+            for (int u = 0; u < kRowsPerWarp; ++u) v[u] = (data[u] && inside) ? __ldcs(src[u] + w) : value;
+#pragma unroll
+            for (int u = 0; u < kRowsPerWarp; ++u)
+                if (live[u]) __stcs(dst + static_cast<int64_t>(u) * Wp + w, v[u]);
         }
     }
 }
@@ -1579,14 +1595,29 @@ crop2d_rows_kernel(const T* __restrict__ xp, T* __restrict__ y, int Hp, int Wp, 
                    kd::FastDiv by_h) {
     kd::pdl_prologue();
     const int lane = threadIdx.x & 31;
-    for (unsigned r = blockIdx.x * kWarps + (threadIdx.x >> 5); r < rows; r += gridDim.x * kWarps) {
-        const unsigned nc = by_h.div(r);
-        const int hp = static_cast<int>(r - nc * static_cast<unsigned>(H)) + ph;
-        if (hp >= Hp) continue;                       // rows the padded plane does not have stay untouched, as in the flat kernel
-        const T* src = xp + (static_cast<int64_t>(nc) * Hp + hp) * Wp + pw;
-        T* dst = y + static_cast<int64_t>(r) * W;
-        for (int w = lane; w < W; w += 32)
-            if (w + pw < Wp) dst[w] = src[w];
+    for (unsigned r0 = (blockIdx.x * kWarps + (threadIdx.x >> 5)) * kRowsPerWarp; r0 < rows; r0 += gridDim.x * kWarps * kRowsPerWarp) {
+        const T* src[kRowsPerWarp];
+        bool live[kRowsPerWarp];
+#pragma unroll
+        for (int u = 0; u < kRowsPerWarp; ++u) {
+            const unsigned r = r0 + u;
+            const bool in_range = r < rows;
+            const unsigned nc = by_h.div(in_range ? r : 0u);
+            const int hp = static_cast<int>((in_range ? r : 0u) - nc * static_cast<unsigned>(H)) + ph;
+            live[u] = in_range && hp < Hp;            // rows the padded plane does not have stay untouched, as in the flat kernel
+            src[u] = xp + (static_cast<int64_t>(nc) * Hp + (live[u] ? hp : 0)) * Wp + pw;
+        }
+        T* dst = y + static_cast<int64_t>(r0) * W;
+#pragma unroll 1
+        for (int w = lane; w < W; w += 32) {
+            const bool inside = w + pw < Wp;
+            T v[kRowsPerWarp];
+#pragma unroll
+            for (int u = 0; u < kRowsPerWarp; ++u) v[u] = (live[u] && inside) ? __ldcs(src[u] + w) : T(0);
+#pragma unroll
+            for (int u = 0; u < kRowsPerWarp; ++u)
+                if (live[u] && inside) __stcs(dst + static_cast<int64_t>(u) * W + w, v[u]);
+        }
     }
 }
 
@@ -1919,7 +1950,7 @@ int pad2d(const T* x, T* y, int N, int C, int H, int W, int ph, int pw, T value)
         return kd::status(cudaMemcpyAsync(y, x, static_cast<size_t>(total) * sizeof(T), cudaMemcpyDeviceToDevice, kd::stream()));
     const int64_t rows = static_cast<int64_t>(N) * C * (H + 2 * ph);
     if (rows < (int64_t(1) << 31)) {
-        KD_LAUNCH_W(pad2d_rows_kernel<T>, 8, (rows + kWarps - 1) / kWarps, kThreads, 0, x, y, H, W, ph, pw, value,
+        KD_LAUNCH_W(pad2d_rows_kernel<T>, 8, (rows + kWarps * kRowsPerWarp - 1) / (kWarps * kRowsPerWarp), kThreads, 0, x, y, H, W, ph, pw, value,
                     static_cast<unsigned>(rows), kd::FastDiv(static_cast<unsigned>(H + 2 * ph)));
         return kd::launch_status();
     }
@@ -1939,7 +1970,7 @@ int crop2d(const T* xp, T* y, int N, int C, int Hp, int Wp, int ph, int pw, int 
         return kd::status(cudaMemcpyAsync(y, xp, static_cast<size_t>(total) * sizeof(T), cudaMemcpyDeviceToDevice, kd::stream()));
     const int64_t rows = static_cast<int64_t>(N) * C * H;
     if (rows < (int64_t(1) << 31)) {
-        KD_LAUNCH_W(crop2d_rows_kernel<T>, 8, (rows + kWarps - 1) / kWarps, kThreads, 0, xp, y, Hp, Wp, ph, pw, H, W,
+        KD_LAUNCH_W(crop2d_rows_kernel<T>, 8, (rows + kWarps * kRowsPerWarp - 1) / (kWarps * kRowsPerWarp), kThreads, 0, xp, y, Hp, Wp, ph, pw, H, W,
                     static_cast<unsigned>(rows), kd::FastDiv(static_cast<unsigned>(H)));
         return kd::launch_status();
     }
