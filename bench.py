@@ -1195,7 +1195,7 @@ def run_dropin(args) -> None:
     print(json.dumps({"metric": "the reference's own Python stack on CUDA: ms per iteration over its own library and over this one",
                       "unit": "ms", "higher_is_better": False, "n_gpus": 1, "data": "synthetic", "rows": rows,
                       "config": {"workload": "reference stack (staged copy, unmodified) over two native libraries; host time per "
-                                             "iteration, device synchronised at both ends; inputs resident on the device"}}), flush=True)
+                                             "iteration, device synchronised at both ends, best of three loops; inputs resident on the device"}}), flush=True)
 
 
 def run_abi(args) -> None:

@@ -12,10 +12,11 @@ two runs.  Usage (child process):
 
 prints one JSON object {workload: milliseconds per iteration}.  Inputs are uploaded once; an iteration is the
 forward + backward (or the training step) through the reference's Tensor API, with the device synchronised before
-the first and after the last iteration.
+the first and after the last iteration of a loop; the best of three loops is reported.
 """
 from __future__ import annotations
 
+import gc
 import json
 import sys
 import time
@@ -57,14 +58,20 @@ def main() -> None:
         return t
 
     def timed(fn) -> float:
+        # best of three loops: the reference's pooling Contexts reference themselves, so their device buffers wait for
+        # the cyclic collector, and a loop in which it happens to run late pays for fresh allocations
         for _ in range(2):
             fn()
-        cuda_synchronize(lib)
-        t0 = time.perf_counter()
-        for _ in range(repeats):
-            fn()
-        cuda_synchronize(lib)
-        return (time.perf_counter() - t0) / repeats * 1e3
+        best = float("inf")
+        for _ in range(3):
+            gc.collect()
+            cuda_synchronize(lib)
+            t0 = time.perf_counter()
+            for _ in range(repeats):
+                fn()
+            cuda_synchronize(lib)
+            best = min(best, (time.perf_counter() - t0) / repeats * 1e3)
+        return best
 
     out = {}
     # element-wise chain with autograd: (a + b) * a / b, negated, summed, backward  (2048 x 2048 fp32)
