@@ -404,6 +404,68 @@ softmax_strided_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __re
     }
 }
 
+// Forward for long packet-aligned rows, the row kept in registers: every thread requests its PER packets of the row at
+// once (all of the row's loads are in flight together, nothing is staged in shared memory and nothing is read twice),
+// then the block maximum, the exponentials with their block sum, and the normalised row go out.  Same assignment of
+// elements to threads, same order of additions and same block reductions as softmax_block_kernel: same bits.
+template <typename T, int kBlockThreads, int PER>
+__global__ void __launch_bounds__(kBlockThreads)
+softmax_fwd_regs_kernel(const T* __restrict__ a, T* __restrict__ out, int64_t rows, int len) {
+    kd::pdl_prologue();
+    constexpr int kBlockWarps = kBlockThreads / 32;
+    __shared__ T red[kBlockWarps];
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* pa = a + row * len;
+        T* po = out + row * len;
+        kd::Pack4<T> x[PER];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int c = (threadIdx.x + i * kBlockThreads) * 4;
+            if (c < len) x[i] = kd::load4_stream(pa + c);
+        }
+        T m = neg_inf<T>();
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            if ((threadIdx.x + i * kBlockThreads) * 4 < len) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) m = x[i].v[k] > m ? x[i].v[k] : m;
+            }
+        }
+        m = block_max<T, kBlockWarps>(m, red);
+        T s = T(0);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            if ((threadIdx.x + i * kBlockThreads) * 4 < len) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    x[i].v[k] = t_exp(Rn<T>::sub(x[i].v[k], m));
+                    s = Rn<T>::add(s, x[i].v[k]);
+                }
+            }
+        }
+        const T inv = t_div(T(1), block_add<T, kBlockWarps>(s, red));
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int c = (threadIdx.x + i * kBlockThreads) * 4;
+            if (c < len) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) x[i].v[k] = Rn<T>::mul(x[i].v[k], inv);
+                kd::store4(po + c, x[i]);
+            }
+        }
+    }
+}
+
+template <typename T, int THREADS, int PER>
+int launch_fwd_regs(const T* a, T* out, int64_t rows, int len) {
+    auto kernel = softmax_fwd_regs_kernel<T, THREADS, PER>;
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+    const int64_t cap = static_cast<int64_t>(kd::sm_count()) * per_sm * 4;
+    (void)kd::launch(kernel, dim3(static_cast<unsigned>(rows < cap ? rows : cap)), THREADS, 0, a, out, rows, len);
+    return kd::launch_status();
+}
+
 template <typename T, int G, int R, int K, bool BWD>
 void launch_warp(const T* a, const T* b, T* out, int64_t rows, int len) {
     constexpr int RPW = (32 / G) * K;
@@ -445,6 +507,16 @@ int launch_block(const T* a, const T* b, T* out, int64_t rows, int len) {
 template <typename T, bool BWD, bool VEC>
 int launch_block_for(const T* a, const T* b, T* out, int64_t rows, int len) {
     const size_t bytes = static_cast<size_t>(len) * sizeof(T) * (BWD ? 2 : 1);
+    if constexpr (!BWD && VEC) {
+        // rows of 1024 to 16384 elements: in registers, two to eight packets per thread
+        if (len >= 1024 && len <= 512 * 4 * 8) {
+            if (len <= 128 * 4 * 2) return launch_fwd_regs<T, 128, 2>(a, out, rows, len);
+            if (len <= 128 * 4 * 4) return launch_fwd_regs<T, 128, 4>(a, out, rows, len);
+            if (len <= 256 * 4 * 4) return launch_fwd_regs<T, 256, 4>(a, out, rows, len);
+            if (len <= 512 * 4 * 4) return launch_fwd_regs<T, 512, 4>(a, out, rows, len);
+            if constexpr (sizeof(T) == 4) return launch_fwd_regs<T, 512, 8>(a, out, rows, len);
+        }
+    }
     int threads = len <= 256 ? 32 : (len <= 512 ? 64 : 128);
     if (bytes <= 100 * 1024) {
         while (threads < 512 && static_cast<size_t>(threads) * 112 < bytes) threads *= 2;

@@ -195,7 +195,11 @@ SOFTMAX_SHAPES = [(1, 1, 1), (7, 1, 1), (5, 10, 1), (33, 33, 1), (64, 100, 1), (
                   (6, 1500, 1), (3, 5000, 1), (2, 60000, 1), (4, 10, 7), (3, 37, 64), (1, 50, 1000), (2000, 2, 1),
                   # rows split over a thread-block cluster (32 KiB and more): 2, 4 and 8 pieces, a ragged last piece,
                   # pieces above 48 KiB, and more rows than resident clusters (every cluster walks several rows)
-                  (16, 8192, 1), (8, 16384, 1), (5, 8196, 1), (3, 150000, 1), (4000, 8192, 1)]
+                  (16, 8192, 1), (8, 16384, 1), (5, 8196, 1), (3, 150000, 1), (4000, 8192, 1),
+                  # rows kept in registers (1024 .. 16384 elements in whole packets): every CTA width / packets-per-thread
+                  # class, full and ragged last packets
+                  (9, 1024, 1), (7, 1028, 1), (6, 2048, 1), (5, 3000, 1), (5, 4096, 1), (7, 4100, 1), (6, 6144, 1),
+                  (3, 12000, 1), (2, 16380, 1), (700, 1024, 1)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
