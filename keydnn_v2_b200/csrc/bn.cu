@@ -429,8 +429,15 @@ struct SumsPlan {
 };
 
 // scratch layout: [2*C doubles of sums][nslices*C*2 doubles of partials]
-inline bool plan_sums(int N, int C, SumsPlan& p) {
+// plane_bytes = 0: one resident wave of CTAs that hold eight per SM (the forward statistics: 32 registers).
+// plane_bytes > 0: many short CTAs of about 32 KiB of x each, handed out as SMs free up - for the backward sums, whose
+// registers let five CTAs share an SM, so that a grid sized for eight ran as 1.6 waves.
+inline bool plan_sums(int N, int C, SumsPlan& p, int64_t plane_bytes = 0) {
     int nslices = static_cast<int>((static_cast<int64_t>(kd::sm_count()) * 8 + C - 1) / C);
+    if (plane_bytes > 0) {
+        const int64_t images = std::max<int64_t>(1, (32 * 1024) / plane_bytes);
+        nslices = static_cast<int>(std::min<int64_t>((N + images - 1) / images, 1024));
+    }
     if (nslices > N) nslices = N;
     if (nslices < 1) nslices = 1;
     p.ach = (N + nslices - 1) / nslices;
@@ -582,7 +589,7 @@ int bn_backward(const T* x, const T* gamma, const T* beta, const T* go, const T*
     }
     const GradSrc<T> gsrc{pool_idx ? 1 : (gap ? 2 : 0), pool_idx, by_w, T(1) / static_cast<T>(HW)};
     SumsPlan p;
-    if (!plan_sums(N, C, p)) return static_cast<int>(cudaErrorMemoryAllocation);
+    if (!plan_sums(N, C, p, HW * static_cast<int64_t>(sizeof(T)))) return static_cast<int>(cudaErrorMemoryAllocation);
     dim3 grid(C, p.nslices);
 #define KD_BN_SUMS(V, R) (void)kd::launch(bn_channel_sums<T, 1, V, R>, dim3(grid), kThreads, 0, x, go, mean, invstd, gamma, beta, pre_bias, N, C, HW, p.ach, p.partials, p.counters, p.sums, gsrc)
     if (relu) { if (vec) KD_BN_SUMS(true, true); else KD_BN_SUMS(false, true); }
