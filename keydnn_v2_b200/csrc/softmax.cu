@@ -456,6 +456,60 @@ softmax_fwd_regs_kernel(const T* __restrict__ a, T* __restrict__ out, int64_t ro
     }
 }
 
+// Backward of the same rows: g and y in registers (PER packets each), dot = sum g*y with one accumulator per packet
+// lane over the thread's packets in order, lanes combined, block sum; grad_x = y * (g - dot).  The arithmetic and the
+// order inside a thread are those of softmax_block_kernel.
+template <typename T, int kBlockThreads, int PER>
+__global__ void __launch_bounds__(kBlockThreads)
+softmax_bwd_regs_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t rows, int len) {
+    kd::pdl_prologue();
+    constexpr int kBlockWarps = kBlockThreads / 32;
+    __shared__ T red[kBlockWarps];
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* pa = a + row * len;
+        const T* pb = b + row * len;
+        T* po = out + row * len;
+        kd::Pack4<T> g[PER], y[PER];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int c = (threadIdx.x + i * kBlockThreads) * 4;
+            if (c < len) { g[i] = kd::load4_stream(pa + c); y[i] = kd::load4_stream(pb + c); }
+        }
+        T dot[4] = {T(0), T(0), T(0), T(0)};
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            if ((threadIdx.x + i * kBlockThreads) * 4 < len) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) dot[k] = Rn<T>::add(dot[k], Rn<T>::mul(g[i].v[k], y[i].v[k]));
+            }
+        }
+        T d = dot[0];
+#pragma unroll
+        for (int k = 1; k < 4; ++k) d = Rn<T>::add(d, dot[k]);
+        d = block_add<T, kBlockWarps>(d, red);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int c = (threadIdx.x + i * kBlockThreads) * 4;
+            if (c < len) {
+                kd::Pack4<T> r;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) r.v[k] = Rn<T>::mul(y[i].v[k], Rn<T>::sub(g[i].v[k], d));
+                kd::store4(po + c, r);
+            }
+        }
+    }
+}
+
+template <typename T, int THREADS, int PER>
+int launch_bwd_regs(const T* a, const T* b, T* out, int64_t rows, int len) {
+    auto kernel = softmax_bwd_regs_kernel<T, THREADS, PER>;
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+    const int64_t cap = static_cast<int64_t>(kd::sm_count()) * per_sm * 4;
+    (void)kd::launch(kernel, dim3(static_cast<unsigned>(rows < cap ? rows : cap)), THREADS, 0, a, b, out, rows, len);
+    return kd::launch_status();
+}
+
 template <typename T, int THREADS, int PER>
 int launch_fwd_regs(const T* a, T* out, int64_t rows, int len) {
     auto kernel = softmax_fwd_regs_kernel<T, THREADS, PER>;
@@ -507,6 +561,13 @@ int launch_block(const T* a, const T* b, T* out, int64_t rows, int len) {
 template <typename T, bool BWD, bool VEC>
 int launch_block_for(const T* a, const T* b, T* out, int64_t rows, int len) {
     const size_t bytes = static_cast<size_t>(len) * sizeof(T) * (BWD ? 2 : 1);
+    if constexpr (BWD && VEC && sizeof(T) == 4) {
+        // backward rows of up to 16384 elements: g and y in registers, two to four packets of each per thread
+        if (len <= 256 * 4 * 2) return launch_bwd_regs<T, 256, 2>(a, b, out, rows, len);
+        if (len <= 256 * 4 * 4) return launch_bwd_regs<T, 256, 4>(a, b, out, rows, len);
+        if (len <= 512 * 4 * 4) return launch_bwd_regs<T, 512, 4>(a, b, out, rows, len);
+        if (len <= 1024 * 4 * 4) return launch_bwd_regs<T, 1024, 4>(a, b, out, rows, len);
+    }
     if constexpr (!BWD && VEC) {
         // rows of 1024 to 16384 elements: in registers, two to eight packets per thread
         if (len >= 1024 && len <= 512 * 4 * 8) {
