@@ -708,7 +708,9 @@ template <typename T, int TAPS> struct WindowDiv {
 // Forward kernels.  KH, KW: the window when the kernel is compiled for it, 0 = taken from g.  EDGES: a window may
 // reach outside the plane (padding, or an output size that lets the last window hang over); such taps contribute +0
 // to an average, which leaves the running sum as it is (it starts at +0 and is therefore never -0), and are no
-// candidates for a maximum.
+// candidates for a maximum.  Only the outputs on the rim of the plane have such windows: the rectangle of outputs
+// whose windows lie inside runs through the unchecked loop, the rim (a few rows and columns) through a checked one
+// spread over all threads, so that no warp executes both.
 // The staging is asynchronous (cp.async, 16 bytes each, no registers) into one of two buffers: the span of the CTA's
 // next item is requested before the stencil of the current one runs, so its loads are in flight under the arithmetic
 // and a CTA never waits for a full memory round trip between items.
@@ -754,7 +756,7 @@ __device__ __forceinline__ void band_wait_all_but_newest() { asm volatile("cp.as
 template <typename T, int KH, int KW, bool EDGES>
 __global__ void __launch_bounds__(kBandThreads)
 avgpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int rows, unsigned items, kd::FastDiv by_bands,
-                 int lane_bits, int buffer_elems) {
+                 int lane_bits, int buffer_elems, kd::FastDiv by_wo, kd::FastDiv by_edge_cols) {
     extern __shared__ __align__(16) unsigned char band_smem[];
     T* const buf = reinterpret_cast<T*>(band_smem);
     kd::pdl_prologue();
@@ -787,37 +789,62 @@ avgpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int row
         __syncthreads();
         const T* s = buf + cur * buffer_elems;
         const int nrows = it.nrows;
-        T* dst = y + it.nc * plane_out + it.out_off + group * g.Wo;
-        for (int j = lig; j < g.Wo; j += lanes) {
+        T* const dst = y + it.nc * plane_out + it.out_off;
+        // one output whose window may reach outside the plane: every tap checked
+        auto checked = [&](int ii, int j) {
+            const int hh = it.top + ii * g.sh, w0 = j * g.sw - g.pw;
+            const T* t = s + mis + hh * g.W + w0;
+            T sum = T(0);
+            for (int a = 0; a < kh; ++a) {
+                if (hh + a < 0 || hh + a >= nrows) continue;
+                for (int b = 0; b < kw; ++b) {
+                    if (w0 + b < 0 || w0 + b >= g.W) continue;
+                    sum += t[a * g.W + b];
+                }
+            }
+            dst[ii * g.Wo + j] = divide(sum);
+        };
+        // the outputs whose windows lie inside the staged rows and inside the plane: rows [ia, ib], columns [ja, jb]
+        int ia = 0, ib = it.nout - 1, ja = 0, jb = g.Wo - 1;
+        if (EDGES) {
+            ia = it.top >= 0 ? 0 : (-it.top + g.sh - 1) / g.sh;
+            ib = nrows - kh - it.top >= 0 ? min(it.nout - 1, (nrows - kh - it.top) / g.sh) : -1;
+            ja = (g.pw + g.sw - 1) / g.sw;
+            jb = g.W - kw + g.pw >= 0 ? min(g.Wo - 1, (g.W - kw + g.pw) / g.sw) : -1;
+            if (ib < ia || jb < ja) { ia = it.nout; ib = it.nout - 1; ja = 0; jb = -1; }      // none: everything is an edge
+        }
+        for (int j = ja + lig; j <= jb; j += lanes) {
             const int w0 = j * g.sw - g.pw;
-            int hh = it.top + group * g.sh;                                    // staged row of this thread's first tap
-            const T* t = s + mis + hh * g.W + w0;                              // dereferenced only where the tap exists
-            T* out = dst + j;
-            for (int ii = group; ii < it.nout; ii += ngroups, hh += step, t += step * g.W, out += ngroups * g.Wo) {
+            const T* t = s + mis + (it.top + (ia + group) * g.sh) * g.W + w0;
+            T* out = dst + (ia + group) * g.Wo + j;
+            for (int ii = ia + group; ii <= ib; ii += ngroups, t += step * g.W, out += ngroups * g.Wo) {
                 T sum = T(0);
-                if (KH > 0 && !EDGES) {
+                if (KH > 0) {
 #pragma unroll
                     for (int a = 0; a < KH; ++a)
 #pragma unroll
                         for (int b = 0; b < KW; ++b) sum += t[a * g.W + b];
-                } else if (KH > 0) {
-#pragma unroll
-                    for (int a = 0; a < KH; ++a) {
-                        const bool row_ok = hh + a >= 0 && hh + a < nrows;
-#pragma unroll
-                        for (int b = 0; b < KW; ++b)
-                            sum += (row_ok && w0 + b >= 0 && w0 + b < g.W) ? t[a * g.W + b] : T(0);
-                    }
                 } else {
-                    for (int a = 0; a < kh; ++a) {
-                        if (EDGES && (hh + a < 0 || hh + a >= nrows)) continue;
-                        for (int b = 0; b < kw; ++b) {
-                            if (EDGES && (w0 + b < 0 || w0 + b >= g.W)) continue;
-                            sum += t[a * g.W + b];
-                        }
-                    }
+                    for (int a = 0; a < kh; ++a)
+                        for (int b = 0; b < kw; ++b) sum += t[a * g.W + b];
                 }
                 *out = divide(sum);
+            }
+        }
+        if (EDGES) {
+            // the rows above ia and below ib, all columns; then the columns left of ja and right of jb in the rows between
+            const int inner_rows = max(0, ib - ia + 1);
+            const int edge_rows = it.nout - inner_rows;
+            for (int e = threadIdx.x; e < edge_rows * g.Wo; e += blockDim.x) {
+                unsigned r, j;
+                by_wo.divmod(static_cast<unsigned>(e), r, j);
+                checked(static_cast<int>(r) < ia ? static_cast<int>(r) : ib + 1 + (static_cast<int>(r) - ia), static_cast<int>(j));
+            }
+            const int edge_cols = inner_rows > 0 ? ja + (g.Wo - 1 - jb) : 0;
+            for (int e = threadIdx.x; e < inner_rows * edge_cols; e += blockDim.x) {
+                unsigned r, k;
+                by_edge_cols.divmod(static_cast<unsigned>(e), r, k);
+                checked(ia + static_cast<int>(r), static_cast<int>(k) < ja ? static_cast<int>(k) : jb + 1 + (static_cast<int>(k) - ja));
             }
         }
         __syncthreads();
@@ -832,7 +859,7 @@ avgpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, PoolGeom g, int row
 template <typename T, int KH, int KW, bool EDGES>
 __global__ void __launch_bounds__(kBandThreads)
 maxpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, long long* __restrict__ idx, PoolGeom g, int rows, unsigned items,
-                 kd::FastDiv by_bands, int lane_bits, int buffer_elems) {
+                 kd::FastDiv by_bands, int lane_bits, int buffer_elems, kd::FastDiv by_wo, kd::FastDiv by_edge_cols) {
     extern __shared__ __align__(16) unsigned char band_smem[];
     T* const buf = reinterpret_cast<T*>(band_smem);
     kd::pdl_prologue();
@@ -865,40 +892,73 @@ maxpool_fwd_band(const T* __restrict__ x, T* __restrict__ y, long long* __restri
         __syncthreads();
         const T* s = buf + cur * buffer_elems;
         const int nrows = it.nrows;
-        const int64_t obase = it.nc * plane_out + it.out_off + group * g.Wo;
-        for (int j = lig; j < g.Wo; j += lanes) {
+        const int64_t obase = it.nc * plane_out + it.out_off;
+        auto checked = [&](int ii, int j) {
+            const int hh = it.top + ii * g.sh, wp0 = j * g.sw, w0 = wp0 - g.pw;
+            const T* t = s + mis + hh * g.W + w0;
+            T best = kd::neg_inf<T>();
+            int ba = 0, bb = 0;
+            for (int a = 0; a < kh; ++a) {
+                if (hh + a < 0 || hh + a >= nrows) continue;
+                for (int b = 0; b < kw; ++b) {
+                    if (w0 + b < 0 || w0 + b >= g.W) continue;
+                    const T v = t[a * g.W + b];
+                    if (v > best) { best = v; ba = a; bb = b; }
+                }
+            }
+            const int64_t o = obase + static_cast<int64_t>(ii) * g.Wo + j;
+            y[o] = best;
+            idx[o] = static_cast<long long>((it.i0 + ii) * g.sh + ba) * Wp + (wp0 + bb);
+        };
+        int ia = 0, ib = it.nout - 1, ja = 0, jb = g.Wo - 1;
+        if (EDGES) {
+            ia = it.top >= 0 ? 0 : (-it.top + g.sh - 1) / g.sh;
+            ib = nrows - kh - it.top >= 0 ? min(it.nout - 1, (nrows - kh - it.top) / g.sh) : -1;
+            ja = (g.pw + g.sw - 1) / g.sw;
+            jb = g.W - kw + g.pw >= 0 ? min(g.Wo - 1, (g.W - kw + g.pw) / g.sw) : -1;
+            if (ib < ia || jb < ja) { ia = it.nout; ib = it.nout - 1; ja = 0; jb = -1; }      // none: everything is an edge
+        }
+        for (int j = ja + lig; j <= jb; j += lanes) {
             const int wp0 = j * g.sw;
             const int w0 = wp0 - g.pw;
-            int hh = it.top + group * g.sh, hp0 = (it.i0 + group) * g.sh;      // staged row / padded-plane row of the first tap
-            const T* t = s + mis + hh * g.W + w0;                              // dereferenced only where the tap exists
-            int64_t o = obase + j;
-            for (int ii = group; ii < it.nout; ii += ngroups, hh += step, hp0 += step, t += step * g.W, o += ngroups * g.Wo) {
+            int hp0 = (it.i0 + ia + group) * g.sh;                             // padded-plane row of the first tap
+            const T* t = s + mis + (it.top + (ia + group) * g.sh) * g.W + w0;
+            int64_t o = obase + static_cast<int64_t>(ia + group) * g.Wo + j;
+            for (int ii = ia + group; ii <= ib; ii += ngroups, hp0 += step, t += step * g.W, o += ngroups * g.Wo) {
                 T best = kd::neg_inf<T>();
                 int ba = 0, bb = 0;
                 if (KH > 0) {
 #pragma unroll
-                    for (int a = 0; a < KH; ++a) {
-                        const bool row_ok = !EDGES || (hh + a >= 0 && hh + a < nrows);
+                    for (int a = 0; a < KH; ++a)
 #pragma unroll
                         for (int b = 0; b < KW; ++b) {
-                            if (!EDGES || (row_ok && w0 + b >= 0 && w0 + b < g.W)) {
-                                const T v = t[a * g.W + b];
-                                if (v > best) { best = v; ba = a; bb = b; }
-                            }
-                        }
-                    }
-                } else {
-                    for (int a = 0; a < kh; ++a) {
-                        if (EDGES && (hh + a < 0 || hh + a >= nrows)) continue;
-                        for (int b = 0; b < kw; ++b) {
-                            if (EDGES && (w0 + b < 0 || w0 + b >= g.W)) continue;
                             const T v = t[a * g.W + b];
                             if (v > best) { best = v; ba = a; bb = b; }
                         }
-                    }
+                } else {
+                    for (int a = 0; a < kh; ++a)
+                        for (int b = 0; b < kw; ++b) {
+                            const T v = t[a * g.W + b];
+                            if (v > best) { best = v; ba = a; bb = b; }
+                        }
                 }
                 y[o] = best;
                 idx[o] = static_cast<long long>(hp0 + ba) * Wp + (wp0 + bb);
+            }
+        }
+        if (EDGES) {
+            const int inner_rows = max(0, ib - ia + 1);
+            const int edge_rows = it.nout - inner_rows;
+            for (int e = threadIdx.x; e < edge_rows * g.Wo; e += blockDim.x) {
+                unsigned r, j;
+                by_wo.divmod(static_cast<unsigned>(e), r, j);
+                checked(static_cast<int>(r) < ia ? static_cast<int>(r) : ib + 1 + (static_cast<int>(r) - ia), static_cast<int>(j));
+            }
+            const int edge_cols = inner_rows > 0 ? ja + (g.Wo - 1 - jb) : 0;
+            for (int e = threadIdx.x; e < inner_rows * edge_cols; e += blockDim.x) {
+                unsigned r, k;
+                by_edge_cols.divmod(static_cast<unsigned>(e), r, k);
+                checked(ia + static_cast<int>(r), static_cast<int>(k) < ja ? static_cast<int>(k) : jb + 1 + (static_cast<int>(k) - ja));
             }
         }
         __syncthreads();
@@ -1653,6 +1713,14 @@ inline int band_max_windows(const PoolGeom& g) {
     return 0;
 }
 
+// forward bands: the number of output columns whose windows reach over the left or right edge of the plane (a divisor)
+inline kd::FastDiv band_edge_cols(const PoolGeom& g) {
+    const int ja = (g.pw + g.sw - 1) / g.sw;
+    const int jb = g.W - g.kw + g.pw >= 0 ? std::min(g.Wo - 1, (g.W - g.kw + g.pw) / g.sw) : -1;
+    const int n = jb < ja ? 0 : ja + (g.Wo - 1 - jb);
+    return kd::FastDiv(static_cast<unsigned>(n > 0 ? n : 1));
+}
+
 // the band kernels index inside a plane with 32-bit integers
 inline bool band_indexable(const PoolGeom& g) {
     return static_cast<int64_t>(g.H) * g.W < (int64_t(1) << 31) && static_cast<int64_t>(g.Ho) * g.Wo < (int64_t(1) << 31);
@@ -1700,7 +1768,7 @@ int maxpool_forward(const T* x, T* y, long long* idx, int N, int C, PoolGeom g) 
         const bool inside = windows_inside(g);
 #define KD_FWD_BAND(KH_, KW_, EDGES_)                                                                               \
     KD_LAUNCH_W((maxpool_fwd_band<T, KH_, KW_, EDGES_>), 2, items, threads, plan.smem, x, y, idx, g, plan.rows, items, \
-                by_bands, lanes, plan.buffer)
+                by_bands, lanes, plan.buffer, kd::FastDiv(g.Wo), band_edge_cols(g))
         if (g.kh == 3 && g.kw == 3) { if (inside) KD_FWD_BAND(3, 3, false); else KD_FWD_BAND(3, 3, true); }
         else if (g.kh == 2 && g.kw == 2) { if (inside) KD_FWD_BAND(2, 2, false); else KD_FWD_BAND(2, 2, true); }
         else if (inside) KD_FWD_BAND(0, 0, false);
@@ -1817,7 +1885,7 @@ int avgpool_forward(const T* x, T* y, int N, int C, PoolGeom g) {
         const bool inside = windows_inside(g);
 #define KD_FWD_BAND(KH_, KW_, EDGES_)                                                                               \
     KD_LAUNCH_W((avgpool_fwd_band<T, KH_, KW_, EDGES_>), 2, items, threads, plan.smem, x, y, g, plan.rows, items, by_bands, lanes, \
-                plan.buffer)
+                plan.buffer, kd::FastDiv(g.Wo), band_edge_cols(g))
         if (g.kh == 3 && g.kw == 3) { if (inside) KD_FWD_BAND(3, 3, false); else KD_FWD_BAND(3, 3, true); }
         else if (g.kh == 2 && g.kw == 2) { if (inside) KD_FWD_BAND(2, 2, false); else KD_FWD_BAND(2, 2, true); }
         else if (inside) KD_FWD_BAND(0, 0, false);
